@@ -1,0 +1,592 @@
+// ConvLogic block kernels: fused (gather -> 4 -> 2 -> 1 gates -> 2x2 max pool) and stand-alone
+// first level, forward and backward.  General-shape path (any stride / padding / kernel window /
+// image size, fp32 and fp64); the shape-specialised fp32 forward lives in convtree_fast.cu.
+//
+// Layouts (all contiguous): x [N,Ci,H,W]; fused y [N,C,Hp,Wp] with Hp = Ho/2; split y [N,C,Ho,Wo,4].
+// One thread block works on ONE output channel c at a time, so the 7 gates (4 coefficients each,
+// see clb_common.cuh) and the 8 tap offsets are block-uniform values kept in shared memory.
+//
+// Backward design (deterministic, no floating-point atomics):
+//   * input gradient: a block owns the gradient tile of `nb` images x `cg` consecutive input channels
+//     in shared memory and walks, in ascending order, the output channels that have a tap in those
+//     channels.  For one (output channel, tap) the map output position -> input pixel is a
+//     translation, hence injective, so all threads can add their contribution with a plain
+//     read-modify-write; a block barrier separates the 8 taps.  The order of additions into any
+//     pixel is therefore fixed: (channel ascending, tap ascending).
+//   * gate gradient: every thread accumulates the 4 basis sums of each gate in registers over its
+//     share of (image, position), then warp shuffles + one shared-memory stage give a per-block
+//     partial; a second kernel adds the partials in a fixed order and applies K^T (and, for
+//     CLB_W_SOFTMAX, the soft-max Jacobian).
+#include "clb_common.cuh"
+
+namespace clb {
+
+struct ConvShape {
+    int N, Ci, H, W, C, Ho, Wo, sh, sw, ph, pw;
+};
+
+template <typename T> struct BlockGates {
+    Gate<T> g[7];
+    Tap tap[8];
+};
+
+// Threads 0..ngates-1 build the gates of channel c, threads 32..39 the taps.  Caller syncs.
+template <typename T>
+__device__ __forceinline__ void load_channel(BlockGates<T> &bg, const T *__restrict__ w, const int32_t *__restrict__ sel,
+                                             int c, int ngates, int wmode, int ph, int pw)
+{
+    const int t = threadIdx.x;
+    if (t < ngates) bg.g[t] = gate_load<T>(w + ((size_t)c * ngates + t) * 16, wmode);
+    if (t >= 32 && t < 40) bg.tap[t - 32] = unpack_tap(sel[c * 8 + (t - 32)], ph, pw);
+}
+
+template <typename T>
+__device__ __forceinline__ T tap_value(const T *__restrict__ ximg, const Tap &tp, int oy, int ox, const ConvShape &s)
+{
+    const int iy = oy * s.sh + tp.dy, ix = ox * s.sw + tp.dx;
+    if ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) return __ldg(ximg + ((size_t)tp.ch * s.H + iy) * s.W + ix);
+    return T(0);
+}
+
+template <typename T> struct Chain {
+    T a[8], g[4], t[2], z;
+};
+
+template <typename T>
+__device__ __forceinline__ void eval_chain(Chain<T> &ch, const BlockGates<T> &bg, const T *__restrict__ ximg, int oy, int ox,
+                                           const ConvShape &s, bool full)
+{
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ch.a[k] = tap_value<T>(ximg, bg.tap[k], oy, ox, s);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) ch.g[p] = gate_eval<T>(bg.g[p], ch.a[2 * p], ch.a[2 * p + 1]);
+    if (full) {
+        ch.t[0] = gate_eval<T>(bg.g[4], ch.g[0], ch.g[1]);
+        ch.t[1] = gate_eval<T>(bg.g[5], ch.g[2], ch.g[3]);
+        ch.z = gate_eval<T>(bg.g[6], ch.t[0], ch.t[1]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------- forward
+// grid (chunks of windows, C); thread <-> pooled window (n, py, px), px fastest.
+template <typename T>
+__global__ void __launch_bounds__(256) convtree_fwd_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                                                           const int32_t *__restrict__ sel, T *__restrict__ y,
+                                                           uint8_t *__restrict__ amax, T *__restrict__ x2, T *__restrict__ x3,
+                                                           int32_t *__restrict__ idx, ConvShape s, int wmode)
+{
+    __shared__ BlockGates<T> bg;
+    const int c = blockIdx.y;
+    load_channel<T>(bg, w, sel, c, 7, wmode, s.ph, s.pw);
+    __syncthreads();
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
+    const long long total = (long long)s.N * I;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(j / I), rem = (int)(j % I);
+        const int py = rem / Wp, px = rem % Wp;
+        const T *ximg = x + (size_t)n * s.Ci * s.H * s.W;
+        T best = T(0);
+        int bd = 0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const int oy = 2 * py + (d >> 1), ox = 2 * px + (d & 1);
+            Chain<T> ch;
+            eval_chain<T>(ch, bg, ximg, oy, ox, s, true);
+            if (x2 != nullptr) {
+                const size_t pos = (((size_t)n * s.C + c) * s.Ho + oy) * s.Wo + ox;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) x2[pos * 4 + p] = ch.g[p];
+                x3[pos * 2] = ch.t[0];
+                x3[pos * 2 + 1] = ch.t[1];
+            }
+            if (d == 0 || ch.z > best) { // strict '>' in scan order keeps the first maximum
+                best = ch.z;
+                bd = d;
+            }
+        }
+        const size_t o = ((size_t)n * s.C + c) * I + rem;
+        y[o] = best;
+        if (amax != nullptr) amax[o] = (uint8_t)bd;
+        if (idx != nullptr) idx[o] = (2 * py + (bd >> 1)) * s.Wo + 2 * px + (bd & 1);
+    }
+}
+
+// grid (chunks of positions, C); thread <-> conv position (n, oy, ox); writes the 4 first-level gates.
+template <typename T>
+__global__ void __launch_bounds__(256) conv_fwd_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                                                       const int32_t *__restrict__ sel, T *__restrict__ y, ConvShape s, int wmode)
+{
+    __shared__ BlockGates<T> bg;
+    const int c = blockIdx.y;
+    load_channel<T>(bg, w, sel, c, 4, wmode, s.ph, s.pw);
+    __syncthreads();
+    const int P = s.Ho * s.Wo;
+    const long long total = (long long)s.N * P;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(j / P), rem = (int)(j % P);
+        Chain<T> ch;
+        eval_chain<T>(ch, bg, x + (size_t)n * s.Ci * s.H * s.W, rem / s.Wo, rem % s.Wo, s, false);
+        T *o = y + (((size_t)n * s.C + c) * P + rem) * 4;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) o[p] = ch.g[p];
+    }
+}
+
+// ------------------------------------------------------------------------------- backward helpers
+// Position and upstream gradients of work item j (a pooled window in fused mode, a conv position in
+// split mode) of channel c.  Returns false when j is out of range.
+template <typename T, bool FUSED> struct Upstream {
+    int oy, ox;
+    T dg[4]; // gradient arriving at the 4 first-level gate outputs
+};
+
+template <typename T, bool FUSED>
+__device__ __forceinline__ void backprop_item(Upstream<T, FUSED> &u, Chain<T> &ch, const BlockGates<T> &bg,
+                                              const T *__restrict__ ximg, const T *__restrict__ gy, const uint8_t *__restrict__ amax,
+                                              size_t item /* (n*C + c)*items_per_image + rem */, int rem, const ConvShape &s,
+                                              T *acc /* 28 or 16 basis sums, may be null */)
+{
+    if (FUSED) {
+        const int Wp = s.Wo / 2;
+        const int py = rem / Wp, px = rem % Wp;
+        int bd;
+        if (amax != nullptr) {
+            bd = amax[item];
+        } else {
+            T best = T(0);
+            bd = 0;
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                eval_chain<T>(ch, bg, ximg, 2 * py + (d >> 1), 2 * px + (d & 1), s, true);
+                if (d == 0 || ch.z > best) {
+                    best = ch.z;
+                    bd = d;
+                }
+            }
+        }
+        u.oy = 2 * py + (bd >> 1);
+        u.ox = 2 * px + (bd & 1);
+        eval_chain<T>(ch, bg, ximg, u.oy, u.ox, s, true);
+        const T dz = gy[item];
+        const T dt0 = dz * gate_da<T>(bg.g[6], ch.t[1]);
+        const T dt1 = dz * gate_db<T>(bg.g[6], ch.t[0]);
+        u.dg[0] = dt0 * gate_da<T>(bg.g[4], ch.g[1]);
+        u.dg[1] = dt0 * gate_db<T>(bg.g[4], ch.g[0]);
+        u.dg[2] = dt1 * gate_da<T>(bg.g[5], ch.g[3]);
+        u.dg[3] = dt1 * gate_db<T>(bg.g[5], ch.g[2]);
+        if (acc != nullptr) {
+            acc[24] = fma_t<T>(dz, ch.t[0] * ch.t[1], acc[24]);
+            acc[25] = fma_t<T>(dz, ch.t[0], acc[25]);
+            acc[26] = fma_t<T>(dz, ch.t[1], acc[26]);
+            acc[27] += dz;
+            acc[16] = fma_t<T>(dt0, ch.g[0] * ch.g[1], acc[16]);
+            acc[17] = fma_t<T>(dt0, ch.g[0], acc[17]);
+            acc[18] = fma_t<T>(dt0, ch.g[1], acc[18]);
+            acc[19] += dt0;
+            acc[20] = fma_t<T>(dt1, ch.g[2] * ch.g[3], acc[20]);
+            acc[21] = fma_t<T>(dt1, ch.g[2], acc[21]);
+            acc[22] = fma_t<T>(dt1, ch.g[3], acc[22]);
+            acc[23] += dt1;
+        }
+    } else {
+        u.oy = rem / s.Wo;
+        u.ox = rem % s.Wo;
+        eval_chain<T>(ch, bg, ximg, u.oy, u.ox, s, false);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) u.dg[p] = gy[item * 4 + p];
+    }
+    if (acc != nullptr) {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const T a = ch.a[2 * p], b = ch.a[2 * p + 1], d = u.dg[p];
+            acc[4 * p + 0] = fma_t<T>(d, a * b, acc[4 * p + 0]);
+            acc[4 * p + 1] = fma_t<T>(d, a, acc[4 * p + 1]);
+            acc[4 * p + 2] = fma_t<T>(d, b, acc[4 * p + 2]);
+            acc[4 * p + 3] += d;
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- backward: input grad
+// grid (ceil(N / nb), G); dynamic shared memory: tile [nb][cg][H][W] of T, then 2 BlockGates<T>.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(256) conv_bwd_x_kernel(const T *__restrict__ gy, const T *__restrict__ x, const T *__restrict__ w,
+                                                         const int32_t *__restrict__ sel, const uint8_t *__restrict__ amax,
+                                                         T *__restrict__ gx, const int32_t *__restrict__ grp_start,
+                                                         const int32_t *__restrict__ grp_list, int cg, int nb, ConvShape s, int wmode)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int HW = s.H * s.W;
+    T *tile = reinterpret_cast<T *>(smem_raw);
+    const size_t tile_elems = (size_t)nb * cg * HW;
+    BlockGates<T> *bgs = reinterpret_cast<BlockGates<T> *>(smem_raw + ((tile_elems * sizeof(T) + 15) / 16) * 16);
+
+    const int g = blockIdx.y, n0 = blockIdx.x * nb;
+    const int nimg = min(nb, s.N - n0);
+    const int ch0 = g * cg;
+    for (size_t i = threadIdx.x; i < tile_elems; i += blockDim.x) tile[i] = T(0);
+
+    const int items = FUSED ? (s.Ho / 2) * (s.Wo / 2) : s.Ho * s.Wo; // per image and channel
+    const int total = nimg * items;
+    const int lo = grp_start[g], hi = grp_start[g + 1];
+    constexpr int NG = FUSED ? 7 : 4;
+    for (int li = lo; li < hi; ++li) {
+        const int c = grp_list[li];
+        BlockGates<T> &bg = bgs[(li - lo) & 1];
+        load_channel<T>(bg, w, sel, c, NG, wmode, s.ph, s.pw);
+        __syncthreads(); // publishes bg; also orders the tile zero-fill / previous channel's last tap
+        for (int base = 0; base < total; base += blockDim.x) {
+            const int j = base + threadIdx.x;
+            const bool live = j < total;
+            Upstream<T, FUSED> u;
+            Chain<T> chn;
+            int img = 0;
+            if (live) {
+                img = j / items;
+                const int rem = j % items;
+                const int n = n0 + img;
+                backprop_item<T, FUSED>(u, chn, bg, x + (size_t)n * s.Ci * HW, gy, amax, ((size_t)n * s.C + c) * items + rem, rem, s,
+                                        nullptr);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const Tap tp = bg.tap[k];
+                const int chl = tp.ch - ch0;
+                if (chl >= 0 && chl < cg) { // block-uniform
+                    if (live) {
+                        const int iy = u.oy * s.sh + tp.dy, ix = u.ox * s.sw + tp.dx;
+                        if ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) {
+                            const T other = chn.a[k ^ 1];
+                            const T d = (k & 1) ? gate_db<T>(bg.g[k >> 1], other) : gate_da<T>(bg.g[k >> 1], other);
+                            T *cell = tile + ((size_t)img * cg + chl) * HW + iy * s.W + ix;
+                            *cell = fma_t<T>(d, u.dg[k >> 1], *cell);
+                        }
+                    }
+                    __syncthreads();
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int nch = min(cg, s.Ci - ch0);
+    for (size_t i = threadIdx.x; i < (size_t)nimg * nch * HW; i += blockDim.x) {
+        const int img = (int)(i / ((size_t)nch * HW));
+        const size_t r = i % ((size_t)nch * HW);
+        const int chl = (int)(r / HW), p = (int)(r % HW);
+        gx[((size_t)(n0 + img) * s.Ci + ch0 + chl) * HW + p] = tile[((size_t)img * cg + chl) * HW + p];
+    }
+}
+
+// ---------------------------------------------------------------------------- backward: gate grad
+// grid (parts, C).  Block `part` covers items [part*per, (part+1)*per) of the N*items range of channel c.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(256) conv_bwd_w_kernel(const T *__restrict__ gy, const T *__restrict__ x, const T *__restrict__ w,
+                                                         const int32_t *__restrict__ sel, const uint8_t *__restrict__ amax,
+                                                         T *__restrict__ partial /* [parts][C][NB] */, ConvShape s, int wmode)
+{
+    constexpr int NG = FUSED ? 7 : 4, NB = NG * 4;
+    __shared__ BlockGates<T> bg;
+    __shared__ T red[8][NB];
+    const int c = blockIdx.y;
+    load_channel<T>(bg, w, sel, c, NG, wmode, s.ph, s.pw);
+    __syncthreads();
+    const int items = FUSED ? (s.Ho / 2) * (s.Wo / 2) : s.Ho * s.Wo;
+    const long long total = (long long)s.N * items;
+    const long long per = (total + gridDim.x - 1) / gridDim.x;
+    const long long lo = per * blockIdx.x, hi = min(total, lo + per);
+    T acc[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) acc[i] = T(0);
+    const int HW = s.H * s.W;
+    for (long long j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        const int n = (int)(j / items), rem = (int)(j % items);
+        Upstream<T, FUSED> u;
+        Chain<T> chn;
+        backprop_item<T, FUSED>(u, chn, bg, x + (size_t)n * s.Ci * HW, gy, amax, ((size_t)n * s.C + c) * items + rem, rem, s, acc);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const T v = warp_sum<T>(acc[i]);
+        if (lane == 0) red[warp][i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < NB) {
+        T v = T(0);
+        for (int wv = 0; wv < (int)(blockDim.x >> 5); ++wv) v += red[wv][threadIdx.x];
+        partial[((size_t)blockIdx.x * s.C + c) * NB + threadIdx.x] = v;
+    }
+}
+
+// One thread per gate: adds the per-part basis sums in part order and writes the 16 gradients.
+template <typename T>
+__global__ void gate_grad_finalize_kernel(const T *__restrict__ partial, const T *__restrict__ w, T *__restrict__ gw, int parts,
+                                          long long ngates, int wmode)
+{
+    const long long gi = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= ngates) return;
+    T sums[4] = {T(0), T(0), T(0), T(0)};
+    for (int p = 0; p < parts; ++p) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sums[k] += partial[((size_t)p * ngates + gi) * 4 + k];
+    }
+    gate_grad_store<T>(sums, w + gi * 16, wmode, gw + gi * 16);
+}
+
+} // namespace clb
+
+// ================================================================================== host side ====
+using namespace clb;
+using namespace clb_host;
+
+static int make_shape(ConvShape &s, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, bool fused)
+{
+    if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_ARG;
+    s = ConvShape{N, Ci, H, W, C, conv_out(H, ph, kh, sh), conv_out(W, pw, kw, sw), sh, sw, ph, pw};
+    if (s.Ho <= 0 || s.Wo <= 0) return CLB_ERR_SHAPE;
+    if (fused && ((s.Ho & 1) || (s.Wo & 1))) return CLB_ERR_ODD_OUTPUT;
+    return CLB_OK;
+}
+
+static int grid_x_for(long long total_items, int C)
+{
+    long long want = (total_items + 255) / 256;
+    // enough blocks to fill 148 SMs several times over, without starving each block of work
+    long long cap = (148LL * 16 + C - 1) / (C > 0 ? C : 1);
+    if (cap < 1) cap = 1;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    return (int)want;
+}
+
+// implemented in convtree_fast.cu; returns CLB_ERR_SHAPE when the shape is outside its fast path
+int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H,
+                              int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st);
+
+extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel, void *y, uint8_t *amax, void *x2, void *x3,
+                                int32_t *idx, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
+                                int wmode, int dtype, void *stream)
+{
+    ConvShape s;
+    int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, true);
+    if (rc) return rc;
+    if (!x || !w || !sel || !y || (x2 == nullptr) != (x3 == nullptr) || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (N == 0 || C == 0) return CLB_OK;
+    if (C > 65535) return CLB_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == CLB_F32 && !x2 && !idx) {
+        rc = clb_convtree_fwd_fast_f32((const float *)x, (const float *)w, sel, (float *)y, amax, N, Ci, H, W, C, sh, sw, ph, pw,
+                                       kh, kw, wmode, st);
+        if (rc != CLB_ERR_SHAPE) return rc;
+    }
+    const long long total = (long long)N * (s.Ho / 2) * (s.Wo / 2);
+    dim3 grid(grid_x_for(total, C), C);
+    if (dtype == CLB_F32)
+        convtree_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, (float *)x2,
+                                                          (float *)x3, idx, s, wmode);
+    else if (dtype == CLB_F64)
+        convtree_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, amax,
+                                                           (double *)x2, (double *)x3, idx, s, wmode);
+    else
+        return CLB_ERR_ARG;
+    return check_launch();
+}
+
+extern "C" int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, void *y, int N, int Ci, int H, int W, int C, int sh,
+                            int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
+{
+    ConvShape s;
+    int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, false);
+    if (rc) return rc;
+    if (!x || !w || !sel || !y || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (N == 0 || C == 0) return CLB_OK;
+    if (C > 65535) return CLB_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(grid_x_for((long long)N * s.Ho * s.Wo, C), C);
+    if (dtype == CLB_F32)
+        conv_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, s, wmode);
+    else if (dtype == CLB_F64)
+        conv_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, s, wmode);
+    else
+        return CLB_ERR_ARG;
+    return check_launch();
+}
+
+// ---- input gradient ---------------------------------------------------------------------------
+static const size_t kTileBudget = 96 * 1024;   // lets two blocks share one SM
+static const size_t kTileBudgetMax = 200 * 1024;
+
+extern "C" int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int dtype,
+                                   int *cg, int *nb)
+{
+    if (!cg || !nb || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
+    if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_ARG;
+    const size_t esz = dtype == CLB_F32 ? 4 : 8;
+    const size_t hw = (size_t)H * W;
+    const int Ho = conv_out(H, ph, kh, sh), Wo = conv_out(W, pw, kw, sw);
+    if (Ho <= 0 || Wo <= 0) return CLB_ERR_SHAPE;
+    if (hw * esz > kTileBudgetMax) return CLB_ERR_SHAPE; // one channel plane must fit in shared memory
+    // images per block: enough (image, window) items for 256 threads when windows are few
+    long long items = (long long)((Ho + 1) / 2) * ((Wo + 1) / 2);
+    int n_b = (int)((256 + items - 1) / items);
+    if (n_b < 1) n_b = 1;
+    if (n_b > (N > 0 ? N : 1)) n_b = N > 0 ? N : 1;
+    while (n_b > 1 && (size_t)n_b * hw * esz > kTileBudget) --n_b;
+    size_t budget = (size_t)n_b * hw * esz > kTileBudget ? kTileBudgetMax : kTileBudget;
+    long long c_g = (long long)(budget / ((size_t)n_b * hw * esz));
+    if (c_g < 1) c_g = 1;
+    if (c_g > Ci) c_g = Ci;
+    *cg = (int)c_g;
+    *nb = n_b;
+    return CLB_OK;
+}
+
+extern "C" int clb_conv_build_groups(const int32_t *sel_host, int C, int Ci, int cg, int32_t *grp_start, int32_t *grp_list,
+                                     int list_cap)
+{
+    if (!sel_host || !grp_start || (!grp_list && list_cap > 0) || C < 0 || Ci <= 0 || cg <= 0) return CLB_ERR_ARG;
+    const int G = (Ci + cg - 1) / cg;
+    int n = 0;
+    for (int g = 0; g < G; ++g) {
+        grp_start[g] = n;
+        for (int c = 0; c < C; ++c) {
+            bool hit = false;
+            for (int k = 0; k < 8 && !hit; ++k) {
+                const int ch = (sel_host[c * 8 + k] >> 16) & 0xFFFF;
+                if (ch >= Ci) return CLB_ERR_ARG; // selection names a channel the input does not have
+                hit = ch / cg == g;
+            }
+            if (hit) {
+                if (n >= list_cap) return CLB_ERR_SCRATCH;
+                grp_list[n++] = c;
+            }
+        }
+    }
+    grp_start[G] = n;
+    return n;
+}
+
+template <bool FUSED>
+static int launch_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx,
+                        const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W, int C,
+                        int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
+{
+    ConvShape s;
+    int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, FUSED);
+    if (rc) return rc;
+    if (!gy || !x || !w || !sel || !gx || !grp_start || !grp_list || cg <= 0 || nb <= 0 || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (dtype != CLB_F32 && dtype != CLB_F64) return CLB_ERR_ARG;
+    if (N == 0) return CLB_OK;
+    const size_t esz = dtype == CLB_F32 ? 4 : 8;
+    const size_t tile = (((size_t)nb * cg * H * W * esz + 15) / 16) * 16;
+    const size_t bgsz = dtype == CLB_F32 ? sizeof(BlockGates<float>) : sizeof(BlockGates<double>);
+    const size_t smem = tile + 2 * bgsz;
+    if (smem > 227 * 1024) return CLB_ERR_SHAPE;
+    const int G = (Ci + cg - 1) / cg;
+    if (G > 65535) return CLB_ERR_SHAPE;
+    dim3 grid((N + nb - 1) / nb, G);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == CLB_F32) {
+        auto k = conv_bwd_x_kernel<float, FUSED>;
+        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
+        k<<<grid, 256, smem, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start, grp_list,
+                                   cg, nb, s, wmode);
+    } else {
+        auto k = conv_bwd_x_kernel<double, FUSED>;
+        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
+        k<<<grid, 256, smem, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax, (double *)gx, grp_start,
+                                   grp_list, cg, nb, s, wmode);
+    }
+    return check_launch();
+}
+
+extern "C" int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx,
+                                  const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W,
+                                  int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
+{
+    return launch_bwd_x<true>(gy, x, w, sel, amax, gx, grp_start, grp_list, cg, nb, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
+                              dtype, stream);
+}
+
+extern "C" int clb_conv_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, void *gx, const int32_t *grp_start,
+                              const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W, int C, int sh, int sw, int ph,
+                              int pw, int kh, int kw, int wmode, int dtype, void *stream)
+{
+    return launch_bwd_x<false>(gy, x, w, sel, nullptr, gx, grp_start, grp_list, cg, nb, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw,
+                               wmode, dtype, stream);
+}
+
+// ---- gate gradient ----------------------------------------------------------------------------
+static int bwd_w_parts(long long total_items, int C)
+{
+    long long parts = (148LL * 8 + C - 1) / (C > 0 ? C : 1);
+    long long most = total_items / 2048;
+    if (parts > most) parts = most;
+    if (parts < 1) parts = 1;
+    if (parts > 1024) parts = 1024;
+    return (int)parts;
+}
+
+static size_t bwd_w_scratch(int N, int C, long long items, int ngates, int dtype)
+{
+    const size_t esz = dtype == CLB_F64 ? 8 : 4;
+    return (size_t)bwd_w_parts((long long)N * items, C) * (size_t)C * ngates * 4 * esz;
+}
+
+extern "C" size_t clb_convtree_bwd_w_scratch_bytes(int N, int C, int Ho, int Wo, int dtype)
+{
+    return bwd_w_scratch(N, C, (long long)(Ho / 2) * (Wo / 2), 7, dtype);
+}
+extern "C" size_t clb_conv_bwd_w_scratch_bytes(int N, int C, int Ho, int Wo, int dtype)
+{
+    return bwd_w_scratch(N, C, (long long)Ho * Wo, 4, dtype);
+}
+
+template <bool FUSED>
+static int launch_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gw,
+                        void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
+                        int kh, int kw, int wmode, int dtype, void *stream)
+{
+    ConvShape s;
+    int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, FUSED);
+    if (rc) return rc;
+    if (!gy || !x || !w || !sel || !gw || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (dtype != CLB_F32 && dtype != CLB_F64) return CLB_ERR_ARG;
+    if (C == 0) return CLB_OK;
+    if (C > 65535) return CLB_ERR_SHAPE;
+    constexpr int NG = FUSED ? 7 : 4;
+    const long long items = FUSED ? (long long)(s.Ho / 2) * (s.Wo / 2) : (long long)s.Ho * s.Wo;
+    const int parts = bwd_w_parts((long long)N * items, C);
+    const size_t need = bwd_w_scratch(N, C, items, NG, dtype);
+    if (!scratch || scratch_bytes < need) return CLB_ERR_SCRATCH;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(parts, C);
+    const long long ngates = (long long)C * NG;
+    const int fb = (int)((ngates + 127) / 128);
+    if (dtype == CLB_F32) {
+        conv_bwd_w_kernel<float, FUSED><<<grid, 256, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
+                                                               (float *)scratch, s, wmode);
+        gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
+    } else {
+        conv_bwd_w_kernel<double, FUSED><<<grid, 256, 0, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax,
+                                                                (double *)scratch, s, wmode);
+        gate_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates,
+                                                              wmode);
+    }
+    return check_launch();
+}
+
+extern "C" int clb_convtree_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gw,
+                                  void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph,
+                                  int pw, int kh, int kw, int wmode, int dtype, void *stream)
+{
+    return launch_bwd_w<true>(gy, x, w, sel, amax, gw, scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, dtype,
+                              stream);
+}
+extern "C" int clb_conv_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, void *gw, void *scratch,
+                              size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                              int kw, int wmode, int dtype, void *stream)
+{
+    return launch_bwd_w<false>(gy, x, w, sel, nullptr, gw, scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
+                               dtype, stream);
+}

@@ -1,0 +1,337 @@
+// Flat LogicLayer kernels on feature-major activations: x [in,B], y [out,B], batch contiguous.
+//
+// The work is HBM-bound (two gathered input rows and one output row per neuron, three FMAs per
+// element), so the layout of the loop is chosen for memory: one warp owns one neuron (forward, gate
+// gradient) or one input feature (input gradient) and sweeps the batch with 128-bit accesses, every
+// row access being a fully coalesced 512-byte segment per warp.  The 16 gate values of a neuron are
+// read once per warp: 16 lanes load one value each and the soft-max / 4-coefficient reduction runs on
+// shuffles inside the half-warp, two neurons at a time.
+//
+// Input gradient: segmented reduction over the consumer lists (CSR), no atomics, fixed order.
+// A neuron whose two inputs are the same feature is listed twice in a row; the first entry takes the
+// derivative w.r.t. its first input and the second w.r.t. its second input, so the sum is the true
+// derivative (the reference kernel, src/difflogic/cuda/difflogic_kernel.cu:196-226, applies the
+// first-input derivative twice in that case; its CPU path gives the sum used here).
+#include "clb_common.cuh"
+
+namespace clb {
+
+// Each half-warp reduces the 16 values of one neuron: the lane handles value (lane & 15) of neuron
+// `j` (the same j in all 16 lanes of a half-warp; the two halves may name unrelated neurons).
+// Returns that neuron's gate in every lane of the half-warp, plus the lane's mixture value p.
+// Neurons outside [0, out_dim) give zeros.
+template <typename T>
+__device__ __forceinline__ Gate<T> half_warp_gate(const T *__restrict__ w, long long j, long long out_dim, int wmode, int lane, T &p)
+{
+    const int i = lane & 15;
+    T v = (j >= 0 && j < out_dim) ? w[j * 16 + i] : T(0);
+    if (wmode == CLB_W_SOFTMAX) {
+        T m = v;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            const T u = __shfl_xor_sync(0xffffffffu, m, o);
+            m = u > m ? u : m;
+        }
+        v = exp(v - m);
+        T s = v;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        v = v / s;
+    } else if (wmode == CLB_W_ARGMAX) {
+        // first maximum: compare (value, -index) pairs
+        T m = v;
+        int bi = i;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            const T um = __shfl_xor_sync(0xffffffffu, m, o);
+            const int ui = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (um > m || (um == m && ui < bi)) {
+                m = um;
+                bi = ui;
+            }
+        }
+        v = (i == bi) ? T(1) : T(0);
+    }
+    p = v;
+    Gate<T> g;
+    g.kab = T(kcoef(0, i)) * v;
+    g.ka = T(kcoef(1, i)) * v;
+    g.kb = T(kcoef(2, i)) * v;
+    g.k1 = T(kcoef(3, i)) * v;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+        g.kab += __shfl_xor_sync(0xffffffffu, g.kab, o);
+        g.ka += __shfl_xor_sync(0xffffffffu, g.ka, o);
+        g.kb += __shfl_xor_sync(0xffffffffu, g.kb, o);
+        g.k1 += __shfl_xor_sync(0xffffffffu, g.k1, o);
+    }
+    return g;
+}
+
+template <typename T> __device__ __forceinline__ Gate<T> gate_from_lane(const Gate<T> &g, int src)
+{
+    Gate<T> r;
+    r.kab = __shfl_sync(0xffffffffu, g.kab, src);
+    r.ka = __shfl_sync(0xffffffffu, g.ka, src);
+    r.kb = __shfl_sync(0xffffffffu, g.kb, src);
+    r.k1 = __shfl_sync(0xffffffffu, g.k1, src);
+    return r;
+}
+
+template <typename T, int V> struct Vec;
+template <> struct Vec<float, 4> { using type = float4; };
+template <> struct Vec<float, 1> { using type = float; };
+template <> struct Vec<double, 1> { using type = double; };
+template <> struct Vec<double, 2> { using type = double2; };
+
+template <typename T, int V> __device__ __forceinline__ void vload(const T *p, T (&r)[V])
+{
+    using VT = typename Vec<T, V>::type;
+    const VT v = __ldg(reinterpret_cast<const VT *>(p));
+    const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) r[k] = e[k];
+}
+template <typename T, int V> __device__ __forceinline__ void vstore(T *p, const T (&r)[V])
+{
+    using VT = typename Vec<T, V>::type;
+    VT v;
+    T *e = reinterpret_cast<T *>(&v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) e[k] = r[k];
+    *reinterpret_cast<VT *>(p) = v;
+}
+
+// ---------------------------------------------------------------------------------------- forward
+template <typename T, int V>
+__global__ void __launch_bounds__(256) logic_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ ia,
+                                                        const int64_t *__restrict__ ib, const T *__restrict__ w, T *__restrict__ y,
+                                                        long long out_dim, long long B, int wmode)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long j0 = warp * 2; j0 < out_dim; j0 += nwarps * 2) {
+        T p;
+        const Gate<T> gh = half_warp_gate<T>(w, j0 + (lane >> 4), out_dim, wmode, lane, p);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const long long j = j0 + h;
+            if (j >= out_dim) break;
+            const Gate<T> g = gate_from_lane<T>(gh, h * 16);
+            const T *xa = x + ia[j] * B, *xb = x + ib[j] * B;
+            T *yo = y + j * B;
+            for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
+                T a[V], b[V], r[V];
+                vload<T, V>(xa + b0, a);
+                vload<T, V>(xb + b0, b);
+#pragma unroll
+                for (int k = 0; k < V; ++k) r[k] = gate_eval<T>(g, a[k], b[k]);
+                vstore<T, V>(yo + b0, r);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ gate grads
+template <typename T, int V>
+__global__ void __launch_bounds__(256) logic_bwd_w_kernel(const T *__restrict__ x, const int64_t *__restrict__ ia,
+                                                          const int64_t *__restrict__ ib, const T *__restrict__ w,
+                                                          const T *__restrict__ gy, T *__restrict__ gw, long long out_dim, long long B,
+                                                          int wmode)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long j0 = warp * 2; j0 < out_dim; j0 += nwarps * 2) {
+        T s[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const long long j = j0 + h;
+            T acc[4] = {T(0), T(0), T(0), T(0)};
+            if (j < out_dim) {
+                const T *xa = x + ia[j] * B, *xb = x + ib[j] * B, *g = gy + j * B;
+                for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
+                    T a[V], b[V], d[V];
+                    vload<T, V>(xa + b0, a);
+                    vload<T, V>(xb + b0, b);
+                    vload<T, V>(g + b0, d);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        acc[0] = fma_t<T>(d[k], a[k] * b[k], acc[0]);
+                        acc[1] = fma_t<T>(d[k], a[k], acc[1]);
+                        acc[2] = fma_t<T>(d[k], b[k], acc[2]);
+                        acc[3] += d[k];
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s[h][k] = warp_sum<T>(acc[k]);
+        }
+        // lane l writes gradient (l & 15) of neuron j0 + (l >> 4)
+        const int h = lane >> 4, i = lane & 15;
+        const long long j = j0 + h;
+        T sh4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sh4[k] = h ? s[1][k] : s[0][k];
+        T gi = T(kcoef(0, i)) * sh4[0] + T(kcoef(1, i)) * sh4[1] + T(kcoef(2, i)) * sh4[2] + T(kcoef(3, i)) * sh4[3];
+        if (wmode == CLB_W_SOFTMAX) {
+            T p;
+            (void)half_warp_gate<T>(w, j, out_dim, CLB_W_SOFTMAX, lane, p);
+            T dot = p * gi;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            gi = p * (gi - dot);
+        }
+        if (j < out_dim) gw[j * 16 + i] = gi;
+    }
+}
+
+// ----------------------------------------------------------------------------------- input grads
+template <typename T, int V>
+__global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ x, const int64_t *__restrict__ ia,
+                                                          const int64_t *__restrict__ ib, const T *__restrict__ w,
+                                                          const T *__restrict__ gy, T *__restrict__ gx,
+                                                          const int64_t *__restrict__ start, const int64_t *__restrict__ cons,
+                                                          long long in_dim, long long out_dim, long long B, int wmode,
+                                                          int batch_splits)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    // unit = (feature, batch split); a split is a multiple of 32*V elements
+    const long long span = ((B + (long long)batch_splits * 32 * V - 1) / ((long long)batch_splits * 32 * V)) * 32 * V;
+    for (long long unit = warp; unit < in_dim * batch_splits; unit += nwarps) {
+        const long long f = unit / batch_splits;
+        const long long blo = (unit % batch_splits) * span, bhi = min(B, blo + span);
+        const long long lo = start[f], hi = start[f + 1];
+        // The running sums of up to MAXV vector slots per lane stay in registers across consumers.
+        constexpr int SLOTS = 4;
+        for (long long bb = blo; bb < bhi; bb += (long long)SLOTS * 32 * V) {
+            T acc[SLOTS][V];
+#pragma unroll
+            for (int q = 0; q < SLOTS; ++q)
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[q][k] = T(0);
+            for (long long cur = lo; cur < hi; cur += 2) {
+                // two consumers per step: lanes 0-15 prepare the first one's gate, lanes 16-31 the second's
+                const long long mine = cur + (lane >> 4);
+                const long long jm = mine < hi ? cons[mine] : -1;
+                T p;
+                const Gate<T> gh = half_warp_gate<T>(w, jm, out_dim, wmode, lane, p);
+                (void)p;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const long long c2 = cur + h;
+                    if (c2 >= hi) break;
+                    const long long j = cons[c2];
+                    const Gate<T> g = gate_from_lane<T>(gh, h * 16);
+                    const long long a_j = ia[j], b_j = ib[j];
+                    const bool second = (a_j == f) && (b_j == f) && (c2 > lo) && (cons[c2 - 1] == j);
+                    const bool wrt_a = (a_j == f) && !second;
+                    const T *xo = x + (wrt_a ? b_j : a_j) * B; // the other operand's row
+                    const T k0 = wrt_a ? g.ka : g.kb;
+                    const T *gr = gy + j * B;
+#pragma unroll
+                    for (int q = 0; q < SLOTS; ++q) {
+                        const long long b0 = bb + ((long long)q * 32 + lane) * V;
+                        if (b0 < bhi) {
+                            T o[V], d[V];
+                            vload<T, V>(xo + b0, o);
+                            vload<T, V>(gr + b0, d);
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc[q][k] = fma_t<T>(d[k], fma_t<T>(g.kab, o[k], k0), acc[q][k]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < SLOTS; ++q) {
+                const long long b0 = bb + ((long long)q * 32 + lane) * V;
+                if (b0 < bhi) vstore<T, V>(gx + f * B + b0, acc[q]);
+            }
+        }
+    }
+}
+
+} // namespace clb
+
+using namespace clb;
+using namespace clb_host;
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int logic_grid(long long units_of_warps)
+{
+    long long blocks = (units_of_warps + 7) / 8; // 8 warps per block
+    const long long cap = 148LL * 8 * 4;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+extern "C" int clb_logic_fwd(const void *x, const int64_t *a, const int64_t *b, const void *w, void *y, int64_t in_dim,
+                             int64_t out_dim, int64_t B, int wmode, int dtype, void *stream)
+{
+    if (!x || !a || !b || !w || !y || in_dim <= 0 || out_dim < 0 || B < 0 || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (out_dim == 0 || B == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = logic_grid((out_dim + 1) / 2);
+    if (dtype == CLB_F32) {
+        if (B % 4 == 0 && aligned16(x) && aligned16(y))
+            logic_fwd_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode);
+        else
+            logic_fwd_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode);
+    } else if (dtype == CLB_F64) {
+        logic_fwd_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (double *)y, out_dim, B, wmode);
+    } else
+        return CLB_ERR_ARG;
+    return check_launch();
+}
+
+extern "C" int clb_logic_bwd_w(const void *x, const int64_t *a, const int64_t *b, const void *w, const void *gy, void *gw,
+                               int64_t in_dim, int64_t out_dim, int64_t B, int wmode, int dtype, void *stream)
+{
+    if (!x || !a || !b || !w || !gy || !gw || in_dim <= 0 || out_dim < 0 || B < 0 || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (out_dim == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = logic_grid((out_dim + 1) / 2);
+    if (dtype == CLB_F32) {
+        if (B % 4 == 0 && aligned16(x) && aligned16(gy))
+            logic_bwd_w_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode);
+        else
+            logic_bwd_w_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode);
+    } else if (dtype == CLB_F64) {
+        logic_bwd_w_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (const double *)gy, (double *)gw, out_dim, B, wmode);
+    } else
+        return CLB_ERR_ARG;
+    return check_launch();
+}
+
+extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b, const void *w, const void *gy, void *gx,
+                               const int64_t *start, const int64_t *consumers, int64_t in_dim, int64_t out_dim, int64_t B,
+                               int wmode, int dtype, void *stream)
+{
+    if (!x || !a || !b || !w || !gy || !gx || !start || !consumers || in_dim <= 0 || out_dim < 0 || B < 0 || wmode < 0 || wmode > 2)
+        return CLB_ERR_ARG;
+    if (B == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = dtype == CLB_F32 && B % 4 == 0 && aligned16(x) && aligned16(gy) && aligned16(gx);
+    const int V = vec ? 4 : 1;
+    // split the batch when there are too few features to occupy the GPU
+    long long splits = 1;
+    const long long max_splits = (B + 32LL * V * 4 - 1) / (32LL * V * 4);
+    while (in_dim * splits < 148LL * 8 * 8 && splits < max_splits) splits *= 2;
+    if (splits > max_splits) splits = max_splits;
+    const int grid = logic_grid(in_dim * splits);
+    if (dtype == CLB_F32) {
+        if (vec)
+            logic_bwd_x_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
+        else
+            logic_bwd_x_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
+    } else if (dtype == CLB_F64) {
+        logic_bwd_x_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (const double *)gy, (double *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
+    } else
+        return CLB_ERR_ARG;
+    return check_launch();
+}

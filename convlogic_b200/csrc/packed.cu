@@ -1,0 +1,364 @@
+// Packed (discretised) inference kernels: every bit of a word is one sample.
+//
+// A packed tensor is [rows, words] of `bits`-wide integers, sample bits*word + i in bit i.  On a
+// little-endian machine that is the same as a row of ceil(B/bits)*bits/8 BYTES with sample s in bit
+// (s & 7) of byte (s >> 3), whatever `bits` is; bitwise gates do not care about the word width either.
+// The kernels therefore see rows of bytes and move them in the widest unit the row length and the
+// pointers allow (8 bytes when the row length is a multiple of 8 and the bases are 8-byte aligned,
+// single bytes otherwise); `bits` only fixes how many pad samples a row ends with.
+//
+// A 2-input gate with truth table (f00, f01, f10, f11), given as four all-ones/all-zero masks, is the
+// two-level multiplexer  y = a ? (b ? m11 : m10) : (b ? m01 : m00): three 3-input logic operations per
+// 32 bits, branch-free, with the masks uniform over the thread block.
+#include "clb_common.cuh"
+
+namespace clb {
+
+template <typename U> struct OpMasks {
+    U m00, m01, m10, m11;
+};
+template <typename U> __device__ __forceinline__ OpMasks<U> op_masks(int op)
+{
+    OpMasks<U> m;
+    const U ones = ~U(0);
+    m.m00 = (op & 8) ? ones : U(0);
+    m.m01 = (op & 4) ? ones : U(0);
+    m.m10 = (op & 2) ? ones : U(0);
+    m.m11 = (op & 1) ? ones : U(0);
+    return m;
+}
+template <typename U> __device__ __forceinline__ U op_apply(const OpMasks<U> &m, U a, U b)
+{
+    const U r1 = (b & m.m11) | (~b & m.m10);
+    const U r0 = (b & m.m01) | (~b & m.m00);
+    return (a & r1) | (~a & r0);
+}
+
+// ------------------------------------------------------------------------------------- pack bits
+// feature-major source t [F,B]; one thread builds one output byte from 8 consecutive samples.
+__global__ void pack_bits_kernel(const uint8_t *__restrict__ t, uint8_t *__restrict__ out, long long F, long long B, long long rowbytes)
+{
+    const long long total = F * rowbytes;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long f = i / rowbytes, q = i % rowbytes;
+        const uint8_t *src = t + f * B + q * 8;
+        unsigned v = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (q * 8 + k < B) v |= (src[k] != 0 ? 1u : 0u) << k;
+        out[i] = (uint8_t)v;
+    }
+}
+
+// sample-major source t [N,F]: thread <-> feature, loops over 8*BY samples and writes BY bytes of its row.
+template <int BY>
+__global__ void __launch_bounds__(256) pack_bits_nmajor_kernel(const uint8_t *__restrict__ t, uint8_t *__restrict__ out, long long N,
+                                                               long long F, long long rowbytes)
+{
+    const long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= F) return;
+    for (long long q0 = (long long)blockIdx.y * BY; q0 < rowbytes; q0 += (long long)gridDim.y * BY) {
+        uint8_t bytes[BY];
+#pragma unroll
+        for (int q = 0; q < BY; ++q) {
+            unsigned v = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const long long n = (q0 + q) * 8 + k;
+                if (n < N) v |= (__ldg(t + n * F + f) != 0 ? 1u : 0u) << k;
+            }
+            bytes[q] = (uint8_t)v;
+        }
+        uint8_t *dst = out + f * rowbytes + q0;
+        if (BY == 32 && q0 + BY <= rowbytes && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+            const uint4 *b4 = reinterpret_cast<const uint4 *>(bytes);
+            reinterpret_cast<uint4 *>(dst)[0] = b4[0];
+            reinterpret_cast<uint4 *>(dst)[1] = b4[1];
+        } else {
+#pragma unroll
+            for (int q = 0; q < BY; ++q)
+                if (q0 + q < rowbytes) dst[q] = bytes[q];
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------- flat layer
+// U = transfer unit; units = units per row.  thread <-> (neuron, unit), unit fastest.
+template <typename U>
+__global__ void __launch_bounds__(256) packed_logic_kernel(const U *__restrict__ x, const int64_t *__restrict__ ia,
+                                                           const int64_t *__restrict__ ib, const uint8_t *__restrict__ ops,
+                                                           U *__restrict__ y, long long out_dim, long long units)
+{
+    const long long total = out_dim * units;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long j = i / units, u = i % units;
+        const OpMasks<U> m = op_masks<U>(ops[j]);
+        y[i] = op_apply<U>(m, x[ia[j] * units + u], x[ib[j] * units + u]);
+    }
+}
+
+// 16-byte variant: one thread moves a uint4 (two 64-bit units) per operand.
+__global__ void __launch_bounds__(256) packed_logic_v4_kernel(const uint4 *__restrict__ x, const int64_t *__restrict__ ia,
+                                                              const int64_t *__restrict__ ib, const uint8_t *__restrict__ ops,
+                                                              uint4 *__restrict__ y, long long out_dim, long long units)
+{
+    const long long total = out_dim * units;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long j = i / units, u = i % units;
+        const OpMasks<unsigned> m = op_masks<unsigned>(ops[j]);
+        const uint4 a = __ldg(x + ia[j] * units + u), b = __ldg(x + ib[j] * units + u);
+        uint4 r;
+        r.x = op_apply<unsigned>(m, a.x, b.x);
+        r.y = op_apply<unsigned>(m, a.y, b.y);
+        r.z = op_apply<unsigned>(m, a.z, b.z);
+        r.w = op_apply<unsigned>(m, a.w, b.w);
+        y[i] = r;
+    }
+}
+
+// ----------------------------------------------------------------------------------- group sum
+// x rows as 32-bit units (32 samples each).  thread <-> (class, row split, unit).  Rows are added 16 at
+// a time into bit-sliced counters (carry-save adders: ones, twos, fours, eights + ripple counter for
+// the sixteens), so a row costs a handful of logic operations per 32 samples; the per-sample integers
+// are only extracted once at the end.  With more than one row split the partial counts are combined
+// with integer atomics (exact, order-independent) into a zeroed output.
+__device__ __forceinline__ void csa(unsigned &hi, unsigned &lo, unsigned a, unsigned b, unsigned c)
+{
+    const unsigned u = a ^ b;
+    hi = (a & b) | (u & c);
+    lo = u ^ c;
+}
+
+constexpr int kUpperPlanes = 28; // counts up to 16 * 2^28 rows per class
+
+__global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__restrict__ x, int *__restrict__ counts, long long S,
+                                                             long long units, long long B, int k, int splits)
+{
+    const long long total = (long long)k * splits * units;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long u = i % units;
+        const int sp = (int)((i / units) % splits);
+        const int cls = (int)(i / (units * splits));
+        const long long per = ((S + splits - 1) / splits + 15) / 16 * 16;
+        const long long r_lo = per * sp, r_hi = min(S, r_lo + per);
+        const unsigned *base = x + ((long long)cls * S) * units + u;
+        unsigned ones = 0, twos = 0, fours = 0, eights = 0;
+        unsigned up[kUpperPlanes];
+#pragma unroll
+        for (int p = 0; p < kUpperPlanes; ++p) up[p] = 0;
+        for (long long r = r_lo; r < r_hi; r += 16) {
+            unsigned v[16];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = (r + q < r_hi) ? __ldg(base + (r + q) * units) : 0u;
+            unsigned t2a, t2b, t4a, t4b, t8a, t8b, t16;
+            csa(t2a, ones, ones, v[0], v[1]);
+            csa(t2b, ones, ones, v[2], v[3]);
+            csa(t4a, twos, twos, t2a, t2b);
+            csa(t2a, ones, ones, v[4], v[5]);
+            csa(t2b, ones, ones, v[6], v[7]);
+            csa(t4b, twos, twos, t2a, t2b);
+            csa(t8a, fours, fours, t4a, t4b);
+            csa(t2a, ones, ones, v[8], v[9]);
+            csa(t2b, ones, ones, v[10], v[11]);
+            csa(t4a, twos, twos, t2a, t2b);
+            csa(t2a, ones, ones, v[12], v[13]);
+            csa(t2b, ones, ones, v[14], v[15]);
+            csa(t4b, twos, twos, t2a, t2b);
+            csa(t8b, fours, fours, t4a, t4b);
+            csa(t16, eights, eights, t8a, t8b);
+            // ripple the sixteens into the upper counter
+            unsigned carry = t16;
+#pragma unroll
+            for (int p = 0; p < kUpperPlanes; ++p) {
+                const unsigned nc = up[p] & carry;
+                up[p] ^= carry;
+                carry = nc;
+            }
+        }
+#pragma unroll 1
+        for (int bit = 0; bit < 32; ++bit) {
+            const long long s = u * 32 + bit;
+            if (s >= B) break;
+            int c = ((ones >> bit) & 1) + 2 * ((twos >> bit) & 1) + 4 * ((fours >> bit) & 1) + 8 * ((eights >> bit) & 1);
+#pragma unroll
+            for (int p = 0; p < kUpperPlanes; ++p) c += (int)((up[p] >> bit) & 1u) << (4 + p);
+            if (splits == 1)
+                counts[s * k + cls] = c;
+            else if (c)
+                atomicAdd(counts + s * k + cls, c);
+        }
+    }
+}
+
+// byte-unit fallback for rows whose length is not a multiple of 4 bytes: thread <-> (sample, class)
+__global__ void group_popcount_bytes_kernel(const uint8_t *__restrict__ x, int *__restrict__ counts, long long S, long long rowbytes,
+                                            long long B, int k)
+{
+    const long long total = B * k;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long s = i / k;
+        const int cls = (int)(i % k);
+        const uint8_t *base = x + (long long)cls * S * rowbytes + (s >> 3);
+        int c = 0;
+        for (long long r = 0; r < S; ++r) c += (base[r * rowbytes] >> (s & 7)) & 1;
+        counts[i] = c;
+    }
+}
+
+// --------------------------------------------------------------------------- packed ConvLogic block
+struct PackedShape {
+    int Ci, H, W, C, Ho, Wo, sh, sw, ph, pw;
+};
+
+// grid (chunks over (py, px, unit), C); thread <-> (py, px, unit) with unit fastest.
+template <typename U>
+__global__ void __launch_bounds__(256) packed_convtree_kernel(const U *__restrict__ x, const uint8_t *__restrict__ ops,
+                                                              const int32_t *__restrict__ sel, U *__restrict__ y, PackedShape s,
+                                                              long long units)
+{
+    __shared__ OpMasks<U> sm[7];
+    __shared__ Tap stap[8];
+    const int c = blockIdx.y;
+    if (threadIdx.x < 7) sm[threadIdx.x] = op_masks<U>(ops[c * 7 + threadIdx.x]);
+    if (threadIdx.x >= 32 && threadIdx.x < 40) stap[threadIdx.x - 32] = unpack_tap(sel[c * 8 + threadIdx.x - 32], s.ph, s.pw);
+    __syncthreads();
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2;
+    const long long total = (long long)Hp * Wp * units;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long u = i % units;
+        const int win = (int)(i / units);
+        const int py = win / Wp, px = win % Wp;
+        U acc = U(0);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const int oy = 2 * py + (d >> 1), ox = 2 * px + (d & 1);
+            U a[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int iy = oy * s.sh + stap[t].dy, ix = ox * s.sw + stap[t].dx;
+                a[t] = ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W)
+                           ? __ldg(x + (((long long)stap[t].ch * s.H + iy) * s.W + ix) * units + u)
+                           : U(0);
+            }
+            const U g0 = op_apply<U>(sm[0], a[0], a[1]), g1 = op_apply<U>(sm[1], a[2], a[3]);
+            const U g2 = op_apply<U>(sm[2], a[4], a[5]), g3 = op_apply<U>(sm[3], a[6], a[7]);
+            const U t0 = op_apply<U>(sm[4], g0, g1), t1 = op_apply<U>(sm[5], g2, g3);
+            acc |= op_apply<U>(sm[6], t0, t1);
+        }
+        y[((long long)c * Hp * Wp + win) * units + u] = acc;
+    }
+}
+
+} // namespace clb
+
+using namespace clb;
+using namespace clb_host;
+
+static bool bits_ok(int bits) { return bits == 8 || bits == 16 || bits == 32 || bits == 64; }
+static bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+static int flat_grid(long long items, int threads)
+{
+    long long blocks = (items + threads - 1) / threads;
+    const long long cap = 148LL * 32;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+extern "C" int clb_pack_bits(const uint8_t *t, void *packed, int64_t F, int64_t B, int bits, void *stream)
+{
+    if (!t || !packed || F < 0 || B < 0 || !bits_ok(bits)) return CLB_ERR_ARG;
+    const long long words = (B + bits - 1) / bits, rowbytes = words * (bits / 8);
+    if (F == 0 || rowbytes == 0) return CLB_OK;
+    pack_bits_kernel<<<flat_grid(F * rowbytes, 256), 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, F, B, rowbytes);
+    return check_launch();
+}
+
+extern "C" int clb_pack_bits_nmajor(const uint8_t *t, void *packed, int64_t N, int64_t F, int bits, void *stream)
+{
+    if (!t || !packed || F < 0 || N < 0 || !bits_ok(bits)) return CLB_ERR_ARG;
+    const long long words = (N + bits - 1) / bits, rowbytes = words * (bits / 8);
+    if (F == 0 || rowbytes == 0) return CLB_OK;
+    long long gy = (rowbytes + 31) / 32;
+    if (gy > 4096) gy = 4096;
+    dim3 grid((unsigned)((F + 255) / 256), (unsigned)gy);
+    pack_bits_nmajor_kernel<32><<<grid, 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, N, F, rowbytes);
+    return check_launch();
+}
+
+extern "C" int clb_packed_logic(const void *x, const int64_t *a, const int64_t *b, const uint8_t *ops, void *y, int64_t in_dim,
+                                int64_t out_dim, int64_t words, int bits, void *stream)
+{
+    if (!x || !a || !b || !ops || !y || in_dim <= 0 || out_dim < 0 || words < 0 || !bits_ok(bits)) return CLB_ERR_ARG;
+    const long long rowbytes = words * (bits / 8);
+    if (out_dim == 0 || rowbytes == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16)) {
+        const long long units = rowbytes / 16;
+        packed_logic_v4_kernel<<<flat_grid(out_dim * units, 256), 256, 0, st>>>((const uint4 *)x, a, b, ops, (uint4 *)y, out_dim, units);
+    } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
+        const long long units = rowbytes / 8;
+        packed_logic_kernel<unsigned long long><<<flat_grid(out_dim * units, 256), 256, 0, st>>>(
+            (const unsigned long long *)x, a, b, ops, (unsigned long long *)y, out_dim, units);
+    } else {
+        packed_logic_kernel<uint8_t><<<flat_grid(out_dim * rowbytes, 256), 256, 0, st>>>((const uint8_t *)x, a, b, ops, (uint8_t *)y,
+                                                                                        out_dim, rowbytes);
+    }
+    return check_launch();
+}
+
+extern "C" int clb_group_popcount(const void *x, int32_t *counts, int64_t F, int64_t words, int bits, int pad_len, int k,
+                                  void *stream)
+{
+    if (!x || !counts || F < 0 || words < 0 || !bits_ok(bits) || k <= 0 || pad_len < 0 || pad_len >= bits) return CLB_ERR_ARG;
+    if (F % k) return CLB_ERR_SHAPE;
+    const long long rowbytes = words * (bits / 8);
+    const long long B = words * bits - pad_len;
+    if (B <= 0) return CLB_OK;
+    const long long S = F / k;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rowbytes % 4 == 0 && aligned_to(x, 4)) {
+        const long long units = rowbytes / 4;
+        long long splits = 1;
+        while ((long long)k * splits * units < 148LL * 128 * 4 && S / (splits * 2) >= 64) splits *= 2;
+        if (splits > 1) {
+            if (cudaMemsetAsync(counts, 0, (size_t)B * k * sizeof(int32_t), st) != cudaSuccess) return check_launch();
+        }
+        group_popcount_kernel<<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B, k,
+                                                                                             (int)splits);
+    } else {
+        group_popcount_bytes_kernel<<<flat_grid(B * k, 256), 256, 0, st>>>((const uint8_t *)x, counts, S, rowbytes, B, k);
+    }
+    return check_launch();
+}
+
+extern "C" int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, void *y, int Ci, int H, int W, int C,
+                                   int sh, int sw, int ph, int pw, int kh, int kw, int64_t words, int bits, void *stream)
+{
+    if (!conv_args_ok(1, Ci, H, W, C, sh, sw, ph, pw, kh, kw) || !x || !ops || !sel || !y || words < 0 || !bits_ok(bits))
+        return CLB_ERR_ARG;
+    PackedShape s{Ci, H, W, C, conv_out(H, ph, kh, sh), conv_out(W, pw, kw, sw), sh, sw, ph, pw};
+    if (s.Ho <= 0 || s.Wo <= 0) return CLB_ERR_SHAPE;
+    if ((s.Ho & 1) || (s.Wo & 1)) return CLB_ERR_ODD_OUTPUT;
+    if (C > 65535) return CLB_ERR_SHAPE;
+    const long long rowbytes = words * (bits / 8);
+    if (C == 0 || rowbytes == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long wins = (long long)(s.Ho / 2) * (s.Wo / 2);
+    if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
+        const long long units = rowbytes / 8;
+        long long gx = (wins * units + 255) / 256;
+        const long long cap = (148LL * 32 + C - 1) / C;
+        if (gx > cap) gx = cap;
+        dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
+        packed_convtree_kernel<unsigned long long><<<grid, 256, 0, st>>>((const unsigned long long *)x, ops, sel,
+                                                                         (unsigned long long *)y, s, units);
+    } else {
+        long long gx = (wins * rowbytes + 255) / 256;
+        const long long cap = (148LL * 32 + C - 1) / C;
+        if (gx > cap) gx = cap;
+        dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
+        packed_convtree_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)x, ops, sel, (uint8_t *)y, s, rowbytes);
+    }
+    return check_launch();
+}

@@ -1,0 +1,146 @@
+"""Flat LogicLayer and GroupSum with the reference's constructor and state layout
+(src/difflogic/difflogic.py:14-211).
+
+Buffers ``indices_0`` / ``indices_1`` (int64 ``[out]``) and the consumer lists
+``given_x_indices_of_y_start`` / ``given_x_indices_of_y`` keep their names, shapes and dtypes.
+The consumer lists are built with a stable sort instead of the reference's per-neuron Python
+loop (same result, seconds instead of minutes for million-neuron layers).
+"""
+
+import torch
+
+from . import ops
+from ._lib import W_ARGMAX, W_SOFTMAX
+from .functional import GradFactor, LogicLayerCudaFunction
+from .packbitstensor import PackBitsTensor
+
+
+def get_unique_connections(in_dim, out_dim):
+    """Pairs (0,1),(2,3),..., then (1,2),(3,4),..., then growing offsets, shuffled
+    (src/difflogic/functional.py:77-125)."""
+    assert out_dim * 2 >= in_dim, (
+        f"The number of neurons ({out_dim}) must not be smaller than half of the number of inputs "
+        f"({in_dim}) because otherwise not all inputs could be used or considered.")
+    x = torch.arange(in_dim).long()
+
+    def trimmed(a, b):
+        m = min(a.shape[0], b.shape[0])
+        return a[:m], b[:m]
+
+    a, b = trimmed(x[::2], x[1::2])
+    if a.shape[0] < out_dim:
+        a2, b2 = trimmed(x[1::2], x[2::2])
+        a, b = trimmed(torch.cat([a, a2]), torch.cat([b, b2]))
+    offset = 2
+    while out_dim > a.shape[0] > offset:
+        a, b = torch.cat([a, x[:-offset]]), torch.cat([b, x[offset:]])
+        offset += 1
+    if a.shape[0] < out_dim:
+        raise AssertionError((a.shape[0], offset, out_dim))
+    perm = torch.randperm(out_dim)
+    return a[:out_dim][perm].contiguous(), b[:out_dim][perm].contiguous()
+
+
+class LogicLayer(torch.nn.Module):
+    def __init__(self, in_dim, out_dim, grad_factor=1.0, implementation=None, connections="random",
+                 residual_init=False):
+        super().__init__()
+        if implementation not in (None, "cuda"):
+            raise ValueError(f"convlogic_b200 only provides the CUDA implementation, got {implementation!r}")
+        if residual_init:
+            w = torch.zeros(out_dim, 16)
+            w[:, 3] = 5.0
+        else:
+            w = torch.randn(out_dim, 16)
+        self.weights = torch.nn.Parameter(w)
+        self.in_dim, self.out_dim, self.grad_factor = in_dim, out_dim, grad_factor
+        self.implementation = "cuda"
+        self.connections = connections
+        assert connections in ("random", "unique"), connections
+        a, b = self.get_connections(connections)
+        self.register_buffer("indices_0", a.to(torch.int64))
+        self.register_buffer("indices_1", b.to(torch.int64))
+        start, cons = self.build_consumer_lists(self.indices_0, self.indices_1, in_dim)
+        self.register_buffer("given_x_indices_of_y_start", start)
+        self.register_buffer("given_x_indices_of_y", cons)
+        self.num_neurons = self.num_weights = out_dim
+
+    @staticmethod
+    def build_consumer_lists(a, b, in_dim):
+        """CSR of 'which neurons read input feature i', neurons ascending, a neuron listed twice when
+        both inputs are feature i (what the loop at src/difflogic/difflogic.py:71-87 produces)."""
+        out = a.shape[0]
+        feat = torch.stack([a, b], 1).reshape(-1).cpu()
+        neuron = torch.arange(out, dtype=torch.int64).repeat_interleave(2)
+        order = torch.sort(feat, stable=True).indices
+        counts = torch.bincount(feat, minlength=in_dim)
+        start = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)])
+        return start.to(a.device), neuron[order].to(a.device)
+
+    def load_state_dict(self, state_dict, strict=True, assign=False):
+        res = super().load_state_dict(state_dict, strict=strict, assign=assign)
+        return res
+
+    def forward(self, x):
+        if isinstance(x, PackBitsTensor):
+            assert not self.training, "PackBitsTensor is not supported for the differentiable training mode."
+            return self.forward_cuda_eval(x)
+        if self.grad_factor != 1.0:
+            x = GradFactor.apply(x, self.grad_factor)
+        return self.forward_cuda(x)
+
+    def forward_cuda(self, x):
+        assert x.is_cuda, f"x must be a CUDA tensor, got device: {x.device}"
+        assert x.ndim == 2, x.ndim
+        x = x.transpose(0, 1).contiguous()  # feature-major; free when x came from another LogicLayer
+        assert x.shape[0] == self.in_dim, (x.shape, self.in_dim)
+        w = self.weights if self.weights.dtype == x.dtype else self.weights.to(x.dtype)
+        args = (x, self.indices_0, self.indices_1, w, self.given_x_indices_of_y_start, self.given_x_indices_of_y)
+        if self.training:
+            return LogicLayerCudaFunction.apply(*args, W_SOFTMAX).transpose(0, 1)
+        with torch.no_grad():
+            return LogicLayerCudaFunction.apply(*args, W_ARGMAX).transpose(0, 1)
+
+    def forward_cuda_eval(self, x: PackBitsTensor):
+        """Packed inference; returns a new PackBitsTensor (the reference rebinds ``x.t``)."""
+        assert not self.training
+        t = x.t.reshape(-1, x.t.shape[-1])
+        assert t.shape[0] == self.in_dim, (tuple(t.shape), self.in_dim)
+        gate_ids = self.weights.argmax(-1).to(torch.uint8)
+        y = ops.packed_logic(t, self.indices_0, self.indices_1, gate_ids)
+        return PackBitsTensor.from_packed(y, x.pad_len)
+
+    def extra_repr(self):
+        return "{}, {}, {}".format(self.in_dim, self.out_dim, "train" if self.training else "eval")
+
+    def get_connections(self, connections):
+        assert self.out_dim * 2 >= self.in_dim, (
+            f"The number of neurons ({self.out_dim}) must not be smaller than half of the "
+            f"number of inputs ({self.in_dim}) because otherwise not all inputs could be "
+            "used or considered.")
+        if connections == "random":
+            # same draws, in the same order, as src/difflogic/difflogic.py:176-181
+            c = torch.randperm(2 * self.out_dim) % self.in_dim
+            c = torch.randperm(self.in_dim)[c].reshape(2, self.out_dim)
+            return c[0].to(torch.int64), c[1].to(torch.int64)
+        if connections == "unique":
+            return get_unique_connections(self.in_dim, self.out_dim)
+        raise ValueError(connections)
+
+
+class GroupSum(torch.nn.Module):
+    """Sum the outputs in k groups; float input is divided by tau, packed input gives raw int32
+    counts ``[B, k]`` (src/difflogic/difflogic.py:188-211)."""
+
+    def __init__(self, k: int, tau: float = 1.0):
+        super().__init__()
+        self.k, self.tau = k, tau
+
+    def forward(self, x):
+        if isinstance(x, PackBitsTensor):
+            return x.group_sum(self.k)
+        assert x.shape[-1] % self.k == 0, (x.shape, self.k)
+        return x.reshape(*x.shape[:-1], self.k, x.shape[-1] // self.k).sum(-1) / self.tau
+
+    def extra_repr(self):
+        return f"k={self.k}, tau={self.tau}"

@@ -1,0 +1,133 @@
+"""Autograd Functions with the reference's names and argument lists.
+
+``FullConvLogicFunction``, ``ConvLogicFunction`` (src/convlogic/convlogic_layer.py:16-82),
+``TreeLogicFunction`` (src/convlogic/treelogic_layer.py:15-30), ``LogicLayerCudaFunction``
+(src/difflogic/difflogic.py:214-230) and ``GradFactor`` (src/difflogic/functional.py:131-139).
+
+As in the reference the gate argument is a MIXTURE over the 16 gates (soft-max already taken,
+or one-hot) and the returned gradient is w.r.t. that mixture.  Each Function accepts one extra,
+optional trailing argument ``wmode``; the layer modules pass W_SOFTMAX / W_ARGMAX together with
+the raw logits so that the soft-max (and its Jacobian in backward) runs inside the kernels.
+
+Unlike the reference, nothing but the input and an 8-bit arg-max per pooled output is saved for
+backward: the gate tree is recomputed at the arg-max position.
+"""
+
+import torch
+from torch.autograd import Function
+
+from . import ops
+from ._lib import W_ARGMAX, W_PROB, W_SOFTMAX  # noqa: F401
+
+
+class GradFactor(Function):
+    @staticmethod
+    def forward(ctx, x, f):
+        ctx.f = f
+        return x
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        return grad_y * ctx.f, None
+
+
+class FullConvLogicFunction(Function):
+    @staticmethod
+    def forward(ctx, x, w_prob, selection, stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w,
+                return_intermediate=False, return_indices=False, wmode=W_PROB):
+        x = x.contiguous()
+        w_prob = w_prob.contiguous()
+        geom = (stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w)
+        need_bwd = any(ctx.needs_input_grad[:2])
+        y, amax, x2, x3, idx = ops.convtree_fwd(x, w_prob, selection, geom, wmode, want_amax=need_bwd,
+                                                want_intermediate=return_intermediate, want_indices=return_indices)
+        ctx.save_for_backward(x, w_prob, selection, amax)
+        ctx.geom, ctx.wmode = geom, wmode
+        extra = []
+        if return_intermediate:
+            extra += [x2, x3]
+        if return_indices:
+            extra.append(idx)
+        if extra:
+            ctx.mark_non_differentiable(*extra)
+            return (y, *extra)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y, *unused):
+        x, w, sel, amax = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.convtree_bwd_x(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode)
+        if ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX:
+            gw = ops.convtree_bwd_w(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode)
+        return (gx, gw) + (None,) * 10
+
+
+class ConvLogicFunction(Function):
+    @staticmethod
+    def forward(ctx, x, w_prob, selection, stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w, wmode=W_PROB):
+        x = x.contiguous()
+        w_prob = w_prob.contiguous()
+        geom = (stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w)
+        y = ops.conv_fwd(x, w_prob, selection, geom, wmode)
+        ctx.save_for_backward(x, w_prob, selection)
+        ctx.geom, ctx.wmode = geom, wmode
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, w, sel = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.conv_bwd_x(grad_y, x, w, sel, ctx.geom, ctx.wmode)
+        if ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX:
+            gw = ops.conv_bwd_w(grad_y, x, w, sel, ctx.geom, ctx.wmode)
+        return (gx, gw) + (None,) * 8
+
+
+class TreeLogicFunction(Function):
+    @staticmethod
+    def forward(ctx, x, w_prob, wmode=W_PROB):
+        x = x.contiguous()
+        w_prob = w_prob.contiguous()
+        y = ops.tree_fwd(x, w_prob, wmode)
+        ctx.save_for_backward(x, w_prob)
+        ctx.wmode = wmode
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, w = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.tree_bwd_x(grad_y, x, w, ctx.wmode)
+        if ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX:
+            gw = ops.tree_bwd_w(grad_y, x, w, ctx.wmode)
+        return gx, gw, None
+
+
+class LogicLayerCudaFunction(Function):
+    """x is feature-major [in_dim, batch]; returns [out_dim, batch]."""
+
+    @staticmethod
+    def forward(ctx, x, a, b, w, given_x_indices_of_y_start, given_x_indices_of_y, wmode=W_PROB):
+        x = x.contiguous()
+        w = w.contiguous()
+        ctx.save_for_backward(x, a, b, w, given_x_indices_of_y_start, given_x_indices_of_y)
+        ctx.wmode = wmode
+        return ops.logic_fwd(x, a, b, w, wmode)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, a, b, w, start, cons = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.logic_bwd_x(x, a, b, w, grad_y, start, cons, ctx.wmode)
+        if ctx.needs_input_grad[3] and ctx.wmode != W_ARGMAX:
+            gw = ops.logic_bwd_w(x, a, b, w, grad_y, ctx.wmode)
+        return gx, None, None, gw, None, None, None

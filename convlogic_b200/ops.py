@@ -1,0 +1,298 @@
+"""Thin tensor-level wrappers over the C ABI: validate, allocate outputs, launch on the
+current stream.  No arithmetic happens in Python.  Shapes follow the reference's pybind
+entry points (src/convlogic/cuda/convlogic.cpp:29-44, src/difflogic/cuda/difflogic.cpp:15-34).
+"""
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check, check_input, dtype_code, lib, ptr, stream
+
+
+def _geom(stride, padding, kernel):
+    return (*stride, *padding, *kernel)
+
+
+def _out_hw(h, w, sh, sw, ph, pw, kh, kw):
+    return (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+
+
+def _sel_ok(sel, c):
+    if sel.dtype != torch.int32 or sel.shape != (c, 8):
+        raise RuntimeError(f"convlogic_b200: selection must be int32 [{c}, 8], got {sel.dtype} {tuple(sel.shape)}")
+
+
+# ------------------------------------------------------------------------------ fused block
+def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False, want_indices=False):
+    check_input(x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    if w.shape != (c, 7, 16) or w.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: gate tensor must be [{c}, 7, 16] {x.dtype}")
+    _sel_ok(sel, c)
+    ho, wo = _out_hw(h, wd, *geom)
+    if ho <= 0 or wo <= 0:
+        raise RuntimeError(f"Invalid output shape: H_out={ho}, W_out={wo}")
+    if ho % 2 or wo % 2:
+        raise RuntimeError(
+            "Output height and width after convolution must be divisible by 2 for 2x2 max pooling, "
+            f"but got H_out={ho}, W_out={wo}")
+    y = torch.empty((n, c, ho // 2, wo // 2), dtype=x.dtype, device=x.device)
+    amax = torch.empty((n, c, ho // 2, wo // 2), dtype=torch.uint8, device=x.device) if want_amax else None
+    x2 = x3 = idx = None
+    if want_intermediate:
+        x2 = torch.empty((n, c, ho, wo, 4), dtype=x.dtype, device=x.device)
+        x3 = torch.empty((n, c, ho, wo, 2), dtype=x.dtype, device=x.device)
+    if want_indices:
+        idx = torch.empty((n, c, (ho // 2) * (wo // 2)), dtype=torch.int32, device=x.device)
+    check(lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), ptr(amax), ptr(x2), ptr(x3), ptr(idx),
+                                 n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return y, amax, x2, x3, idx
+
+
+_group_cache = {}
+
+
+def conv_groups(sel, x_shape, geom, dtype):
+    """Device tables for the input-gradient kernels (cached per selection tensor and shape)."""
+    n, ci, h, w = x_shape
+    c = sel.shape[0]
+    key = (sel.data_ptr(), sel._version, sel.device, n, ci, h, w, geom, dtype)
+    hit = _group_cache.get(key)
+    if hit is not None:
+        return hit
+    cg, nb = C.c_int(0), C.c_int(0)
+    check(lib().clb_conv_group_plan(n, ci, h, w, c, *geom, _lib.F32 if dtype == torch.float32 else _lib.F64,
+                                    C.byref(cg), C.byref(nb)))
+    cg, nb = cg.value, nb.value
+    g = -(-ci // cg)
+    sel_host = np.ascontiguousarray(sel.detach().cpu().numpy(), dtype=np.int32)
+    start = np.zeros(g + 1, dtype=np.int32)
+    cap = max(1, c * min(g, 8))
+    lst = np.zeros(cap, dtype=np.int32)
+    cnt = lib().clb_conv_build_groups(sel_host.ctypes.data_as(C.c_void_p), c, ci, cg,
+                                      start.ctypes.data_as(C.c_void_p), lst.ctypes.data_as(C.c_void_p), cap)
+    if cnt < 0:
+        if cnt == -1:
+            raise RuntimeError("convlogic_b200: selection refers to a channel the input does not have")
+        check(cnt)
+    out = (torch.from_numpy(start).to(sel.device), torch.from_numpy(lst[:max(cnt, 1)].copy()).to(sel.device), cg, nb)
+    if len(_group_cache) > 256:
+        _group_cache.clear()
+    _group_cache[key] = out
+    return out
+
+
+def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode):
+    check_input(gy, x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    gx = torch.empty_like(x)
+    start, lst, cg, nb = conv_groups(sel, tuple(x.shape), geom, x.dtype)
+    check(lib().clb_convtree_bwd_x(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(start), ptr(lst),
+                                   cg, nb, n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return gx
+
+
+def convtree_bwd_w(gy, x, w, sel, amax, geom, wmode):
+    check_input(gy, x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    ho, wo = _out_hw(h, wd, *geom)
+    gw = torch.empty_like(w)
+    nbytes = lib().clb_convtree_bwd_w_scratch_bytes(n, c, ho, wo, dtype_code(x))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    check(lib().clb_convtree_bwd_w(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gw), ptr(scratch), nbytes,
+                                   n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return gw
+
+
+# --------------------------------------------------------------------- stand-alone first level
+def conv_fwd(x, w, sel, geom, wmode):
+    check_input(x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    if w.shape != (c, 4, 16) or w.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: gate tensor must be [{c}, 4, 16] {x.dtype}")
+    _sel_ok(sel, c)
+    ho, wo = _out_hw(h, wd, *geom)
+    if ho <= 0 or wo <= 0:
+        raise RuntimeError(f"Invalid output shape: H_out={ho}, W_out={wo}")
+    y = torch.empty((n, c, ho, wo, 4), dtype=x.dtype, device=x.device)
+    check(lib().clb_conv_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return y
+
+
+def conv_bwd_x(gy, x, w, sel, geom, wmode):
+    check_input(gy, x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    gx = torch.empty_like(x)
+    start, lst, cg, nb = conv_groups(sel, tuple(x.shape), geom, x.dtype)
+    check(lib().clb_conv_bwd_x(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(gx), ptr(start), ptr(lst), cg, nb,
+                               n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return gx
+
+
+def conv_bwd_w(gy, x, w, sel, geom, wmode):
+    check_input(gy, x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    ho, wo = _out_hw(h, wd, *geom)
+    gw = torch.empty_like(w)
+    nbytes = lib().clb_conv_bwd_w_scratch_bytes(n, c, ho, wo, dtype_code(x))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    check(lib().clb_conv_bwd_w(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(gw), ptr(scratch), nbytes,
+                               n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return gw
+
+
+# -------------------------------------------------------------------------------- tree level
+def _tree_dims(x, w):
+    if x.dim() != 5:
+        raise RuntimeError(f"Expected input tensor x to be 5D (N, C, H, W, 2*Xout), but got {x.dim()}")
+    n, c, h, wd, xin = x.shape
+    xo = w.shape[1]
+    if xin != 2 * xo:
+        raise RuntimeError(f"Expected input x.size(4) (Xin) to equal 2*Xout ({2 * xo}), but got {xin}")
+    if w.shape != (c, xo, 16) or w.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: gate tensor must be [{c}, {xo}, 16] {x.dtype}")
+    return n, c, h * wd, xo
+
+
+def tree_fwd(x, w, wmode):
+    check_input(x, w)
+    n, c, hw, xo = _tree_dims(x, w)
+    y = torch.empty((*x.shape[:4], xo), dtype=x.dtype, device=x.device)
+    check(lib().clb_tree_fwd(ptr(x), ptr(w), ptr(y), n, c, hw, xo, wmode, dtype_code(x), stream()))
+    return y
+
+
+def tree_bwd_x(gy, x, w, wmode):
+    check_input(gy, x, w)
+    n, c, hw, xo = _tree_dims(x, w)
+    gx = torch.empty_like(x)
+    check(lib().clb_tree_bwd_x(ptr(gy), ptr(x), ptr(w), ptr(gx), n, c, hw, xo, wmode, dtype_code(x), stream()))
+    return gx
+
+
+def tree_bwd_w(gy, x, w, wmode):
+    check_input(gy, x, w)
+    n, c, hw, xo = _tree_dims(x, w)
+    gw = torch.empty_like(w)
+    nbytes = lib().clb_tree_bwd_w_scratch_bytes(n, c, hw, xo, dtype_code(x))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    check(lib().clb_tree_bwd_w(ptr(gy), ptr(x), ptr(w), ptr(gw), ptr(scratch), nbytes, n, c, hw, xo, wmode,
+                               dtype_code(x), stream()))
+    return gw
+
+
+# -------------------------------------------------------------------------------- flat layer
+def _logic_dims(x, a, b, w):
+    if x.dim() != 2:
+        raise RuntimeError(f"convlogic_b200: x must be [in_dim, batch], got {tuple(x.shape)}")
+    out = w.shape[0]
+    if w.shape != (out, 16) or w.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: gate tensor must be [{out}, 16] {x.dtype}")
+    if a.dtype != torch.int64 or b.dtype != torch.int64 or a.shape != (out,) or b.shape != (out,):
+        raise RuntimeError("convlogic_b200: connection indices must be int64 [out_dim]")
+    return x.shape[0], out, x.shape[1]
+
+
+def logic_fwd(x, a, b, w, wmode):
+    check_input(x, a, b, w)
+    i, o, bsz = _logic_dims(x, a, b, w)
+    y = torch.empty((o, bsz), dtype=x.dtype, device=x.device)
+    check(lib().clb_logic_fwd(ptr(x), ptr(a), ptr(b), ptr(w), ptr(y), i, o, bsz, wmode, dtype_code(x), stream()))
+    return y
+
+
+def logic_bwd_w(x, a, b, w, gy, wmode):
+    check_input(x, a, b, w, gy)
+    i, o, bsz = _logic_dims(x, a, b, w)
+    gw = torch.empty_like(w)
+    check(lib().clb_logic_bwd_w(ptr(x), ptr(a), ptr(b), ptr(w), ptr(gy), ptr(gw), i, o, bsz, wmode, dtype_code(x),
+                                stream()))
+    return gw
+
+
+def logic_bwd_x(x, a, b, w, gy, start, consumers, wmode):
+    check_input(x, a, b, w, gy, start, consumers)
+    i, o, bsz = _logic_dims(x, a, b, w)
+    if start.dtype != torch.int64 or consumers.dtype != torch.int64 or start.numel() != i + 1 or consumers.numel() != 2 * o:
+        raise RuntimeError("convlogic_b200: consumer lists must be int64 [in_dim + 1] and [2 * out_dim]")
+    gx = torch.empty_like(x)
+    check(lib().clb_logic_bwd_x(ptr(x), ptr(a), ptr(b), ptr(w), ptr(gy), ptr(gx), ptr(start), ptr(consumers),
+                                i, o, bsz, wmode, dtype_code(x), stream()))
+    return gx
+
+
+# ------------------------------------------------------------------------------------ packed
+_INT = {8: torch.int8, 16: torch.int16, 32: torch.int32, 64: torch.int64}
+
+
+def _bits_of(t):
+    return t.element_size() * 8
+
+
+def pack_bits(t, bit_count, sample_major=False):
+    """bool tensor -> (packed, pad_len).  ``sample_major=False``: t [F, B] (the reference's
+    ``tensor_packbits_cuda`` layout); ``True``: t [B, F]."""
+    if bit_count not in _INT:
+        raise ValueError("`bit_count` has to be in { 8, 16, 32, 64 }")
+    check_input(t)
+    if t.dtype not in (torch.bool, torch.uint8):
+        raise RuntimeError("convlogic_b200: pack_bits expects a bool or uint8 tensor")
+    src = t.view(torch.uint8) if t.dtype == torch.bool else t
+    if sample_major:
+        b, f = src.shape
+    else:
+        f, b = src.shape
+    words = -(-b // bit_count)
+    packed = torch.empty((f, words), dtype=_INT[bit_count], device=t.device)
+    fn = lib().clb_pack_bits_nmajor if sample_major else lib().clb_pack_bits
+    check(fn(ptr(src), ptr(packed), b if sample_major else f, f if sample_major else b, bit_count, stream()))
+    return packed, (bit_count - b % bit_count) % bit_count
+
+
+def packed_logic(x, a, b, ops):
+    check_input(x, a, b, ops)
+    if ops.dtype != torch.uint8:
+        raise RuntimeError("convlogic_b200: gate ids must be uint8")
+    out = ops.shape[0]
+    y = torch.empty((out, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(lib().clb_packed_logic(ptr(x), ptr(a), ptr(b), ptr(ops), ptr(y), x.shape[0], out, x.shape[1], _bits_of(x),
+                                 stream()))
+    return y
+
+
+def group_popcount(x, pad_len, k):
+    check_input(x)
+    f, words = x.shape
+    if f % k:
+        raise ValueError(f"in_dim ({f}) has to be divisible by k ({k}) but it is not")
+    bits = _bits_of(x)
+    counts = torch.empty((words * bits - pad_len, k), dtype=torch.int32, device=x.device)
+    check(lib().clb_group_popcount(ptr(x), ptr(counts), f, words, bits, pad_len, k, stream()))
+    return counts
+
+
+def packed_convtree(x, ops, sel, geom):
+    check_input(x, ops, sel)
+    ci, h, w, words = x.shape
+    c = sel.shape[0]
+    _sel_ok(sel, c)
+    if ops.dtype != torch.uint8 or ops.shape != (c, 7):
+        raise RuntimeError(f"convlogic_b200: gate ids must be uint8 [{c}, 7]")
+    ho, wo = _out_hw(h, w, *geom)
+    if ho <= 0 or wo <= 0 or ho % 2 or wo % 2:
+        raise RuntimeError(
+            "Output height and width after convolution must be divisible by 2 for 2x2 max pooling, "
+            f"but got H_out={ho}, W_out={wo}")
+    y = torch.empty((c, ho // 2, wo // 2, words), dtype=x.dtype, device=x.device)
+    check(lib().clb_packed_convtree(ptr(x), ptr(ops), ptr(sel), ptr(y), ci, h, w, c, *geom, words, _bits_of(x),
+                                    stream()))
+    return y

@@ -1,0 +1,64 @@
+"""Bit-packed activations for discretised inference.
+
+Mirrors the reference's ``PackBitsTensor`` (src/difflogic/packbitstensor.py:11-43): ``.t`` is
+feature-major ``[features, ceil(B / bits)]`` with sample ``bits * word + i`` in bit ``i``,
+``.pad_len`` the number of pad samples, ``group_sum(k)`` the per-class bit counts and
+``flatten()`` a no-op.  Two additions, both needed for ConvLogic blocks, which the reference
+cannot run packed: a 4-D bool input ``[B, C, H, W]`` is packed to ``.t`` of shape
+``[C, H, W, words]`` (so that ``flatten`` onto ``[C*H*W, words]`` is a free view in the same
+feature order as ``nn.Flatten`` on NCHW), and the sample-major input is packed in one pass
+without the transposed copy.
+"""
+
+import numpy as np
+import torch
+
+from . import ops
+
+
+class PackBitsTensor:
+    def __init__(self, t: torch.Tensor, bit_count: int = 32):
+        assert t.dim() in (2, 4), t.shape
+        self.bit_count = bit_count
+        if not t.is_cuda:
+            raise NotImplementedError(f"PackBitsTensor only supports CUDA tensors, but got {t.device}.")
+        t = t.contiguous()
+        flat = t.reshape(t.shape[0], -1)
+        packed, self.pad_len = ops.pack_bits(flat, bit_count, sample_major=True)
+        self.t = packed.view(*t.shape[1:], packed.shape[-1]) if t.dim() == 4 else packed
+
+    @classmethod
+    def from_packed(cls, t, pad_len):
+        self = cls.__new__(cls)
+        self.t, self.pad_len, self.bit_count = t, pad_len, t.element_size() * 8
+        return self
+
+    @property
+    def is_cuda(self):
+        return self.t.is_cuda
+
+    @property
+    def device(self):
+        return self.t.device
+
+    def contiguous(self):
+        return self
+
+    def group_sum(self, k):
+        return ops.group_popcount(self.t.reshape(-1, self.t.shape[-1]), self.pad_len, k)
+
+    def flatten(self, start_dim=0, end_dim=-1, **kwargs):
+        """Returns the tensor itself viewed as [features, words]; arguments are ignored."""
+        if self.t.dim() != 2:
+            return PackBitsTensor.from_packed(self.t.reshape(-1, self.t.shape[-1]), self.pad_len)
+        return self
+
+    def _get_member_repr(self, member):
+        rows = [np.binary_repr(int(v) & ((1 << self.bit_count) - 1), width=self.bit_count)[::-1] for v in member]
+        if len(rows) <= 4:
+            return " ".join(rows)
+        return f"{' '.join(rows[:3])} ... {rows[-1]}"
+
+    def __repr__(self):
+        t2 = self.t.reshape(-1, self.t.shape[-1]).cpu()
+        return "\n".join(self._get_member_repr(item.tolist()) for item in t2)

@@ -1,0 +1,177 @@
+/*
+ * convlogic_b200 -- C ABI of the B200 (sm_100a) logic-gate kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * a cudaStream_t), launches on that stream and returns immediately: nothing here allocates,
+ * frees, synchronises the device, throws or exits.  The return value is CLB_OK (0) or a negative
+ * CLB_ERR_* code; clb_status_string() gives the text.  Inputs are borrowed for the duration of the
+ * launched work; outputs and any scratch buffer are supplied by the caller.
+ *
+ * The citations name the entry point of lkorinek/convlogic that each function stands in for
+ * (paths inside that project).
+ *
+ * Conventions
+ *   dtype   CLB_F32 or CLB_F64 for every floating tensor of one call.
+ *   wmode   how the gate tensor `w` ([..., 16] per gate) is to be read:
+ *             CLB_W_PROB     a mixture over the 16 gates (soft-max already applied, or one-hot);
+ *             CLB_W_SOFTMAX  raw logits, soft-max taken inside the kernel;
+ *             CLB_W_ARGMAX   raw logits, one-hot of the first arg-max taken inside the kernel.
+ *           Backward functions given CLB_W_SOFTMAX return the gradient w.r.t. the logits, given
+ *           CLB_W_PROB the gradient w.r.t. the mixture (what the reference's autograd Functions
+ *           return).
+ *   sel     int32 [C, 8] selection words, (channel << 16) | (row << 8) | col; taps (2p, 2p+1) feed
+ *           first-level gate p (src/convlogic/convlogic_layer.py:175-179, 450-451).
+ *   gates   slot order of a fused block's 7 gates: 0-3 first level, 4-5 second, 6 third
+ *           (src/convlogic/cuda/full_convlogic_kernel.cu:6-8).
+ */
+#ifndef CONVLOGIC_B200_H
+#define CONVLOGIC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CLB_OK 0
+#define CLB_ERR_ARG (-1)         /* null pointer, bad enum value, negative size */
+#define CLB_ERR_SHAPE (-2)       /* shapes inconsistent or outside what the kernels support */
+#define CLB_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch; see clb_last_cuda_error() */
+#define CLB_ERR_SCRATCH (-4)     /* scratch buffer missing or too small */
+#define CLB_ERR_ODD_OUTPUT (-5)  /* fused block: conv output height/width must be even (2x2 pool) */
+#define CLB_ERR_TOO_LARGE (-6)   /* size beyond a documented fixed maximum */
+
+#define CLB_F32 0
+#define CLB_F64 1
+
+#define CLB_W_PROB 0
+#define CLB_W_SOFTMAX 1
+#define CLB_W_ARGMAX 2
+
+int clb_version(void);
+const char *clb_status_string(int status);
+/* cudaError_t value of the most recent failed launch made through this library by the calling thread. */
+int clb_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Fused ConvLogic block: 8-tap gather -> 4 gates -> 2 gates -> 1 gate -> 2x2 max pool.
+ * Replaces convlogic_cuda.full_convlogic_forward (src/convlogic/cuda/convlogic.cpp:39;
+ * full_convlogic_kernel.cu:147-231).
+ *   x [N,Ci,H,W]   w [C,7,16]   sel [C,8]   y [N,C,Ho/2,Wo/2],  Ho = (H + 2*ph - kh)/sh + 1.
+ * Optional outputs (pass NULL to skip): amax uint8 [N,C,Ho/2,Wo/2] = 2*dy+dx of the first maximum
+ * of each window; x2 [N,C,Ho,Wo,4], x3 [N,C,Ho,Wo,2] (the reference's intermediates);
+ * idx int32 [N,C,(Ho/2)*(Wo/2)] = in_y*Wo + in_x of the first maximum.
+ */
+int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel, void *y, uint8_t *amax, void *x2, void *x3,
+                     int32_t *idx, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                     int kw, int wmode, int dtype, void *stream);
+
+/* Input gradient of the fused block; deterministic (no floating-point atomics).
+ * Replaces convlogic_cuda.full_convlogic_backward_x (convlogic.cpp:40-41;
+ * full_convlogic_kernel.cu:365-461).  gy like y, gx like x (fully overwritten).
+ * amax may be NULL (the arg-max is then recomputed).  The input channels are processed in groups
+ * of `cg` consecutive channels; grp_start int32 [G+1] / grp_list int32 [grp_start[G]] list, for each
+ * group, the output channels with at least one tap in it (ascending).  Build them with
+ * clb_conv_group_plan() + clb_conv_build_groups().
+ */
+int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax,
+                       void *gx, const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci,
+                       int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype,
+                       void *stream);
+
+/* Host-side helpers for the tables above (pure CPU, no CUDA call).
+ * clb_conv_group_plan: picks cg (channels per group) and nb (images per thread block) for a shape.
+ * clb_conv_build_groups: sel_host int32 [C,8] in host memory -> grp_start [G+1], grp_list (capacity
+ * list_cap entries, at most min(C*G, C*8)); returns the number of list entries or a negative status. */
+int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int dtype,
+                        int *cg, int *nb);
+int clb_conv_build_groups(const int32_t *sel_host, int C, int Ci, int cg, int32_t *grp_start, int32_t *grp_list,
+                          int list_cap);
+
+/* Gate-weight gradient of the fused block; deterministic two-stage reduction.
+ * Replaces convlogic_cuda.full_convlogic_backward_weight (convlogic.cpp:42-43;
+ * full_convlogic_kernel.cu:616-701).  gw [C,7,16].  scratch: clb_convtree_bwd_w_scratch_bytes().
+ */
+size_t clb_convtree_bwd_w_scratch_bytes(int N, int C, int Ho, int Wo, int dtype);
+int clb_convtree_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax,
+                       void *gw, void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh,
+                       int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stand-alone first gate level (ConvLogicLayer with complete=False).
+ * Replace convlogic_cuda.convlogic_forward / convlogic_backward_x / convlogic_backward_weight
+ * (convlogic.cpp:31-33; convlogic_kernel.cu:67-107, 322-359, 197-247).
+ *   y, gy [N,C,Ho,Wo,4]   w, gw [C,4,16].  Backward-x uses the same group tables as above.
+ */
+int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, void *y, int N, int Ci, int H, int W, int C,
+                 int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream);
+int clb_conv_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, void *gx,
+                   const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W,
+                   int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream);
+size_t clb_conv_bwd_w_scratch_bytes(int N, int C, int Ho, int Wo, int dtype);
+int clb_conv_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, void *gw, void *scratch,
+                   size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                   int kw, int wmode, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * One pairwise gate level on the trailing dimension (TreeLogicLayer).
+ * Replace convlogic_cuda.treelogic_forward / treelogic_backward_x / treelogic_backward_weight
+ * (convlogic.cpp:35-37; treelogic_kernel.cu:46-86, 252-285, 160-205).
+ *   x, gx [N,C,H,W,2X]   y, gy [N,C,H,W,X]   w, gw [C,X,16];  HW = H*W.  Any X >= 1.
+ */
+int clb_tree_fwd(const void *x, const void *w, void *y, int N, int C, int HW, int X, int wmode, int dtype,
+                 void *stream);
+int clb_tree_bwd_x(const void *gy, const void *x, const void *w, void *gx, int N, int C, int HW, int X, int wmode,
+                   int dtype, void *stream);
+size_t clb_tree_bwd_w_scratch_bytes(int N, int C, int HW, int X, int dtype);
+int clb_tree_bwd_w(const void *gy, const void *x, const void *w, void *gw, void *scratch, size_t scratch_bytes,
+                   int N, int C, int HW, int X, int wmode, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Flat LogicLayer on feature-major activations.
+ * Replace difflogic_cuda.forward / backward_w / backward_x (src/difflogic/cuda/difflogic.cpp:17-19;
+ * difflogic_kernel.cu:89-126, 128-173, 232-269).
+ *   x, gx [in,B]   y, gy [out,B]   a, b int64 [out]   w, gw [out,16]
+ *   start int64 [in+1], consumers int64 [2*out]: for input feature i the neurons reading it
+ *   (the reference's given_x_indices_of_y_start / given_x_indices_of_y).  Any batch size.
+ */
+int clb_logic_fwd(const void *x, const int64_t *a, const int64_t *b, const void *w, void *y, int64_t in_dim,
+                  int64_t out_dim, int64_t B, int wmode, int dtype, void *stream);
+int clb_logic_bwd_w(const void *x, const int64_t *a, const int64_t *b, const void *w, const void *gy, void *gw,
+                    int64_t in_dim, int64_t out_dim, int64_t B, int wmode, int dtype, void *stream);
+int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b, const void *w, const void *gy, void *gx,
+                    const int64_t *start, const int64_t *consumers, int64_t in_dim, int64_t out_dim, int64_t B,
+                    int wmode, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Packed (discretised) inference.  A packed tensor is [rows, words] of `bits`-wide integers
+ * (bits in {8,16,32,64}); sample bits*word + i sits in bit i (LSB first), pad bits are zero.
+ */
+/* Replaces difflogic_cuda.tensor_packbits_cuda (difflogic.cpp:21; difflogic_kernel.cu:335-413).
+ * t bool/uint8 [F,B] (non-zero = 1) -> packed [F, ceil(B/bits)]. */
+int clb_pack_bits(const uint8_t *t, void *packed, int64_t F, int64_t B, int bits, void *stream);
+/* Same, for image batches: t [N, F] sample-major (e.g. a [N,C,H,W] tensor, F = C*H*W) -> packed
+ * [F, ceil(N/bits)], i.e. the transpose and the packing in one pass. */
+int clb_pack_bits_nmajor(const uint8_t *t, void *packed, int64_t N, int64_t F, int bits, void *stream);
+/* Replaces difflogic_cuda.eval (difflogic.cpp:20; difflogic_kernel.cu:272-329).
+ * x [in,words], ops uint8 [out] gate ids 0..15 -> y [out,words]. */
+int clb_packed_logic(const void *x, const int64_t *a, const int64_t *b, const uint8_t *ops, void *y,
+                     int64_t in_dim, int64_t out_dim, int64_t words, int bits, void *stream);
+/* Replaces difflogic_cuda.groupbitsum (difflogic.cpp:22-33; difflogic_kernel.cu:418-482).
+ * x [F,words] -> counts int32 [B,k], B = words*bits - pad_len; F must be divisible by k
+ * (CLB_ERR_SHAPE otherwise, the reference's ValueError). */
+int clb_group_popcount(const void *x, int32_t *counts, int64_t F, int64_t words, int bits, int pad_len, int k,
+                       void *stream);
+/* Packed fused ConvLogic block: bitwise 7-gate tree and OR-pool.  The reference declares such a
+ * path (src/convlogic/convlogic_layer.py:357-372, forward_cuda_eval) but never implemented it; it is
+ * defined here by the eval-mode float block on {0,1} inputs.
+ * x [Ci,H,W,words]  ops uint8 [C,7]  ->  y [C,Ho/2,Wo/2,words]. */
+int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, void *y, int Ci, int H, int W,
+                        int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t words, int bits,
+                        void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CONVLOGIC_B200_H */

@@ -1,0 +1,125 @@
+"""Flat LogicLayer and GroupSum on the GPU against the reference's golden tensors and the oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def _layer(cb, g, pre):
+    a, b = torch.from_numpy(g[f"{pre}/a"]), torch.from_numpy(g[f"{pre}/b"])
+    in_dim, out_dim = g[f"{pre}/x"].shape[1], a.shape[0]
+    layer = cb.LogicLayer(in_dim, out_dim)
+    state = layer.state_dict()
+    start, cons = cb.LogicLayer.build_consumer_lists(a, b, in_dim)
+    state.update(weights=torch.from_numpy(g[f"{pre}/logits"]), indices_0=a, indices_1=b,
+                 given_x_indices_of_y_start=start, given_x_indices_of_y=cons)
+    layer.load_state_dict(state)
+    return layer.cuda()
+
+
+@pytest.mark.parametrize("j", [0, 1, 2])
+def test_matches_reference_golden(golden, j):
+    import convlogic_b200 as cb
+
+    g = golden("flat_layers")
+    pre = f"flat{j}"
+    layer = _layer(cb, g, pre).train()
+    k, tau = g[f"{pre}/k_tau"]
+    x = torch.from_numpy(g[f"{pre}/x"]).cuda().requires_grad_(True)
+    y = layer(x)
+    gx, gw = torch.autograd.grad((y * torch.from_numpy(g[f"{pre}/gy"]).cuda()).sum(), (x, layer.weights), retain_graph=True)
+    assert_close(y, g[f"{pre}/y_soft"], TOL, "soft forward")
+    assert_close(gx, g[f"{pre}/gx"], TOL, "input gradient")
+    assert_close(gw, g[f"{pre}/gw_logits"], TOL, "logit gradient")
+    assert_close(cb.GroupSum(int(k), float(tau))(y), g[f"{pre}/group_sum"], TOL, "group sum")
+    layer.eval()
+    yh = layer(x.detach())
+    assert_close(yh, g[f"{pre}/y_hard"], TOL, "hard forward")
+    if j == 0:
+        assert np.array_equal(yh.cpu().numpy(), g[f"{pre}/y_hard"])
+
+
+@pytest.mark.parametrize("batch,in_dim,out_dim", [(1, 8, 16), (3, 10, 30), (256, 64, 200), (1028, 32, 96), (2050, 6, 12)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float64, 1e-10)])
+def test_function_api_matches_oracle(batch, in_dim, out_dim, dtype, tol):
+    """Reference-style call: feature-major x, probabilities in, gradient w.r.t. probabilities out;
+    batches beyond the reference kernel's 1024 limit included."""
+    import convlogic_b200 as cb
+
+    g = torch.Generator().manual_seed(batch)
+    a = torch.randint(0, in_dim, (out_dim,), generator=g)
+    b = torch.randint(0, in_dim, (out_dim,), generator=g)
+    b[0] = a[0]  # a neuron reading the same feature twice
+    x = torch.rand(batch, in_dim, generator=g, dtype=dtype)
+    p = torch.softmax(torch.randn(out_dim, 16, generator=g, dtype=dtype), -1)
+    gy = torch.randn(batch, out_dim, generator=g, dtype=dtype)
+    xo, po = x.clone().requires_grad_(True), p.clone().requires_grad_(True)
+    yo = oracle.logic_layer(xo, a, b, po)
+    gxo, gpo = torch.autograd.grad((yo * gy).sum(), (xo, po))
+    start, cons = cb.LogicLayer.build_consumer_lists(a, b, in_dim)
+    xd = x.T.contiguous().cuda().requires_grad_(True)
+    pd = p.cuda().requires_grad_(True)
+    y = cb.LogicLayerCudaFunction.apply(xd, a.cuda(), b.cuda(), pd, start.cuda(), cons.cuda())
+    gx, gp = torch.autograd.grad((y * gy.T.contiguous().cuda()).sum(), (xd, pd))
+    assert_close(y.T, yo.detach(), tol)
+    assert_close(gx.T, gxo, tol)
+    assert_close(gp, gpo, tol)
+
+
+def test_all_logic_gates_flat():
+    """Known-answer test of the 16 gates (tests/difflogic/test_difflogic_forward.py:74-100)."""
+    import convlogic_b200 as cb
+
+    layer = cb.LogicLayer(2, 16).cuda().eval()
+    w = torch.full((16, 16), -float("inf"))
+    w[torch.arange(16), torch.arange(16)] = 0.0
+    layer.weights.data = w.cuda()
+    layer.indices_0.zero_()
+    layer.indices_1.fill_(1)
+    x = torch.tensor([[0.0, 0.0], [0.0, 1.0], [1.0, 0.0], [1.0, 1.0]], device="cuda")
+    y = layer(x).cpu()
+    for gate in range(16):
+        want = oracle.bin_op(x[:, 0].cpu(), x[:, 1].cpu(), gate)
+        assert torch.equal(y[:, gate], want), gate
+
+
+def test_gradcheck_like_reference():
+    """tests/difflogic/test_difflogic_autograd.py:31-54."""
+    import convlogic_b200 as cb
+    from torch.autograd import gradcheck
+
+    torch.manual_seed(0)
+    layer = cb.LogicLayer(6, 10).double().cuda()
+    x = torch.rand(6, 5, dtype=torch.double, device="cuda", requires_grad=True)
+    w = layer.weights.detach().clone().requires_grad_(True)
+
+    def fn(inp, logits):
+        return cb.LogicLayerCudaFunction.apply(inp, layer.indices_0, layer.indices_1, torch.softmax(logits, -1),
+                                               layer.given_x_indices_of_y_start, layer.given_x_indices_of_y)
+
+    assert gradcheck(fn, (x, w), eps=1e-6, atol=1e-4)
+
+
+def test_layer_stack_stays_feature_major_and_deterministic():
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    l1, l2 = cb.LogicLayer(32, 64).cuda(), cb.LogicLayer(64, 40).cuda()
+    x = torch.rand(20, 32, device="cuda", requires_grad=True)
+    outs = []
+    for _ in range(2):
+        for m in (l1, l2):
+            m.weights.grad = None
+        x.grad = None
+        h = l1(x)
+        assert h.T.is_contiguous()  # the next layer's transpose is a free view
+        y = cb.GroupSum(10, 3.0)(l2(h))
+        y.square().sum().backward()
+        outs.append((y.detach().clone(), x.grad.clone(), l1.weights.grad.clone()))
+    assert all(torch.equal(u, v) for u, v in zip(*outs))

@@ -1,0 +1,190 @@
+"""Fused ConvLogic block on the GPU against the golden tensors of the reference's CPU path and
+against the CPU oracle.  Tolerances: soft mode fp32 1e-5 relative (to the tensor's max), fp64 1e-10;
+hard mode on {0,1} inputs exact."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.golden.make_golden import FUSED_CASES
+from tests.util import assert_close, random_selection, rel_err
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL, F64_TOL = 1e-5, 1e-10
+
+
+def _layer(cb, g, name, dtype):
+    sh, sw, ph, pw, kh, kw = (int(v) for v in g[f"{name}/geom"])
+    sel = torch.from_numpy(g[f"{name}/selection"])
+    c, ci = sel.shape[0], g[f"{name}/x"].shape[1]
+    layer = cb.ConvLogicLayer(ci, c, stride=(sh, sw), padding=(ph, pw), kernel=(kh, kw), selection=sel, complete=True)
+    layer.weights.data = torch.from_numpy(g[f"{name}/logits"])
+    return layer.to("cuda", dtype)
+
+
+@pytest.mark.parametrize("name", [c[0] for c in FUSED_CASES])
+@pytest.mark.parametrize("tag,dtype,tol", [("f32", torch.float32, F32_TOL), ("f64", torch.float64, F64_TOL)])
+def test_matches_reference_golden(golden, name, tag, dtype, tol):
+    import convlogic_b200 as cb
+
+    g = golden("fused_block")
+    layer = _layer(cb, g, name, dtype).train()
+    x = torch.from_numpy(g[f"{name}/x"]).to("cuda", dtype).requires_grad_(True)
+    gy = torch.from_numpy(g[f"{name}/gy"]).to("cuda", dtype)
+    y = layer(x)
+    (y * gy).sum().backward()
+    assert_close(y, g[f"{name}/{tag}/y_soft"], tol, "soft forward")
+    assert_close(x.grad, g[f"{name}/{tag}/gx"], tol, "input gradient")
+    assert_close(layer.weights.grad, g[f"{name}/{tag}/gw_logits"], tol, "logit gradient")
+    layer.eval()
+    with torch.no_grad():
+        yh = layer(x.detach())
+    if "bits" in name:
+        assert np.array_equal(yh.cpu().numpy(), g[f"{name}/{tag}/y_hard"])
+    else:
+        assert_close(yh, g[f"{name}/{tag}/y_hard"], max(tol, 1e-6), "hard forward")
+
+
+SHAPES = [
+    # N, Ci, C, H, W, stride, pad, kernel, input
+    (8, 9, 32, 32, 32, 1, 1, 3, "bits"),     # the microbenchmark's block at reduced batch / width
+    (5, 16, 24, 12, 12, 1, 1, 3, "rand"),    # mnist_s block 2 shape
+    (3, 1, 16, 28, 28, 1, 0, 5, "bits"),     # mnist_s block 1: 5x5 window, no padding
+    (7, 48, 40, 6, 6, 1, 1, 3, "rand"),      # small images, several images per block in backward
+    (2, 300, 20, 4, 4, 1, 1, 3, "rand"),     # more input channels than one shared-memory group holds
+    (2, 3, 5, 70, 66, 1, 1, 3, "rand"),      # > 1024 pooled positions (the reference's limit)
+    (4, 3, 6, 13, 9, 2, 2, 4, "randn"),      # stride 2
+    (1, 1, 1, 3, 3, 1, 0, 2, "randn"),       # single output
+]
+
+
+def _case(shape, seed=0):
+    n, ci, c, h, w, st, pd, k, kind = shape
+    rng = np.random.default_rng(seed)
+    g = torch.Generator().manual_seed(seed)
+    sel = random_selection(rng, c, ci, k, k)
+    logits = torch.randn(c, 7, 16, generator=g)
+    if kind == "bits":
+        x = (torch.rand(n, ci, h, w, generator=g) < 0.5).float()
+    elif kind == "rand":
+        x = torch.rand(n, ci, h, w, generator=g)
+    else:
+        x = torch.randn(n, ci, h, w, generator=g)
+    ho, wo = oracle.conv_oracle.out_size(h, w, st, pd, k)
+    gy = torch.randn(n, c, ho // 2, wo // 2, generator=g)
+    return x, logits, sel, gy, (st, st, pd, pd, k, k)
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(str(v) for v in s))
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, F32_TOL), (torch.float64, F64_TOL)])
+def test_matches_oracle_function_api(shape, dtype, tol):
+    """The reference-style call: probabilities in, gradient w.r.t. probabilities out."""
+    from convlogic_b200 import FullConvLogicFunction
+
+    x, logits, sel, gy, geom = _case(shape)
+    x, logits, gy = x.to(dtype), logits.to(dtype), gy.to(dtype)
+    xo = x.clone().requires_grad_(True)
+    po = torch.softmax(logits, -1).requires_grad_(True)
+    yo, x2o, x3o, idxo = oracle.full_convlogic(xo, po, sel, geom[0:2], geom[2:4], geom[4:6])
+    gxo, gpo = torch.autograd.grad((yo * gy).sum(), (xo, po))
+
+    xd = x.cuda().requires_grad_(True)
+    pd = torch.softmax(logits, -1).cuda().requires_grad_(True)
+    y, x2, x3, idx = FullConvLogicFunction.apply(xd, pd, sel.cuda(), *geom, True, True)
+    gx, gp = torch.autograd.grad((y * gy.cuda()).sum(), (xd, pd))
+    assert_close(y, yo.detach(), tol, "y")
+    assert_close(x2, x2o.detach(), tol, "x2")
+    assert_close(x3, x3o.detach(), tol, "x3")
+    same = (idx.cpu() == idxo)
+    if not bool(same.all()):  # a different arg-max is only acceptable between numerically tied candidates
+        assert dtype == torch.float32 and float((~same).float().mean()) < 1e-3
+    else:
+        assert_close(gx, gxo, tol, "gx")
+        assert_close(gp, gpo, tol, "gw (mixture)")
+    # plain path (no intermediates) gives the same y and gradients
+    y2 = FullConvLogicFunction.apply(xd, pd, sel.cuda(), *geom)
+    gx2, gp2 = torch.autograd.grad((y2 * gy.cuda()).sum(), (xd, pd))
+    assert torch.equal(y2, y) or rel_err(y2, y) < tol
+    assert_close(gx2, gx, tol)
+    assert_close(gp2, gp, tol)
+
+
+def test_backward_is_bitwise_deterministic():
+    import convlogic_b200 as cb
+
+    x, logits, sel, gy, geom = _case((16, 9, 64, 32, 32, 1, 1, 3, "bits"), seed=3)
+    layer = cb.ConvLogicLayer(9, 64, selection=sel, complete=True).cuda().train()
+    layer.weights.data = logits.cuda()
+    outs = []
+    for _ in range(3):
+        xd = x.cuda().requires_grad_(True)
+        layer.weights.grad = None
+        (layer(xd) * gy.cuda()).sum().backward()
+        outs.append((xd.grad.clone(), layer.weights.grad.clone()))
+    for gx, gw in outs[1:]:
+        assert torch.equal(gx, outs[0][0]) and torch.equal(gw, outs[0][1])
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+@pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 1), (1, 3)])
+@pytest.mark.parametrize("stride,pad,kernel", [(1, 1, 3), (2, 2, 4)])
+def test_gradcheck_like_reference(batch, c_in, c_out, stride, pad, kernel):
+    """The reference's own gradient test (tests/convlogic/test_full_convlogic_autograd.py:36-104)."""
+    import convlogic_b200 as cb
+    from torch.autograd import gradcheck
+
+    torch.manual_seed(0)
+    layer = cb.ConvLogicLayer(c_in, c_out, stride=stride, padding=pad, kernel=kernel, complete=True).double().cuda()
+    x = torch.sigmoid(torch.rand(batch, c_in, 6, 6, dtype=torch.double, device="cuda")).requires_grad_(True)
+    w = layer.weights.detach().clone().requires_grad_(True)
+    sel = layer.selection
+
+    def fn(inp, logits):
+        return cb.FullConvLogicFunction.apply(inp, torch.softmax(logits, -1), sel, stride, stride, pad, pad, kernel, kernel, False)
+
+    assert gradcheck(fn, (x, w), eps=1e-6, atol=1e-4)
+
+
+def test_hard_mode_binary_in_binary_out_and_residual_init():
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    layer = cb.ConvLogicLayer(2, 2, padding=1, residual_init=True, complete=True).cuda().eval()
+    assert torch.all(layer.weights.argmax(-1) == 3)
+    x = (torch.rand(4, 2, 6, 6, device="cuda") < 0.5).float()
+    y = layer(x)
+    assert y.shape == (4, 2, 3, 3)
+    assert set(y.unique().tolist()) <= {0.0, 1.0}
+    layer2 = cb.ConvLogicLayer(1, 5, complete=True).cuda().eval()
+    assert layer2(torch.randn(1, 1, 6, 6, device="cuda")).shape == (1, 5, 3, 3)
+    yr = layer2(torch.rand(3, 1, 6, 6, device="cuda"))
+    assert (yr >= 0).all() and (yr <= 1).all() and torch.isfinite(yr).all()
+
+
+def test_shape_errors_surface_as_exceptions():
+    import convlogic_b200 as cb
+
+    layer = cb.ConvLogicLayer(1, 1, kernel=3, padding=0, complete=True).cuda()
+    with pytest.raises(RuntimeError, match="divisible by 2"):
+        layer(torch.rand(1, 1, 5, 5, device="cuda"))  # 3x3 conv output
+    with pytest.raises(RuntimeError):
+        layer(torch.rand(1, 1, 6, 6))  # CPU tensor: there is no CPU path
+    y = layer(torch.rand(2, 1, 6, 6, device="cuda"))  # the context is still usable
+    assert y.shape == (2, 1, 2, 2)
+
+
+def test_grad_factor_and_eval_mode_input_gradient():
+    import convlogic_b200 as cb
+
+    x, logits, sel, gy, geom = _case((3, 4, 6, 8, 8, 1, 1, 3, "rand"), seed=5)
+    layer = cb.ConvLogicLayer(4, 6, selection=sel, complete=True, grad_factor=2.0).cuda().eval()
+    layer.weights.data = logits.cuda()
+    xd = x.cuda().requires_grad_(True)
+    (layer(xd) * gy.cuda()).sum().backward()
+    xo = x.clone().requires_grad_(True)
+    yo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, False), sel)[0]
+    (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
+    assert_close(xd.grad, 2.0 * gxo, F32_TOL)
+    assert layer.weights.grad is None

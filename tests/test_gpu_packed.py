@@ -1,0 +1,100 @@
+"""Packed (bit-level) inference on the GPU: bit-exact against the numpy oracle and against the
+eval-mode float path of the same layers."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import random_selection
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("bits", [8, 16, 32, 64])
+@pytest.mark.parametrize("batch,feat", [(1, 3), (70, 33), (256, 40), (1000, 7)])
+def test_pack_bits_and_group_sum(bits, batch, feat):
+    import convlogic_b200 as cb
+    from convlogic_b200 import ops
+
+    rng = np.random.default_rng(batch + bits)
+    xb = rng.random((batch, feat * 4)) < 0.4
+    want, pad = oracle.pack_bits(xb.T, bits)
+    p = cb.PackBitsTensor(torch.from_numpy(xb).cuda(), bits)
+    assert p.pad_len == pad and p.t.dtype == torch.from_numpy(want).dtype
+    assert np.array_equal(p.t.cpu().numpy(), want)
+    got2, pad2 = ops.pack_bits(torch.from_numpy(np.ascontiguousarray(xb.T)).cuda(), bits)  # the reference's [F, B] layout
+    assert pad2 == pad and np.array_equal(got2.cpu().numpy(), want)
+    counts = p.group_sum(4)
+    assert counts.dtype == torch.int32 and counts.shape == (batch, 4)
+    assert np.array_equal(counts.cpu().numpy(), oracle.packed_group_sum(want, pad, 4))
+    with pytest.raises(ValueError):
+        p.group_sum(feat * 4 + 1)
+
+
+def test_group_sum_many_rows_uses_row_splits():
+    import convlogic_b200 as cb
+
+    rng = np.random.default_rng(0)
+    xb = rng.random((96, 10 * 700)) < 0.5
+    p = cb.PackBitsTensor(torch.from_numpy(xb).cuda(), 64)
+    want = xb.reshape(96, 10, 700).sum(-1).astype(np.int32)
+    for _ in range(2):
+        assert np.array_equal(cb.GroupSum(10)(p).cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("bits", [8, 32, 64])
+@pytest.mark.parametrize("batch", [5, 64, 130, 1024])
+def test_packed_logic_layer(bits, batch):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(batch)
+    rng = np.random.default_rng(batch)
+    layer = cb.LogicLayer(24, 60).cuda().eval()
+    xb = rng.random((batch, 24)) < 0.5
+    p = cb.PackBitsTensor(torch.from_numpy(xb).cuda(), bits)
+    y = layer(p)
+    want = oracle.packed_logic(oracle.pack_bits(xb.T, bits)[0], layer.indices_0.cpu().numpy(), layer.indices_1.cpu().numpy(),
+                               layer.weights.argmax(-1).cpu().numpy().astype(np.uint8))
+    # pad bits of the oracle's output may be set by negating gates; compare real samples only
+    assert np.array_equal(oracle.unpack_bits(y.t.cpu().numpy(), batch), oracle.unpack_bits(want, batch))
+    yf = layer(torch.from_numpy(xb).float().cuda())
+    assert np.array_equal(oracle.unpack_bits(y.t.cpu().numpy(), batch).T.astype(np.float32), yf.cpu().numpy())
+
+
+@pytest.mark.parametrize("bits,batch", [(64, 70), (64, 256), (32, 33), (8, 9)])
+@pytest.mark.parametrize("geom", [(3, 6, 8, 8, 1, 1, 3), (1, 4, 12, 12, 1, 0, 5), (5, 3, 6, 10, 2, 2, 4)])
+def test_packed_conv_block(bits, batch, geom):
+    import convlogic_b200 as cb
+
+    ci, c, h, w, st, pd, k = geom
+    rng = np.random.default_rng(bits + batch)
+    torch.manual_seed(bits + batch)
+    sel = random_selection(rng, c, ci, k, k)
+    layer = cb.ConvLogicLayer(ci, c, stride=st, padding=pd, kernel=k, selection=sel, complete=True).cuda().eval()
+    xb = rng.random((batch, ci, h, w)) < 0.5
+    p = cb.PackBitsTensor(torch.from_numpy(xb).cuda(), bits)
+    assert p.t.shape[:3] == (ci, h, w)
+    y = layer(p)
+    want = oracle.packed_convtree(oracle.pack_bits(xb.reshape(batch, -1).T, bits)[0].reshape(ci, h, w, -1),
+                                  layer.weights.argmax(-1).cpu().numpy().astype(np.uint8), sel.numpy(), st, pd, k)
+    got = oracle.unpack_bits(y.t.cpu().numpy(), batch)
+    assert np.array_equal(got, oracle.unpack_bits(want, batch))
+    yf = layer(torch.from_numpy(xb).float().cuda())
+    assert np.array_equal(np.moveaxis(got, -1, 0).astype(np.float32), yf.cpu().numpy())
+
+
+def test_packed_model_equals_float_eval_model():
+    """A whole (small) CIFAR-shaped stack: packed class counts == tau * float eval-mode scores."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    net = cb.ConvLogicCifarModel(k_param=4, input_channels=6, input_size=32, tau=10.0).cuda().eval()
+    for prm in net.parameters():
+        prm.data = torch.randn_like(prm)
+    x = torch.rand(100, 6, 32, 32, device="cuda") < 0.5
+    with torch.no_grad():
+        scores = net(x.float())
+        counts = net(cb.PackBitsTensor(x, 64))
+    assert counts.dtype == torch.int32 and counts.shape == (100, 10)
+    assert torch.equal(counts.float(), scores * 10.0)

@@ -168,3 +168,32 @@ def test_thermometer_thresholds():
     assert t.shape == (1, 93, 1, 4)
     assert t[0, :, 0, 0].sum() == 0 and t[0, 0:3, 0, 1].sum() == 0  # strict '>'
     assert t[0, :, 0, 2].sum() == 3 * 15 and t[0, :, 0, 3].sum() == 93
+
+
+def test_mnist_s_stack_matches_reference_scores(golden):
+    """The oracle, assembled into the mnist_s-shaped stack, reproduces the class scores the
+    reference's CPU path gave for the same seeded network (first 24 of the 256 images)."""
+    from tests.golden.make_golden import mnist_inputs
+
+    g = golden("mnist_s")
+    gen = torch.Generator().manual_seed(1)
+    k, n = 16, 24
+    conv_shapes = [(k, 7, 16), (3 * k, 7, 16), (9 * k, 7, 16)]
+    flat_shapes = [(1280 * k, 16), (640 * k, 16), (320 * k, 16)]
+    logits = [torch.randn(*s, generator=gen) for s in conv_shapes + flat_shapes]
+    np.testing.assert_allclose([float(w.double().sum()) for w in logits], g["logit_checksum"], rtol=1e-12)
+    x0 = mnist_inputs()[:n]
+    for training, key in ((True, "scores_soft"), (False, "scores_hard")):
+        x = x0
+        for i, (kern, pad) in enumerate([(5, 0), (3, 1), (3, 1)]):
+            x = oracle.full_convlogic(x, oracle.gate_probabilities(logits[i], training),
+                                      torch.from_numpy(g[f"conv{i}/selection"]), 1, pad, kern)[0]
+        x = x.flatten(1)
+        for i in range(3):
+            x = oracle.logic_layer(x, torch.from_numpy(g[f"flat{i}/a"]), torch.from_numpy(g[f"flat{i}/b"]),
+                                   oracle.gate_probabilities(logits[3 + i], training))
+        s = oracle.group_sum(x, 10, 6.5).numpy()
+        if training:
+            np.testing.assert_allclose(s, g[key][:n], rtol=1e-5, atol=1e-5)
+        else:
+            assert np.array_equal(s, g[key][:n])
