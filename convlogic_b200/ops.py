@@ -53,15 +53,18 @@ def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False
     return y, amax, x2, x3, idx
 
 
-_group_cache = {}
-
-
 def conv_groups(sel, x_shape, geom, dtype):
-    """Device tables for the input-gradient kernels (cached per selection tensor and shape)."""
+    """Device tables for the input-gradient kernels.  They depend only on the selection tensor and
+    the shapes, so they are cached ON the selection tensor object (keyed by its in-place version
+    counter): no global state that could outlive the tensor and be matched by a recycled address."""
     n, ci, h, w = x_shape
     c = sel.shape[0]
-    key = (sel.data_ptr(), sel._version, sel.device, n, ci, h, w, geom, dtype)
-    hit = _group_cache.get(key)
+    key = (sel._version, n, ci, h, w, c, geom, dtype)
+    cache = getattr(sel, "_clb_groups", None)
+    if cache is None:
+        cache = {}
+        sel._clb_groups = cache
+    hit = cache.get(key)
     if hit is not None:
         return hit
     cg, nb = C.c_int(0), C.c_int(0)
@@ -80,9 +83,9 @@ def conv_groups(sel, x_shape, geom, dtype):
             raise RuntimeError("convlogic_b200: selection refers to a channel the input does not have")
         check(cnt)
     out = (torch.from_numpy(start).to(sel.device), torch.from_numpy(lst[:max(cnt, 1)].copy()).to(sel.device), cg, nb)
-    if len(_group_cache) > 256:
-        _group_cache.clear()
-    _group_cache[key] = out
+    if len(cache) > 16:
+        cache.clear()
+    cache[key] = out
     return out
 
 

@@ -55,7 +55,7 @@ SHAPES = [
     (7, 48, 40, 6, 6, 1, 1, 3, "rand"),      # small images, several images per block in backward
     (2, 300, 20, 4, 4, 1, 1, 3, "rand"),     # more input channels than one shared-memory group holds
     (2, 3, 5, 70, 66, 1, 1, 3, "rand"),      # > 1024 pooled positions (the reference's limit)
-    (4, 3, 6, 13, 9, 2, 2, 4, "randn"),      # stride 2
+    (4, 3, 6, 14, 10, 2, 2, 4, "randn"),     # stride 2
     (1, 1, 1, 3, 3, 1, 0, 2, "randn"),       # single output
 ]
 
@@ -188,3 +188,21 @@ def test_grad_factor_and_eval_mode_input_gradient():
     (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
     assert_close(xd.grad, 2.0 * gxo, F32_TOL)
     assert layer.weights.grad is None
+
+
+def test_group_tables_follow_the_selection_not_its_address():
+    """Two layers of equal shape but different taps (and different widths) in a row: the cached
+    channel-group tables must never be shared between selection tensors."""
+    import convlogic_b200 as cb
+
+    for c in (1, 3, 5, 3):
+        x, logits, sel, gy, geom = _case((2, 300, c, 4, 4, 1, 1, 3, "rand"), seed=c)
+        layer = cb.ConvLogicLayer(300, c, selection=sel, complete=True).cuda().train()
+        layer.weights.data = logits.cuda()
+        xd = x.cuda().requires_grad_(True)
+        (layer(xd) * gy.cuda()).sum().backward()
+        xo = x.clone().requires_grad_(True)
+        yo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel)[0]
+        (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
+        assert_close(xd.grad, gxo, F32_TOL)
+        del layer, xd

@@ -5,7 +5,7 @@ import torch
 def rel_err(got, want):
     got = torch.as_tensor(got).double().cpu()
     want = torch.as_tensor(want).double().cpu()
-    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    return float((got.detach() - want.detach()).abs().max() / want.abs().max().clamp_min(1e-30))
 
 
 def assert_close(got, want, tol, what=""):
