@@ -25,6 +25,7 @@ _SIGNATURES = {
     "clb_version": ([], _i),
     "clb_status_string": ([_i], C.c_char_p),
     "clb_last_cuda_error": ([], _i),
+    "clb_kernel_launches": ([], C.c_longlong),
     "clb_convtree_fwd": ([_vp] * 8 + _conv + [_i, _i, _vp], _i),
     "clb_convtree_bwd_x": ([_vp] * 8 + [_i, _i] + _conv + [_i, _i, _vp], _i),
     "clb_conv_group_plan": (_conv + [_i, C.POINTER(_i), C.POINTER(_i)], _i),

@@ -1,10 +1,16 @@
 // Library-wide entry points: version, status text, last CUDA error of the calling thread.
 #include "clb_common.cuh"
 
+#include <atomic>
+
 static thread_local int g_last_cuda_error = 0;
+static std::atomic<long long> g_launches{0};
 namespace clb_host {
 void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 } // namespace clb_host
+
+extern "C" long long clb_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int clb_version(void) { return 100; }
 

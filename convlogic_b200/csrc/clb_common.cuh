@@ -141,7 +141,9 @@ template <typename T> __device__ __forceinline__ T warp_sum(T v)
 // ---- host side ----------------------------------------------------------------------------------
 namespace clb_host {
 void set_last_cuda_error(int e);
-inline int check_launch()
+void count_launches(int n);
+// Call after launching `n` kernels: reports a refused launch, else adds n to the library's counter.
+inline int check_launch(int n = 1)
 {
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) {
@@ -149,6 +151,7 @@ inline int check_launch()
         cudaGetLastError(); // clear the sticky-less launch error so later calls start clean
         return CLB_ERR_LAUNCH;
     }
+    count_launches(n);
     return CLB_OK;
 }
 inline int conv_out(int in, int pad, int k, int stride) { return (in + 2 * pad - k) / stride + 1; }

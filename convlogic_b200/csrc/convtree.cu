@@ -573,7 +573,7 @@ static int launch_bwd_w(const void *gy, const void *x, const void *w, const int3
         gate_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates,
                                                               wmode);
     }
-    return check_launch();
+    return check_launch(2);
 }
 
 extern "C" int clb_convtree_bwd_w(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gw,

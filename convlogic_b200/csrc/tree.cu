@@ -163,5 +163,5 @@ extern "C" int clb_tree_bwd_w(const void *gy, const void *x, const void *w, void
         tree_bwd_w_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)gy, (double *)scratch, N, C, HW, X, threads_used);
         tree_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates, wmode);
     }
-    return check_launch();
+    return check_launch(2);
 }

@@ -53,6 +53,8 @@ int clb_version(void);
 const char *clb_status_string(int status);
 /* cudaError_t value of the most recent failed launch made through this library by the calling thread. */
 int clb_last_cuda_error(void);
+/* Number of kernels this library has launched in the calling process since it was loaded. */
+long long clb_kernel_launches(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Fused ConvLogic block: 8-tap gather -> 4 gates -> 2 gates -> 1 gate -> 2x2 max pool.
