@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libconvlogic_b200.so")
 
 F32, F64 = 0, 1
 W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
+SEL_UNBOUNDED = 0x100
 ERR_SHAPE, ERR_ODD_OUTPUT = -2, -5
 
 _lib = None

@@ -367,6 +367,8 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
                                 int32_t *idx, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
                                 int wmode, int dtype, void *stream)
 {
+    const bool sel_unbounded = (wmode & CLB_SEL_UNBOUNDED) != 0;
+    wmode &= ~CLB_SEL_UNBOUNDED;
     ConvShape s;
     int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, true);
     if (rc) return rc;
@@ -374,7 +376,7 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
     if (N == 0 || C == 0) return CLB_OK;
     if (C > 65535) return CLB_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == CLB_F32 && !x2 && !idx) {
+    if (dtype == CLB_F32 && !x2 && !idx && !sel_unbounded) {
         rc = clb_convtree_fwd_fast_f32((const float *)x, (const float *)w, sel, (float *)y, amax, N, Ci, H, W, C, sh, sw, ph, pw,
                                        kh, kw, wmode, st);
         if (rc != CLB_ERR_SHAPE) return rc;
@@ -395,6 +397,7 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
 extern "C" int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, void *y, int N, int Ci, int H, int W, int C, int sh,
                             int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
 {
+    wmode &= ~CLB_SEL_UNBOUNDED;
     ConvShape s;
     int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, false);
     if (rc) return rc;
@@ -471,6 +474,7 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
                         const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W, int C,
                         int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
 {
+    wmode &= ~CLB_SEL_UNBOUNDED;
     ConvShape s;
     int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, FUSED);
     if (rc) return rc;
@@ -547,6 +551,7 @@ static int launch_bwd_w(const void *gy, const void *x, const void *w, const int3
                         void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
                         int kh, int kw, int wmode, int dtype, void *stream)
 {
+    wmode &= ~CLB_SEL_UNBOUNDED;
     ConvShape s;
     int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, FUSED);
     if (rc) return rc;

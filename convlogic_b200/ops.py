@@ -25,6 +25,19 @@ def _sel_ok(sel, c):
         raise RuntimeError(f"convlogic_b200: selection must be int32 [{c}, 8], got {sel.dtype} {tuple(sel.shape)}")
 
 
+def _sel_flag(sel, geom):
+    """SEL_UNBOUNDED when some tap lies outside the kh x kw window (checked once per selection
+    tensor and in-place version; the result is cached on the tensor object)."""
+    key = (sel._version, geom[4], geom[5])
+    cache = getattr(sel, "_clb_window", None)
+    if cache is None or cache[0] != key:
+        rows, cols = (sel >> 8) & 0xFF, sel & 0xFF
+        inside = bool((rows.max() < geom[4]) & (cols.max() < geom[5])) if sel.numel() else True
+        cache = (key, 0 if inside else _lib.SEL_UNBOUNDED)
+        sel._clb_window = cache
+    return cache[1]
+
+
 # ------------------------------------------------------------------------------ fused block
 def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False, want_indices=False):
     check_input(x, w, sel)
@@ -49,7 +62,7 @@ def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False
     if want_indices:
         idx = torch.empty((n, c, (ho // 2) * (wo // 2)), dtype=torch.int32, device=x.device)
     check(lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), ptr(amax), ptr(x2), ptr(x3), ptr(idx),
-                                 n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+                                 n, ci, h, wd, c, *geom, wmode | _sel_flag(sel, geom), dtype_code(x), stream()))
     return y, amax, x2, x3, idx
 
 

@@ -48,6 +48,11 @@ extern "C" {
 #define CLB_W_PROB 0
 #define CLB_W_SOFTMAX 1
 #define CLB_W_ARGMAX 2
+/* OR-ed into wmode of the conv entry points: the selection may hold taps with row >= kh or col >= kw
+ * (never produced by the reference's generate_selection, but accepted by its kernels).  Such
+ * selections are served by the general kernels only; without this flag the caller guarantees
+ * row < kh and col < kw for every tap. */
+#define CLB_SEL_UNBOUNDED 0x100
 
 int clb_version(void);
 const char *clb_status_string(int status);

@@ -206,3 +206,57 @@ def test_group_tables_follow_the_selection_not_its_address():
         (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
         assert_close(xd.grad, gxo, F32_TOL)
         del layer, xd
+
+
+def test_taps_outside_the_kernel_window_are_served():
+    """A user selection may name rows/cols beyond the window; the reference kernels read them as
+    long as they land inside the image.  The shape-specialised kernel must not be used then."""
+    import convlogic_b200 as cb
+
+    g = torch.Generator().manual_seed(9)
+    n, ci, c = 4, 3, 8
+    ch = torch.randint(0, ci, (c, 8), generator=g)
+    r = torch.randint(0, 6, (c, 8), generator=g)   # window is 3x3
+    s = torch.randint(0, 6, (c, 8), generator=g)
+    sel = ((ch << 16) | (r << 8) | s).to(torch.int32)
+    logits = torch.randn(c, 7, 16, generator=g)
+    x = torch.rand(n, ci, 16, 16, generator=g)
+    layer = cb.ConvLogicLayer(ci, c, selection=sel, complete=True).cuda().train()
+    layer.weights.data = logits.cuda()
+    xd = x.cuda().requires_grad_(True)
+    y = layer(xd)
+    gy = torch.randn(*y.shape, generator=g)
+    (y * gy.cuda()).sum().backward()
+    xo = x.clone().requires_grad_(True)
+    wo = logits.clone().requires_grad_(True)
+    yo = oracle.full_convlogic(xo, oracle.gate_probabilities(wo, True), sel)[0]
+    gxo, gwo = torch.autograd.grad((yo * gy).sum(), (xo, wo))
+    assert_close(y, yo.detach(), F32_TOL)
+    assert_close(xd.grad, gxo, F32_TOL)
+    assert_close(layer.weights.grad, gwo, F32_TOL)
+
+
+@pytest.mark.parametrize("shape", [
+    (256, 9, 256, 32, 32, 1, 1, 3, "bits"),   # the benchmark block at full size
+    (37, 9, 19, 32, 32, 1, 1, 3, "rand"),     # ragged batch / channel counts
+    (64, 16, 48, 12, 12, 1, 1, 3, "rand"),
+    (9, 1, 16, 28, 28, 1, 0, 5, "bits"),
+    (33, 32, 20, 16, 16, 1, 1, 3, "rand"),
+    (70, 48, 24, 8, 8, 1, 1, 3, "rand"),
+    (130, 12, 10, 4, 4, 1, 1, 3, "rand"),
+], ids=lambda s: "x".join(str(v) for v in s))
+def test_tiled_forward_equals_general_forward(shape):
+    """The shape-specialised forward (used when no intermediates are requested) against the
+    general kernel (forced by asking for the indices) and, for values, against the oracle."""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy, geom = _case(shape, seed=11)
+    xd, wd, sd = x.cuda(), logits.cuda(), sel.cuda()
+    y_fast, amax_fast, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX)
+    y_gen, amax_gen, _, _, idx = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)
+    assert torch.equal(y_fast, y_gen)
+    assert torch.equal(amax_fast, amax_gen)
+    if x.shape[0] <= 40:
+        yo = oracle.full_convlogic(x, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])[0]
+        assert_close(y_fast, yo, F32_TOL)
