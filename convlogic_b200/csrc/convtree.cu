@@ -504,10 +504,29 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
     return check_launch();
 }
 
-extern "C" int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx,
-                                  const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci, int H, int W,
-                                  int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
+size_t clb_convtree_bwd_x_fast_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw);
+int clb_convtree_bwd_x_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
+                                void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
+                                int kh, int kw, int wmode, cudaStream_t st);
+
+extern "C" size_t clb_convtree_bwd_x_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
+                                                   int dtype)
 {
+    if (dtype != CLB_F32 || !conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return 0;
+    return clb_convtree_bwd_x_fast_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw);
+}
+
+extern "C" int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx,
+                                  const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, void *scratch,
+                                  size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                                  int kw, int wmode, int dtype, void *stream)
+{
+    if (dtype == CLB_F32 && !(wmode & CLB_SEL_UNBOUNDED) && scratch && amax && gy && x && w && sel && gx && N > 0 && C > 0 &&
+        (wmode & 0xff) <= 2 && conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) {
+        const int rc = clb_convtree_bwd_x_fast_f32((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, scratch,
+                                                   scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, (cudaStream_t)stream);
+        if (rc != CLB_ERR_SHAPE) return rc;
+    }
     return launch_bwd_x<true>(gy, x, w, sel, amax, gx, grp_start, grp_list, cg, nb, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
                               dtype, stream);
 }

@@ -2,7 +2,7 @@
 // channels all fit in shared memory (the first blocks of the CIFAR/MNIST stacks and the
 // single-block benchmark: 9 x 32 x 32 inputs).
 //
-// Forward (convtree_fwd_tile_kernel)
+// Common design
 //   * A persistent grid (one wave: SM count x resident blocks) splits the flattened
 //     (image group, output channel) space into equal contiguous ranges, so the load is balanced to
 //     within one channel and a block re-stages its input tile only when its range crosses into
@@ -15,8 +15,17 @@
 //     every gather is one conflict-free wavefront.
 //   * Per output channel a thread needs 28 gate coefficients and 16 tap base offsets; they are
 //     built once per channel by a few threads (soft-max included) and read by all as 128-bit
-//     broadcast loads, amortised over WPT windows (4*WPT conv positions) per thread.
-//   * Nothing but y (and the 1-byte arg-max the backward uses) is written to global memory.
+//     broadcast loads.
+//
+// Forward (convtree_fwd_tile_kernel): WPT windows (4*WPT conv positions) per thread and channel;
+// nothing but y (and the 1-byte arg-max the backward uses) is written to global memory.
+//
+// Input gradient (convtree_bwd_x_tile_kernel): a second tile with the same layout accumulates the
+// gradient of the staged images.  For one (channel, tap) the map window -> input pixel is injective,
+// so threads add with plain read-modify-writes and a block barrier separates the 8 taps: the order
+// of additions into a pixel is fixed (channel ascending, tap ascending).  A block whose range holds
+// all channels of a group writes the final gradient; otherwise it writes a partial tile to scratch
+// and convtree_bwd_x_reduce_kernel adds the partials of a group in block order.  No atomics.
 #include "clb_common.cuh"
 
 namespace clb {
@@ -26,7 +35,7 @@ constexpr int kChanBuf = 16; // channels prepared per refill of the coefficient 
 
 struct alignas(16) ChanRec {
     float g[28];  // 7 gates x (k1, ka, kb, kab)
-    int tb0[8];   // tile offset of tap k for the dx = 0 positions
+    int tb0[8];   // BYTE offset in the tile of tap k for the dx = 0 positions
     int tb1[8];   // ... for the dx = 1 positions
 };
 
@@ -39,22 +48,104 @@ struct FastShape {
     int wmode;
 };
 
+__device__ __forceinline__ int tile_index(const FastShape &s, int pwh, int img, int ch, int row, int col)
+{
+    const int xp = col + s.pw;
+    return img * s.IS + ch * s.CS + (row + s.ph) * 2 * pwh + (xp & 1) * pwh + (xp >> 1);
+}
+
+// Copies images n0 .. n0+nimg-1 into the (already zero-haloed) tile.
+__device__ __forceinline__ void stage_group(float *tile, const float *__restrict__ x, const FastShape &s, int pwh, int n0, int nimg)
+{
+    const int tid = threadIdx.x;
+    if ((s.W & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0)) {
+        const int q = s.W >> 2;
+        const int total = nimg * s.Ci * s.H * q;
+        for (int i = tid; i < total; i += kFastThreads) {
+            const int xq = i % q;
+            int r = i / q;
+            const int row = r % s.H;
+            r /= s.H;
+            const int ch = r % s.Ci, img = r / s.Ci;
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (((size_t)(n0 + img) * s.Ci + ch) * s.H + row) * s.W) + xq);
+            tile[tile_index(s, pwh, img, ch, row, xq * 4)] = v.x;
+            tile[tile_index(s, pwh, img, ch, row, xq * 4 + 1)] = v.y;
+            tile[tile_index(s, pwh, img, ch, row, xq * 4 + 2)] = v.z;
+            tile[tile_index(s, pwh, img, ch, row, xq * 4 + 3)] = v.w;
+        }
+    } else {
+        const int total = nimg * s.Ci * s.H * s.W;
+        for (int i = tid; i < total; i += kFastThreads) {
+            const int xc = i % s.W;
+            int r = i / s.W;
+            const int row = r % s.H;
+            r /= s.H;
+            const int ch = r % s.Ci, img = r / s.Ci;
+            tile[tile_index(s, pwh, img, ch, row, xc)] = __ldg(x + (((size_t)(n0 + img) * s.Ci + ch) * s.H + row) * s.W + xc);
+        }
+    }
+}
+
+// Gate coefficients and tap offsets of channels c0 .. c0+cnt-1.
+__device__ __forceinline__ void build_records(ChanRec *chan, const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                              const FastShape &s, int pwh, int c0, int cnt)
+{
+    const int tid = threadIdx.x;
+    for (int i = tid; i < cnt * 7; i += kFastThreads) {
+        const int cc = i / 7, gi = i - cc * 7;
+        const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
+        float *o = chan[cc].g + gi * 4;
+        o[0] = g.k1, o[1] = g.ka, o[2] = g.kb, o[3] = g.kab;
+    }
+    for (int i = tid; i < cnt * 8; i += kFastThreads) {
+        const int cc = i >> 3, k = i & 7;
+        const int word = sel[(c0 + cc) * 8 + k];
+        // clamped to the tile, so that a selection outside the kernel window (which callers must route
+        // to the general kernel) can never index beyond shared memory
+        const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1), r = min((word >> 8) & 0xFF, s.kh - 1), sx = min(word & 0xFF, s.kw - 1);
+        const int base = ch * s.CS + r * 2 * pwh;
+        chan[cc].tb0[k] = 4 * (base + (sx & 1) * pwh + (sx >> 1));
+        chan[cc].tb1[k] = 4 * (base + ((sx + 1) & 1) * pwh + ((sx + 1) >> 1));
+    }
+}
+
+struct ChanRegs {
+    Gate<float> g[7];
+    int tb0[8], tb1[8];
+};
+__device__ __forceinline__ void load_record(ChanRegs &r, const ChanRec &rec)
+{
+    const float4 *gp = reinterpret_cast<const float4 *>(rec.g);
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+        const float4 q = gp[i];
+        r.g[i].k1 = q.x, r.g[i].ka = q.y, r.g[i].kb = q.z, r.g[i].kab = q.w;
+    }
+    const int4 *t0 = reinterpret_cast<const int4 *>(rec.tb0), *t1 = reinterpret_cast<const int4 *>(rec.tb1);
+    const int4 a0 = t0[0], a1 = t0[1], b0 = t1[0], b1 = t1[1];
+    r.tb0[0] = a0.x, r.tb0[1] = a0.y, r.tb0[2] = a0.z, r.tb0[3] = a0.w, r.tb0[4] = a1.x, r.tb0[5] = a1.y, r.tb0[6] = a1.z, r.tb0[7] = a1.w;
+    r.tb1[0] = b0.x, r.tb1[1] = b0.y, r.tb1[2] = b0.z, r.tb1[3] = b0.w, r.tb1[4] = b1.x, r.tb1[5] = b1.y, r.tb1[6] = b1.z, r.tb1[7] = b1.w;
+}
+
+__device__ __forceinline__ float ld_tile(const unsigned char *base, int byte_off) { return *reinterpret_cast<const float *>(base + byte_off); }
+
+// =========================================================================================== forward
 // PWH > 0: row stride known at compile time (2*PWH); PWH == 0: taken from the shape.
 template <int WPT, int PWH>
 __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(const float *__restrict__ x, const float *__restrict__ w,
-                                                                        const int32_t *__restrict__ sel, float *__restrict__ y,
-                                                                        uint8_t *__restrict__ amax, FastShape s)
+                                                                           const int32_t *__restrict__ sel, float *__restrict__ y,
+                                                                           uint8_t *__restrict__ amax, FastShape s)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     ChanRec *chan = reinterpret_cast<ChanRec *>(smem_raw);
     float *tile = reinterpret_cast<float *>(smem_raw + sizeof(ChanRec) * kChanBuf);
+    const unsigned char *tileb = reinterpret_cast<const unsigned char *>(tile);
 
     const int pwh = PWH > 0 ? PWH : s.pwh;
-    const int RS = 2 * pwh;
+    const int RSB = 8 * pwh; // row stride in bytes
     const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
     const int tid = threadIdx.x;
 
-    // contiguous range of (group, channel) units for this block
     const int NG = (s.N + s.G - 1) / s.G;
     const long long units = (long long)NG * s.C;
     const long long lo = units * blockIdx.x / gridDim.x, hi = units * (blockIdx.x + 1) / gridDim.x;
@@ -69,7 +160,7 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
         const int py = win / Wp, px = win - py * Wp;
         wimg[j] = img < s.G ? img : -1;
         wwin[j] = win;
-        toff[j] = img * s.IS + 2 * py * RS + px;
+        toff[j] = 4 * (img * s.IS + 2 * py * 2 * pwh + px);
     }
 
     // halo (and everything else) starts at zero; staging overwrites the interior only
@@ -82,104 +173,41 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
         int cnt = s.C - c0;
         if (cnt > kChanBuf) cnt = kChanBuf;
         if (cnt > hi - u0) cnt = (int)(hi - u0);
+        const int n0 = grp * s.G;
         __syncthreads(); // previous chunk's readers are done with chan[] (and with the tile, if it changes)
         if (grp != cur_group) {
             cur_group = grp;
-            const int n0 = grp * s.G;
-            const int nimg = min(s.G, s.N - n0);
-            const int rowsz = s.W;
-            if ((rowsz & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0)) {
-                const int q = rowsz >> 2;
-                const int total = nimg * s.Ci * s.H * q;
-                for (int i = tid; i < total; i += kFastThreads) {
-                    const int xq = i % q;
-                    int r = i / q;
-                    const int row = r % s.H;
-                    r /= s.H;
-                    const int ch = r % s.Ci, img = r / s.Ci;
-                    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (((size_t)(n0 + img) * s.Ci + ch) * s.H + row) * s.W) + xq);
-                    float *dst = tile + img * s.IS + ch * s.CS + (row + s.ph) * RS;
-                    const int xp = xq * 4 + s.pw;
-                    dst[((xp)&1) * pwh + ((xp) >> 1)] = v.x;
-                    dst[((xp + 1) & 1) * pwh + ((xp + 1) >> 1)] = v.y;
-                    dst[((xp + 2) & 1) * pwh + ((xp + 2) >> 1)] = v.z;
-                    dst[((xp + 3) & 1) * pwh + ((xp + 3) >> 1)] = v.w;
-                }
-            } else {
-                const int total = nimg * s.Ci * s.H * rowsz;
-                for (int i = tid; i < total; i += kFastThreads) {
-                    const int xc = i % rowsz;
-                    int r = i / rowsz;
-                    const int row = r % s.H;
-                    r /= s.H;
-                    const int ch = r % s.Ci, img = r / s.Ci;
-                    const int xp = xc + s.pw;
-                    tile[img * s.IS + ch * s.CS + (row + s.ph) * RS + (xp & 1) * pwh + (xp >> 1)] =
-                        __ldg(x + (((size_t)(n0 + img) * s.Ci + ch) * s.H + row) * s.W + xc);
-                }
-            }
+            stage_group(tile, x, s, pwh, n0, min(s.G, s.N - n0));
         }
-        // coefficient records of channels c0 .. c0+cnt-1
-        for (int i = tid; i < cnt * 7; i += kFastThreads) {
-            const int cc = i / 7, gi = i - cc * 7;
-            const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
-            float *o = chan[cc].g + gi * 4;
-            o[0] = g.k1, o[1] = g.ka, o[2] = g.kb, o[3] = g.kab;
-        }
-        for (int i = tid; i < cnt * 8; i += kFastThreads) {
-            const int cc = i >> 3, k = i & 7;
-            const int word = sel[(c0 + cc) * 8 + k];
-            // clamped to the tile, so that a selection outside the kernel window (which callers must route
-            // to the general kernel) can never index beyond shared memory
-            const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1), r = min((word >> 8) & 0xFF, s.kh - 1),
-                      sx = min(word & 0xFF, s.kw - 1);
-            const int base = ch * s.CS + r * RS;
-            chan[cc].tb0[k] = base + (sx & 1) * pwh + (sx >> 1);
-            chan[cc].tb1[k] = base + ((sx + 1) & 1) * pwh + ((sx + 1) >> 1);
-        }
+        build_records(chan, w, sel, s, pwh, c0, cnt);
         __syncthreads();
 
-        const int n0 = grp * s.G;
         for (int cc = 0; cc < cnt; ++cc) {
             const int c = c0 + cc;
-            // 11 x 128-bit broadcast loads
-            float4 gq[7];
-            int4 t0q[2], t1q[2];
-            const float4 *gp = reinterpret_cast<const float4 *>(chan[cc].g);
-#pragma unroll
-            for (int i = 0; i < 7; ++i) gq[i] = gp[i];
-            const int4 *tp0 = reinterpret_cast<const int4 *>(chan[cc].tb0);
-            const int4 *tp1 = reinterpret_cast<const int4 *>(chan[cc].tb1);
-            t0q[0] = tp0[0], t0q[1] = tp0[1], t1q[0] = tp1[0], t1q[1] = tp1[1];
-            const int tb0[8] = {t0q[0].x, t0q[0].y, t0q[0].z, t0q[0].w, t0q[1].x, t0q[1].y, t0q[1].z, t0q[1].w};
-            const int tb1[8] = {t1q[0].x, t1q[0].y, t1q[0].z, t1q[0].w, t1q[1].x, t1q[1].y, t1q[1].z, t1q[1].w};
-            Gate<float> g[7];
-#pragma unroll
-            for (int i = 0; i < 7; ++i) g[i].k1 = gq[i].x, g[i].ka = gq[i].y, g[i].kb = gq[i].z, g[i].kab = gq[i].w;
-
+            ChanRegs r;
+            load_record(r, chan[cc]);
 #pragma unroll
             for (int j = 0; j < WPT; ++j) {
                 if (wimg[j] < 0 || n0 + wimg[j] >= s.N) continue;
                 float v[4][8]; // [position d = 2*dy+dx][tap]
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const float *p0 = tile + toff[j] + tb0[k];
-                    const float *p1 = tile + toff[j] + tb1[k];
-                    v[0][k] = p0[0];
-                    v[2][k] = p0[RS];
-                    v[1][k] = p1[0];
-                    v[3][k] = p1[RS];
+                    const int a0 = toff[j] + r.tb0[k], a1 = toff[j] + r.tb1[k];
+                    v[0][k] = ld_tile(tileb, a0);
+                    v[2][k] = ld_tile(tileb, a0 + RSB);
+                    v[1][k] = ld_tile(tileb, a1);
+                    v[3][k] = ld_tile(tileb, a1 + RSB);
                 }
                 float z[4];
 #pragma unroll
                 for (int d = 0; d < 4; ++d) {
-                    const float g0 = gate_eval<float>(g[0], v[d][0], v[d][1]);
-                    const float g1 = gate_eval<float>(g[1], v[d][2], v[d][3]);
-                    const float g2 = gate_eval<float>(g[2], v[d][4], v[d][5]);
-                    const float g3 = gate_eval<float>(g[3], v[d][6], v[d][7]);
-                    const float t0 = gate_eval<float>(g[4], g0, g1);
-                    const float t1 = gate_eval<float>(g[5], g2, g3);
-                    z[d] = gate_eval<float>(g[6], t0, t1);
+                    const float g0 = gate_eval<float>(r.g[0], v[d][0], v[d][1]);
+                    const float g1 = gate_eval<float>(r.g[1], v[d][2], v[d][3]);
+                    const float g2 = gate_eval<float>(r.g[2], v[d][4], v[d][5]);
+                    const float g3 = gate_eval<float>(r.g[3], v[d][6], v[d][7]);
+                    const float t0 = gate_eval<float>(r.g[4], g0, g1);
+                    const float t1 = gate_eval<float>(r.g[5], g2, g3);
+                    z[d] = gate_eval<float>(r.g[6], t0, t1);
                 }
                 float best = z[0];
                 int bd = 0;
@@ -195,6 +223,158 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
             }
         }
         u0 += cnt;
+    }
+}
+
+// ==================================================================================== input gradient
+// One window per thread.  Shared memory: records | x tile | gradient tile (same layout).
+template <int PWH>
+__global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+                                                                             const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                             const uint8_t *__restrict__ amax, float *__restrict__ gx,
+                                                                             float *__restrict__ partial, FastShape s)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    ChanRec *chan = reinterpret_cast<ChanRec *>(smem_raw);
+    float *xt = reinterpret_cast<float *>(smem_raw + sizeof(ChanRec) * kChanBuf);
+    float *gt = xt + s.G * s.IS;
+    const unsigned char *xtb = reinterpret_cast<const unsigned char *>(xt);
+    unsigned char *gtb = reinterpret_cast<unsigned char *>(gt);
+
+    const int pwh = PWH > 0 ? PWH : s.pwh;
+    const int RSB = 8 * pwh;
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
+    const int tid = threadIdx.x;
+    const int HW = s.H * s.W;
+
+    const int NG = (s.N + s.G - 1) / s.G;
+    const long long units = (long long)NG * s.C;
+    const long long lo = units * blockIdx.x / gridDim.x, hi = units * (blockIdx.x + 1) / gridDim.x;
+    if (lo >= hi) return;
+    const int first_group = (int)(lo / s.C);
+
+    const int img = tid / I, win = tid - img * I;
+    const int py = win / Wp, px = win - py * Wp;
+    const bool has_window = img < s.G;
+    const int toff = 4 * (img * s.IS + 2 * py * 2 * pwh + px);
+
+    for (int i = tid; i < 2 * s.G * s.IS; i += kFastThreads) xt[i] = 0.f; // both tiles
+
+    // Writes the gradient tile of group `grp` (final when the block saw all its channels, else partial).
+    auto flush = [&](int grp) {
+        const int n0 = grp * s.G;
+        const int nimg = min(s.G, s.N - n0);
+        const bool whole = lo <= (long long)grp * s.C && hi >= (long long)(grp + 1) * s.C;
+        float *dst = whole ? gx + (size_t)n0 * s.Ci * HW
+                           : partial + ((size_t)blockIdx.x * 2 + (grp == first_group ? 0 : 1)) * (size_t)s.G * s.Ci * HW;
+        const int total = nimg * s.Ci * HW;
+        for (int i = tid; i < total; i += kFastThreads) {
+            const int col = i % s.W;
+            int r = i / s.W;
+            const int row = r % s.H;
+            r /= s.H;
+            const int ch = r % s.Ci, im = r / s.Ci;
+            dst[i] = gt[tile_index(s, pwh, im, ch, row, col)];
+        }
+        __syncthreads();
+        for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
+    };
+
+    int cur_group = -1;
+    for (long long u0 = lo; u0 < hi;) {
+        const int grp = (int)(u0 / s.C);
+        const int c0 = (int)(u0 - (long long)grp * s.C);
+        int cnt = s.C - c0;
+        if (cnt > kChanBuf) cnt = kChanBuf;
+        if (cnt > hi - u0) cnt = (int)(hi - u0);
+        const int n0 = grp * s.G;
+        __syncthreads();
+        if (grp != cur_group) {
+            if (cur_group >= 0) flush(cur_group);
+            cur_group = grp;
+            stage_group(xt, x, s, pwh, n0, min(s.G, s.N - n0));
+        }
+        build_records(chan, w, sel, s, pwh, c0, cnt);
+        __syncthreads();
+
+        const bool live = has_window && n0 + img < s.N;
+        const size_t obase = live ? ((size_t)(n0 + img) * s.C + c0) * I + win : 0;
+        // software pipeline: the next channel's gy / arg-max loads are in flight during this channel's work
+        float gy_next = live ? __ldg(gy + obase) : 0.f;
+        int bd_next = live ? (int)__ldg(amax + obase) : 0;
+        for (int cc = 0; cc < cnt; ++cc) {
+            const float dz = gy_next;
+            const int bd = bd_next;
+            if (live && cc + 1 < cnt) {
+                gy_next = __ldg(gy + obase + (size_t)(cc + 1) * I);
+                bd_next = (int)__ldg(amax + obase + (size_t)(cc + 1) * I);
+            }
+            ChanRegs r;
+            load_record(r, chan[cc]);
+            int addr[8];
+            float tg[8];
+            if (live) {
+                const int dyo = (bd >> 1) ? RSB : 0;
+                const bool dx = bd & 1;
+                float a[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    addr[k] = toff + (dx ? r.tb1[k] : r.tb0[k]) + dyo;
+                    a[k] = ld_tile(xtb, addr[k]);
+                }
+                const float g0 = gate_eval<float>(r.g[0], a[0], a[1]), g1 = gate_eval<float>(r.g[1], a[2], a[3]);
+                const float g2 = gate_eval<float>(r.g[2], a[4], a[5]), g3 = gate_eval<float>(r.g[3], a[6], a[7]);
+                const float t0 = gate_eval<float>(r.g[4], g0, g1), t1 = gate_eval<float>(r.g[5], g2, g3);
+                const float dt0 = dz * gate_da<float>(r.g[6], t1), dt1 = dz * gate_db<float>(r.g[6], t0);
+                const float dg0 = dt0 * gate_da<float>(r.g[4], g1), dg1 = dt0 * gate_db<float>(r.g[4], g0);
+                const float dg2 = dt1 * gate_da<float>(r.g[5], g3), dg3 = dt1 * gate_db<float>(r.g[5], g2);
+                tg[0] = dg0 * gate_da<float>(r.g[0], a[1]), tg[1] = dg0 * gate_db<float>(r.g[0], a[0]);
+                tg[2] = dg1 * gate_da<float>(r.g[1], a[3]), tg[3] = dg1 * gate_db<float>(r.g[1], a[2]);
+                tg[4] = dg2 * gate_da<float>(r.g[2], a[5]), tg[5] = dg2 * gate_db<float>(r.g[2], a[4]);
+                tg[6] = dg3 * gate_da<float>(r.g[3], a[7]), tg[7] = dg3 * gate_db<float>(r.g[3], a[6]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (live) {
+                    float *cell = reinterpret_cast<float *>(gtb + addr[k]);
+                    *cell += tg[k];
+                }
+                __syncthreads();
+            }
+        }
+        u0 += cnt;
+    }
+    __syncthreads();
+    flush(cur_group);
+}
+
+// gx of every group that no single block covered = sum of that group's partial tiles, in block order.
+__global__ void convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gx, FastShape s, int grid)
+{
+    const int HW = s.H * s.W;
+    const size_t per_group = (size_t)s.G * s.Ci * HW;
+    const int NG = (s.N + s.G - 1) / s.G;
+    const long long units = (long long)NG * s.C;
+    const size_t total = (size_t)NG * per_group;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int grp = (int)(i / per_group);
+        const size_t e = i - (size_t)grp * per_group;
+        if (i >= (size_t)s.N * s.Ci * HW) continue; // image beyond the batch
+        // owner(u): the block b with units*b/grid <= u < units*(b+1)/grid
+        auto owner = [&](long long u) {
+            long long b = u * grid / units;
+            while (b + 1 < grid && units * (b + 1) / grid <= u) ++b;
+            while (b > 0 && units * b / grid > u) --b;
+            return (int)b;
+        };
+        const int b1 = owner((long long)grp * s.C), b2 = owner((long long)(grp + 1) * s.C - 1);
+        if (b1 == b2) continue; // that block wrote the final values itself
+        float acc = 0.f;
+        for (int b = b1; b <= b2; ++b) {
+            const int fg = (int)((units * b / grid) / s.C);
+            acc += partial[((size_t)b * 2 + (grp == fg ? 0 : 1)) * per_group + e];
+        }
+        gx[i] = acc;
     }
 }
 
@@ -216,9 +396,26 @@ static int pick_pwh(int need, int Wp)
     return need;
 }
 
+// Fills everything but G; false when the shape is outside the tiled kernels' domain.
+static bool make_fast_shape(FastShape &s, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode)
+{
+    if (sh != 1 || sw != 1) return false;
+    s.N = N, s.Ci = Ci, s.H = H, s.W = W, s.C = C, s.ph = ph, s.pw = pw, s.kh = kh, s.kw = kw, s.wmode = wmode;
+    s.Ho = conv_out(H, ph, kh, 1), s.Wo = conv_out(W, pw, kw, 1);
+    if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return false;
+    s.PH = H + 2 * ph;
+    // every tap (row < kh, col < kw) of every conv position stays inside the padded image:
+    // row <= Ho-1 + kh-1 = PH-1, column <= Wo-1 + kw-1 = W + 2*pw - 1
+    s.pwh = pick_pwh((W + 2 * pw + 1) / 2, s.Wo / 2);
+    s.CS = s.PH * 2 * s.pwh;
+    s.IS = Ci * s.CS;
+    s.G = 1;
+    return (size_t)s.IS * 4 <= 200 * 1024;
+}
+
 template <int WPT, int PWH>
-static int launch_fast(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, FastShape s, size_t smem,
-                       int blocks_per_sm, cudaStream_t st)
+static int launch_fwd(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, FastShape s, size_t smem,
+                      int blocks_per_sm, cudaStream_t st)
 {
     auto k = convtree_fwd_tile_kernel<WPT, PWH>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
@@ -232,19 +429,9 @@ static int launch_fast(const float *x, const float *w, const int32_t *sel, float
 int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W,
                               int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st)
 {
-    if (sh != 1 || sw != 1) return CLB_ERR_SHAPE;
     FastShape s;
-    s.N = N, s.Ci = Ci, s.H = H, s.W = W, s.C = C, s.ph = ph, s.pw = pw, s.kh = kh, s.kw = kw, s.wmode = wmode;
-    s.Ho = conv_out(H, ph, kh, 1), s.Wo = conv_out(W, pw, kw, 1);
-    if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return CLB_ERR_SHAPE;
-    const int I = (s.Ho / 2) * (s.Wo / 2), Wp = s.Wo / 2;
-    s.PH = H + 2 * ph;
-    // every tap (row < kh, col < kw) of every conv position stays inside the padded image:
-    // row <= Ho-1 + kh-1 = PH-1, column <= Wo-1 + kw-1 = W + 2*pw - 1
-    const int need = (W + 2 * pw + 1) / 2;
-    s.pwh = pick_pwh(need, Wp);
-    s.CS = s.PH * 2 * s.pwh;
-    s.IS = Ci * s.CS;
+    if (!make_fast_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
+    const int I = (s.Ho / 2) * (s.Wo / 2);
     const size_t img_bytes = (size_t)s.IS * 4;
     const size_t fixed = sizeof(ChanRec) * kChanBuf;
     // windows per thread: prefer 2 (amortises the per-channel coefficient loads), fall back to 1
@@ -263,13 +450,74 @@ int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel
         s.G = G;
         const int bps = smem <= 110 * 1024 ? 2 : 1;
         if (wpt == 2) {
-            if (s.pwh == 20) return launch_fast<2, 20>(x, w, sel, y, amax, s, smem, bps, st);
-            if (s.pwh == 10) return launch_fast<2, 10>(x, w, sel, y, amax, s, smem, bps, st);
-            return launch_fast<2, 0>(x, w, sel, y, amax, s, smem, bps, st);
+            if (s.pwh == 20) return launch_fwd<2, 20>(x, w, sel, y, amax, s, smem, bps, st);
+            if (s.pwh == 10) return launch_fwd<2, 10>(x, w, sel, y, amax, s, smem, bps, st);
+            return launch_fwd<2, 0>(x, w, sel, y, amax, s, smem, bps, st);
         }
-        if (s.pwh == 20) return launch_fast<1, 20>(x, w, sel, y, amax, s, smem, bps, st);
-        if (s.pwh == 10) return launch_fast<1, 10>(x, w, sel, y, amax, s, smem, bps, st);
-        return launch_fast<1, 0>(x, w, sel, y, amax, s, smem, bps, st);
+        if (s.pwh == 20) return launch_fwd<1, 20>(x, w, sel, y, amax, s, smem, bps, st);
+        if (s.pwh == 10) return launch_fwd<1, 10>(x, w, sel, y, amax, s, smem, bps, st);
+        return launch_fwd<1, 0>(x, w, sel, y, amax, s, smem, bps, st);
     }
     return CLB_ERR_SHAPE;
+}
+
+// ---- input gradient --------------------------------------------------------------------------
+// Plan shared by the scratch-size query and the launch: false when the tiled kernel does not apply.
+static bool plan_bwd_x(FastShape &s, size_t &smem, int &grid, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                       int kw, int wmode)
+{
+    if (N <= 0 || C <= 0 || !make_fast_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return false;
+    const int I = (s.Ho / 2) * (s.Wo / 2);
+    int G = kFastThreads / I;
+    if (G < 1) return false;
+    if (G > N) G = N;
+    const size_t fixed = sizeof(ChanRec) * kChanBuf;
+    while (G > 1 && fixed + 2 * (size_t)G * s.IS * 4 > 110 * 1024) --G;
+    smem = fixed + 2 * (size_t)G * s.IS * 4;
+    if (smem > 220 * 1024) return false;
+    s.G = G;
+    const int bps = smem <= 110 * 1024 ? 2 : 1;
+    const long long units = (long long)((N + G - 1) / G) * C;
+    long long g = 148LL * bps;
+    if (g > units) g = units;
+    grid = (int)g;
+    return true;
+}
+
+size_t clb_convtree_bwd_x_fast_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw)
+{
+    FastShape s;
+    size_t smem;
+    int grid;
+    if (!plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, 0)) return 0;
+    return (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
+}
+
+template <int PWH>
+static int launch_bwd_x_tile(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
+                             float *partial, FastShape s, size_t smem, int grid, cudaStream_t st)
+{
+    auto k = convtree_bwd_x_tile_kernel<PWH>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    k<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, partial, s);
+    const size_t total = (size_t)((s.N + s.G - 1) / s.G) * s.G * s.Ci * s.H * s.W;
+    long long rb = (long long)((total + 255) / 256);
+    if (rb > 148 * 16) rb = 148 * 16;
+    convtree_bwd_x_reduce_kernel<<<(unsigned)rb, 256, 0, st>>>(partial, gx, s, grid);
+    return check_launch(2);
+}
+
+int clb_convtree_bwd_x_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
+                                void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
+                                int kh, int kw, int wmode, cudaStream_t st)
+{
+    FastShape s;
+    size_t smem;
+    int grid;
+    if (amax == nullptr || !plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
+    const size_t need = (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
+    if (scratch == nullptr || scratch_bytes < need) return CLB_ERR_SHAPE;
+    if (s.pwh == 20) return launch_bwd_x_tile<20>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
+    if (s.pwh == 10) return launch_bwd_x_tile<10>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
+    return launch_bwd_x_tile<0>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
 }

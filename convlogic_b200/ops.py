@@ -102,14 +102,18 @@ def conv_groups(sel, x_shape, geom, dtype):
     return out
 
 
-def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode):
+def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
     check_input(gy, x, w, sel)
     n, ci, h, wd = x.shape
     c = w.shape[0]
     gx = torch.empty_like(x)
+    flag = _sel_flag(sel, geom)
+    nbytes = lib().clb_convtree_bwd_x_scratch_bytes(n, ci, h, wd, c, *geom, dtype_code(x)) if (use_scratch and not flag) else 0
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
     start, lst, cg, nb = conv_groups(sel, tuple(x.shape), geom, x.dtype)
     check(lib().clb_convtree_bwd_x(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(start), ptr(lst),
-                                   cg, nb, n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+                                   cg, nb, ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode | flag, dtype_code(x),
+                                   stream()))
     return gx
 
 

@@ -81,11 +81,17 @@ int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel, void *y, 
  * of `cg` consecutive channels; grp_start int32 [G+1] / grp_list int32 [grp_start[G]] list, for each
  * group, the output channels with at least one tap in it (ascending).  Build them with
  * clb_conv_group_plan() + clb_conv_build_groups().
+ * scratch is optional: with clb_convtree_bwd_x_scratch_bytes() bytes of it (0 = no use for it) the
+ * fp32, stride-1, all-channels-in-shared-memory shapes run a faster tiled kernel that spreads the
+ * output channels of an image over several thread blocks and adds their partial tiles in a fixed
+ * order; without it (NULL / too small) the general kernel runs.
  */
+size_t clb_convtree_bwd_x_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                                        int kw, int dtype);
 int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax,
-                       void *gx, const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, int N, int Ci,
-                       int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype,
-                       void *stream);
+                       void *gx, const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, void *scratch,
+                       size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
+                       int kh, int kw, int wmode, int dtype, void *stream);
 
 /* Host-side helpers for the tables above (pure CPU, no CUDA call).
  * clb_conv_group_plan: picks cg (channels per group) and nb (images per thread block) for a shape.

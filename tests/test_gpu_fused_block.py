@@ -260,3 +260,41 @@ def test_tiled_forward_equals_general_forward(shape):
     if x.shape[0] <= 40:
         yo = oracle.full_convlogic(x, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])[0]
         assert_close(y_fast, yo, F32_TOL)
+
+
+@pytest.mark.parametrize("shape", [
+    (256, 9, 256, 32, 32, 1, 1, 3, "bits"),
+    (37, 9, 19, 32, 32, 1, 1, 3, "rand"),
+    (3, 9, 700, 32, 32, 1, 1, 3, "rand"),     # fewer images than blocks: an image's channels are split over many blocks
+    (64, 16, 48, 12, 12, 1, 1, 3, "rand"),
+    (9, 1, 16, 28, 28, 1, 0, 5, "bits"),
+    (33, 32, 20, 16, 16, 1, 1, 3, "rand"),
+    (70, 48, 24, 8, 8, 1, 1, 3, "rand"),
+    (130, 12, 10, 4, 4, 1, 1, 3, "rand"),
+], ids=lambda s: "x".join(str(v) for v in s))
+def test_tiled_input_gradient_equals_general(shape):
+    """The tiled input-gradient kernel (scratch given) against the general one (no scratch): same
+    mathematics, different summation order, so equality is to rounding; and bitwise repeatable."""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy, geom = _case(shape, seed=12)
+    xd, wd, sd, gd = x.cuda(), logits.cuda(), sel.cuda(), gy.cuda()
+    _, amax, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX)
+    g_fast = ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX)
+    g_gen = ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX, use_scratch=False)
+    assert_close(g_fast, g_gen, 2e-6)
+    assert torch.equal(g_fast, ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX))
+    if x.shape[0] <= 40 and shape[2] <= 64:
+        xo = x.clone().requires_grad_(True)
+        yo, _, _, idxo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])
+        (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
+        idx = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)[4].cpu()
+        if bool((idx == idxo).all()):
+            assert_close(g_fast, gxo, F32_TOL)
+        else:
+            # two candidates of a window tie to within fp32 rounding and the CPU picked the other one:
+            # the gradient is then routed differently for that window only
+            assert float((idx != idxo).float().mean()) < 1e-4
+            bad = ((g_fast.cpu() - gxo).abs() > F32_TOL * gxo.abs().max()).float().mean()
+            assert float(bad) < 1e-3
