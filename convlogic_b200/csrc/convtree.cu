@@ -318,6 +318,90 @@ __global__ void __launch_bounds__(256) conv_bwd_w_kernel(const T *__restrict__ g
     }
 }
 
+// Fused block, fp32, arg-max available, at most 256 pooled positions per image: the block size is a
+// multiple of the positions per image, so a thread keeps ONE pooled window for its whole life and
+// only the image index advances.  Its 8 tap offsets (for the window's first position) and the
+// in-bounds flags of the 4 x 8 (position, tap) pairs are computed once; per image a tap costs one
+// add, one predicate and one cached global load.  grid (parts, C); block `part` covers images
+// [N*part/parts, N*(part+1)/parts).
+__global__ void __launch_bounds__(256) convtree_bwd_w_win_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+                                                                 const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                 const uint8_t *__restrict__ amax, float *__restrict__ partial,
+                                                                 ConvShape s, int wmode)
+{
+    __shared__ BlockGates<float> bg;
+    __shared__ float red[8][28];
+    const int c = blockIdx.y;
+    load_channel<float>(bg, w, sel, c, 7, wmode, s.ph, s.pw);
+    __syncthreads();
+    const int Wp = s.Wo / 2, I = (s.Ho / 2) * Wp;
+    const int ipb = blockDim.x / I; // images per block iteration
+    const int lane_img = threadIdx.x / I, win = threadIdx.x - lane_img * I;
+    const int py = win / Wp, px = win - py * Wp;
+    const int HW = s.H * s.W;
+    int base[8];
+    unsigned valid = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const Tap tp = bg.tap[k];
+        const int iy0 = 2 * py * s.sh + tp.dy, ix0 = 2 * px * s.sw + tp.dx;
+        base[k] = tp.ch * HW + iy0 * s.W + ix0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const int iy = iy0 + (d >> 1) * s.sh, ix = ix0 + (d & 1) * s.sw;
+            if ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) valid |= 1u << (d * 8 + k);
+        }
+    }
+    Gate<float> g[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g[i] = bg.g[i];
+    float acc[28];
+#pragma unroll
+    for (int i = 0; i < 28; ++i) acc[i] = 0.f;
+
+    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+    const bool active = lane_img < ipb;
+    for (int n = n_lo + lane_img; active && n < n_hi; n += ipb) {
+        const size_t item = ((size_t)n * s.C + c) * I + win;
+        const int bd = amax[item];
+        const float dz = __ldg(gy + item);
+        const float *ximg = x + (size_t)n * s.Ci * HW + ((bd >> 1) ? s.sh * s.W : 0) + ((bd & 1) ? s.sw : 0);
+        const unsigned vm = valid >> (bd * 8);
+        float a[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = ((vm >> k) & 1u) ? __ldg(ximg + base[k]) : 0.f;
+        const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+        const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+        const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+        const float dt0 = dz * gate_da<float>(g[6], t1), dt1 = dz * gate_db<float>(g[6], t0);
+        float dg[4];
+        dg[0] = dt0 * gate_da<float>(g[4], g1), dg[1] = dt0 * gate_db<float>(g[4], g0);
+        dg[2] = dt1 * gate_da<float>(g[5], g3), dg[3] = dt1 * gate_db<float>(g[5], g2);
+        acc[24] = fmaf(dz, t0 * t1, acc[24]), acc[25] = fmaf(dz, t0, acc[25]), acc[26] = fmaf(dz, t1, acc[26]), acc[27] += dz;
+        acc[16] = fmaf(dt0, g0 * g1, acc[16]), acc[17] = fmaf(dt0, g0, acc[17]), acc[18] = fmaf(dt0, g1, acc[18]), acc[19] += dt0;
+        acc[20] = fmaf(dt1, g2 * g3, acc[20]), acc[21] = fmaf(dt1, g2, acc[21]), acc[22] = fmaf(dt1, g3, acc[22]), acc[23] += dt1;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            acc[4 * p] = fmaf(dg[p], a[2 * p] * a[2 * p + 1], acc[4 * p]);
+            acc[4 * p + 1] = fmaf(dg[p], a[2 * p], acc[4 * p + 1]);
+            acc[4 * p + 2] = fmaf(dg[p], a[2 * p + 1], acc[4 * p + 2]);
+            acc[4 * p + 3] += dg[p];
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 28; ++i) {
+        const float v = warp_sum<float>(acc[i]);
+        if (lane == 0) red[warp][i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 28) {
+        float v = 0.f;
+        for (int wv = 0; wv < (int)((blockDim.x + 31) >> 5); ++wv) v += red[wv][threadIdx.x];
+        partial[((size_t)blockIdx.x * s.C + c) * 28 + threadIdx.x] = v;
+    }
+}
+
 // One thread per gate: adds the per-part basis sums in part order and writes the 16 gradients.
 template <typename T>
 __global__ void gate_grad_finalize_kernel(const T *__restrict__ partial, const T *__restrict__ w, T *__restrict__ gw, int parts,
@@ -542,7 +626,7 @@ extern "C" int clb_conv_bwd_x(const void *gy, const void *x, const void *w, cons
 // ---- gate gradient ----------------------------------------------------------------------------
 static int bwd_w_parts(long long total_items, int C)
 {
-    long long parts = (148LL * 8 + C - 1) / (C > 0 ? C : 1);
+    long long parts = (148LL * 20 + C - 1) / (C > 0 ? C : 1); // about ten waves of two resident blocks per SM
     long long most = total_items / 2048;
     if (parts > most) parts = most;
     if (parts < 1) parts = 1;
@@ -587,7 +671,12 @@ static int launch_bwd_w(const void *gy, const void *x, const void *w, const int3
     dim3 grid(parts, C);
     const long long ngates = (long long)C * NG;
     const int fb = (int)((ngates + 127) / 128);
-    if (dtype == CLB_F32) {
+    if (dtype == CLB_F32 && FUSED && amax != nullptr && items <= 256 && parts <= N) {
+        const int threads = (int)((256 / items) * items); // whole images per block iteration
+        convtree_bwd_w_win_kernel<<<grid, threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
+                                                            (float *)scratch, s, wmode);
+        gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
+    } else if (dtype == CLB_F32) {
         conv_bwd_w_kernel<float, FUSED><<<grid, 256, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
                                                                (float *)scratch, s, wmode);
         gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
