@@ -361,15 +361,48 @@ __global__ void __launch_bounds__(256) convtree_bwd_w_win_kernel(const float *__
 
     const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
     const bool active = lane_img < ipb;
-    for (int n = n_lo + lane_img; active && n < n_hi; n += ipb) {
-        const size_t item = ((size_t)n * s.C + c) * I + win;
-        const int bd = amax[item];
-        const float dz = __ldg(gy + item);
-        const float *ximg = x + (size_t)n * s.Ci * HW + ((bd >> 1) ? s.sh * s.W : 0) + ((bd & 1) ? s.sw : 0);
+    // Software pipeline over this thread's images: the arg-max / gy of image i+2 and the 8 gathered
+    // taps of image i+1 are in flight while image i is evaluated (arg-max -> address -> gather are
+    // two dependent global-memory latencies otherwise).
+    const size_t item_step = (size_t)ipb * s.C * I;
+    const size_t x_step = (size_t)ipb * s.Ci * HW;
+    int n = n_lo + lane_img;
+    size_t item = ((size_t)n * s.C + c) * I + win;
+    const float *ximg = x + (size_t)n * s.Ci * HW;
+    int bd1 = 0, bd2 = 0;
+    float dz1 = 0.f, dz2 = 0.f, a1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a1[k] = 0.f;
+    auto gather = [&](float(&a)[8], int bd, const float *img) {
+        const float *p = img + ((bd >> 1) ? s.sh * s.W : 0) + ((bd & 1) ? s.sw : 0);
         const unsigned vm = valid >> (bd * 8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = ((vm >> k) & 1u) ? __ldg(p + base[k]) : 0.f;
+    };
+    if (active && n < n_hi) {
+        bd1 = amax[item];
+        dz1 = __ldg(gy + item);
+        gather(a1, bd1, ximg);
+        if (n + ipb < n_hi) {
+            bd2 = amax[item + item_step];
+            dz2 = __ldg(gy + item + item_step);
+        }
+    }
+    for (; active && n < n_hi; n += ipb) {
         float a[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) a[k] = ((vm >> k) & 1u) ? __ldg(ximg + base[k]) : 0.f;
+        for (int k = 0; k < 8; ++k) a[k] = a1[k];
+        const float dz = dz1;
+        // advance the pipeline
+        item += item_step;
+        ximg += x_step;
+        bd1 = bd2;
+        dz1 = dz2;
+        if (n + ipb < n_hi) gather(a1, bd1, ximg);
+        if (n + 2 * ipb < n_hi) {
+            bd2 = amax[item + item_step];
+            dz2 = __ldg(gy + item + item_step);
+        }
         const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
         const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
         const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
