@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libconvlogic_b200.so")
 F32, F64 = 0, 1
 W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
 SEL_UNBOUNDED = 0x100
-ERR_SHAPE, ERR_ODD_OUTPUT = -2, -5
+ERR_SHAPE, ERR_ODD_OUTPUT, ERR_TOO_LARGE = -2, -5, -6
 
 _lib = None
 
@@ -34,6 +34,8 @@ _SIGNATURES = {
     "clb_conv_build_groups": ([_vp, _i, _i, _i, _vp, _vp, _i], _i),
     "clb_convtree_bwd_w_scratch_bytes": ([_i, _i, _i, _i, _i], _sz),
     "clb_convtree_bwd_w": ([_vp] * 7 + [_sz] + _conv + [_i, _i, _vp], _i),
+    "clb_convtree_bwd_w_noalloc_max_bytes": ([], _sz),
+    "clb_convtree_bwd_w_noalloc": ([_vp] * 6 + _conv + [_i, _i, _vp], _i),
     "clb_conv_fwd": ([_vp] * 4 + _conv + [_i, _i, _vp], _i),
     "clb_conv_bwd_x": ([_vp] * 7 + [_i, _i] + _conv + [_i, _i, _vp], _i),
     "clb_conv_bwd_w_scratch_bytes": ([_i, _i, _i, _i, _i], _sz),
@@ -79,7 +81,7 @@ def check(status):
     if status == -3:
         err = lib().clb_last_cuda_error()
         raise RuntimeError(f"convlogic_b200: {text} (cudaError {err})")
-    if status == ERR_SHAPE:
+    if status in (ERR_SHAPE, ERR_TOO_LARGE):
         raise ValueError(f"convlogic_b200: {text}")
     raise RuntimeError(f"convlogic_b200: {text}")
 

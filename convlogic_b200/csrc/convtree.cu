@@ -19,6 +19,8 @@
 //     CLB_W_SOFTMAX, the soft-max Jacobian).
 #include "clb_common.cuh"
 
+#include <mutex>
+
 namespace clb {
 
 struct ConvShape {
@@ -735,4 +737,56 @@ extern "C" int clb_conv_bwd_w(const void *gy, const void *x, const void *w, cons
 {
     return launch_bwd_w<false>(gy, x, w, sel, nullptr, gw, scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
                                dtype, stream);
+}
+
+// ---- gate gradient of the fused block for callers that must not allocate -----------------------
+// Same kernels as clb_convtree_bwd_w; the per-block partial sums live in a fixed array that is part
+// of the loaded library image instead of a caller-supplied buffer.
+constexpr size_t kStaticScratchBytes = 4u << 20; // 4 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_bwd_w_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void *g_static_scratch_addr[kMaxDevices] = {}; // device address of the array, per device ordinal
+
+// In host code the array's name is only a handle for the runtime; the address a kernel can use has
+// to be asked for, once per device, with that device current.
+int static_scratch_for_current_device(void **out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        return CLB_ERR_LAUNCH;
+    }
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_bwd_w_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_last_cuda_error((int)e);
+            cudaGetLastError();
+            return CLB_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return CLB_OK;
+}
+} // namespace
+
+extern "C" size_t clb_convtree_bwd_w_noalloc_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int clb_convtree_bwd_w_noalloc(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax,
+                                          void *gw, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
+                                          int wmode, int dtype, void *stream)
+{
+    if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_ARG;
+    const size_t need = clb_convtree_bwd_w_scratch_bytes(N, C, conv_out(H, ph, kh, sh), conv_out(W, pw, kw, sw), dtype);
+    if (need > kStaticScratchBytes) return CLB_ERR_TOO_LARGE;
+    void *scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != CLB_OK) return rc;
+    return launch_bwd_w<true>(gy, x, w, sel, amax, gw, scratch, kStaticScratchBytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
+                              dtype, stream);
 }

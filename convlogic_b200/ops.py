@@ -130,6 +130,23 @@ def convtree_bwd_w(gy, x, w, sel, amax, geom, wmode):
     return gw
 
 
+def convtree_bwd_w_noalloc(gy, x, w, sel, amax, geom, wmode, out):
+    """Gate gradient of the fused block written into the caller's ``out`` ([C, 7, 16]) without
+    any allocation on the way: the kernels' partial sums go to a fixed array inside the library
+    instead of a scratch tensor.  For callers that may not allocate (inside a memory-planned or
+    pre-allocated region).  Raises ValueError when the shape needs more than that array holds.
+    All calls on a device share the array, so do not let two of them overlap on the GPU; make the
+    first call on a device outside any stream capture (it looks the array's address up once)."""
+    check_input(gy, x, w, sel, out)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    if out.shape != w.shape or out.dtype != w.dtype:
+        raise RuntimeError("convlogic_b200: `out` must have the gate tensor's shape and dtype")
+    check(lib().clb_convtree_bwd_w_noalloc(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(out),
+                                           n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
+    return out
+
+
 # --------------------------------------------------------------------- stand-alone first level
 def conv_fwd(x, w, sel, geom, wmode):
     check_input(x, w, sel)

@@ -111,6 +111,28 @@ int clb_convtree_bwd_w(const void *gy, const void *x, const void *w, const int32
                        void *gw, void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh,
                        int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream);
 
+/* Gate-weight gradient of the fused block for callers that cannot allocate GPU memory.
+ * No counterpart in the reference (every reference entry point allocates through torch).
+ * Some hosts of this library own no allocator they may call at this point: a plugin invoked inside a
+ * framework's memory-planned region, a real-time loop that pre-allocates everything at start-up, or a
+ * thin FFI caller that can pass pointers but has no device-memory API of its own.  For them the
+ * partial sums that clb_convtree_bwd_w() keeps in a caller-supplied scratch buffer are kept in a
+ * fixed 4 MiB array inside the library (clb_convtree_bwd_w_noalloc_max_bytes(); every GPU that loads
+ * the library holds it until the process exits).  Arguments, results and kernels are otherwise those
+ * of clb_convtree_bwd_w(); the call itself performs no cudaMalloc/cudaFree or other allocation.
+ *   - Shapes whose scratch need (clb_convtree_bwd_w_scratch_bytes()) exceeds the array return
+ *     CLB_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on each device looks the array's device address up (a one-off runtime query);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the array, and it keeps whatever the previous call left there.
+ *     Nothing in it needs to start at zero (every slot is written before it is read), but two calls
+ *     whose kernels overlap on the GPU (different streams, no ordering) race on it: serialise them.
+ */
+size_t clb_convtree_bwd_w_noalloc_max_bytes(void);
+int clb_convtree_bwd_w_noalloc(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax,
+                               void *gw, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                               int kw, int wmode, int dtype, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Stand-alone first gate level (ConvLogicLayer with complete=False).
  * Replace convlogic_cuda.convlogic_forward / convlogic_backward_x / convlogic_backward_weight
