@@ -1,0 +1,81 @@
+"""Data-parallel plumbing for the logic-gate layers: one process per GPU, batch-sharded replicas.
+
+The only tensors that differ between ranks after a backward pass are the gate-logit gradients
+(``weights.grad`` of every layer); connections (``selection``, ``indices_*``) are buffers and equal
+on all ranks.  So a training step exchanges exactly one flat fp32 bucket, and inference exchanges
+nothing.  The reference gets the same effect implicitly from Lightning's DDP strategy
+(configs/config.yaml:20, src/convlogic/model.py:149-176).
+"""
+
+import torch
+import torch.distributed as dist
+
+
+def gate_parameters(model):
+    """The ``weights`` parameters of every logic layer, in module order."""
+    return [p for name, p in model.named_parameters() if name.split(".")[-1] == "weights"]
+
+
+class GradBucket:
+    """Keeps all gate-logit gradients in ONE flat buffer (each ``weights.grad`` is a view into it),
+    so that the data-parallel exchange is a single all-reduce with no packing copies."""
+
+    def __init__(self, model):
+        self.params = gate_parameters(model)
+        if not self.params:
+            raise ValueError("model has no logic-gate parameters")
+        p0 = self.params[0]
+        self.numel = sum(p.numel() for p in self.params)
+        self.flat = torch.zeros(self.numel, dtype=p0.dtype, device=p0.device)
+        off = 0
+        for p in self.params:
+            p.grad = self.flat[off:off + p.numel()].view_as(p)
+            off += p.numel()
+
+    def zero(self):
+        self.flat.zero_()
+
+    def allreduce(self, group=None, average=True, async_op=False):
+        """Sum (or mean) over ranks.  A no-op without an initialised process group."""
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return None
+        work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+        if average:
+            if async_op:
+                work.wait()
+            self.flat.div_(dist.get_world_size(group))
+        return work
+
+
+def allreduce_gate_gradients(model, group=None, average=True):
+    """One-shot variant: flattens the existing ``weights.grad`` tensors, all-reduces, copies back."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    grads = [p.grad for p in gate_parameters(model) if p.grad is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1) for g in grads])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    if average:
+        flat.div_(dist.get_world_size(group))
+    off = 0
+    for g in grads:
+        g.copy_(flat[off:off + g.numel()].view_as(g))
+        off += g.numel()
+
+
+def broadcast_state(model, src=0, group=None):
+    """Make parameters and connection buffers identical on all ranks (rank `src` wins)."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    for t in list(model.parameters()) + list(model.buffers()):
+        dist.broadcast(t.data, src=src, group=group)
+
+
+def shard_range(n_items, rank=None, world=None):
+    """[lo, hi) of the items rank `rank` owns when `n_items` are split as evenly as possible."""
+    if rank is None:
+        rank = dist.get_rank() if dist.is_initialized() else 0
+    if world is None:
+        world = dist.get_world_size() if dist.is_initialized() else 1
+    return n_items * rank // world, n_items * (rank + 1) // world

@@ -1,0 +1,79 @@
+"""Data-parallel helpers on CPU ranks (gloo, world size 2): the N > 1 host logic of training and
+of batch-sharded inference, without a GPU."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fail_rank):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import convlogic_b200 as cb
+        from convlogic_b200 import dp
+
+        torch.manual_seed(100 + rank)  # deliberately different: broadcast_state must fix it
+        model = torch.nn.Sequential(cb.ConvLogicLayer(3, 4, complete=True), torch.nn.Flatten(), cb.LogicLayer(16, 40),
+                                    cb.GroupSum(10, 2.0))
+        dp.broadcast_state(model)
+        ref = [t.clone() for t in list(model.parameters()) + list(model.buffers())]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [t.tolist() for t in ref[:2]] + [ref[2].tolist()])
+        assert gathered[0] == gathered[1], "state differs after broadcast"
+
+        # flat bucket: gradients are views, one all-reduce averages them
+        bucket = dp.GradBucket(model)
+        params = dp.gate_parameters(model)
+        assert [tuple(p.shape) for p in params] == [(4, 7, 16), (40, 16)]
+        assert bucket.numel == 4 * 7 * 16 + 40 * 16
+        for p in params:
+            p.grad.fill_(float(rank + 1))
+        assert float(bucket.flat.min()) == rank + 1  # views share storage
+        bucket.allreduce(average=True)
+        assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
+        assert all(torch.allclose(p.grad, torch.full_like(p, 1.5)) for p in params)
+        bucket.zero()
+        assert float(params[1].grad.abs().max()) == 0.0
+
+        # one-shot variant on ordinary .grad tensors
+        for p in params:
+            p.grad = torch.full_like(p, float(10 * (rank + 1)))
+        dp.allreduce_gate_gradients(model, average=False)
+        assert all(torch.allclose(p.grad, torch.full_like(p, 30.0)) for p in params)
+
+        # inference shards: disjoint, exhaustive, no collective needed
+        lo, hi = dp.shard_range(1001)
+        spans = [None] * world
+        dist.all_gather_object(spans, (lo, hi))
+        assert spans[0][0] == 0 and spans[-1][1] == 1001 and spans[0][1] == spans[1][0]
+
+        # a rank that fails on the host before the collective: the others see it through the store
+        # (no collective is entered, nothing hangs)
+        flags = [None] * world
+        dist.all_gather_object(flags, "error" if rank == fail_rank else "ok")
+        if "error" in flags:
+            raise RuntimeError("peer failure reported before the collective")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_gradient_bucket_and_sharding():
+    mp.spawn(_worker, args=(2, _free_port(), -1), nprocs=2, join=True)
+
+
+@pytest.mark.timeout(300)
+def test_host_side_failure_is_reported_not_hung():
+    with pytest.raises(Exception):
+        mp.spawn(_worker, args=(2, _free_port(), 1), nprocs=2, join=True)
