@@ -20,8 +20,8 @@
 // Forward (convtree_fwd_tile_kernel): WPT windows (4*WPT conv positions) per thread and channel;
 // nothing but y (and the 1-byte arg-max the backward uses) is written to global memory.
 //
-// Input gradient (convtree_bwd_x_tile_kernel): a second tile with the same layout accumulates the
-// gradient of the staged images.  For one (channel, tap) the map window -> input pixel is injective,
+// Input gradient (convtree_bwd_x_cls_kernel): a second tile accumulates the gradient of the staged
+// images (both tiles use the halo-free parity-class layout described at the kernel).  For one (channel, tap) the map window -> input pixel is injective,
 // so threads add with plain read-modify-writes and a block barrier separates the 8 taps: the order
 // of additions into a pixel is fixed (channel ascending, tap ascending).  A block whose range holds
 // all channels of a group writes the final gradient; otherwise it writes a partial tile to scratch
@@ -227,22 +227,50 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
 }
 
 // ==================================================================================== input gradient
-// One window per thread.  Shared memory: records | x tile | gradient tile (same layout).
-template <int PWH>
-__global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(const float *__restrict__ gy, const float *__restrict__ x,
-                                                                             const float *__restrict__ w, const int32_t *__restrict__ sel,
-                                                                             const uint8_t *__restrict__ amax, float *__restrict__ gx,
-                                                                             float *__restrict__ partial, FastShape s)
+// Layout of the two backward tiles (x and its gradient): NO halo; a channel plane is split into the four
+// parity classes of (row, column) -- class = 2*(row & 1) + (col & 1) -- each stored as a dense
+// [ceil(H/2)][ceil(W/2)] array.  A thread owns one pooled window; the pixel a tap reaches from the
+// window's arg-max position (dy, dx) is  toff + base_k + dy*A_k + dx*B_k  with per-channel uniform
+// base/A/B, and whatever (dy, dx) the lanes of a warp have, lane px lands in bank (px + const) of its
+// class plane: the data-dependent arg-max costs ~1.7 wavefronts per access instead of ~3 with the
+// forward's row-major layout (which also needs a third more shared memory for its halo).
+// Out-of-image taps are predicated off instead of reading a zero halo.
+constexpr int kBwdChanBuf = 8;
+
+struct alignas(16) BwdRec {
+    float g[28]; // 7 gates x (k1, ka, kb, kab)
+    int base[8]; // byte offset of tap k from the window's first position
+    int dA[8];   // added when the arg-max is in the window's second row
+    int dB[8];   // added when it is in the second column
+    int ty[8];   // tap row offset (row - pad), for the bounds test
+    int tx[8];
+};
+
+struct ClsShape {
+    int N, Ci, H, W, C, Ho, Wo, ph, pw, kh, kw;
+    int G;          // images per group
+    int Hh, Wh;     // class-plane extent
+    int PL, CS, IS; // class plane, channel and image stride in floats
+    int wmode;
+};
+
+__device__ __forceinline__ int cls_index(const ClsShape &s, int img, int ch, int row, int col)
+{
+    return img * s.IS + ch * s.CS + ((row & 1) * 2 + (col & 1)) * s.PL + (row >> 1) * s.Wh + (col >> 1);
+}
+
+__global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+                                                                            const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                            const uint8_t *__restrict__ amax, float *__restrict__ gx,
+                                                                            float *__restrict__ partial, ClsShape s)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    ChanRec *chan = reinterpret_cast<ChanRec *>(smem_raw);
-    float *xt = reinterpret_cast<float *>(smem_raw + sizeof(ChanRec) * kChanBuf);
+    BwdRec *chan = reinterpret_cast<BwdRec *>(smem_raw);
+    float *xt = reinterpret_cast<float *>(smem_raw + sizeof(BwdRec) * kBwdChanBuf);
     float *gt = xt + s.G * s.IS;
     const unsigned char *xtb = reinterpret_cast<const unsigned char *>(xt);
     unsigned char *gtb = reinterpret_cast<unsigned char *>(gt);
 
-    const int pwh = PWH > 0 ? PWH : s.pwh;
-    const int RSB = 8 * pwh;
     const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
     const int tid = threadIdx.x;
     const int HW = s.H * s.W;
@@ -256,10 +284,34 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(co
     const int img = tid / I, win = tid - img * I;
     const int py = win / Wp, px = win - py * Wp;
     const bool has_window = img < s.G;
-    const int toff = 4 * (img * s.IS + 2 * py * 2 * pwh + px);
+    const int toff = 4 * (img * s.IS + py * s.Wh + px);
 
-    for (int i = tid; i < 2 * s.G * s.IS; i += kFastThreads) xt[i] = 0.f; // both tiles
+    for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
 
+    auto stage = [&](int n0, int nimg) {
+        const int total = nimg * s.Ci * HW;
+        if ((s.W & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0)) {
+            for (int i = tid; i < (total >> 2); i += kFastThreads) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)n0 * s.Ci * HW) + i);
+                const int e = i << 2;
+                const int col = e % s.W;
+                int r = e / s.W;
+                const int row = r % s.H;
+                r /= s.H;
+                const int ch = r % s.Ci, im = r / s.Ci;
+                const int b0 = cls_index(s, im, ch, row, col); // col is a multiple of 4: classes alternate
+                xt[b0] = v.x, xt[b0 + s.PL] = v.y, xt[b0 + 1] = v.z, xt[b0 + s.PL + 1] = v.w;
+            }
+        } else {
+            for (int i = tid; i < total; i += kFastThreads) {
+                const int col = i % s.W;
+                int r = i / s.W;
+                const int row = r % s.H;
+                r /= s.H;
+                xt[cls_index(s, r / s.Ci, r % s.Ci, row, col)] = __ldg(x + (size_t)n0 * s.Ci * HW + i);
+            }
+        }
+    };
     // Writes the gradient tile of group `grp` (final when the block saw all its channels, else partial).
     auto flush = [&](int grp) {
         const int n0 = grp * s.G;
@@ -273,28 +325,46 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(co
             int r = i / s.W;
             const int row = r % s.H;
             r /= s.H;
-            const int ch = r % s.Ci, im = r / s.Ci;
-            dst[i] = gt[tile_index(s, pwh, im, ch, row, col)];
+            dst[i] = gt[cls_index(s, r / s.Ci, r % s.Ci, row, col)];
         }
         __syncthreads();
         for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
     };
+    // f(t): offset of row/col displacement t inside the class layout (t may be negative)
+    auto fy = [&](int t) { return (t & 1) * 2 * s.PL + (t >> 1) * s.Wh; };
+    auto fx = [&](int t) { return (t & 1) * s.PL + (t >> 1); };
 
     int cur_group = -1;
     for (long long u0 = lo; u0 < hi;) {
         const int grp = (int)(u0 / s.C);
         const int c0 = (int)(u0 - (long long)grp * s.C);
         int cnt = s.C - c0;
-        if (cnt > kChanBuf) cnt = kChanBuf;
+        if (cnt > kBwdChanBuf) cnt = kBwdChanBuf;
         if (cnt > hi - u0) cnt = (int)(hi - u0);
         const int n0 = grp * s.G;
         __syncthreads();
         if (grp != cur_group) {
             if (cur_group >= 0) flush(cur_group);
             cur_group = grp;
-            stage_group(xt, x, s, pwh, n0, min(s.G, s.N - n0));
+            stage(n0, min(s.G, s.N - n0));
         }
-        build_records(chan, w, sel, s, pwh, c0, cnt);
+        for (int i = tid; i < cnt * 7; i += kFastThreads) {
+            const int cc = i / 7, gi = i - cc * 7;
+            const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
+            float *o = chan[cc].g + gi * 4;
+            o[0] = g.k1, o[1] = g.ka, o[2] = g.kb, o[3] = g.kab;
+        }
+        for (int i = tid; i < cnt * 8; i += kFastThreads) {
+            const int cc = i >> 3, k = i & 7;
+            const int word = sel[(c0 + cc) * 8 + k];
+            const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1);
+            const int ty = ((word >> 8) & 0xFF) - s.ph, tx = (word & 0xFF) - s.pw;
+            chan[cc].base[k] = 4 * (ch * s.CS + fy(ty) + fx(tx));
+            chan[cc].dA[k] = 4 * (fy(ty + 1) - fy(ty));
+            chan[cc].dB[k] = 4 * (fx(tx + 1) - fx(tx));
+            chan[cc].ty[k] = ty;
+            chan[cc].tx[k] = tx;
+        }
         __syncthreads();
 
         const bool live = has_window && n0 + img < s.N;
@@ -309,33 +379,53 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(co
                 gy_next = __ldg(gy + obase + (size_t)(cc + 1) * I);
                 bd_next = (int)__ldg(amax + obase + (size_t)(cc + 1) * I);
             }
-            ChanRegs r;
-            load_record(r, chan[cc]);
+            const BwdRec &rec = chan[cc];
+            Gate<float> g[7];
+            {
+                const float4 *gp = reinterpret_cast<const float4 *>(rec.g);
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const float4 q = gp[i];
+                    g[i].k1 = q.x, g[i].ka = q.y, g[i].kb = q.z, g[i].kab = q.w;
+                }
+            }
             int addr[8];
             float tg[8];
+            unsigned ok = 0;
             if (live) {
-                const int dyo = (bd >> 1) ? RSB : 0;
-                const bool dx = bd & 1;
+                const int dyi = bd >> 1, dxi = bd & 1;
+                const int oy = 2 * py + dyi, ox = 2 * px + dxi;
                 float a[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    addr[k] = toff + (dx ? r.tb1[k] : r.tb0[k]) + dyo;
-                    a[k] = ld_tile(xtb, addr[k]);
+                for (int q = 0; q < 2; ++q) {
+                    const int4 b4 = reinterpret_cast<const int4 *>(rec.base)[q], a4 = reinterpret_cast<const int4 *>(rec.dA)[q];
+                    const int4 c4 = reinterpret_cast<const int4 *>(rec.dB)[q], y4 = reinterpret_cast<const int4 *>(rec.ty)[q];
+                    const int4 x4 = reinterpret_cast<const int4 *>(rec.tx)[q];
+                    const int bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w}, cc4[4] = {c4.x, c4.y, c4.z, c4.w};
+                    const int yy[4] = {y4.x, y4.y, y4.z, y4.w}, xx[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int k = q * 4 + j;
+                        addr[k] = toff + bb[j] + dyi * aa[j] + dxi * cc4[j];
+                        const bool v = (unsigned)(oy + yy[j]) < (unsigned)s.H && (unsigned)(ox + xx[j]) < (unsigned)s.W;
+                        ok |= (v ? 1u : 0u) << k;
+                        a[k] = v ? ld_tile(xtb, addr[k]) : 0.f;
+                    }
                 }
-                const float g0 = gate_eval<float>(r.g[0], a[0], a[1]), g1 = gate_eval<float>(r.g[1], a[2], a[3]);
-                const float g2 = gate_eval<float>(r.g[2], a[4], a[5]), g3 = gate_eval<float>(r.g[3], a[6], a[7]);
-                const float t0 = gate_eval<float>(r.g[4], g0, g1), t1 = gate_eval<float>(r.g[5], g2, g3);
-                const float dt0 = dz * gate_da<float>(r.g[6], t1), dt1 = dz * gate_db<float>(r.g[6], t0);
-                const float dg0 = dt0 * gate_da<float>(r.g[4], g1), dg1 = dt0 * gate_db<float>(r.g[4], g0);
-                const float dg2 = dt1 * gate_da<float>(r.g[5], g3), dg3 = dt1 * gate_db<float>(r.g[5], g2);
-                tg[0] = dg0 * gate_da<float>(r.g[0], a[1]), tg[1] = dg0 * gate_db<float>(r.g[0], a[0]);
-                tg[2] = dg1 * gate_da<float>(r.g[1], a[3]), tg[3] = dg1 * gate_db<float>(r.g[1], a[2]);
-                tg[4] = dg2 * gate_da<float>(r.g[2], a[5]), tg[5] = dg2 * gate_db<float>(r.g[2], a[4]);
-                tg[6] = dg3 * gate_da<float>(r.g[3], a[7]), tg[7] = dg3 * gate_db<float>(r.g[3], a[6]);
+                const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+                const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+                const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+                const float dt0 = dz * gate_da<float>(g[6], t1), dt1 = dz * gate_db<float>(g[6], t0);
+                const float dg0 = dt0 * gate_da<float>(g[4], g1), dg1 = dt0 * gate_db<float>(g[4], g0);
+                const float dg2 = dt1 * gate_da<float>(g[5], g3), dg3 = dt1 * gate_db<float>(g[5], g2);
+                tg[0] = dg0 * gate_da<float>(g[0], a[1]), tg[1] = dg0 * gate_db<float>(g[0], a[0]);
+                tg[2] = dg1 * gate_da<float>(g[1], a[3]), tg[3] = dg1 * gate_db<float>(g[1], a[2]);
+                tg[4] = dg2 * gate_da<float>(g[2], a[5]), tg[5] = dg2 * gate_db<float>(g[2], a[4]);
+                tg[6] = dg3 * gate_da<float>(g[3], a[7]), tg[7] = dg3 * gate_db<float>(g[3], a[6]);
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                if (live) {
+                if ((ok >> k) & 1u) {
                     float *cell = reinterpret_cast<float *>(gtb + addr[k]);
                     *cell += tg[k];
                 }
@@ -349,32 +439,31 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_bwd_x_tile_kernel(co
 }
 
 // gx of every group that no single block covered = sum of that group's partial tiles, in block order.
-__global__ void convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gx, FastShape s, int grid)
+// grid (chunks, groups): the owners of a group's first and last channel are found once per thread.
+__global__ void convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gx, ClsShape s, int grid)
 {
     const int HW = s.H * s.W;
-    const size_t per_group = (size_t)s.G * s.Ci * HW;
+    const int per_group = s.G * s.Ci * HW;
     const int NG = (s.N + s.G - 1) / s.G;
     const long long units = (long long)NG * s.C;
-    const size_t total = (size_t)NG * per_group;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int grp = (int)(i / per_group);
-        const size_t e = i - (size_t)grp * per_group;
-        if (i >= (size_t)s.N * s.Ci * HW) continue; // image beyond the batch
-        // owner(u): the block b with units*b/grid <= u < units*(b+1)/grid
-        auto owner = [&](long long u) {
-            long long b = u * grid / units;
-            while (b + 1 < grid && units * (b + 1) / grid <= u) ++b;
-            while (b > 0 && units * b / grid > u) --b;
-            return (int)b;
-        };
-        const int b1 = owner((long long)grp * s.C), b2 = owner((long long)(grp + 1) * s.C - 1);
-        if (b1 == b2) continue; // that block wrote the final values itself
-        float acc = 0.f;
-        for (int b = b1; b <= b2; ++b) {
-            const int fg = (int)((units * b / grid) / s.C);
-            acc += partial[((size_t)b * 2 + (grp == fg ? 0 : 1)) * per_group + e];
-        }
-        gx[i] = acc;
+    const int grp = blockIdx.y;
+    // owner(u): the block b with units*b/grid <= u < units*(b+1)/grid
+    auto owner = [&](long long u) {
+        long long b = u * grid / units;
+        while (b + 1 < grid && units * (b + 1) / grid <= u) ++b;
+        while (b > 0 && units * b / grid > u) --b;
+        return (int)b;
+    };
+    const int b1 = owner((long long)grp * s.C), b2 = owner((long long)(grp + 1) * s.C - 1);
+    if (b1 == b2) return; // that block wrote the final values itself
+    const int live = min(s.G, s.N - grp * s.G) * s.Ci * HW; // the last group may hold fewer images
+    const float *p1 = partial + ((size_t)b1 * 2 + ((int)((units * b1 / grid) / s.C) == grp ? 0 : 1)) * per_group;
+    float *out = gx + (size_t)grp * per_group;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < live; e += gridDim.x * blockDim.x) {
+        float acc = p1[e];
+        // every later block starts inside this group, so the group is its first: slot 0
+        for (int b = b1 + 1; b <= b2; ++b) acc += partial[(size_t)b * 2 * per_group + e];
+        out[e] = acc;
     }
 }
 
@@ -463,20 +552,29 @@ int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel
 
 // ---- input gradient --------------------------------------------------------------------------
 // Plan shared by the scratch-size query and the launch: false when the tiled kernel does not apply.
-static bool plan_bwd_x(FastShape &s, size_t &smem, int &grid, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
                        int kw, int wmode)
 {
-    if (N <= 0 || C <= 0 || !make_fast_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return false;
+    if (N <= 0 || C <= 0 || sh != 1 || sw != 1) return false;
+    s.N = N, s.Ci = Ci, s.H = H, s.W = W, s.C = C, s.ph = ph, s.pw = pw, s.kh = kh, s.kw = kw, s.wmode = wmode;
+    s.Ho = conv_out(H, ph, kh, 1), s.Wo = conv_out(W, pw, kw, 1);
+    if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return false;
+    s.Hh = (H + 1) / 2, s.Wh = (W + 1) / 2;
+    s.PL = s.Hh * s.Wh;
+    s.CS = 4 * s.PL;
+    s.IS = Ci * s.CS;
     const int I = (s.Ho / 2) * (s.Wo / 2);
     int G = kFastThreads / I;
     if (G < 1) return false;
     if (G > N) G = N;
-    const size_t fixed = sizeof(ChanRec) * kChanBuf;
+    const size_t fixed = sizeof(BwdRec) * kBwdChanBuf;
     while (G > 1 && fixed + 2 * (size_t)G * s.IS * 4 > 110 * 1024) --G;
     smem = fixed + 2 * (size_t)G * s.IS * 4;
     if (smem > 220 * 1024) return false;
     s.G = G;
-    const int bps = smem <= 110 * 1024 ? 2 : 1;
+    if ((N + G - 1) / G > 65535) return false; // the reduce kernel's grid.y
+    // resident blocks per SM: 233472 bytes of shared memory, 1 KiB reserved per block
+    const int bps = 3 * (smem + 1024) <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
     const long long units = (long long)((N + G - 1) / G) * C;
     long long g = 148LL * bps;
     if (g > units) g = units;
@@ -486,38 +584,31 @@ static bool plan_bwd_x(FastShape &s, size_t &smem, int &grid, int N, int Ci, int
 
 size_t clb_convtree_bwd_x_fast_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw)
 {
-    FastShape s;
+    ClsShape s;
     size_t smem;
     int grid;
     if (!plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, 0)) return 0;
     return (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
 }
 
-template <int PWH>
-static int launch_bwd_x_tile(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
-                             float *partial, FastShape s, size_t smem, int grid, cudaStream_t st)
-{
-    auto k = convtree_bwd_x_tile_kernel<PWH>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
-    k<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, partial, s);
-    const size_t total = (size_t)((s.N + s.G - 1) / s.G) * s.G * s.Ci * s.H * s.W;
-    long long rb = (long long)((total + 255) / 256);
-    if (rb > 148 * 16) rb = 148 * 16;
-    convtree_bwd_x_reduce_kernel<<<(unsigned)rb, 256, 0, st>>>(partial, gx, s, grid);
-    return check_launch(2);
-}
-
 int clb_convtree_bwd_x_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
                                 void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
                                 int kh, int kw, int wmode, cudaStream_t st)
 {
-    FastShape s;
+    ClsShape s;
     size_t smem;
     int grid;
     if (amax == nullptr || !plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
     const size_t need = (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
     if (scratch == nullptr || scratch_bytes < need) return CLB_ERR_SHAPE;
-    if (s.pwh == 20) return launch_bwd_x_tile<20>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
-    if (s.pwh == 10) return launch_bwd_x_tile<10>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
-    return launch_bwd_x_tile<0>(gy, x, w, sel, amax, gx, (float *)scratch, s, smem, grid, st);
+    auto k = convtree_bwd_x_cls_kernel;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    k<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, (float *)scratch, s);
+    const int NG = (s.N + s.G - 1) / s.G;
+    const int per_group = s.G * s.Ci * s.H * s.W;
+    int chunks = (per_group + 1023) / 1024;
+    if (chunks > 32) chunks = 32;
+    dim3 rgrid(chunks, NG);
+    convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>((const float *)scratch, gx, s, grid);
+    return check_launch(2);
 }
