@@ -139,8 +139,7 @@ def c2_algorithmic_bytes():
     x = b * ci * s * s * 4
     y = b * c * (s // 2) ** 2 * 4
     w, sel = c * 7 * 16 * 4, c * 8 * 4
-    return {"fwd": x + y + w + sel, "bwd_x": y + x + x + w + sel, "bwd_w": y + x + 2 * w + sel,
-            "step": (x + y + w + sel) + (y + x + x + 2 * w + sel)}
+    return {"fwd": x + y + w + sel, "bwd": y + x + x + 2 * w + sel, "step": (x + y + w + sel) + (y + x + x + 2 * w + sel)}
 
 
 def run_ours(args):
@@ -209,8 +208,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     for name, fn in (
         ("fwd", lambda i: ops.convtree_fwd(xs[i % sets].detach(), w, sel, geom, W_SOFTMAX)),
-        ("bwd_x", lambda i: ops.convtree_bwd_x(gys[i % sets], xs[i % sets].detach(), w, sel, amaxes[i % sets], geom, W_SOFTMAX)),
-        ("bwd_w", lambda i: ops.convtree_bwd_w(gys[i % sets], xs[i % sets].detach(), w, sel, amaxes[i % sets], geom, W_SOFTMAX)),
+        ("bwd", lambda i: ops.convtree_bwd(gys[i % sets], xs[i % sets].detach(), w, sel, amaxes[i % sets], geom, W_SOFTMAX)),
     ):
         for i in range(3):
             fn(i)

@@ -30,6 +30,8 @@ _SIGNATURES = {
     "clb_convtree_fwd": ([_vp] * 8 + _conv + [_i, _i, _vp], _i),
     "clb_convtree_bwd_x_scratch_bytes": (_conv + [_i], _sz),
     "clb_convtree_bwd_x": ([_vp] * 8 + [_i, _i, _vp, _sz] + _conv + [_i, _i, _vp], _i),
+    "clb_convtree_bwd_scratch_bytes": (_conv + [_i, _i, _i], _sz),
+    "clb_convtree_bwd": ([_vp] * 9 + [_i, _i, _vp, _sz] + _conv + [_i, _i, _vp], _i),
     "clb_conv_group_plan": (_conv + [_i, C.POINTER(_i), C.POINTER(_i)], _i),
     "clb_conv_build_groups": ([_vp, _i, _i, _i, _vp, _vp, _i], _i),
     "clb_convtree_bwd_w_scratch_bytes": ([_i, _i, _i, _i, _i], _sz),

@@ -790,3 +790,42 @@ extern "C" int clb_convtree_bwd_w_noalloc(const void *gy, const void *x, const v
     return launch_bwd_w<true>(gy, x, w, sel, amax, gw, scratch, kStaticScratchBytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode,
                               dtype, stream);
 }
+
+// ---- both gradients of the fused block --------------------------------------------------------
+size_t clb_convtree_bwd_fast_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int want_gx,
+                                     int want_gw);
+int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
+                              float *gw, void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph,
+                              int pw, int kh, int kw, int wmode, cudaStream_t st);
+
+extern "C" size_t clb_convtree_bwd_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
+                                                 int want_gx, int want_gw, int dtype)
+{
+    if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return 0;
+    size_t fast = dtype == CLB_F32 ? clb_convtree_bwd_fast_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, want_gx, want_gw) : 0;
+    size_t general = want_gw ? clb_convtree_bwd_w_scratch_bytes(N, C, conv_out(H, ph, kh, sh), conv_out(W, pw, kw, sw), dtype) : 0;
+    return fast > general ? fast : general;
+}
+
+extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx, void *gw,
+                                const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, void *scratch, size_t scratch_bytes,
+                                int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype,
+                                void *stream)
+{
+    if (!gx && !gw) return CLB_ERR_ARG;
+    if (dtype == CLB_F32 && !(wmode & CLB_SEL_UNBOUNDED) && scratch && amax && gy && x && w && sel && N > 0 && C > 0 &&
+        (wmode & 0xff) <= 2 && conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) {
+        const int rc = clb_convtree_bwd_fast_f32((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, (float *)gw,
+                                                 scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, (cudaStream_t)stream);
+        if (rc != CLB_ERR_SHAPE) return rc;
+    }
+    if (gx) {
+        const int rc = launch_bwd_x<true>(gy, x, w, sel, amax, gx, grp_start, grp_list, cg, nb, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw,
+                                          wmode, dtype, stream);
+        if (rc) return rc;
+    }
+    if (gw)
+        return launch_bwd_w<true>(gy, x, w, sel, amax, gw, scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, dtype,
+                                  stream);
+    return CLB_OK;
+}

@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
 // class plane: the data-dependent arg-max costs ~1.7 wavefronts per access instead of ~3 with the
 // forward's row-major layout (which also needs a third more shared memory for its halo).
 // Out-of-image taps are predicated off instead of reading a zero halo.
-constexpr int kBwdChanBuf = 8;
+constexpr int kBwdChanBuf = 6; // sized so that three blocks (two tiles + records + 1 KiB static) fit one SM
 
 struct alignas(16) BwdRec {
     float g[28]; // 7 gates x (k1, ka, kb, kab)
@@ -259,11 +259,34 @@ __device__ __forceinline__ int cls_index(const ClsShape &s, int img, int ch, int
     return img * s.IS + ch * s.CS + ((row & 1) * 2 + (col & 1)) * s.PL + (row >> 1) * s.Wh + (col >> 1);
 }
 
-__global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(const float *__restrict__ gy, const float *__restrict__ x,
-                                                                            const float *__restrict__ w, const int32_t *__restrict__ sel,
-                                                                            const uint8_t *__restrict__ amax, float *__restrict__ gx,
-                                                                            float *__restrict__ partial, ClsShape s)
+// Sum over the 32 lanes of 32 per-lane values at once: lane l returns the warp total of v[l].
+// A butterfly that halves the number of live values at every step (16+8+4+2+1 = 31 shuffles) instead
+// of 32 x 5 for value-by-value reductions.
+__device__ __forceinline__ float warp_reduce_transposed(float (&v)[32], int lane)
 {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    return v[0];
+}
+
+// GX: accumulate and write the input gradient.  GW: write, per (image group, channel), the 28 basis sums
+// of the gate gradient to `wpartial` [groups][C][28]; both share the gate chain recomputed at the arg-max.
+template <bool GX, bool GW>
+__global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+                                                                          const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                          const uint8_t *__restrict__ amax, float *__restrict__ gx,
+                                                                          float *__restrict__ partial, float *__restrict__ wpartial,
+                                                                          ClsShape s)
+{
+    __shared__ float wred[kFastThreads / 32][32];
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdRec *chan = reinterpret_cast<BwdRec *>(smem_raw);
     float *xt = reinterpret_cast<float *>(smem_raw + sizeof(BwdRec) * kBwdChanBuf);
@@ -286,7 +309,8 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(con
     const bool has_window = img < s.G;
     const int toff = 4 * (img * s.IS + py * s.Wh + px);
 
-    for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
+    if (GX)
+        for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
 
     auto stage = [&](int n0, int nimg) {
         const int total = nimg * s.Ci * HW;
@@ -344,7 +368,7 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(con
         const int n0 = grp * s.G;
         __syncthreads();
         if (grp != cur_group) {
-            if (cur_group >= 0) flush(cur_group);
+            if (GX && cur_group >= 0) flush(cur_group);
             cur_group = grp;
             stage(n0, min(s.G, s.N - n0));
         }
@@ -391,6 +415,9 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(con
             }
             int addr[8];
             float tg[8];
+            float bs[32]; // 28 basis products of this window (GW), padded to a power of two
+#pragma unroll
+            for (int i = 0; i < 32; ++i) bs[i] = 0.f;
             unsigned ok = 0;
             if (live) {
                 const int dyi = bd >> 1, dxi = bd & 1;
@@ -422,20 +449,67 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_x_cls_kernel(con
                 tg[2] = dg1 * gate_da<float>(g[1], a[3]), tg[3] = dg1 * gate_db<float>(g[1], a[2]);
                 tg[4] = dg2 * gate_da<float>(g[2], a[5]), tg[5] = dg2 * gate_db<float>(g[2], a[4]);
                 tg[6] = dg3 * gate_da<float>(g[3], a[7]), tg[7] = dg3 * gate_db<float>(g[3], a[6]);
-            }
+                if (GW) {
+                    const float dgp[4] = {dg0, dg1, dg2, dg3};
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if ((ok >> k) & 1u) {
-                    float *cell = reinterpret_cast<float *>(gtb + addr[k]);
-                    *cell += tg[k];
+                    for (int p = 0; p < 4; ++p) {
+                        bs[4 * p] = dgp[p] * (a[2 * p] * a[2 * p + 1]), bs[4 * p + 1] = dgp[p] * a[2 * p];
+                        bs[4 * p + 2] = dgp[p] * a[2 * p + 1], bs[4 * p + 3] = dgp[p];
+                    }
+                    bs[16] = dt0 * (g0 * g1), bs[17] = dt0 * g0, bs[18] = dt0 * g1, bs[19] = dt0;
+                    bs[20] = dt1 * (g2 * g3), bs[21] = dt1 * g2, bs[22] = dt1 * g3, bs[23] = dt1;
+                    bs[24] = dz * (t0 * t1), bs[25] = dz * t0, bs[26] = dz * t1, bs[27] = dz;
                 }
+            }
+            if (GW) {
+                // block total of the 28 basis sums of this (group, channel): warps first, then 8 -> 1 by warp 0
+                const float tot = warp_reduce_transposed(bs, tid & 31);
+                if (!GX) __syncthreads(); // the previous channel's cross-warp read is over
+                wred[tid >> 5][tid & 31] = tot;
+            }
+            if (GX) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if ((ok >> k) & 1u) {
+                        float *cell = reinterpret_cast<float *>(gtb + addr[k]);
+                        *cell += tg[k];
+                    }
+                    __syncthreads();
+                    if (GW && k == 0 && tid < 28) {
+                        float t = 0.f;
+#pragma unroll
+                        for (int wv = 0; wv < kFastThreads / 32; ++wv) t += wred[wv][tid];
+                        wpartial[((size_t)grp * s.C + c0 + cc) * 28 + tid] = t;
+                    }
+                }
+            } else if (GW) {
                 __syncthreads();
+                if (tid < 28) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int wv = 0; wv < kFastThreads / 32; ++wv) t += wred[wv][tid];
+                    wpartial[((size_t)grp * s.C + c0 + cc) * 28 + tid] = t;
+                }
             }
         }
         u0 += cnt;
     }
     __syncthreads();
-    flush(cur_group);
+    if (GX) flush(cur_group);
+}
+
+// Adds the per-group basis sums in group order and turns them into the 16 gradients of every gate.
+__global__ void convtree_gw_finalize_kernel(const float *__restrict__ wpartial, const float *__restrict__ w, float *__restrict__ gw,
+                                            int groups, int ngates, int wmode)
+{
+    const int gi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= ngates) return;
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < groups; ++p) {
+        const float4 q = *reinterpret_cast<const float4 *>(wpartial + ((size_t)p * ngates + gi) * 4);
+        sums[0] += q.x, sums[1] += q.y, sums[2] += q.z, sums[3] += q.w;
+    }
+    gate_grad_store<float>(sums, w + (size_t)gi * 16, wmode, gw + (size_t)gi * 16);
 }
 
 // gx of every group that no single block covered = sum of that group's partial tiles, in block order.
@@ -574,7 +648,7 @@ static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int 
     s.G = G;
     if ((N + G - 1) / G > 65535) return false; // the reduce kernel's grid.y
     // resident blocks per SM: 233472 bytes of shared memory, 1 KiB reserved per block
-    const int bps = 3 * (smem + 1024) <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
+    const int bps = 3 * (smem + 2048) <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
     const long long units = (long long)((N + G - 1) / G) * C;
     long long g = 148LL * bps;
     if (g > units) g = units;
@@ -588,27 +662,72 @@ size_t clb_convtree_bwd_x_fast_scratch(int N, int Ci, int H, int W, int C, int s
     size_t smem;
     int grid;
     if (!plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, 0)) return 0;
-    return (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
+    return 16 + (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
+}
+
+// Combined fast backward: gx and/or gw (either may be NULL).  Scratch layout:
+// [partial gradient tiles: grid*2*G*Ci*H*W floats, only when gx][per-group basis sums: groups*C*28 floats, only when gw].
+size_t clb_convtree_bwd_fast_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int want_gx,
+                                     int want_gw)
+{
+    ClsShape s;
+    size_t smem;
+    int grid;
+    if (!plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, 0)) return 0;
+    size_t bytes = 16;
+    if (want_gx) bytes += (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
+    if (want_gw) bytes += (size_t)((N + s.G - 1) / s.G) * C * 28 * sizeof(float);
+    return bytes;
+}
+
+int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
+                              float *gw, void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph,
+                              int pw, int kh, int kw, int wmode, cudaStream_t st)
+{
+    ClsShape s;
+    size_t smem;
+    int grid;
+    if (amax == nullptr || (!gx && !gw) || !plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
+    const size_t need = clb_convtree_bwd_fast_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, gx != nullptr, gw != nullptr);
+    if (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 15)) return CLB_ERR_SHAPE;
+    const int NG = (s.N + s.G - 1) / s.G;
+    float *tiles = (float *)scratch;
+    const size_t tile_floats = gx ? (size_t)grid * 2 * s.G * Ci * H * W : 0;
+    float *wpartial = tiles + ((tile_floats + 3) / 4) * 4;
+    auto launch = [&](auto kern) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        kern<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s);
+        return true;
+    };
+    bool ok;
+    if (gx && gw)
+        ok = launch(convtree_bwd_cls_kernel<true, true>);
+    else if (gx)
+        ok = launch(convtree_bwd_cls_kernel<true, false>);
+    else
+        ok = launch(convtree_bwd_cls_kernel<false, true>);
+    if (!ok) return check_launch(0);
+    int launched = 1;
+    if (gx) {
+        const int per_group = s.G * s.Ci * s.H * s.W;
+        int chunks = (per_group + 1023) / 1024;
+        if (chunks > 32) chunks = 32;
+        dim3 rgrid(chunks, NG);
+        convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, gx, s, grid);
+        ++launched;
+    }
+    if (gw) {
+        const int ngates = C * 7;
+        convtree_gw_finalize_kernel<<<(ngates + 63) / 64, 64, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
+        ++launched;
+    }
+    return check_launch(launched);
 }
 
 int clb_convtree_bwd_x_fast_f32(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *gx,
                                 void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
                                 int kh, int kw, int wmode, cudaStream_t st)
 {
-    ClsShape s;
-    size_t smem;
-    int grid;
-    if (amax == nullptr || !plan_bwd_x(s, smem, grid, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
-    const size_t need = (size_t)grid * 2 * s.G * Ci * H * W * sizeof(float);
-    if (scratch == nullptr || scratch_bytes < need) return CLB_ERR_SHAPE;
-    auto k = convtree_bwd_x_cls_kernel;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
-    k<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, (float *)scratch, s);
-    const int NG = (s.N + s.G - 1) / s.G;
-    const int per_group = s.G * s.Ci * s.H * s.W;
-    int chunks = (per_group + 1023) / 1024;
-    if (chunks > 32) chunks = 32;
-    dim3 rgrid(chunks, NG);
-    convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>((const float *)scratch, gx, s, grid);
-    return check_launch(2);
+    return clb_convtree_bwd_fast_f32(gy, x, w, sel, amax, gx, nullptr, scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw,
+                                     wmode, st);
 }

@@ -57,11 +57,11 @@ class FullConvLogicFunction(Function):
     def backward(ctx, grad_y, *unused):
         x, w, sel, amax = ctx.saved_tensors
         grad_y = grad_y.contiguous()
+        need_gx = ctx.needs_input_grad[0]
+        need_gw = ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX
         gx = gw = None
-        if ctx.needs_input_grad[0]:
-            gx = ops.convtree_bwd_x(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode)
-        if ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX:
-            gw = ops.convtree_bwd_w(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode)
+        if need_gx or need_gw:
+            gx, gw = ops.convtree_bwd(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode, need_gx, need_gw)
         return (gx, gw) + (None,) * 10
 
 

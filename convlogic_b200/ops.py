@@ -117,6 +117,26 @@ def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
     return gx
 
 
+def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
+    """Both gradients of the fused block in one C-ABI call; returns (gx or None, gw or None)."""
+    check_input(gy, x, w, sel)
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    gx = torch.empty_like(x) if need_gx else None
+    gw = torch.empty_like(w) if need_gw else None
+    flag = _sel_flag(sel, geom)
+    nbytes = lib().clb_convtree_bwd_scratch_bytes(n, ci, h, wd, c, *geom, int(need_gx), int(need_gw), dtype_code(x))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    if need_gx:
+        start, lst, cg, nb = conv_groups(sel, tuple(x.shape), geom, x.dtype)
+    else:
+        start = lst = None
+        cg = nb = 1
+    check(lib().clb_convtree_bwd(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(gw), ptr(start), ptr(lst),
+                                 cg, nb, ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode | flag, dtype_code(x), stream()))
+    return gx, gw
+
+
 def convtree_bwd_w(gy, x, w, sel, amax, geom, wmode):
     check_input(gy, x, w, sel)
     n, ci, h, wd = x.shape

@@ -93,6 +93,20 @@ int clb_convtree_bwd_x(const void *gy, const void *x, const void *w, const int32
                        size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw,
                        int kh, int kw, int wmode, int dtype, void *stream);
 
+/* Both gradients of the fused block in one call (either output may be NULL).  For the fp32 shapes
+ * the tiled kernels cover, one kernel recomputes the gate chain at the arg-max once and produces the
+ * input gradient and the per-image-group basis sums of the gate gradient together; other shapes run
+ * clb_convtree_bwd_x / clb_convtree_bwd_w one after the other.  scratch: clb_convtree_bwd_scratch_bytes()
+ * (16-byte aligned); amax is required for the combined kernel (NULL falls back to the separate ones).
+ * Stands in for the pair full_convlogic_backward_x + full_convlogic_backward_weight that the
+ * reference's autograd Function calls back to back (src/convlogic/convlogic_layer.py:71-82). */
+size_t clb_convtree_bwd_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                                      int kw, int want_gx, int want_gw, int dtype);
+int clb_convtree_bwd(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx,
+                     void *gw, const int32_t *grp_start, const int32_t *grp_list, int cg, int nb, void *scratch,
+                     size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
+                     int kw, int wmode, int dtype, void *stream);
+
 /* Host-side helpers for the tables above (pure CPU, no CUDA call).
  * clb_conv_group_plan: picks cg (channels per group) and nb (images per thread block) for a shape.
  * clb_conv_build_groups: sel_host int32 [C,8] in host memory -> grp_start [G+1], grp_list (capacity

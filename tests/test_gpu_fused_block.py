@@ -285,6 +285,14 @@ def test_tiled_input_gradient_equals_general(shape):
     g_gen = ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX, use_scratch=False)
     assert_close(g_fast, g_gen, 2e-6)
     assert torch.equal(g_fast, ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX))
+    # the combined kernel (one arg-max recompute for both gradients) against the separate ones
+    gx_c, gw_c = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX)
+    assert torch.equal(gx_c, g_fast)
+    assert_close(gw_c, ops.convtree_bwd_w(gd, xd, wd, sd, amax, geom, W_SOFTMAX), 2e-5)
+    _, gw_only = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX, need_gx=False)
+    assert torch.equal(gw_only, gw_c)
+    gx_only, none = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX, need_gw=False)
+    assert none is None and torch.equal(gx_only, g_fast)
     if x.shape[0] <= 40 and shape[2] <= 64:
         xo = x.clone().requires_grad_(True)
         yo, _, _, idxo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])
