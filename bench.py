@@ -313,6 +313,237 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------- secondary workloads
+def _timed(fn, steps, warmup, world, dev):
+    """CUDA-event time of `steps` calls of fn(i) after `warmup` calls; max over ranks; returns ms."""
+    import torch.distributed as dist
+
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def _finish(out, world):
+    import torch.distributed as dist
+
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_c3(args):
+    """cifar10_m-shaped full training step: soft forward, cross-entropy, backward, Adam(lr 0.01); batch 256
+    per GPU; data-parallel with one all-reduce of the flat gate-logit gradient bucket."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib, dp
+
+    world, rank, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    net = cb.ConvLogicCifarModel(k_param=256, input_channels=9, input_size=32, tau=40).network
+    g = torch.Generator().manual_seed(1)
+    for prm in net.parameters():
+        prm.data = torch.randn(*prm.shape, generator=g)
+    net = net.to(dev).train()
+    bucket = dp.GradBucket(net)
+    opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
+    sets = 4
+    gi = torch.Generator().manual_seed(100 + rank)
+    xs_h = [(torch.rand(256, 9, 32, 32, generator=gi) < 0.5).float().pin_memory() for _ in range(sets)]
+    ls_h = [torch.randint(0, 10, (256,), generator=gi).pin_memory() for _ in range(sets)]
+    xs, ls = [x.to(dev) for x in xs_h], [l.to(dev) for l in ls_h]
+    loss_host = torch.zeros(1).pin_memory()
+
+    def step(i, host=False):
+        x = xs_h[i % sets].to(dev, non_blocking=True) if host else xs[i % sets]
+        lab = ls_h[i % sets].to(dev, non_blocking=True) if host else ls[i % sets]
+        bucket.zero()
+        loss = torch.nn.functional.cross_entropy(net(x), lab)
+        loss.backward()
+        bucket.allreduce(average=True)
+        opt.step()
+        if host:
+            loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+
+    lib = _lib.lib()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = lib.clb_kernel_launches()
+    ms = _timed(step, args.steps, args.warmup, world, dev)
+    launches = (lib.clb_kernel_launches() - l0) * args.steps // (args.steps + args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = _timed(lambda i: step(i, host=True), args.steps, 3, world, dev)
+    imgs = 256 * world * args.steps
+    peak, kind = measured_peaks()
+    step_bytes = 15.80e6 * 256 + 0.47e9  # algorithmic bytes of one step (activations + parameter/Adam traffic)
+    _finish({
+        "metric": "train imgs/sec (fwd+bwd+Adam), cifar10_m-shaped LogicTreeNet", "value": imgs / (ms * 1e-3), "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c3: cifar10_m-shaped stack (k=256, tau=40), 9x32x32 Bernoulli(0.5) bits, batch 256 per GPU, Adam lr 0.01",
+                   "l2": "activations of one step (~1.5 GB) exceed the 126 MB L2", "parameters": bucket.numel,
+                   "parallelism": f"dp{world}, one all-reduce of {bucket.numel * 4 / 1e6:.1f} MB per step" if world > 1 else "single GPU"},
+        "e2e": {"value": imgs / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": 256 * 9 * 32 * 32 * 4 + 256 * 8,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": step_bytes / (ms / args.steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": step_bytes / (ms / args.steps * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
+                     "note": "whole step, algorithmic bytes 4.52 GB"},
+        "clocks": clocks}, world)
+
+
+def run_c4(args):
+    """cifar10_l-shaped discretised inference on bit-packed activations (64 images per word), the batch of
+    2^20 images sharded over the ranks and streamed in chunks; no collective."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib, dp, ops
+
+    world, rank, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    net = cb.ConvLogicCifarModel(k_param=1024, input_channels=93, input_size=32, tau=340).network
+    g = torch.Generator().manual_seed(1)
+    for prm in net.parameters():
+        prm.data = torch.randn(*prm.shape, generator=g)
+    net = net.to(dev).eval()
+    total = args.images
+    lo, hi = dp.shard_range(total, rank, world)
+    chunk = args.chunk
+    n_chunks = (hi - lo + chunk - 1) // chunk
+    resident = min(n_chunks, 16)  # 16 packed chunks of 8192 images = 1.6 GB, far beyond L2
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    th = (torch.arange(1, 32, device=dev, dtype=torch.float32) / 32).view(1, 31, 1, 1, 1)
+    packed = []
+    for _ in range(resident):
+        px = torch.rand(chunk, 3, 32, 32, device=dev, generator=gen)
+        bits = (px.unsqueeze(1) > th).reshape(chunk, 93, 32, 32)  # channel 3*(i-1)+c holds pixel[c] > i/32
+        packed.append(cb.PackBitsTensor(bits, 64))
+        del px, bits
+    host = [p.t.cpu().pin_memory() for p in packed[:2]]
+
+    def infer(i, from_host=False):
+        with torch.no_grad():
+            if from_host:
+                t = host[i % 2].to(dev, non_blocking=True)
+                p = cb.PackBitsTensor.from_packed(t, 0)
+            else:
+                p = packed[i % resident]
+            counts = net(p)
+            return counts.argmax(-1)
+
+    def step(i, from_host=False):
+        out = None
+        for j in range(n_chunks):
+            out = infer(i * n_chunks + j, from_host)
+        if from_host:
+            out.cpu()
+
+    lib = _lib.lib()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = lib.clb_kernel_launches()
+    steps = max(1, min(args.steps, 5))
+    ms = _timed(step, steps, 1, world, dev)
+    launches = (lib.clb_kernel_launches() - l0) * steps // (steps + 1)
+    clocks = sampler.stop() if rank == 0 else None
+    # per-layer times of one chunk
+    layer_ms = []
+    with torch.no_grad():
+        h = packed[0]
+        for m in net:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            o = m(h)
+            e1.record()
+            torch.cuda.synchronize()
+            layer_ms.append(round(e0.elapsed_time(e1), 4))
+            h = o
+    ms_e2e = _timed(lambda i: step(i, True), 1, 1, world, dev)
+    imgs = total * steps
+    peak, kind = measured_peaks()
+    alg = 1388200.0 * total / world  # layer-by-layer algorithmic bytes per image, per rank and step
+    _finish({
+        "metric": "packed-inference imgs/sec, cifar10_l-shaped LogicTreeNet", "value": imgs / (ms * 1e-3), "unit": "images/s",
+        "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": {"workload": f"c4: cifar10_l-shaped stack (k=1024), {total} images of 93x32x32 thermometer bits, 64 per word, "
+                               f"chunks of {chunk}", "l2": f"{resident} resident packed chunks (~{resident * 93 * 1024 * chunk / 8 / 1e9:.1f} GB)",
+                   "parallelism": f"batch sharded over {world} ranks, no collective"},
+        "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": 93 * 1024 * (hi - lo) // 8,
+                "d2h_bytes_per_step": (hi - lo) * 8},
+        "gpu_launches": int(launches), "layer_ms_per_chunk": layer_ms,
+        "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
+                     "note": "whole pipeline, 1 388 200 algorithmic bytes per image"},
+        "clocks": clocks}, world)
+
+
+def run_c5(args):
+    """Flat difflogic stack: 3072 -> 8 x 256000 LogicLayers -> GroupSum(10, tau=100), batch 1024, fwd + bwd."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib
+
+    world, rank, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    dims = [3072] + [256000] * 8
+    net = torch.nn.Sequential(*[cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])], cb.GroupSum(10, 100.0)).to(dev).train()
+    gi = torch.Generator().manual_seed(100 + rank)
+    x = (torch.rand(1024, 3072, generator=gi) < 0.5).float().to(dev)
+    gy = torch.randn(1024, 10, generator=gi).to(dev)
+
+    def step(i):
+        for prm in net.parameters():
+            prm.grad = None
+        net(x).backward(gy)
+        if world > 1:
+            from convlogic_b200 import dp
+            dp.allreduce_gate_gradients(net)
+
+    lib = _lib.lib()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    steps = max(1, min(args.steps, 20))
+    l0 = lib.clb_kernel_launches()
+    ms = _timed(step, steps, 3, world, dev)
+    launches = (lib.clb_kernel_launches() - l0) * steps // (steps + 3)
+    clocks = sampler.stop() if rank == 0 else None
+    peak, kind = measured_peaks()
+    alg = 39.9e9
+    _finish({
+        "metric": "train samples/sec (fwd+bwd), flat difflogic stack", "value": 1024 * world * steps / (ms * 1e-3), "unit": "samples/s",
+        "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c5: 8 LogicLayers 3072->256000x8 + GroupSum(10, tau=100), batch 1024, fwd+bwd",
+                   "l2": "every activation is 1.05 GB (> 126 MB L2)"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
+                     "note": "whole step, 39.9 GB algorithmic"},
+        "clocks": clocks}, world)
+
+
 # ---------------------------------------------------------------------------------- CPU baseline
 def cpu_baseline_c2(sample_batch, passes):
     """The CPU oracle (port of the reference's Python path) on `sample_batch` images of workload c2."""
@@ -371,7 +602,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--images", type=int, default=1 << 20, help="c4: total images")
+    ap.add_argument("--chunk", type=int, default=8192, help="c4: images per streamed chunk")
     ap.add_argument("--cpu-sample", type=int, default=32)
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -379,7 +612,7 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     else:
-        run_ours(args)
+        {"c2": run_ours, "c3": run_c3, "c4": run_c4, "c5": run_c5}[args.workload](args)
 
 
 if __name__ == "__main__":
