@@ -249,6 +249,78 @@ __global__ void __launch_bounds__(256) packed_convtree_kernel(const U *__restric
     }
 }
 
+// 16-byte variant for rows that are a multiple of 16 bytes (the usual case: 64-bit words, batches that
+// are a multiple of 128).  One thread produces one uint4 (128 samples) of one pooled output.  Everything
+// block-uniform (the 7 gates as 32-bit multiplexer masks, the 8 tap offsets) sits in registers; a window
+// whose 4 x 8 taps all fall inside the image takes a path without bounds tests; indices are 32-bit.
+struct Masks32 {
+    unsigned m00, m01, m10, m11;
+};
+__device__ __forceinline__ unsigned mux32(const Masks32 &m, unsigned a, unsigned b)
+{
+    const unsigned r1 = (b & m.m11) | (~b & m.m10);
+    const unsigned r0 = (b & m.m01) | (~b & m.m00);
+    return (a & r1) | (~a & r0);
+}
+__device__ __forceinline__ uint4 mux128(const Masks32 &m, const uint4 &a, const uint4 &b)
+{
+    return make_uint4(mux32(m, a.x, b.x), mux32(m, a.y, b.y), mux32(m, a.z, b.z), mux32(m, a.w, b.w));
+}
+
+__global__ void __launch_bounds__(256) packed_convtree_v4_kernel(const uint4 *__restrict__ x, const uint8_t *__restrict__ ops,
+                                                                 const int32_t *__restrict__ sel, uint4 *__restrict__ y, PackedShape s,
+                                                                 int units)
+{
+    const int c = blockIdx.y;
+    Masks32 gm[7];
+#pragma unroll
+    for (int g = 0; g < 7; ++g) {
+        const int op = ops[c * 7 + g];
+        gm[g].m00 = (op & 8) ? ~0u : 0u, gm[g].m01 = (op & 4) ? ~0u : 0u, gm[g].m10 = (op & 2) ? ~0u : 0u, gm[g].m11 = (op & 1) ? ~0u : 0u;
+    }
+    int tb[8], tdy[8], tdx[8]; // tap: element offset (in units) relative to the position, row / col displacement
+    int ymin = 0, ymax = 0, xmin = 0, xmax = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const Tap t = unpack_tap(sel[c * 8 + k], s.ph, s.pw);
+        tdy[k] = t.dy, tdx[k] = t.dx;
+        tb[k] = ((t.ch * s.H + t.dy) * s.W + t.dx) * units;
+        ymin = min(ymin, t.dy), ymax = max(ymax, t.dy), xmin = min(xmin, t.dx), xmax = max(xmax, t.dx);
+    }
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2;
+    const int total = Hp * Wp * units;
+    const int rowstep = s.sh * s.W * units, colstep = s.sw * units;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int win = i / units, u = i - win * units;
+        const int py = win / Wp, px = win - py * Wp;
+        const int oy0 = 2 * py * s.sh, ox0 = 2 * px * s.sw;
+        const int p0 = (oy0 * s.W + ox0) * units + u; // first position of the window
+        const bool interior = oy0 + ymin >= 0 && oy0 + s.sh + ymax < s.H && ox0 + xmin >= 0 && ox0 + s.sw + xmax < s.W;
+        uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const int pd = p0 + ((d >> 1) ? rowstep : 0) + ((d & 1) ? colstep : 0);
+            uint4 a[8];
+            if (interior) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) a[k] = __ldg(x + (pd + tb[k]));
+            } else {
+                const int oy = oy0 + (d >> 1) * s.sh, ox = ox0 + (d & 1) * s.sw;
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    a[k] = ((unsigned)(oy + tdy[k]) < (unsigned)s.H && (unsigned)(ox + tdx[k]) < (unsigned)s.W) ? __ldg(x + (pd + tb[k]))
+                                                                                                              : make_uint4(0u, 0u, 0u, 0u);
+            }
+            const uint4 g0 = mux128(gm[0], a[0], a[1]), g1 = mux128(gm[1], a[2], a[3]);
+            const uint4 g2 = mux128(gm[2], a[4], a[5]), g3 = mux128(gm[3], a[6], a[7]);
+            const uint4 t0 = mux128(gm[4], g0, g1), t1 = mux128(gm[5], g2, g3);
+            const uint4 z = mux128(gm[6], t0, t1);
+            acc.x |= z.x, acc.y |= z.y, acc.z |= z.z, acc.w |= z.w;
+        }
+        y[(c * Hp * Wp + win) * units + u] = acc;
+    }
+}
+
 } // namespace clb
 
 using namespace clb;
@@ -345,7 +417,15 @@ extern "C" int clb_packed_convtree(const void *x, const uint8_t *ops, const int3
     if (C == 0 || rowbytes == 0) return CLB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const long long wins = (long long)(s.Ho / 2) * (s.Wo / 2);
-    if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
+    const long long in_units16 = (long long)Ci * H * W * (rowbytes / 16), out_units16 = (long long)C * wins * (rowbytes / 16);
+    if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16) && in_units16 < (1LL << 30) && out_units16 < (1LL << 30)) {
+        const int units = (int)(rowbytes / 16);
+        long long gx = (wins * units + 255) / 256;
+        const long long cap = (148LL * 32 + C - 1) / C;
+        if (gx > cap) gx = cap;
+        dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
+        packed_convtree_v4_kernel<<<grid, 256, 0, st>>>((const uint4 *)x, ops, sel, (uint4 *)y, s, units);
+    } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         long long gx = (wins * units + 255) / 256;
         const long long cap = (148LL * 32 + C - 1) / C;
