@@ -38,6 +38,9 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 C2 = dict(batch=256, cin=9, cout=256, size=32)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two c2 kernels, from the ncu captures
+# summarised in profiles/convtree_fwd_tile_c2.md and profiles/convtree_bwd_cls_c2.md
+NCU_TRAFFIC = {"fwd": 37.4e6, "bwd": 104.6e6}
 
 
 # ------------------------------------------------------------------------------------------ utils
@@ -302,7 +305,7 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "kernel_ms": {k: round(v, 5) for k, v in kern_ms.items()},
         "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "algorithmic_bytes": alg[top], "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "algorithmic_bytes": alg[top], "traffic": NCU_TRAFFIC.get(top),
                      "step_frac": alg["step"] / (ms / args.steps * 1e-3) / 1e9 / peak},
         "clocks": clocks,
     }
