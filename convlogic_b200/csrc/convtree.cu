@@ -279,6 +279,141 @@ __global__ void __launch_bounds__(256) conv_bwd_x_kernel(const T *__restrict__ g
     }
 }
 
+// Faster variant of the kernel above for the fused block in fp32 with the arg-max available and at most
+// 256 (image, window) items per block, i.e. the layers behind the first one of a stack (many input
+// channels, small images).  Differences: a thread keeps one (image, window) for its whole life; the
+// gates and taps of the next few listed channels are prepared by all threads at once instead of one
+// channel at a time; gy / arg-max are fetched one channel ahead; the gradient tile uses the
+// parity-class layout (see convtree_fast.cu) so that arg-max dependent addresses spread over the banks.
+// Same accumulation order as above: deterministic, no atomics.
+constexpr int kGrpBatch = 8;
+
+struct alignas(16) GrpRec {
+    float g[28];
+    int xoff[8];  // channel * H * W
+    int ty[8];    // tap row / col displacement (pad subtracted)
+    int tx[8];
+    int goff[8];  // local channel * 4 * PL inside the block's gradient tile, or -1 when the tap's channel is not in the group
+};
+
+__global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+                                                                    const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                    const uint8_t *__restrict__ amax, float *__restrict__ gx,
+                                                                    const int32_t *__restrict__ grp_start,
+                                                                    const int32_t *__restrict__ grp_list, int cg, int nb, ConvShape s,
+                                                                    int wmode)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    GrpRec *rec = reinterpret_cast<GrpRec *>(smem_raw);
+    float *tile = reinterpret_cast<float *>(smem_raw + sizeof(GrpRec) * kGrpBatch);
+
+    const int HW = s.H * s.W, Hh = (s.H + 1) / 2, Wh = (s.W + 1) / 2, PL = Hh * Wh;
+    const int Wp = s.Wo / 2, I = (s.Ho / 2) * Wp;
+    const int tid = threadIdx.x;
+    const int g = blockIdx.y, n0 = blockIdx.x * nb;
+    const int nimg = min(nb, s.N - n0);
+    const int ch0 = g * cg;
+    const int tile_elems = nb * cg * 4 * PL;
+    for (int i = tid; i < tile_elems; i += blockDim.x) tile[i] = 0.f;
+
+    const int img = tid / I, win = tid - img * I;
+    const bool live = img < nimg;
+    const int py = win / Wp, px = win - py * Wp;
+    const int n = n0 + img;
+    const float *ximg = x + (size_t)n * s.Ci * HW;
+    float *timg = tile + img * cg * 4 * PL;
+    const size_t obase = ((size_t)n * s.C) * I + win; // + c * I
+
+    const int lo = grp_start[g], hi = grp_start[g + 1];
+    for (int l0 = lo; l0 < hi; l0 += kGrpBatch) {
+        const int cnt = min(kGrpBatch, hi - l0);
+        __syncthreads(); // the previous batch's records are no longer read
+        for (int i = tid; i < cnt * 7; i += blockDim.x) {
+            const int e = i / 7, gi = i - e * 7;
+            const Gate<float> gt = gate_load<float>(w + ((size_t)grp_list[l0 + e] * 7 + gi) * 16, wmode);
+            float *o = rec[e].g + gi * 4;
+            o[0] = gt.k1, o[1] = gt.ka, o[2] = gt.kb, o[3] = gt.kab;
+        }
+        for (int i = tid; i < cnt * 8; i += blockDim.x) {
+            const int e = i >> 3, k = i & 7;
+            const Tap tp = unpack_tap(sel[grp_list[l0 + e] * 8 + k], s.ph, s.pw);
+            rec[e].xoff[k] = tp.ch * HW;
+            rec[e].ty[k] = tp.dy;
+            rec[e].tx[k] = tp.dx;
+            const int chl = tp.ch - ch0;
+            rec[e].goff[k] = (chl >= 0 && chl < cg) ? chl * 4 * PL : -1;
+        }
+        __syncthreads();
+
+        float dz_next = 0.f;
+        int bd_next = 0;
+        if (live) {
+            const size_t o = obase + (size_t)grp_list[l0] * I;
+            dz_next = __ldg(gy + o);
+            bd_next = amax[o];
+        }
+        for (int e = 0; e < cnt; ++e) {
+            const float dz = dz_next;
+            const int bd = bd_next;
+            if (live && e + 1 < cnt) {
+                const size_t o = obase + (size_t)grp_list[l0 + e + 1] * I;
+                dz_next = __ldg(gy + o);
+                bd_next = amax[o];
+            }
+            const GrpRec &r = rec[e];
+            float tg[8];
+            int cell[8];
+            if (live) {
+                const int oy = (2 * py + (bd >> 1)) * s.sh, ox = (2 * px + (bd & 1)) * s.sw;
+                float a[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int iy = oy + r.ty[k], ix = ox + r.tx[k];
+                    const bool v = (unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W;
+                    a[k] = v ? __ldg(ximg + r.xoff[k] + iy * s.W + ix) : 0.f;
+                    const int go = r.goff[k];
+                    cell[k] = (v && go >= 0) ? go + ((iy & 1) * 2 + (ix & 1)) * PL + (iy >> 1) * Wh + (ix >> 1) : -1;
+                }
+                Gate<float> gg[7];
+                const float4 *gp = reinterpret_cast<const float4 *>(r.g);
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const float4 q = gp[i];
+                    gg[i].k1 = q.x, gg[i].ka = q.y, gg[i].kb = q.z, gg[i].kab = q.w;
+                }
+                const float g0 = gate_eval<float>(gg[0], a[0], a[1]), g1 = gate_eval<float>(gg[1], a[2], a[3]);
+                const float g2 = gate_eval<float>(gg[2], a[4], a[5]), g3 = gate_eval<float>(gg[3], a[6], a[7]);
+                const float t0 = gate_eval<float>(gg[4], g0, g1), t1 = gate_eval<float>(gg[5], g2, g3);
+                const float dt0 = dz * gate_da<float>(gg[6], t1), dt1 = dz * gate_db<float>(gg[6], t0);
+                const float dg0 = dt0 * gate_da<float>(gg[4], g1), dg1 = dt0 * gate_db<float>(gg[4], g0);
+                const float dg2 = dt1 * gate_da<float>(gg[5], g3), dg3 = dt1 * gate_db<float>(gg[5], g2);
+                tg[0] = dg0 * gate_da<float>(gg[0], a[1]), tg[1] = dg0 * gate_db<float>(gg[0], a[0]);
+                tg[2] = dg1 * gate_da<float>(gg[1], a[3]), tg[3] = dg1 * gate_db<float>(gg[1], a[2]);
+                tg[4] = dg2 * gate_da<float>(gg[2], a[5]), tg[5] = dg2 * gate_db<float>(gg[2], a[4]);
+                tg[6] = dg3 * gate_da<float>(gg[3], a[7]), tg[7] = dg3 * gate_db<float>(gg[3], a[6]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (r.goff[k] >= 0) { // block-uniform: taps outside the group cost no barrier
+                    if (live && cell[k] >= 0) timg[cell[k]] += tg[k];
+                    __syncthreads();
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int nch = min(cg, s.Ci - ch0);
+    for (int i = tid; i < nimg * nch * HW; i += blockDim.x) {
+        const int col = i % s.W;
+        int q = i / s.W;
+        const int row = q % s.H;
+        q /= s.H;
+        const int chl = q % nch, im = q / nch;
+        gx[((size_t)(n0 + im) * s.Ci + ch0 + chl) * HW + row * s.W + col] =
+            tile[(im * cg + chl) * 4 * PL + ((row & 1) * 2 + (col & 1)) * PL + (row >> 1) * Wh + (col >> 1)];
+    }
+}
+
 // ---------------------------------------------------------------------------- backward: gate grad
 // grid (parts, C).  Block `part` covers items [part*per, (part+1)*per) of the N*items range of channel c.
 template <typename T, bool FUSED>
@@ -535,7 +670,7 @@ extern "C" int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, vo
 }
 
 // ---- input gradient ---------------------------------------------------------------------------
-static const size_t kTileBudget = 96 * 1024;   // lets two blocks share one SM
+static const size_t kTileBudget = 64 * 1024;   // lets three blocks share one SM
 static const size_t kTileBudgetMax = 200 * 1024;
 
 extern "C" int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int dtype,
@@ -544,13 +679,14 @@ extern "C" int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, i
     if (!cg || !nb || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
     if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_ARG;
     const size_t esz = dtype == CLB_F32 ? 4 : 8;
-    const size_t hw = (size_t)H * W;
+    const size_t hw = (size_t)4 * ((H + 1) / 2) * ((W + 1) / 2); // parity-class planes round odd sizes up
     const int Ho = conv_out(H, ph, kh, sh), Wo = conv_out(W, pw, kw, sw);
     if (Ho <= 0 || Wo <= 0) return CLB_ERR_SHAPE;
     if (hw * esz > kTileBudgetMax) return CLB_ERR_SHAPE; // one channel plane must fit in shared memory
     // images per block: enough (image, window) items for 256 threads when windows are few
+    // as many whole images as give at most 256 (image, window) items: a thread then keeps its item
     long long items = (long long)((Ho + 1) / 2) * ((Wo + 1) / 2);
-    int n_b = (int)((256 + items - 1) / items);
+    int n_b = (int)(256 / items);
     if (n_b < 1) n_b = 1;
     if (n_b > (N > 0 ? N : 1)) n_b = N > 0 ? N : 1;
     while (n_b > 1 && (size_t)n_b * hw * esz > kTileBudget) --n_b;
@@ -609,6 +745,18 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
     if (G > 65535) return CLB_ERR_SHAPE;
     dim3 grid((N + nb - 1) / nb, G);
     cudaStream_t st = (cudaStream_t)stream;
+    const long long items = (long long)(s.Ho / 2) * (s.Wo / 2);
+    if (FUSED && dtype == CLB_F32 && amax != nullptr && (long long)nb * items <= 256) {
+        const int PL = ((H + 1) / 2) * ((W + 1) / 2);
+        const size_t smem2 = sizeof(GrpRec) * kGrpBatch + (size_t)nb * cg * 4 * PL * sizeof(float);
+        if (smem2 <= 227 * 1024) {
+            auto k = convtree_bwd_x_grp_kernel;
+            if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess) return check_launch(0);
+            k<<<grid, 256, smem2, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start, grp_list,
+                                        cg, nb, s, wmode);
+            return check_launch();
+        }
+    }
     if (dtype == CLB_F32) {
         auto k = conv_bwd_x_kernel<float, FUSED>;
         if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
