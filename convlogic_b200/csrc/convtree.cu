@@ -113,6 +113,69 @@ __global__ void __launch_bounds__(256) convtree_fwd_kernel(const T *__restrict__
     }
 }
 
+// Forward for layers with many input channels and small images (fp32, at most 256 pooled windows per
+// image, no intermediates): grid (parts, C); the block size is a multiple of the windows per image, so a
+// thread keeps ONE pooled window for its whole life and only the image advances.  The 8 tap offsets of
+// the window's first position and the in-bounds flags of all 4 x 8 (position, tap) pairs are computed
+// once per thread; per image a tap costs a predicate and one cached global load.  An output channel
+// reads only the (normally two) input channels its taps name, so staging whole images is pointless here.
+__global__ void __launch_bounds__(256) convtree_fwd_win_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                               const int32_t *__restrict__ sel, float *__restrict__ y,
+                                                               uint8_t *__restrict__ amax, ConvShape s, int wmode)
+{
+    __shared__ BlockGates<float> bg;
+    const int c = blockIdx.y;
+    load_channel<float>(bg, w, sel, c, 7, wmode, s.ph, s.pw);
+    __syncthreads();
+    const int Wp = s.Wo / 2, I = (s.Ho / 2) * Wp;
+    const int ipb = blockDim.x / I;
+    const int lane_img = threadIdx.x / I, win = threadIdx.x - lane_img * I;
+    const int py = win / Wp, px = win - py * Wp;
+    const int HW = s.H * s.W;
+    int base[8];
+    unsigned valid = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const Tap tp = bg.tap[k];
+        const int iy0 = 2 * py * s.sh + tp.dy, ix0 = 2 * px * s.sw + tp.dx;
+        base[k] = tp.ch * HW + iy0 * s.W + ix0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const int iy = iy0 + (d >> 1) * s.sh, ix = ix0 + (d & 1) * s.sw;
+            if ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) valid |= 1u << (d * 8 + k);
+        }
+    }
+    Gate<float> g[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g[i] = bg.g[i];
+    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+    if (lane_img >= ipb) return;
+    const int rowstep = s.sh * s.W;
+    for (int n = n_lo + lane_img; n < n_hi; n += ipb) {
+        const float *ximg = x + (size_t)n * s.Ci * HW;
+        float best = 0.f;
+        int bd = 0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            const float *p = ximg + ((d >> 1) ? rowstep : 0) + ((d & 1) ? s.sw : 0);
+            const unsigned vm = valid >> (d * 8);
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) a[k] = ((vm >> k) & 1u) ? __ldg(p + base[k]) : 0.f;
+            const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+            const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+            const float z = gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+            if (d == 0 || z > best) { // strict '>' in scan order keeps the first maximum
+                best = z;
+                bd = d;
+            }
+        }
+        const size_t o = ((size_t)n * s.C + c) * I + win;
+        y[o] = best;
+        if (amax != nullptr) amax[o] = (uint8_t)bd;
+    }
+}
+
 // grid (chunks of positions, C); thread <-> conv position (n, oy, ox); writes the 4 first-level gates.
 template <typename T>
 __global__ void __launch_bounds__(256) conv_fwd_kernel(const T *__restrict__ x, const T *__restrict__ w,
@@ -636,6 +699,16 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
         if (rc != CLB_ERR_SHAPE) return rc;
     }
     const long long total = (long long)N * (s.Ho / 2) * (s.Wo / 2);
+    const int items = (s.Ho / 2) * (s.Wo / 2);
+    if (dtype == CLB_F32 && !x2 && !idx && items <= 256) {
+        const int threads = (256 / items) * items;
+        int parts = (int)((148LL * 20 + C - 1) / C); // about ten waves of two resident blocks per SM
+        const int ipb = threads / items;
+        if (parts > (N + ipb - 1) / ipb) parts = (N + ipb - 1) / ipb;
+        if (parts < 1) parts = 1;
+        convtree_fwd_win_kernel<<<dim3(parts, C), threads, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, s, wmode);
+        return check_launch();
+    }
     dim3 grid(grid_x_for(total, C), C);
     if (dtype == CLB_F32)
         convtree_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, (float *)x2,
