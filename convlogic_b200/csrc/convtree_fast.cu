@@ -226,6 +226,193 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
     }
 }
 
+// ======================================================================== forward, many input channels
+// Layers behind the first one have hundreds of input channels and small images; an output channel
+// reads only the channels its 8 taps name (two, by the reference's construction).  grid (parts, C): a
+// block owns ONE output channel, so its 28 coefficients and 16 tap offsets live in registers for the
+// whole kernel, and walks its share of the batch in slices of G images.  Per slice it stages just those
+// two channel planes of the G images into the de-interleaved zero-haloed layout of the kernel above
+// (conflict-free gathers), the next slice's planes being fetched into registers while the current one
+// is evaluated.  A tap whose channel is a third or later distinct one (possible only with a
+// hand-made selection) is gathered from global memory instead.
+constexpr int kChanSlots = 2;
+constexpr int kChanPrefetch = 4; // float4 per thread and slice
+
+template <int WPT>
+__global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_chan_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                                           const int32_t *__restrict__ sel, float *__restrict__ y,
+                                                                           uint8_t *__restrict__ amax, FastShape s, int q4 /* float4 per thread per slice */)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *tile = reinterpret_cast<float *>(smem_raw);
+    const unsigned char *tileb = smem_raw;
+    __shared__ Gate<float> sg[7];
+    __shared__ int sslot[8], sch[kChanSlots], snslot;
+    __shared__ Tap stap[8];
+
+    const int c = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int pwh = s.pwh, RSB = 8 * pwh;
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp, HW = s.H * s.W;
+    if (tid < 7) sg[tid] = gate_load<float>(w + ((size_t)c * 7 + tid) * 16, s.wmode);
+    if (tid >= 64 && tid < 72) stap[tid - 64] = unpack_tap(sel[c * 8 + tid - 64], s.ph, s.pw);
+    if (tid == 32) { // channel -> slot map of this output channel's taps
+        int n = 0;
+        int chs[8];
+        bool inside = true;
+        for (int k = 0; k < 8; ++k) {
+            const int word = sel[c * 8 + k];
+            const int ch = (word >> 16) & 0xFFFF;
+            inside = inside && ch < s.Ci && ((word >> 8) & 0xFF) < s.kh && (word & 0xFF) < s.kw;
+            int slot = -1;
+            for (int j = 0; j < n; ++j)
+                if (chs[j] == ch) slot = j;
+            if (slot < 0) {
+                slot = n;
+                chs[n++] = ch;
+            }
+            sslot[k] = slot;
+        }
+        for (int j = 0; j < kChanSlots; ++j) sch[j] = min(chs[j < n ? j : 0], s.Ci - 1);
+        snslot = inside ? n : kChanSlots + 1;
+    }
+    for (int i = tid; i < s.G * s.IS; i += kFastThreads) tile[i] = 0.f; // halo stays zero
+    __syncthreads();
+
+    Gate<float> g[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g[i] = sg[i];
+    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+
+    if (snslot > kChanSlots) {
+        // Hand-made selection (more than two channels, or taps outside the window): no staging, every tap is a
+        // bounds-checked global load.  Block-uniform branch.
+        for (int f = tid; f < (n_hi - n_lo) * I; f += kFastThreads) {
+            const int img = f / I, win = f - img * I;
+            const int py = win / Wp, px = win - py * Wp;
+            const float *ximg = x + (size_t)(n_lo + img) * s.Ci * HW;
+            float best = 0.f;
+            int bd = 0;
+            for (int d = 0; d < 4; ++d) {
+                float a[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int iy = 2 * py + (d >> 1) + stap[k].dy, ix = 2 * px + (d & 1) + stap[k].dx;
+                    a[k] = ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) ? __ldg(ximg + stap[k].ch * HW + iy * s.W + ix) : 0.f;
+                }
+                const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+                const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+                const float z = gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+                if (d == 0 || z > best) {
+                    best = z;
+                    bd = d;
+                }
+            }
+            const size_t o = ((size_t)(n_lo + img) * s.C + c) * I + win;
+            y[o] = best;
+            if (amax != nullptr) amax[o] = (uint8_t)bd;
+        }
+        return;
+    }
+
+    int tb0[8], tb1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int word = sel[c * 8 + k];
+        const int r = (word >> 8) & 0xFF, sx = word & 0xFF;
+        const int base = sslot[k] * s.CS + r * 2 * pwh;
+        tb0[k] = 4 * (base + (sx & 1) * pwh + (sx >> 1));
+        tb1[k] = 4 * (base + ((sx + 1) & 1) * pwh + ((sx + 1) >> 1));
+    }
+    const int nstage = snslot;
+    const int ch_a = sch[0], ch_b = sch[1];
+
+    int toff[WPT], wimg[WPT], wwin[WPT];
+#pragma unroll
+    for (int j = 0; j < WPT; ++j) {
+        const int f = tid + kFastThreads * j;
+        const int img = f / I, win = f - img * I;
+        const int py = win / Wp, px = win - py * Wp;
+        wimg[j] = img < s.G ? img : -1;
+        wwin[j] = win;
+        toff[j] = 4 * (img * s.IS + 2 * py * 2 * pwh + px);
+    }
+
+    // one float4 = 4 consecutive pixels of one row of plane (img, slot); W % 4 == 0 is a launch condition.
+    // Which float4s a thread moves, and where they land in the tile, is the same for every slice.
+    const int w4 = s.W >> 2, per_plane = s.H * w4, per_slice = s.G * nstage * per_plane;
+    int src[kChanPrefetch], dst[kChanPrefetch], simg[kChanPrefetch];
+#pragma unroll
+    for (int q = 0; q < kChanPrefetch; ++q) {
+        const int i = tid + q * kFastThreads;
+        simg[q] = -1;
+        src[q] = dst[q] = 0;
+        if (q < q4 && i < per_slice) {
+            const int pl = i / per_plane, e = i - pl * per_plane;
+            const int img = pl / nstage, slot = pl - img * nstage;
+            const int row = e / w4, col = (e - row * w4) * 4;
+            simg[q] = img;
+            src[q] = (img * s.Ci + (slot ? ch_b : ch_a)) * HW + e * 4;
+            dst[q] = img * s.IS + slot * s.CS + (row + s.ph) * 2 * pwh + ((col + s.pw) >> 1);
+        }
+    }
+    // the 4 pixels of a float4 alternate between the two column-parity planes (col is a multiple of 4)
+    const int p0 = (s.pw & 1) * pwh, p1 = ((s.pw + 1) & 1) * pwh + ((s.pw & 1) ? 1 : 0);
+    const int p2 = p0 + 1, p3 = p1 + 1;
+    float4 pre[kChanPrefetch];
+    auto fetch = [&](int n0) {
+        const float *xs = x + (size_t)n0 * s.Ci * HW;
+#pragma unroll
+        for (int q = 0; q < kChanPrefetch; ++q)
+            if (simg[q] >= 0)
+                pre[q] = n0 + simg[q] < n_hi ? __ldg(reinterpret_cast<const float4 *>(xs + src[q])) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto deposit = [&]() {
+#pragma unroll
+        for (int q = 0; q < kChanPrefetch; ++q)
+            if (simg[q] >= 0) {
+                float *d = tile + dst[q];
+                d[p0] = pre[q].x, d[p1] = pre[q].y, d[p2] = pre[q].z, d[p3] = pre[q].w;
+            }
+    };
+
+    fetch(n_lo);
+    for (int n0 = n_lo; n0 < n_hi; n0 += s.G) {
+        __syncthreads(); // the previous slice has been read
+        deposit();
+        __syncthreads();
+        if (n0 + s.G < n_hi) fetch(n0 + s.G);
+#pragma unroll
+        for (int j = 0; j < WPT; ++j) {
+            if (wimg[j] < 0 || n0 + wimg[j] >= n_hi) continue;
+            float v[4][8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int a0 = toff[j] + tb0[k], a1 = toff[j] + tb1[k];
+                v[0][k] = ld_tile(tileb, a0);
+                v[2][k] = ld_tile(tileb, a0 + RSB);
+                v[1][k] = ld_tile(tileb, a1);
+                v[3][k] = ld_tile(tileb, a1 + RSB);
+            }
+            float best = 0.f;
+            int bd = 0;
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                const float g0 = gate_eval<float>(g[0], v[d][0], v[d][1]), g1 = gate_eval<float>(g[1], v[d][2], v[d][3]);
+                const float g2 = gate_eval<float>(g[2], v[d][4], v[d][5]), g3 = gate_eval<float>(g[3], v[d][6], v[d][7]);
+                const float z = gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+                if (d == 0 || z > best) { // strict '>' in scan order keeps the first maximum
+                    best = z;
+                    bd = d;
+                }
+            }
+            const size_t o = ((size_t)(n0 + wimg[j]) * s.C + c) * I + wwin[j];
+            y[o] = best;
+            if (amax != nullptr) amax[o] = (uint8_t)bd;
+        }
+    }
+}
+
 // ==================================================================================== input gradient
 // Layout of the two backward tiles (x and its gradient): NO halo; a channel plane is split into the four
 // parity classes of (row, column) -- class = 2*(row & 1) + (col & 1) -- each stored as a dense
@@ -589,10 +776,46 @@ static int launch_fwd(const float *x, const float *w, const int32_t *sel, float 
     return check_launch();
 }
 
+// Two-channel-plane variant: applies when W is a multiple of 4, x is 16-byte aligned and a slice fits.
+static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W, int C,
+                           int ph, int pw, int kh, int kw, int wmode, cudaStream_t st)
+{
+    if ((W & 3) || (reinterpret_cast<uintptr_t>(x) & 15) || C > 65535) return CLB_ERR_SHAPE;
+    FastShape s;
+    s.N = N, s.Ci = Ci, s.H = H, s.W = W, s.C = C, s.ph = ph, s.pw = pw, s.kh = kh, s.kw = kw, s.wmode = wmode;
+    s.Ho = conv_out(H, ph, kh, 1), s.Wo = conv_out(W, pw, kw, 1);
+    if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return CLB_ERR_SHAPE;
+    const int I = (s.Ho / 2) * (s.Wo / 2);
+    s.PH = H + 2 * ph;
+    s.pwh = pick_pwh((W + 2 * pw + 1) / 2, s.Wo / 2);
+    s.CS = s.PH * 2 * s.pwh;
+    s.IS = kChanSlots * s.CS;
+    constexpr int WPT = 2;
+    int G = (kFastThreads * WPT) / I;
+    if (G < 1) return CLB_ERR_SHAPE;
+    if (G > N) G = N;
+    s.G = G;
+    const size_t smem = (size_t)G * s.IS * 4;
+    if (smem > 72 * 1024) return CLB_ERR_SHAPE;
+    const int q4 = (G * kChanSlots * H * (W / 4) + kFastThreads - 1) / kFastThreads;
+    if (q4 > kChanPrefetch) return CLB_ERR_SHAPE;
+    int parts = (int)((148LL * 3 * 8 + C - 1) / C); // about eight waves of three resident blocks per SM
+    if (parts > (N + G - 1) / G) parts = (N + G - 1) / G;
+    if (parts < 1) parts = 1;
+    auto k = convtree_fwd_chan_kernel<WPT>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    k<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4);
+    return check_launch();
+}
+
 int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W,
                               int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st)
 {
     FastShape s;
+    if (sh != 1 || sw != 1) return CLB_ERR_SHAPE;
+    // many input channels: an image's channels do not fit shared memory (or barely one image does)
+    if ((size_t)Ci * (H + 2 * ph) * (W + 2 * pw) * 4 > 48 * 1024)
+        return launch_fwd_chan(x, w, sel, y, amax, N, Ci, H, W, C, ph, pw, kh, kw, wmode, st);
     if (!make_fast_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
     const int I = (s.Ho / 2) * (s.Wo / 2);
     const size_t img_bytes = (size_t)s.IS * 4;

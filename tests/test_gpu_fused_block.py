@@ -306,3 +306,30 @@ def test_tiled_input_gradient_equals_general(shape):
             assert float((idx != idxo).float().mean()) < 1e-4
             bad = ((g_fast.cpu() - gxo).abs() > F32_TOL * gxo.abs().max()).float().mean()
             assert float(bad) < 1e-3
+
+
+@pytest.mark.parametrize("shape", [
+    (40, 64, 24, 16, 16, 1, 1, 3, "rand"),     # channels do not fit shared memory: two-plane staging
+    (33, 128, 20, 8, 8, 1, 1, 3, "rand"),
+    (130, 600, 10, 4, 4, 1, 1, 3, "rand"),
+    (5, 40, 6, 32, 32, 1, 1, 3, "rand"),
+], ids=lambda s: "x".join(str(v) for v in s))
+def test_many_channel_forward_paths_agree(shape):
+    """Staged two-plane forward vs the general kernel; also with a selection that names more than two
+    channels per output channel (third and later channels are gathered from global memory)."""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy, geom = _case(shape, seed=13)   # random_selection: up to 8 distinct channels per output
+    n, ci, c = shape[0], shape[1], shape[2]
+    rng = np.random.default_rng(5)
+    two = rng.integers(0, ci, (c, 2))
+    pick = rng.integers(0, 2, (c, 8))
+    ch2 = np.take_along_axis(two, pick, 1)
+    sel2 = torch.from_numpy(((ch2 << 16) | (rng.integers(0, 3, (c, 8)) << 8) | rng.integers(0, 3, (c, 8))).astype(np.int32))
+    for sel_t in (sel2, sel):
+        xd, wd, sd = x.cuda(), logits.cuda(), sel_t.cuda()
+        y_fast, amax_fast, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX)
+        y_gen, amax_gen, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)
+        assert torch.equal(y_fast, y_gen)
+        assert torch.equal(amax_fast, amax_gen)
