@@ -353,10 +353,13 @@ constexpr int kGrpBatch = 8;
 
 struct alignas(16) GrpRec {
     float g[28];
-    int xoff[8];  // channel * H * W
-    int ty[8];    // tap row / col displacement (pad subtracted)
+    int xo[8];    // channel*H*W + ty*W + tx: offset of the tap's pixel from the conv position's pixel
+    int ty[8];    // tap row / col displacement (pad subtracted), for the bounds test
     int tx[8];
-    int goff[8];  // local channel * 4 * PL inside the block's gradient tile, or -1 when the tap's channel is not in the group
+    int cbase[8]; // float offset of the tap's cell in the gradient tile for a window's first position, from the
+                  // window's own offset; -1 when the tap's channel is not in the block's group
+    int dA[8];    // added when the arg-max is in the window's second row / column (parity-class layout)
+    int dB[8];
 };
 
 __global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float *__restrict__ gy, const float *__restrict__ x,
@@ -383,9 +386,12 @@ __global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float 
     const bool live = img < nimg;
     const int py = win / Wp, px = win - py * Wp;
     const int n = n0 + img;
-    const float *ximg = x + (size_t)n * s.Ci * HW;
-    float *timg = tile + img * cg * 4 * PL;
+    // stride-1 layers only (checked by the launcher): conv position (2py+dy, 2px+dx) reads pixel (position + tap)
+    const float *xwin = x + (size_t)n * s.Ci * HW + 2 * py * s.W + 2 * px;
+    float *twin = tile + img * cg * 4 * PL + py * Wh + px;
     const size_t obase = ((size_t)n * s.C) * I + win; // + c * I
+    auto fy = [&](int t) { return (t & 1) * 2 * PL + (t >> 1) * Wh; };
+    auto fx = [&](int t) { return (t & 1) * PL + (t >> 1); };
 
     const int lo = grp_start[g], hi = grp_start[g + 1];
     for (int l0 = lo; l0 < hi; l0 += kGrpBatch) {
@@ -400,42 +406,92 @@ __global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float 
         for (int i = tid; i < cnt * 8; i += blockDim.x) {
             const int e = i >> 3, k = i & 7;
             const Tap tp = unpack_tap(sel[grp_list[l0 + e] * 8 + k], s.ph, s.pw);
-            rec[e].xoff[k] = tp.ch * HW;
+            rec[e].xo[k] = tp.ch * HW + tp.dy * s.W + tp.dx;
             rec[e].ty[k] = tp.dy;
             rec[e].tx[k] = tp.dx;
             const int chl = tp.ch - ch0;
-            rec[e].goff[k] = (chl >= 0 && chl < cg) ? chl * 4 * PL : -1;
+            rec[e].cbase[k] = (chl >= 0 && chl < cg) ? chl * 4 * PL + fy(tp.dy) + fx(tp.dx) : -1;
+            rec[e].dA[k] = fy(tp.dy + 1) - fy(tp.dy);
+            rec[e].dB[k] = fx(tp.dx + 1) - fx(tp.dx);
         }
         __syncthreads();
 
-        float dz_next = 0.f;
-        int bd_next = 0;
+        // Software pipeline over the batch: gy / arg-max are fetched two channels ahead and the 8 taps of the
+        // next channel are gathered (arg-max -> address -> load is a chain of global latencies) while the
+        // current channel is evaluated and accumulated.
+        float dz1 = 0.f, dz2 = 0.f, a1[8];
+        int bd1 = 0, bd2 = 0;
+        unsigned vm1 = 0;
+        auto gather = [&](int e, int bd, float(&a)[8], unsigned &vm) {
+            const GrpRec &r = rec[e];
+            const int dyi = bd >> 1, dxi = bd & 1;
+            const int oy = 2 * py + dyi, ox = 2 * px + dxi;
+            const float *xpos = xwin + dyi * s.W + dxi;
+            vm = 0;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int4 xo4 = reinterpret_cast<const int4 *>(r.xo)[q], ty4 = reinterpret_cast<const int4 *>(r.ty)[q];
+                const int4 tx4 = reinterpret_cast<const int4 *>(r.tx)[q];
+                const int xo[4] = {xo4.x, xo4.y, xo4.z, xo4.w}, ty[4] = {ty4.x, ty4.y, ty4.z, ty4.w}, tx[4] = {tx4.x, tx4.y, tx4.z, tx4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const bool v = (unsigned)(oy + ty[j]) < (unsigned)s.H && (unsigned)(ox + tx[j]) < (unsigned)s.W;
+                    a[q * 4 + j] = v ? __ldg(xpos + xo[j]) : 0.f;
+                    vm |= (v ? 1u : 0u) << (q * 4 + j);
+                }
+            }
+        };
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a1[k] = 0.f;
         if (live) {
             const size_t o = obase + (size_t)grp_list[l0] * I;
-            dz_next = __ldg(gy + o);
-            bd_next = amax[o];
+            dz1 = __ldg(gy + o);
+            bd1 = amax[o];
+            gather(0, bd1, a1, vm1);
+            if (cnt > 1) {
+                const size_t o2 = obase + (size_t)grp_list[l0 + 1] * I;
+                dz2 = __ldg(gy + o2);
+                bd2 = amax[o2];
+            }
         }
         for (int e = 0; e < cnt; ++e) {
-            const float dz = dz_next;
-            const int bd = bd_next;
-            if (live && e + 1 < cnt) {
-                const size_t o = obase + (size_t)grp_list[l0 + e + 1] * I;
-                dz_next = __ldg(gy + o);
-                bd_next = amax[o];
+            const float dz = dz1;
+            const int bd = bd1;
+            const unsigned vm = vm1;
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) a[k] = a1[k];
+            dz1 = dz2;
+            bd1 = bd2;
+            if (live && e + 1 < cnt) gather(e + 1, bd1, a1, vm1);
+            if (live && e + 2 < cnt) {
+                const size_t o = obase + (size_t)grp_list[l0 + e + 2] * I;
+                dz2 = __ldg(gy + o);
+                bd2 = amax[o];
             }
             const GrpRec &r = rec[e];
+            int cb[8];
+            {
+                const int4 c0 = reinterpret_cast<const int4 *>(r.cbase)[0], c1 = reinterpret_cast<const int4 *>(r.cbase)[1];
+                cb[0] = c0.x, cb[1] = c0.y, cb[2] = c0.z, cb[3] = c0.w, cb[4] = c1.x, cb[5] = c1.y, cb[6] = c1.z, cb[7] = c1.w;
+            }
             float tg[8];
             int cell[8];
             if (live) {
-                const int oy = (2 * py + (bd >> 1)) * s.sh, ox = (2 * px + (bd & 1)) * s.sw;
-                float a[8];
+                const int dyi = bd >> 1, dxi = bd & 1;
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int iy = oy + r.ty[k], ix = ox + r.tx[k];
-                    const bool v = (unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W;
-                    a[k] = v ? __ldg(ximg + r.xoff[k] + iy * s.W + ix) : 0.f;
-                    const int go = r.goff[k];
-                    cell[k] = (v && go >= 0) ? go + ((iy & 1) * 2 + (ix & 1)) * PL + (iy >> 1) * Wh + (ix >> 1) : -1;
+                for (int k = 0; k < 8; ++k) cell[k] = ((vm >> k) & 1u) ? 0 : -1;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    if (cb[4 * q] >= 0 || cb[4 * q + 1] >= 0 || cb[4 * q + 2] >= 0 || cb[4 * q + 3] >= 0) { // block-uniform
+                        const int4 a4 = reinterpret_cast<const int4 *>(r.dA)[q], b4 = reinterpret_cast<const int4 *>(r.dB)[q];
+                        const int dA[4] = {a4.x, a4.y, a4.z, a4.w}, dB[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int k = q * 4 + j;
+                            if (cell[k] == 0) cell[k] = cb[k] + dyi * dA[j] + dxi * dB[j];
+                        }
+                    }
                 }
                 Gate<float> gg[7];
                 const float4 *gp = reinterpret_cast<const float4 *>(r.g);
@@ -457,8 +513,8 @@ __global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float 
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                if (r.goff[k] >= 0) { // block-uniform: taps outside the group cost no barrier
-                    if (live && cell[k] >= 0) timg[cell[k]] += tg[k];
+                if (cb[k] >= 0) { // block-uniform: taps outside the group cost no barrier
+                    if (live && cell[k] >= 0) twin[cell[k]] += tg[k];
                     __syncthreads();
                 }
             }
@@ -819,7 +875,7 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
     dim3 grid((N + nb - 1) / nb, G);
     cudaStream_t st = (cudaStream_t)stream;
     const long long items = (long long)(s.Ho / 2) * (s.Wo / 2);
-    if (FUSED && dtype == CLB_F32 && amax != nullptr && (long long)nb * items <= 256) {
+    if (FUSED && dtype == CLB_F32 && amax != nullptr && (long long)nb * items <= 256 && sh == 1 && sw == 1) {
         const int PL = ((H + 1) / 2) * ((W + 1) / 2);
         const size_t smem2 = sizeof(GrpRec) * kGrpBatch + (size_t)nb * cg * 4 * PL * sizeof(float);
         if (smem2 <= 227 * 1024) {

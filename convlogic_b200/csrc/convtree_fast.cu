@@ -685,18 +685,34 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
     if (GX) flush(cur_group);
 }
 
-// Adds the per-group basis sums in group order and turns them into the 16 gradients of every gate.
-__global__ void convtree_gw_finalize_kernel(const float *__restrict__ wpartial, const float *__restrict__ w, float *__restrict__ gw,
-                                            int groups, int ngates, int wmode)
+// Adds the per-group basis sums and turns them into the 16 gradients of every gate.  Eight threads share a
+// gate: each adds a contiguous eighth of the groups in order, then the eight partial sums are added in
+// order -- a fixed summation tree, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) convtree_gw_finalize_kernel(const float *__restrict__ wpartial, const float *__restrict__ w,
+                                                                   float *__restrict__ gw, int groups, int ngates, int wmode)
 {
-    const int gi = blockIdx.x * blockDim.x + threadIdx.x;
-    if (gi >= ngates) return;
-    float sums[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int p = 0; p < groups; ++p) {
-        const float4 q = *reinterpret_cast<const float4 *>(wpartial + ((size_t)p * ngates + gi) * 4);
-        sums[0] += q.x, sums[1] += q.y, sums[2] += q.z, sums[3] += q.w;
+    __shared__ float4 part[32][8];
+    const int local = threadIdx.x >> 3, sub = threadIdx.x & 7;
+    const int gi = blockIdx.x * 32 + local;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gi < ngates) {
+        const int per = (groups + 7) / 8;
+        const int lo = sub * per, hi = min(groups, lo + per);
+        for (int p = lo; p < hi; ++p) {
+            const float4 q = *reinterpret_cast<const float4 *>(wpartial + ((size_t)p * ngates + gi) * 4);
+            acc.x += q.x, acc.y += q.y, acc.z += q.z, acc.w += q.w;
+        }
     }
-    gate_grad_store<float>(sums, w + (size_t)gi * 16, wmode, gw + (size_t)gi * 16);
+    part[local][sub] = acc;
+    __syncthreads();
+    if (sub == 0 && gi < ngates) {
+        float sums[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < 8; ++k) {
+            const float4 q = part[local][k];
+            sums[0] += q.x, sums[1] += q.y, sums[2] += q.z, sums[3] += q.w;
+        }
+        gate_grad_store<float>(sums, w + (size_t)gi * 16, wmode, gw + (size_t)gi * 16);
+    }
 }
 
 // gx of every group that no single block covered = sum of that group's partial tiles, in block order.
@@ -941,7 +957,7 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
     }
     if (gw) {
         const int ngates = C * 7;
-        convtree_gw_finalize_kernel<<<(ngates + 63) / 64, 64, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
+        convtree_gw_finalize_kernel<<<(ngates + 31) / 32, 256, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
         ++launched;
     }
     return check_launch(launched);
