@@ -466,14 +466,17 @@ __device__ __forceinline__ float warp_reduce_transposed(float (&v)[32], int lane
 
 // GX: accumulate and write the input gradient.  GW: write, per (image group, channel), the 28 basis sums
 // of the gate gradient to `wpartial` [groups][C][28]; both share the gate chain recomputed at the arg-max.
-template <bool GX, bool GW>
-__global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+// WPT pooled windows per thread (blocks of 256 / WPT threads): the per-channel record loads and the warp
+// reduction of the gate sums are paid once per thread, so WPT = 2 halves them per window.
+template <bool GX, bool GW, int WPT>
+__global__ void __launch_bounds__(kFastThreads / WPT, 3) convtree_bwd_cls_kernel(const float *__restrict__ gy, const float *__restrict__ x,
                                                                           const float *__restrict__ w, const int32_t *__restrict__ sel,
                                                                           const uint8_t *__restrict__ amax, float *__restrict__ gx,
                                                                           float *__restrict__ partial, float *__restrict__ wpartial,
                                                                           ClsShape s)
 {
-    __shared__ float wred[kFastThreads / 32][32];
+    constexpr int TPB = kFastThreads / WPT;
+    __shared__ float wred[TPB / 32][32];
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdRec *chan = reinterpret_cast<BwdRec *>(smem_raw);
     float *xt = reinterpret_cast<float *>(smem_raw + sizeof(BwdRec) * kBwdChanBuf);
@@ -491,18 +494,25 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
     if (lo >= hi) return;
     const int first_group = (int)(lo / s.C);
 
-    const int img = tid / I, win = tid - img * I;
-    const int py = win / Wp, px = win - py * Wp;
-    const bool has_window = img < s.G;
-    const int toff = 4 * (img * s.IS + py * s.Wh + px);
+    int wimg[WPT], wwin[WPT], wy[WPT], wx[WPT], toff[WPT];
+#pragma unroll
+    for (int j = 0; j < WPT; ++j) {
+        const int f = tid + TPB * j;
+        const int img = f / I, win = f - img * I;
+        const int py = win / Wp, px = win - py * Wp;
+        wimg[j] = img < s.G ? img : -1;
+        wwin[j] = win;
+        wy[j] = 2 * py, wx[j] = 2 * px;
+        toff[j] = 4 * (img * s.IS + py * s.Wh + px);
+    }
 
     if (GX)
-        for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
+        for (int i = tid; i < s.G * s.IS; i += TPB) gt[i] = 0.f;
 
     auto stage = [&](int n0, int nimg) {
         const int total = nimg * s.Ci * HW;
         if ((s.W & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0)) {
-            for (int i = tid; i < (total >> 2); i += kFastThreads) {
+            for (int i = tid; i < (total >> 2); i += TPB) {
                 const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)n0 * s.Ci * HW) + i);
                 const int e = i << 2;
                 const int col = e % s.W;
@@ -514,7 +524,7 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
                 xt[b0] = v.x, xt[b0 + s.PL] = v.y, xt[b0 + 1] = v.z, xt[b0 + s.PL + 1] = v.w;
             }
         } else {
-            for (int i = tid; i < total; i += kFastThreads) {
+            for (int i = tid; i < total; i += TPB) {
                 const int col = i % s.W;
                 int r = i / s.W;
                 const int row = r % s.H;
@@ -531,7 +541,7 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
         float *dst = whole ? gx + (size_t)n0 * s.Ci * HW
                            : partial + ((size_t)blockIdx.x * 2 + (grp == first_group ? 0 : 1)) * (size_t)s.G * s.Ci * HW;
         const int total = nimg * s.Ci * HW;
-        for (int i = tid; i < total; i += kFastThreads) {
+        for (int i = tid; i < total; i += TPB) {
             const int col = i % s.W;
             int r = i / s.W;
             const int row = r % s.H;
@@ -539,7 +549,7 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
             dst[i] = gt[cls_index(s, r / s.Ci, r % s.Ci, row, col)];
         }
         __syncthreads();
-        for (int i = tid; i < s.G * s.IS; i += kFastThreads) gt[i] = 0.f;
+        for (int i = tid; i < s.G * s.IS; i += TPB) gt[i] = 0.f;
     };
     // f(t): offset of row/col displacement t inside the class layout (t may be negative)
     auto fy = [&](int t) { return (t & 1) * 2 * s.PL + (t >> 1) * s.Wh; };
@@ -559,13 +569,13 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
             cur_group = grp;
             stage(n0, min(s.G, s.N - n0));
         }
-        for (int i = tid; i < cnt * 7; i += kFastThreads) {
+        for (int i = tid; i < cnt * 7; i += TPB) {
             const int cc = i / 7, gi = i - cc * 7;
             const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
             float *o = chan[cc].g + gi * 4;
             o[0] = g.k1, o[1] = g.ka, o[2] = g.kb, o[3] = g.kab;
         }
-        for (int i = tid; i < cnt * 8; i += kFastThreads) {
+        for (int i = tid; i < cnt * 8; i += TPB) {
             const int cc = i >> 3, k = i & 7;
             const int word = sel[(c0 + cc) * 8 + k];
             const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1);
@@ -578,18 +588,19 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
         }
         __syncthreads();
 
-        const bool live = has_window && n0 + img < s.N;
-        const size_t obase = live ? ((size_t)(n0 + img) * s.C + c0) * I + win : 0;
+        bool live[WPT];
+        size_t obase[WPT];
+        float gy_next[WPT];
+        int bd_next[WPT];
         // software pipeline: the next channel's gy / arg-max loads are in flight during this channel's work
-        float gy_next = live ? __ldg(gy + obase) : 0.f;
-        int bd_next = live ? (int)__ldg(amax + obase) : 0;
+#pragma unroll
+        for (int j = 0; j < WPT; ++j) {
+            live[j] = wimg[j] >= 0 && n0 + wimg[j] < s.N;
+            obase[j] = live[j] ? ((size_t)(n0 + wimg[j]) * s.C + c0) * I + wwin[j] : 0;
+            gy_next[j] = live[j] ? __ldg(gy + obase[j]) : 0.f;
+            bd_next[j] = live[j] ? (int)__ldg(amax + obase[j]) : 0;
+        }
         for (int cc = 0; cc < cnt; ++cc) {
-            const float dz = gy_next;
-            const int bd = bd_next;
-            if (live && cc + 1 < cnt) {
-                gy_next = __ldg(gy + obase + (size_t)(cc + 1) * I);
-                bd_next = (int)__ldg(amax + obase + (size_t)(cc + 1) * I);
-            }
             const BwdRec &rec = chan[cc];
             Gate<float> g[7];
             {
@@ -600,52 +611,65 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
                     g[i].k1 = q.x, g[i].ka = q.y, g[i].kb = q.z, g[i].kab = q.w;
                 }
             }
-            int addr[8];
-            float tg[8];
-            float bs[32]; // 28 basis products of this window (GW), padded to a power of two
+            int rb[8], ra[8], rc[8], ry[8], rx[8];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int4 b4 = reinterpret_cast<const int4 *>(rec.base)[q], a4 = reinterpret_cast<const int4 *>(rec.dA)[q];
+                const int4 c4 = reinterpret_cast<const int4 *>(rec.dB)[q], y4 = reinterpret_cast<const int4 *>(rec.ty)[q];
+                const int4 x4 = reinterpret_cast<const int4 *>(rec.tx)[q];
+                rb[4 * q] = b4.x, rb[4 * q + 1] = b4.y, rb[4 * q + 2] = b4.z, rb[4 * q + 3] = b4.w;
+                ra[4 * q] = a4.x, ra[4 * q + 1] = a4.y, ra[4 * q + 2] = a4.z, ra[4 * q + 3] = a4.w;
+                rc[4 * q] = c4.x, rc[4 * q + 1] = c4.y, rc[4 * q + 2] = c4.z, rc[4 * q + 3] = c4.w;
+                ry[4 * q] = y4.x, ry[4 * q + 1] = y4.y, ry[4 * q + 2] = y4.z, ry[4 * q + 3] = y4.w;
+                rx[4 * q] = x4.x, rx[4 * q + 1] = x4.y, rx[4 * q + 2] = x4.z, rx[4 * q + 3] = x4.w;
+            }
+            int addr[WPT][8];
+            float tg[WPT][8];
+            unsigned ok[WPT];
+            float bs[32]; // 28 basis products of this thread's windows (GW), padded to a power of two
 #pragma unroll
             for (int i = 0; i < 32; ++i) bs[i] = 0.f;
-            unsigned ok = 0;
-            if (live) {
-                const int dyi = bd >> 1, dxi = bd & 1;
-                const int oy = 2 * py + dyi, ox = 2 * px + dxi;
-                float a[8];
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int4 b4 = reinterpret_cast<const int4 *>(rec.base)[q], a4 = reinterpret_cast<const int4 *>(rec.dA)[q];
-                    const int4 c4 = reinterpret_cast<const int4 *>(rec.dB)[q], y4 = reinterpret_cast<const int4 *>(rec.ty)[q];
-                    const int4 x4 = reinterpret_cast<const int4 *>(rec.tx)[q];
-                    const int bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w}, cc4[4] = {c4.x, c4.y, c4.z, c4.w};
-                    const int yy[4] = {y4.x, y4.y, y4.z, y4.w}, xx[4] = {x4.x, x4.y, x4.z, x4.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int k = q * 4 + j;
-                        addr[k] = toff + bb[j] + dyi * aa[j] + dxi * cc4[j];
-                        const bool v = (unsigned)(oy + yy[j]) < (unsigned)s.H && (unsigned)(ox + xx[j]) < (unsigned)s.W;
-                        ok |= (v ? 1u : 0u) << k;
-                        a[k] = v ? ld_tile(xtb, addr[k]) : 0.f;
-                    }
+            for (int j = 0; j < WPT; ++j) {
+                const float dz = gy_next[j];
+                const int bd = bd_next[j];
+                if (live[j] && cc + 1 < cnt) {
+                    gy_next[j] = __ldg(gy + obase[j] + (size_t)(cc + 1) * I);
+                    bd_next[j] = (int)__ldg(amax + obase[j] + (size_t)(cc + 1) * I);
                 }
-                const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
-                const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
-                const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
-                const float dt0 = dz * gate_da<float>(g[6], t1), dt1 = dz * gate_db<float>(g[6], t0);
-                const float dg0 = dt0 * gate_da<float>(g[4], g1), dg1 = dt0 * gate_db<float>(g[4], g0);
-                const float dg2 = dt1 * gate_da<float>(g[5], g3), dg3 = dt1 * gate_db<float>(g[5], g2);
-                tg[0] = dg0 * gate_da<float>(g[0], a[1]), tg[1] = dg0 * gate_db<float>(g[0], a[0]);
-                tg[2] = dg1 * gate_da<float>(g[1], a[3]), tg[3] = dg1 * gate_db<float>(g[1], a[2]);
-                tg[4] = dg2 * gate_da<float>(g[2], a[5]), tg[5] = dg2 * gate_db<float>(g[2], a[4]);
-                tg[6] = dg3 * gate_da<float>(g[3], a[7]), tg[7] = dg3 * gate_db<float>(g[3], a[6]);
-                if (GW) {
-                    const float dgp[4] = {dg0, dg1, dg2, dg3};
+                ok[j] = 0;
+                if (live[j]) {
+                    const int dyi = bd >> 1, dxi = bd & 1;
+                    const int oy = wy[j] + dyi, ox = wx[j] + dxi;
+                    float a[8];
 #pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        bs[4 * p] = dgp[p] * (a[2 * p] * a[2 * p + 1]), bs[4 * p + 1] = dgp[p] * a[2 * p];
-                        bs[4 * p + 2] = dgp[p] * a[2 * p + 1], bs[4 * p + 3] = dgp[p];
+                    for (int k = 0; k < 8; ++k) {
+                        addr[j][k] = toff[j] + rb[k] + dyi * ra[k] + dxi * rc[k];
+                        const bool v = (unsigned)(oy + ry[k]) < (unsigned)s.H && (unsigned)(ox + rx[k]) < (unsigned)s.W;
+                        ok[j] |= (v ? 1u : 0u) << k;
+                        a[k] = v ? ld_tile(xtb, addr[j][k]) : 0.f;
                     }
-                    bs[16] = dt0 * (g0 * g1), bs[17] = dt0 * g0, bs[18] = dt0 * g1, bs[19] = dt0;
-                    bs[20] = dt1 * (g2 * g3), bs[21] = dt1 * g2, bs[22] = dt1 * g3, bs[23] = dt1;
-                    bs[24] = dz * (t0 * t1), bs[25] = dz * t0, bs[26] = dz * t1, bs[27] = dz;
+                    const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+                    const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+                    const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+                    const float dt0 = dz * gate_da<float>(g[6], t1), dt1 = dz * gate_db<float>(g[6], t0);
+                    const float dg0 = dt0 * gate_da<float>(g[4], g1), dg1 = dt0 * gate_db<float>(g[4], g0);
+                    const float dg2 = dt1 * gate_da<float>(g[5], g3), dg3 = dt1 * gate_db<float>(g[5], g2);
+                    tg[j][0] = dg0 * gate_da<float>(g[0], a[1]), tg[j][1] = dg0 * gate_db<float>(g[0], a[0]);
+                    tg[j][2] = dg1 * gate_da<float>(g[1], a[3]), tg[j][3] = dg1 * gate_db<float>(g[1], a[2]);
+                    tg[j][4] = dg2 * gate_da<float>(g[2], a[5]), tg[j][5] = dg2 * gate_db<float>(g[2], a[4]);
+                    tg[j][6] = dg3 * gate_da<float>(g[3], a[7]), tg[j][7] = dg3 * gate_db<float>(g[3], a[6]);
+                    if (GW) {
+                        const float dgp[4] = {dg0, dg1, dg2, dg3};
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            bs[4 * p] = fmaf(dgp[p], a[2 * p] * a[2 * p + 1], bs[4 * p]), bs[4 * p + 1] = fmaf(dgp[p], a[2 * p], bs[4 * p + 1]);
+                            bs[4 * p + 2] = fmaf(dgp[p], a[2 * p + 1], bs[4 * p + 2]), bs[4 * p + 3] += dgp[p];
+                        }
+                        bs[16] = fmaf(dt0, g0 * g1, bs[16]), bs[17] = fmaf(dt0, g0, bs[17]), bs[18] = fmaf(dt0, g1, bs[18]), bs[19] += dt0;
+                        bs[20] = fmaf(dt1, g2 * g3, bs[20]), bs[21] = fmaf(dt1, g2, bs[21]), bs[22] = fmaf(dt1, g3, bs[22]), bs[23] += dt1;
+                        bs[24] = fmaf(dz, t0 * t1, bs[24]), bs[25] = fmaf(dz, t0, bs[25]), bs[26] = fmaf(dz, t1, bs[26]), bs[27] += dz;
+                    }
                 }
             }
             if (GW) {
@@ -657,15 +681,17 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
             if (GX) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    if ((ok >> k) & 1u) {
-                        float *cell = reinterpret_cast<float *>(gtb + addr[k]);
-                        *cell += tg[k];
-                    }
+#pragma unroll
+                    for (int j = 0; j < WPT; ++j)
+                        if ((ok[j] >> k) & 1u) {
+                            float *cell = reinterpret_cast<float *>(gtb + addr[j][k]);
+                            *cell += tg[j][k];
+                        }
                     __syncthreads();
                     if (GW && k == 0 && tid < 28) {
                         float t = 0.f;
 #pragma unroll
-                        for (int wv = 0; wv < kFastThreads / 32; ++wv) t += wred[wv][tid];
+                        for (int wv = 0; wv < TPB / 32; ++wv) t += wred[wv][tid];
                         wpartial[((size_t)grp * s.C + c0 + cc) * 28 + tid] = t;
                     }
                 }
@@ -674,7 +700,7 @@ __global__ void __launch_bounds__(kFastThreads, 3) convtree_bwd_cls_kernel(const
                 if (tid < 28) {
                     float t = 0.f;
 #pragma unroll
-                    for (int wv = 0; wv < kFastThreads / 32; ++wv) t += wred[wv][tid];
+                    for (int wv = 0; wv < TPB / 32; ++wv) t += wred[wv][tid];
                     wpartial[((size_t)grp * s.C + c0 + cc) * 28 + tid] = t;
                 }
             }
@@ -933,18 +959,20 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
     float *tiles = (float *)scratch;
     const size_t tile_floats = gx ? (size_t)grid * 2 * s.G * Ci * H * W : 0;
     float *wpartial = tiles + ((tile_floats + 3) / 4) * 4;
-    auto launch = [&](auto kern) {
+    auto launch = [&](auto kern, int threads) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-        kern<<<grid, kFastThreads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s);
+        kern<<<grid, threads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s);
         return true;
     };
+    // two windows per thread once a group has more than 128 of them
+    const bool two = s.G * ((s.Ho / 2) * (s.Wo / 2)) > kFastThreads / 2;
     bool ok;
     if (gx && gw)
-        ok = launch(convtree_bwd_cls_kernel<true, true>);
+        ok = two ? launch(convtree_bwd_cls_kernel<true, true, 2>, kFastThreads / 2) : launch(convtree_bwd_cls_kernel<true, true, 1>, kFastThreads);
     else if (gx)
-        ok = launch(convtree_bwd_cls_kernel<true, false>);
+        ok = two ? launch(convtree_bwd_cls_kernel<true, false, 2>, kFastThreads / 2) : launch(convtree_bwd_cls_kernel<true, false, 1>, kFastThreads);
     else
-        ok = launch(convtree_bwd_cls_kernel<false, true>);
+        ok = two ? launch(convtree_bwd_cls_kernel<false, true, 2>, kFastThreads / 2) : launch(convtree_bwd_cls_kernel<false, true, 1>, kFastThreads);
     if (!ok) return check_launch(0);
     int launched = 1;
     if (gx) {
