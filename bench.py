@@ -67,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -222,7 +222,6 @@ def run_ours(args):
         ev[1].record()
         torch.cuda.synchronize()
         kern_ms[name] = ev[0].elapsed_time(ev[1]) / reps
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- end-to-end: host buffers in, gradients out, copies inside the timed region ----
     xs_p = [x.pin_memory() for x in xs_h]
@@ -281,6 +280,7 @@ def run_ours(args):
         t = torch.tensor([ms_e2e], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None  # sampled over the device-resident, per-kernel and end-to-end regions
 
     if rank != 0:
         if world > 1:
@@ -602,8 +602,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--images", type=int, default=1 << 20, help="c4: total images")
