@@ -223,6 +223,36 @@ def run_ours(args):
         torch.cuda.synchronize()
         kern_ms[name] = ev[0].elapsed_time(ev[1]) / reps
 
+    # ---- the reference's own CUDA kernels on this GPU, when oracle/build_ref.py has built them ----
+    ref_cuda = None
+    if world == 1:
+        try:
+            from oracle.build_ref import load_ref
+
+            rc = load_ref("convlogic_cuda")
+        except Exception:
+            rc = None
+        if rc is not None:
+            wp = torch.softmax(w, -1)
+            t_f = t_b = 0.0
+            nrep = 5
+            for i in range(nrep + 1):
+                xi, gi = xs[i % sets].detach(), gys[i % sets]
+                ev[0].record()
+                y_r, x2_r, x3_r, idx_r = rc.full_convlogic_forward(xi, wp, sel, 1, 1, 1, 1, 3, 3)
+                ev[1].record()
+                gx_r, gx2_r, gx3_r = rc.full_convlogic_backward_x(gi, xi, x2_r, x3_r, wp, idx_r, sel, 1, 1, 1, 1)
+                rc.full_convlogic_backward_weight(gx2_r, gx3_r, gi, xi, x2_r, x3_r, idx_r, sel, 1, 1, 1, 1)
+                ev[2].record()
+                torch.cuda.synchronize()
+                if i:  # first pass warms the allocator
+                    t_f += ev[0].elapsed_time(ev[1])
+                    t_b += ev[1].elapsed_time(ev[2])
+            del y_r, x2_r, x3_r, idx_r, gx_r, gx2_r, gx3_r
+            ref_cuda = {"fwd_ms": t_f / nrep, "bwd_ms": t_b / nrep, "images_per_s": C2["batch"] / ((t_f + t_b) / nrep * 1e-3),
+                        "what": "lkorinek/convlogic full_convlogic_forward + backward_x + backward_weight (its CUDA extension "
+                                "compiled unmodified for sm_100a), same inputs, mixture given as probabilities"}
+
     # ---- end-to-end: host buffers in, gradients out, copies inside the timed region ----
     xs_p = [x.pin_memory() for x in xs_h]
     gys_p = [g.pin_memory() for g in gys_h]
@@ -309,6 +339,8 @@ def run_ours(args):
                      "step_frac": alg["step"] / (ms / args.steps * 1e-3) / 1e9 / peak},
         "clocks": clocks,
     }
+    if ref_cuda is not None:
+        out["reference_cuda_same_gpu"] = ref_cuda
     if world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline_c2(sample_batch=args.cpu_sample, passes=1)
     print(json.dumps(out))

@@ -61,6 +61,8 @@ def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False
         x3 = torch.empty((n, c, ho, wo, 2), dtype=x.dtype, device=x.device)
     if want_indices:
         idx = torch.empty((n, c, (ho // 2) * (wo // 2)), dtype=torch.int32, device=x.device)
+    if n == 0 or c == 0:  # empty batch: nothing to launch
+        return y, amax, x2, x3, idx
     check(lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), ptr(amax), ptr(x2), ptr(x3), ptr(idx),
                                  n, ci, h, wd, c, *geom, wmode | _sel_flag(sel, geom), dtype_code(x), stream()))
     return y, amax, x2, x3, idx
@@ -124,6 +126,8 @@ def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
     c = w.shape[0]
     gx = torch.empty_like(x) if need_gx else None
     gw = torch.empty_like(w) if need_gw else None
+    if n == 0 or c == 0:  # empty batch: the gate gradient is an empty sum
+        return gx, (gw.zero_() if gw is not None else None)
     flag = _sel_flag(sel, geom)
     nbytes = lib().clb_convtree_bwd_scratch_bytes(n, ci, h, wd, c, *geom, int(need_gx), int(need_gw), dtype_code(x))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
@@ -263,6 +267,8 @@ def logic_fwd(x, a, b, w, wmode):
     check_input(x, a, b, w)
     i, o, bsz = _logic_dims(x, a, b, w)
     y = torch.empty((o, bsz), dtype=x.dtype, device=x.device)
+    if bsz == 0 or o == 0:
+        return y
     check(lib().clb_logic_fwd(ptr(x), ptr(a), ptr(b), ptr(w), ptr(y), i, o, bsz, wmode, dtype_code(x), stream()))
     return y
 
@@ -271,6 +277,8 @@ def logic_bwd_w(x, a, b, w, gy, wmode):
     check_input(x, a, b, w, gy)
     i, o, bsz = _logic_dims(x, a, b, w)
     gw = torch.empty_like(w)
+    if bsz == 0 or o == 0:
+        return gw.zero_()
     check(lib().clb_logic_bwd_w(ptr(x), ptr(a), ptr(b), ptr(w), ptr(gy), ptr(gw), i, o, bsz, wmode, dtype_code(x),
                                 stream()))
     return gw
@@ -282,6 +290,8 @@ def logic_bwd_x(x, a, b, w, gy, start, consumers, wmode):
     if start.dtype != torch.int64 or consumers.dtype != torch.int64 or start.numel() != i + 1 or consumers.numel() != 2 * o:
         raise RuntimeError("convlogic_b200: consumer lists must be int64 [in_dim + 1] and [2 * out_dim]")
     gx = torch.empty_like(x)
+    if bsz == 0:
+        return gx
     check(lib().clb_logic_bwd_x(ptr(x), ptr(a), ptr(b), ptr(w), ptr(gy), ptr(gx), ptr(start), ptr(consumers),
                                 i, o, bsz, wmode, dtype_code(x), stream()))
     return gx

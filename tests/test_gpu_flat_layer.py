@@ -123,3 +123,21 @@ def test_layer_stack_stays_feature_major_and_deterministic():
         y.square().sum().backward()
         outs.append((y.detach().clone(), x.grad.clone(), l1.weights.grad.clone()))
     assert all(torch.equal(u, v) for u, v in zip(*outs))
+
+
+def test_empty_batch_runs_through_a_small_stack():
+    """Edge case: a batch of zero samples gives empty outputs and zero gate gradients."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(cb.ConvLogicLayer(3, 4, complete=True), torch.nn.Flatten(), cb.LogicLayer(64, 40),
+                              cb.GroupSum(10, 2.0)).cuda().train()
+    x = torch.zeros(0, 3, 8, 8, device="cuda", requires_grad=True)
+    y = net(x)
+    assert y.shape == (0, 10)
+    y.sum().backward()
+    assert x.grad.shape == x.shape
+    for prm in net.parameters():
+        assert prm.grad is not None and float(prm.grad.abs().sum()) == 0.0
+    # the context is fine afterwards
+    assert net(torch.rand(2, 3, 8, 8, device="cuda")).shape == (2, 10)
