@@ -564,6 +564,44 @@ def run_c5(args):
     ms = _timed(step, steps, 3, world, dev)
     launches = (lib.clb_kernel_launches() - l0) * steps // (steps + 3)
     clocks = sampler.stop() if rank == 0 else None
+    # one 256000 -> 256000 layer, ours and (when built) the reference's CUDA kernels, same tensors
+    layer_cmp = None
+    if world == 1:
+        from convlogic_b200 import ops
+        from convlogic_b200._lib import W_PROB
+
+        lay = net[1]
+        xf = torch.rand(256000, 1024, device=dev)
+        gyf = torch.randn(256000, 1024, device=dev)
+        wp = torch.softmax(lay.weights.detach(), -1)
+        a_, b_, st_, cs_ = lay.indices_0, lay.indices_1, lay.given_x_indices_of_y_start, lay.given_x_indices_of_y
+
+        def t3(fwd, bw, bx):
+            out = []
+            for fn in (fwd, bw, bx):
+                fn()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(3):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                out.append(round(e0.elapsed_time(e1) / 3, 4))
+            return out
+
+        layer_cmp = {"ours_ms_fwd_bwdw_bwdx": t3(lambda: ops.logic_fwd(xf, a_, b_, wp, W_PROB), lambda: ops.logic_bwd_w(xf, a_, b_, wp, gyf, W_PROB),
+                                                  lambda: ops.logic_bwd_x(xf, a_, b_, wp, gyf, st_, cs_, W_PROB))}
+        try:
+            from oracle.build_ref import load_ref
+
+            rf = load_ref("difflogic_cuda")
+        except Exception:
+            rf = None
+        if rf is not None:
+            layer_cmp["reference_cuda_ms_fwd_bwdw_bwdx"] = t3(lambda: rf.forward(xf, a_, b_, wp), lambda: rf.backward_w(xf, a_, b_, gyf),
+                                                              lambda: rf.backward_x(xf, a_, b_, wp, gyf, st_, cs_))
+        del xf, gyf
     peak, kind = measured_peaks()
     alg = 39.9e9
     _finish({
@@ -576,6 +614,7 @@ def run_c5(args):
         "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
                      "note": "whole step, 39.9 GB algorithmic"},
+        "one_layer_256000x1024": layer_cmp,
         "clocks": clocks}, world)
 
 

@@ -72,9 +72,22 @@ class ConvLogicLayer(nn.Module):
         PackBitsTensor ``[C_out, H_out/2, W_out/2, words]``)."""
         assert not self.training, "PackBitsTensor is not supported for the differentiable training mode."
         assert self.complete, "packed inference is defined for the complete block"
-        assert x.t.dim() == 4 and x.t.shape[0] == self.in_channels, (tuple(x.t.shape), self.in_channels)
         gate_ids = self.weights.argmax(-1).to(torch.uint8)
-        y = ops.packed_convtree(x.t, gate_ids, self.selection.contiguous(), (*self.stride, *self.padding, *self.kernel))
+        geom = (*self.stride, *self.padding, *self.kernel)
+        sel = self.selection.contiguous()
+        if not x.slab:
+            assert x.t.dim() == 4 and x.t.shape[0] == self.in_channels, (tuple(x.t.shape), self.in_channels)
+        # The slab layout (one contiguous image per channel and 128-sample slab) is what the fast kernel wants;
+        # activations stay in it from block to block and return to rows at Flatten / GroupSum.
+        h, w = (x.t.shape[2], x.t.shape[3]) if x.slab else (x.t.shape[1], x.t.shape[2])
+        ho = (h + 2 * self.padding[0] - self.kernel[0]) // self.stride[0] + 1
+        wo = (w + 2 * self.padding[1] - self.kernel[1]) // self.stride[1] + 1
+        fits = self.stride == (1, 1) and ho > 0 and wo > 0 and ho % 2 == 0 and wo % 2 == 0 and (ho // 2) * (wo // 2) <= 256
+        slab = x.t if x.slab else (ops.packed_to_slab(x.t) if fits else None)
+        if slab is not None and fits:
+            assert slab.shape[0] == self.in_channels, (tuple(slab.shape), self.in_channels)
+            return PackBitsTensor.from_packed(ops.packed_convtree_slab(slab, gate_ids, sel, geom), x.pad_len, slab=True)
+        y = ops.packed_convtree(x.rows(), gate_ids, sel, geom)
         return PackBitsTensor.from_packed(y, x.pad_len)
 
     def unpack_selection(self, selection):

@@ -321,6 +321,249 @@ __global__ void __launch_bounds__(256) packed_convtree_v4_kernel(const uint4 *__
     }
 }
 
+// ---- slab layout --------------------------------------------------------------------------------
+// The [C][H][W][words] layout makes a pixel's words contiguous, which suits the flat layers but forces the
+// conv block to gather 32 scattered 16-byte pieces per output piece through L1/L2.  In the slab layout
+// [C][U][H][W] of uint4 (U = words/2; one uint4 = 128 samples) the image of one (channel, sample slab) is
+// contiguous.  A persistent block walks (output channel, group of UB slabs) items; for each it copies the two
+// channel planes the output channel reads into a shared tile (halo zeroed once, columns de-interleaved as in
+// the float forward so that window columns are consecutive 16-byte slots) with cp.async into the buffer the
+// previous item is not using, so the copy of item i+1 runs under the gate tree of item i.  Every tap is then a
+// conflict-free 128-bit shared-memory load.  The per-item bookkeeping (tap offsets, gate ids, the two
+// channels) is parsed two items ahead by eight threads into a small shared record, and a gate is applied by a
+// block-uniform switch over its id to eight words at a time: one LOP3 per word instead of the three a
+// multiplexer with run-time masks needs.  UB * windows-per-image <= 256 threads.  An output channel with a tap
+// on a third channel or outside the kernel window (hand-made selections only) takes a global-memory path.
+struct SlabShape {
+    int Ci, H, W, C, Ho, Wo, ph, pw, kh, kw;
+    int U, UB;       // slabs in total / per block
+    int PH, pwh;     // padded rows, uint4 slots per column-parity plane of a padded row
+    int CS, SS;      // plane stride (one channel slot) and slab stride in the tile, in uint4
+    int n_ug, items; // slab groups per channel, items = C * n_ug
+    int per_thread;  // copies per thread and channel plane group: ceil(UB*H*W / threads)
+};
+
+struct __align__(16) SlabRec {
+    int tb0[8], tb1[8]; // tile offsets of tap k for the left / right conv column of a window
+    int op[8];          // gate ids (7 used)
+    int ch[2], nst, all_in_tile;
+    int word[8];        // the raw selection words (global path)
+};
+
+__device__ __forceinline__ void cp_async16(uint4 *dst_shared, const uint4 *src)
+{
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_shared);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// o[w % M] (|)= gate(a[w], b[w]) for N words; `op` is uniform over the block, so the switch does not diverge
+template <int N, int M, bool OR_INTO>
+__device__ __forceinline__ void gate_words(int op, const unsigned (&a)[N], const unsigned (&b)[N], unsigned (&o)[M])
+{
+#define CLB_GATE_CASE(i, expr)                                                                                                   \
+    case i:                                                                                                                      \
+        _Pragma("unroll") for (int w = 0; w < N; ++w)                                                                            \
+        {                                                                                                                        \
+            const unsigned A = a[w], B = b[w];                                                                                   \
+            const unsigned v = (expr);                                                                                           \
+            o[w % M] = OR_INTO ? (o[w % M] | v) : v;                                                                             \
+        }                                                                                                                        \
+        break;
+    switch (op & 15) {
+        CLB_GATE_CASE(0, (A & 0u) & B)
+        CLB_GATE_CASE(1, A & B)
+        CLB_GATE_CASE(2, A & ~B)
+        CLB_GATE_CASE(3, A | (B & 0u))
+        CLB_GATE_CASE(4, ~A & B)
+        CLB_GATE_CASE(5, B | (A & 0u))
+        CLB_GATE_CASE(6, A ^ B)
+        CLB_GATE_CASE(7, A | B)
+        CLB_GATE_CASE(8, ~(A | B))
+        CLB_GATE_CASE(9, ~(A ^ B))
+        CLB_GATE_CASE(10, ~B | (A & 0u))
+        CLB_GATE_CASE(11, A | ~B)
+        CLB_GATE_CASE(12, ~A | (B & 0u))
+        CLB_GATE_CASE(13, ~A | B)
+        CLB_GATE_CASE(14, ~(A & B))
+        CLB_GATE_CASE(15, ~(A & 0u) | B)
+    }
+#undef CLB_GATE_CASE
+}
+
+// one pooled output piece straight from global memory, for selections the tile does not cover
+__device__ __noinline__ uint4 slab_window_global(const uint4 *__restrict__ xg, const SlabRec &R, const SlabShape &s, int py, int px)
+{
+    const int HW = s.H * s.W;
+    Masks32 gm[7];
+    for (int g = 0; g < 7; ++g) {
+        const int op = R.op[g];
+        gm[g].m00 = (op & 8) ? ~0u : 0u, gm[g].m01 = (op & 4) ? ~0u : 0u, gm[g].m10 = (op & 2) ? ~0u : 0u, gm[g].m11 = (op & 1) ? ~0u : 0u;
+    }
+    uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+    for (int d = 0; d < 4; ++d) {
+        uint4 a[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int word = R.word[k];
+            const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1);
+            const int iy = 2 * py + (d >> 1) + ((word >> 8) & 0xFF) - s.ph, ix = 2 * px + (d & 1) + (word & 0xFF) - s.pw;
+            a[k] = ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) ? __ldg(xg + (size_t)ch * s.U * HW + iy * s.W + ix)
+                                                                                : make_uint4(0u, 0u, 0u, 0u);
+        }
+        const uint4 g0 = mux128(gm[0], a[0], a[1]), g1 = mux128(gm[1], a[2], a[3]);
+        const uint4 g2 = mux128(gm[2], a[4], a[5]), g3 = mux128(gm[3], a[6], a[7]);
+        const uint4 t0 = mux128(gm[4], g0, g1), t1 = mux128(gm[5], g2, g3);
+        const uint4 z = mux128(gm[6], t0, t1);
+        acc.x |= z.x, acc.y |= z.y, acc.z |= z.z, acc.w |= z.w;
+    }
+    return acc;
+}
+
+// one record per output channel
+__global__ void packed_slab_records_kernel(const uint8_t *__restrict__ ops, const int32_t *__restrict__ sel, SlabRec *__restrict__ recs,
+                                           SlabShape s)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= s.C) return;
+    SlabRec R;
+    int ch0 = 0, ch1 = -1;
+    bool all = true;
+    for (int k = 0; k < 8; ++k) {
+        const int w = sel[c * 8 + k];
+        const int ch = min((w >> 16) & 0xFFFF, s.Ci - 1), r = (w >> 8) & 0xFF, sx = w & 0xFF;
+        if (k == 0) ch0 = ch;
+        if (ch1 < 0 && ch != ch0) ch1 = ch;
+        all = all && (ch == ch0 || ch == ch1) && r < s.kh && sx < s.kw;
+        const int rr = min(r, s.kh - 1), sc = min(sx, s.kw - 1);
+        const int base = (ch == ch0 ? 0 : s.CS) + rr * 2 * s.pwh;
+        R.tb0[k] = base + (sc & 1) * s.pwh + (sc >> 1);
+        R.tb1[k] = base + ((sc + 1) & 1) * s.pwh + ((sc + 1) >> 1);
+        R.word[k] = w;
+        R.op[k] = k < 7 ? ops[c * 7 + k] : 0;
+    }
+    R.ch[0] = ch0, R.ch[1] = ch1 < 0 ? ch0 : ch1, R.nst = ch1 < 0 ? 1 : 2, R.all_in_tile = all;
+    recs[c] = R;
+}
+
+__global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint4 *__restrict__ x,
+                                                                      const SlabRec *__restrict__ recs, uint4 *__restrict__ y,
+                                                                      SlabShape s)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ __align__(16) SlabRec rec[3];
+    uint4 *tile = reinterpret_cast<uint4 *>(smem_raw);
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int HW = s.H * s.W;
+    const int buf_elems = s.UB * s.SS;
+    int *copy_off = reinterpret_cast<int *>(tile + 2 * buf_elems); // [per_thread][nt] tile offsets of a thread's copies
+    for (int i = tid; i < 2 * buf_elems; i += nt) tile[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int q = tid; q < s.per_thread * nt; q += nt) {
+        const int ub = q / HW, p = q - ub * HW, row = p / s.W, xp = p - row * s.W + s.pw;
+        copy_off[q] = ub * s.SS + (row + s.ph) * 2 * s.pwh + (xp & 1) * s.pwh + (xp >> 1);
+    }
+
+    // the record of an item's output channel: 9 x 16 bytes from the table the record kernel wrote
+    auto fetch_rec = [&](int item, SlabRec &R) {
+        for (int j = tid; j < (int)(sizeof(SlabRec) / 16); j += nt) // a block may have fewer threads than pieces
+            cp_async16(reinterpret_cast<uint4 *>(&R) + j, reinterpret_cast<const uint4 *>(recs + item / s.n_ug) + j);
+    };
+    // copies of the planes of an item whose record is already visible
+    auto stage = [&](int item, const SlabRec &R, uint4 *dst) {
+        const int c = item / s.n_ug, u0 = (item - c * s.n_ug) * s.UB;
+        const int n = min(s.UB, s.U - u0) * HW;
+        if (!R.all_in_tile) return;
+        for (int slot = 0; slot < R.nst; ++slot) {
+            const uint4 *src = x + ((size_t)R.ch[slot] * s.U + u0) * HW;
+            uint4 *d = dst + slot * s.CS;
+            for (int j = 0, q = tid; j < s.per_thread && q < n; ++j, q += nt) cp_async16(d + copy_off[q], src + q);
+        }
+    };
+
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
+    const int ub = tid / I, win = tid - ub * I;
+    const int py = win / Wp, px = win - py * Wp;
+    const int toff = ub * s.SS + 2 * py * 2 * s.pwh + px;
+    const int RS = 2 * s.pwh;
+
+    const int first = blockIdx.x, stride = gridDim.x;
+    if (first < s.items) fetch_rec(first, rec[0]);
+    if (first + stride < s.items) fetch_rec(first + stride, rec[1]);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads(); // records, copy offsets and halo zeros in place
+    if (first < s.items) stage(first, rec[0], tile);
+    cp_async_commit();
+    int cur = 0, r0 = 0; // tile buffer and record slot of the current item
+    for (int item = first; item < s.items; item += stride, cur ^= 1, r0 = r0 == 2 ? 0 : r0 + 1) {
+        const int r1 = r0 == 2 ? 0 : r0 + 1, r2 = r1 == 2 ? 0 : r1 + 1;
+        // one barrier per item: this item's planes and the next item's record have landed, and every thread is
+        // done with the previous item, whose tile buffer and whose predecessor's record slot are refilled now
+        cp_async_wait<0>();
+        __syncthreads();
+        if (item + 2 * stride < s.items) fetch_rec(item + 2 * stride, rec[r2]);
+        if (item + stride < s.items) stage(item + stride, rec[r1], tile + (cur ^ 1) * buf_elems);
+        cp_async_commit();
+
+        const SlabRec &R = rec[r0];
+        const int c = item / s.n_ug, u0 = (item - c * s.n_ug) * s.UB;
+        if (ub < min(s.UB, s.U - u0)) {
+            uint4 out;
+            if (R.all_in_tile) {
+                const uint4 *t = tile + cur * buf_elems + toff;
+                unsigned acc[4] = {0u, 0u, 0u, 0u};
+                // taps of the next gate are fetched before the current gate's switch so that the shared-memory
+                // latency runs under it; the row loop stays rolled to keep the sixteen-way switches few
+                uint4 a0 = t[R.tb0[0]], a1 = t[R.tb1[0]], b0 = t[R.tb0[1]], b1 = t[R.tb1[1]];
+#pragma unroll 1
+                for (int dy = 0; dy < 2; ++dy) {
+                    unsigned g[4][8];
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const unsigned a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                        const unsigned b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                        const int pn = (p + 1) & 3, off = p == 3 ? RS : dy * RS; // after the last row: a harmless reload
+                        a0 = t[R.tb0[2 * pn] + off], a1 = t[R.tb1[2 * pn] + off];
+                        b0 = t[R.tb0[2 * pn + 1] + off], b1 = t[R.tb1[2 * pn + 1] + off];
+                        gate_words<8, 8, false>(R.op[p], a, b, g[p]);
+                    }
+                    gate_words<8, 8, false>(R.op[4], g[0], g[1], g[0]);
+                    gate_words<8, 8, false>(R.op[5], g[2], g[3], g[2]);
+                    gate_words<8, 4, true>(R.op[6], g[0], g[2], acc);
+                }
+                out = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+                out = slab_window_global(x + (size_t)(u0 + ub) * HW, R, s, py, px);
+            }
+            y[((size_t)c * s.U + u0 + ub) * I + win] = out;
+        }
+    }
+    cp_async_wait<0>();
+}
+
+// rows [F][2U] of 64-bit words  <->  slab [C][U][HW] of uint4, F = C*HW (pure data movement)
+__global__ void packed_rows_to_slab_kernel(const uint4 *__restrict__ rows, uint4 *__restrict__ slab, int C, int HW, int U, int to_slab)
+{
+    const long long total = (long long)C * HW * U;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        // i enumerates the rows layout: ((c*HW + p)*U + u)
+        const int u = (int)(i % U);
+        const long long cp = i / U;
+        const int p = (int)(cp % HW);
+        const long long c = cp / HW;
+        const long long j = (c * U + u) * HW + p;
+        if (to_slab)
+            slab[j] = rows[i];
+        else
+            slab[i] = rows[j]; // here `rows` is the slab tensor and `slab` the rows tensor
+    }
+}
+
 } // namespace clb
 
 using namespace clb;
@@ -440,5 +683,59 @@ extern "C" int clb_packed_convtree(const void *x, const uint8_t *ops, const int3
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
         packed_convtree_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)x, ops, sel, (uint8_t *)y, s, rowbytes);
     }
+    return check_launch();
+}
+
+extern "C" int clb_packed_layout(const void *src, void *dst, int64_t C, int64_t HW, int64_t U, int to_slab, void *stream)
+{
+    if (!src || !dst || C < 0 || HW < 0 || U < 0) return CLB_ERR_ARG;
+    if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return CLB_ERR_ARG;
+    if (C > 0x7fffffff || HW > 0x7fffffff || U > 0x7fffffff) return CLB_ERR_SHAPE;
+    const long long total = C * HW * U;
+    if (total == 0) return CLB_OK;
+    packed_rows_to_slab_kernel<<<flat_grid(total, 256), 256, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, (int)C, (int)HW,
+                                                                                        (int)U, to_slab);
+    return check_launch();
+}
+
+extern "C" int64_t clb_packed_convtree_slab_scratch_bytes(int C) { return C < 0 ? 0 : (int64_t)C * (int64_t)sizeof(SlabRec); }
+
+extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const int32_t *sel, void *y, void *scratch, int Ci, int H,
+                                        int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t U, void *stream)
+{
+    if (!conv_args_ok(1, Ci, H, W, C, sh, sw, ph, pw, kh, kw) || !x || !ops || !sel || !y || U < 0) return CLB_ERR_ARG;
+    if (!aligned_to(x, 16) || !aligned_to(y, 16) || (C > 0 && (!scratch || !aligned_to(scratch, 16)))) return CLB_ERR_ARG;
+    if (sh != 1 || sw != 1) return CLB_ERR_SHAPE; // the rows layout serves other strides
+    SlabShape s;
+    s.Ci = Ci, s.H = H, s.W = W, s.C = C, s.ph = ph, s.pw = pw, s.kh = kh, s.kw = kw;
+    s.Ho = conv_out(H, ph, kh, 1), s.Wo = conv_out(W, pw, kw, 1);
+    if (s.Ho <= 0 || s.Wo <= 0) return CLB_ERR_SHAPE;
+    if ((s.Ho & 1) || (s.Wo & 1)) return CLB_ERR_ODD_OUTPUT;
+    const int I = (s.Ho / 2) * (s.Wo / 2);
+    if (C > 65535 || I > 256 || U > 0x7fffffff) return CLB_ERR_SHAPE;
+    if ((long long)Ci * U * H * W >= (1LL << 31) || (long long)C * U * I >= (1LL << 31)) return CLB_ERR_SHAPE;
+    if (C == 0 || U == 0) return CLB_OK;
+    s.U = (int)U;
+    s.UB = 256 / I;
+    if (s.UB > s.U) s.UB = s.U;
+    s.PH = H + 2 * ph;
+    s.pwh = (W + 2 * pw + 1) / 2;
+    s.CS = s.PH * 2 * s.pwh;
+    s.SS = 2 * s.CS;
+    const int threads = s.UB * I;
+    s.per_thread = (s.UB * H * W + threads - 1) / threads;
+    const size_t smem = 2 * (size_t)s.UB * s.SS * 16 + (size_t)s.per_thread * threads * 4; // two buffers + copy offsets
+    if (smem > 200 * 1024) return CLB_ERR_SHAPE;
+    s.n_ug = (s.U + s.UB - 1) / s.UB;
+    s.items = C * s.n_ug;
+    auto k = packed_convtree_slab_kernel;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    int bps = (int)((227 * 1024) / (smem + 1024));
+    if (bps > 2) bps = 2;
+    if (bps < 1) bps = 1;
+    int grid = 148 * bps;
+    if (grid > s.items) grid = s.items;
+    packed_slab_records_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ops, sel, (SlabRec *)scratch, s);
+    k<<<grid, threads, smem, (cudaStream_t)stream>>>((const uint4 *)x, (const SlabRec *)scratch, (uint4 *)y, s);
     return check_launch();
 }

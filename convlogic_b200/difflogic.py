@@ -104,7 +104,8 @@ class LogicLayer(torch.nn.Module):
     def forward_cuda_eval(self, x: PackBitsTensor):
         """Packed inference; returns a new PackBitsTensor (the reference rebinds ``x.t``)."""
         assert not self.training
-        t = x.t.reshape(-1, x.t.shape[-1])
+        t = x.rows()
+        t = t.reshape(-1, t.shape[-1])
         assert t.shape[0] == self.in_dim, (tuple(t.shape), self.in_dim)
         gate_ids = self.weights.argmax(-1).to(torch.uint8)
         y = ops.packed_logic(t, self.indices_0, self.indices_1, gate_ids)

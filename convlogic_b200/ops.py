@@ -363,3 +363,46 @@ def packed_convtree(x, ops, sel, geom):
     check(lib().clb_packed_convtree(ptr(x), ptr(ops), ptr(sel), ptr(y), ci, h, w, c, *geom, words, _bits_of(x),
                                     stream()))
     return y
+
+
+# ---------------------------------------------------------------- packed conv block, slab layout
+def packed_to_slab(t):
+    """[C, H, W, words] -> [C, U, H, W, 16 // itemsize] (U 16-byte units per pixel row); None when a pixel row
+    is not a multiple of 16 bytes."""
+    check_input(t)
+    c, h, w, words = t.shape
+    rowbytes = words * t.element_size()
+    if rowbytes % 16 or t.numel() == 0:
+        return None
+    u = rowbytes // 16
+    out = torch.empty((c, u, h, w, 16 // t.element_size()), dtype=t.dtype, device=t.device)
+    check(lib().clb_packed_layout(ptr(t), ptr(out), c, h * w, u, 1, stream()))
+    return out
+
+
+def packed_to_rows(slab):
+    """[C, U, H, W, 16 // itemsize] -> [C, H, W, words]."""
+    check_input(slab)
+    c, u, h, w, per = slab.shape
+    out = torch.empty((c, h, w, u * per), dtype=slab.dtype, device=slab.device)
+    check(lib().clb_packed_layout(ptr(slab), ptr(out), c, h * w, u, 0, stream()))
+    return out
+
+
+def packed_convtree_slab(x, ops, sel, geom):
+    """Packed fused block on the slab layout; raises ValueError for shapes it does not cover."""
+    check_input(x, ops, sel)
+    ci, u, h, w, per = x.shape
+    c = sel.shape[0]
+    _sel_ok(sel, c)
+    if ops.dtype != torch.uint8 or ops.shape != (c, 7):
+        raise RuntimeError(f"convlogic_b200: gate ids must be uint8 [{c}, 7]")
+    ho, wo = _out_hw(h, w, *geom)
+    if ho <= 0 or wo <= 0 or ho % 2 or wo % 2:
+        raise RuntimeError(
+            "Output height and width after convolution must be divisible by 2 for 2x2 max pooling, "
+            f"but got H_out={ho}, W_out={wo}")
+    y = torch.empty((c, u, ho // 2, wo // 2, per), dtype=x.dtype, device=x.device)
+    scratch = torch.empty(max(lib().clb_packed_convtree_slab_scratch_bytes(c), 16), dtype=torch.uint8, device=x.device)
+    check(lib().clb_packed_convtree_slab(ptr(x), ptr(ops), ptr(sel), ptr(y), ptr(scratch), ci, h, w, c, *geom, u, stream()))
+    return y

@@ -26,12 +26,19 @@ class PackBitsTensor:
         flat = t.reshape(t.shape[0], -1)
         packed, self.pad_len = ops.pack_bits(flat, bit_count, sample_major=True)
         self.t = packed.view(*t.shape[1:], packed.shape[-1]) if t.dim() == 4 else packed
+        self.slab = False
 
     @classmethod
-    def from_packed(cls, t, pad_len):
+    def from_packed(cls, t, pad_len, slab=False):
+        """``slab=True``: ``t`` is a conv activation in the slab layout [C, U, H, W, 16 // itemsize]
+        (see ``ops.packed_to_slab``) instead of [C, H, W, words]."""
         self = cls.__new__(cls)
-        self.t, self.pad_len, self.bit_count = t, pad_len, t.element_size() * 8
+        self.t, self.pad_len, self.bit_count, self.slab = t, pad_len, t.element_size() * 8, slab
         return self
+
+    def rows(self):
+        """The tensor in the rows layout [..., words] (converts a slab-layout activation)."""
+        return ops.packed_to_rows(self.t) if self.slab else self.t
 
     @property
     def is_cuda(self):
@@ -45,12 +52,14 @@ class PackBitsTensor:
         return self
 
     def group_sum(self, k):
-        return ops.group_popcount(self.t.reshape(-1, self.t.shape[-1]), self.pad_len, k)
+        t = self.rows()
+        return ops.group_popcount(t.reshape(-1, t.shape[-1]), self.pad_len, k)
 
     def flatten(self, start_dim=0, end_dim=-1, **kwargs):
         """Returns the tensor itself viewed as [features, words]; arguments are ignored."""
-        if self.t.dim() != 2:
-            return PackBitsTensor.from_packed(self.t.reshape(-1, self.t.shape[-1]), self.pad_len)
+        if self.slab or self.t.dim() != 2:
+            t = self.rows()
+            return PackBitsTensor.from_packed(t.reshape(-1, t.shape[-1]), self.pad_len)
         return self
 
     def _get_member_repr(self, member):
@@ -60,5 +69,6 @@ class PackBitsTensor:
         return f"{' '.join(rows[:3])} ... {rows[-1]}"
 
     def __repr__(self):
-        t2 = self.t.reshape(-1, self.t.shape[-1]).cpu()
+        t2 = self.rows()
+        t2 = t2.reshape(-1, t2.shape[-1]).cpu()
         return "\n".join(self._get_member_repr(item.tolist()) for item in t2)

@@ -220,6 +220,19 @@ int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, v
                         int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t words, int bits,
                         void *stream);
 
+/* The same block on the SLAB layout [C][U][H][W] of 16-byte units (U = words / 2 for 64-bit words; one unit
+ * = 128 samples), in which the image of one (channel, sample slab) is contiguous and can be staged in shared
+ * memory.  Stride 1, at most 256 pooled outputs per image (CLB_ERR_SHAPE otherwise: use the rows layout).
+ * x [Ci,U,H,W] units -> y [C,U,Ho/2,Wo/2] units.  clb_packed_layout converts between rows [C*HW, 2U words]
+ * and slab [C,U,HW] (to_slab != 0: src is rows; else src is slab).  `scratch`: device memory of
+ * clb_packed_convtree_slab_scratch_bytes(C) bytes, 16-byte aligned, holding the per-channel tap records the
+ * call derives from `sel` and `ops`.  No counterpart in the reference. */
+int clb_packed_layout(const void *src, void *dst, int64_t C, int64_t HW, int64_t U, int to_slab, void *stream);
+int64_t clb_packed_convtree_slab_scratch_bytes(int C);
+int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const int32_t *sel, void *y, void *scratch, int Ci,
+                             int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t U,
+                             void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,11 +79,53 @@ def test_packed_conv_block(bits, batch, geom):
     y = layer(p)
     want = oracle.packed_convtree(oracle.pack_bits(xb.reshape(batch, -1).T, bits)[0].reshape(ci, h, w, -1),
                                   layer.weights.argmax(-1).cpu().numpy().astype(np.uint8), sel.numpy(), st, pd, k)
-    got = oracle.unpack_bits(y.t.cpu().numpy(), batch)
+    assert y.slab == (st == 1 and (batch + bits - 1) // bits * bits % 128 == 0)
+    got = oracle.unpack_bits(y.rows().cpu().numpy(), batch)
     assert np.array_equal(got, oracle.unpack_bits(want, batch))
     with torch.no_grad():
         yf = layer(torch.from_numpy(xb).float().cuda())
     assert np.array_equal(np.moveaxis(got, -1, 0).astype(np.float32), yf.cpu().numpy())
+
+
+@pytest.mark.parametrize("geom", [(3, 40, 32, 32, 1, 3), (16, 24, 16, 16, 1, 3), (24, 16, 8, 8, 1, 3), (7, 5, 14, 10, 0, 5),
+                                  (2, 9, 6, 6, 2, 3), (5, 7, 4, 4, 1, 3), (3, 3, 2, 2, 1, 3)])
+@pytest.mark.parametrize("batch", [128, 1000])
+def test_packed_conv_block_slab_layout_equals_rows_layout(geom, batch):
+    """The slab-layout kernel (staged channel planes, and its global-gather path when a window's taps span
+    more channels than are staged) gives the very words of the rows-layout kernel; layout round trip is exact."""
+    from convlogic_b200 import ops
+
+    ci, c, h, w, pd, k = geom
+    rng = np.random.default_rng(ci * 1000 + batch)
+    sel = random_selection(rng, c, ci, k, k).cuda()
+    gate_ids = torch.from_numpy(rng.integers(0, 16, (c, 7)).astype(np.uint8)).cuda()
+    words = (batch + 63) // 64
+    words += words % 2
+    x = torch.from_numpy(rng.integers(-2**63, 2**63 - 1, (ci, h, w, words), dtype=np.int64)).cuda()
+    slab = ops.packed_to_slab(x)
+    assert slab.shape == (ci, words // 2, h, w, 2)
+    assert torch.equal(ops.packed_to_rows(slab), x)
+    g = (1, 1, pd, pd, k, k)
+    want = ops.packed_convtree(x, gate_ids, sel, g)
+    got = ops.packed_convtree_slab(slab, gate_ids, sel, g)
+    assert torch.equal(ops.packed_to_rows(got), want)
+    ref = oracle.packed_convtree(x.cpu().numpy(), gate_ids.cpu().numpy(), sel.cpu().numpy(), 1, pd, k)
+    assert np.array_equal(want.cpu().numpy(), ref)
+
+
+def test_packed_slab_rejects_what_it_does_not_cover():
+    from convlogic_b200 import ops
+
+    rng = np.random.default_rng(0)
+    sel = random_selection(rng, 4, 3, 3, 3).cuda()
+    gate_ids = torch.zeros(4, 7, dtype=torch.uint8).cuda()
+    slab = torch.zeros(3, 1, 8, 8, 2, dtype=torch.int64).cuda()
+    with pytest.raises(Exception):
+        ops.packed_convtree_slab(slab, gate_ids, sel, (2, 2, 1, 1, 3, 3))   # stride 2
+    big = torch.zeros(3, 1, 36, 36, 2, dtype=torch.int64).cuda()
+    with pytest.raises(Exception):
+        ops.packed_convtree_slab(big, gate_ids, sel, (1, 1, 1, 1, 3, 3))    # 18*18 pooled outputs > 256
+    assert ops.packed_to_slab(torch.zeros(3, 4, 4, 3, dtype=torch.int64).cuda()) is None
 
 
 def test_packed_model_equals_float_eval_model():
