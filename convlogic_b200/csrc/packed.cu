@@ -344,7 +344,7 @@ struct SlabShape {
 };
 
 struct __align__(16) SlabRec {
-    int tb0[8], tb1[8]; // tile offsets of tap k for the left / right conv column of a window
+    int tb0[8], tb1[8]; // tile offsets (bytes) of tap k for the left / right conv column of a window
     int op[8];          // gate ids (7 used)
     int ch[2], nst, all_in_tile;
     int word[8];        // the raw selection words (global path)
@@ -362,17 +362,17 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// o[w % M] (|)= gate(a[w], b[w]) for N words; `op` is uniform over the block, so the switch does not diverge
-template <int N, int M, bool OR_INTO>
-__device__ __forceinline__ void gate_words(int op, const unsigned (&a)[N], const unsigned (&b)[N], unsigned (&o)[M])
+// a[w] = gate(a[w], b[w]) for N words, in place so that every case leaves its result in the registers the
+// operand came in; `op` is uniform over the block, so the switch does not diverge
+template <int N>
+__device__ __forceinline__ void gate_words(int op, unsigned (&a)[N], const unsigned (&b)[N])
 {
 #define CLB_GATE_CASE(i, expr)                                                                                                   \
     case i:                                                                                                                      \
         _Pragma("unroll") for (int w = 0; w < N; ++w)                                                                            \
         {                                                                                                                        \
             const unsigned A = a[w], B = b[w];                                                                                   \
-            const unsigned v = (expr);                                                                                           \
-            o[w % M] = OR_INTO ? (o[w % M] | v) : v;                                                                             \
+            a[w] = (expr);                                                                                                       \
         }                                                                                                                        \
         break;
     switch (op & 15) {
@@ -394,6 +394,13 @@ __device__ __forceinline__ void gate_words(int op, const unsigned (&a)[N], const
         CLB_GATE_CASE(15, ~(A & 0u) | B)
     }
 #undef CLB_GATE_CASE
+}
+
+// two 16-byte shared-memory loads (left and right conv column of a tap) into eight words
+__device__ __forceinline__ void lds_pair(unsigned (&d)[8], unsigned addr0, unsigned addr1)
+{
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(addr0));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]) : "r"(addr1));
 }
 
 // one pooled output piece straight from global memory, for selections the tile does not cover
@@ -442,8 +449,8 @@ __global__ void packed_slab_records_kernel(const uint8_t *__restrict__ ops, cons
         all = all && (ch == ch0 || ch == ch1) && r < s.kh && sx < s.kw;
         const int rr = min(r, s.kh - 1), sc = min(sx, s.kw - 1);
         const int base = (ch == ch0 ? 0 : s.CS) + rr * 2 * s.pwh;
-        R.tb0[k] = base + (sc & 1) * s.pwh + (sc >> 1);
-        R.tb1[k] = base + ((sc + 1) & 1) * s.pwh + ((sc + 1) >> 1);
+        R.tb0[k] = 16 * (base + (sc & 1) * s.pwh + (sc >> 1));
+        R.tb1[k] = 16 * (base + ((sc + 1) & 1) * s.pwh + ((sc + 1) >> 1));
         R.word[k] = w;
         R.op[k] = k < 7 ? ops[c * 7 + k] : 0;
     }
@@ -469,13 +476,14 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
     }
 
     // the record of an item's output channel: 9 x 16 bytes from the table the record kernel wrote
-    auto fetch_rec = [&](int item, SlabRec &R) {
+    auto fetch_rec = [&](int c, SlabRec &R) {
         for (int j = tid; j < (int)(sizeof(SlabRec) / 16); j += nt) // a block may have fewer threads than pieces
-            cp_async16(reinterpret_cast<uint4 *>(&R) + j, reinterpret_cast<const uint4 *>(recs + item / s.n_ug) + j);
+            cp_async16(reinterpret_cast<uint4 *>(&R) + j, reinterpret_cast<const uint4 *>(recs + c) + j);
     };
     // copies of the planes of an item whose record is already visible
-    auto stage = [&](int item, const SlabRec &R, uint4 *dst) {
-        const int c = item / s.n_ug, u0 = (item - c * s.n_ug) * s.UB;
+    // copies of the planes of an item whose record is already visible
+    auto stage = [&](int ug, const SlabRec &R, uint4 *dst) {
+        const int u0 = ug * s.UB;
         const int n = min(s.UB, s.U - u0) * HW;
         if (!R.all_in_tile) return;
         for (int slot = 0; slot < R.nst; ++slot) {
@@ -491,50 +499,74 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
     const int toff = ub * s.SS + 2 * py * 2 * s.pwh + px;
     const int RS = 2 * s.pwh;
 
+    // items are (output channel c, slab group ug), ug fastest; a block takes every gridDim.x-th one and keeps the
+    // (c, ug) of its current and next two items by carrying additions instead of dividing
     const int first = blockIdx.x, stride = gridDim.x;
-    if (first < s.items) fetch_rec(first, rec[0]);
-    if (first + stride < s.items) fetch_rec(first + stride, rec[1]);
+    const int dc = stride / s.n_ug, dug = stride - dc * s.n_ug;
+    auto advance = [&](int &c, int &ug) {
+        c += dc, ug += dug;
+        if (ug >= s.n_ug) ug -= s.n_ug, ++c;
+    };
+    int c0 = first / s.n_ug, ug0 = first - c0 * s.n_ug, c1 = c0, ug1 = ug0;
+    advance(c1, ug1);
+    int c2 = c1, ug2 = ug1;
+    advance(c2, ug2);
+    if (c0 < s.C) fetch_rec(c0, rec[0]);
+    if (c1 < s.C) fetch_rec(c1, rec[1]);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads(); // records, copy offsets and halo zeros in place
-    if (first < s.items) stage(first, rec[0], tile);
+    if (c0 < s.C) stage(ug0, rec[0], tile);
     cp_async_commit();
     int cur = 0, r0 = 0; // tile buffer and record slot of the current item
-    for (int item = first; item < s.items; item += stride, cur ^= 1, r0 = r0 == 2 ? 0 : r0 + 1) {
+    for (; c0 < s.C; cur ^= 1, r0 = r0 == 2 ? 0 : r0 + 1) {
         const int r1 = r0 == 2 ? 0 : r0 + 1, r2 = r1 == 2 ? 0 : r1 + 1;
         // one barrier per item: this item's planes and the next item's record have landed, and every thread is
         // done with the previous item, whose tile buffer and whose predecessor's record slot are refilled now
         cp_async_wait<0>();
         __syncthreads();
-        if (item + 2 * stride < s.items) fetch_rec(item + 2 * stride, rec[r2]);
-        if (item + stride < s.items) stage(item + stride, rec[r1], tile + (cur ^ 1) * buf_elems);
+        if (c2 < s.C) fetch_rec(c2, rec[r2]);
+        if (c1 < s.C) stage(ug1, rec[r1], tile + (cur ^ 1) * buf_elems);
         cp_async_commit();
+        const int c = c0, u0 = ug0 * s.UB;
+        c0 = c1, ug0 = ug1, c1 = c2, ug1 = ug2;
+        advance(c2, ug2);
 
         const SlabRec &R = rec[r0];
-        const int c = item / s.n_ug, u0 = (item - c * s.n_ug) * s.UB;
         if (ub < min(s.UB, s.U - u0)) {
             uint4 out;
             if (R.all_in_tile) {
-                const uint4 *t = tile + cur * buf_elems + toff;
+                // tile offsets in the record are in bytes; a tap's two columns for the two conv rows of the window
+                const unsigned t0 = (unsigned)__cvta_generic_to_shared(tile + cur * buf_elems + toff);
+                const int4 o0a = *reinterpret_cast<const int4 *>(&R.tb0[0]), o0b = *reinterpret_cast<const int4 *>(&R.tb0[4]);
+                const int4 o1a = *reinterpret_cast<const int4 *>(&R.tb1[0]), o1b = *reinterpret_cast<const int4 *>(&R.tb1[4]);
+                const int4 opa = *reinterpret_cast<const int4 *>(&R.op[0]), opb = *reinterpret_cast<const int4 *>(&R.op[4]);
+                const int o0[8] = {o0a.x, o0a.y, o0a.z, o0a.w, o0b.x, o0b.y, o0b.z, o0b.w};
+                const int o1[8] = {o1a.x, o1a.y, o1a.z, o1a.w, o1b.x, o1b.y, o1b.z, o1b.w};
+                const int op[7] = {opa.x, opa.y, opa.z, opa.w, opb.x, opb.y, opb.z};
                 unsigned acc[4] = {0u, 0u, 0u, 0u};
-                // taps of the next gate are fetched before the current gate's switch so that the shared-memory
-                // latency runs under it; the row loop stays rolled to keep the sixteen-way switches few
-                uint4 a0 = t[R.tb0[0]], a1 = t[R.tb1[0]], b0 = t[R.tb0[1]], b1 = t[R.tb1[1]];
-#pragma unroll 1
+                // the taps of the next gate are fetched before the current gate's switch so that the
+                // shared-memory latency runs under it
+                unsigned g[2][4][8], b[2][4][8];
+                lds_pair(g[0][0], t0 + o0[0], t0 + o1[0]);
+                lds_pair(b[0][0], t0 + o0[1], t0 + o1[1]);
+#pragma unroll
                 for (int dy = 0; dy < 2; ++dy) {
-                    unsigned g[4][8];
 #pragma unroll
                     for (int p = 0; p < 4; ++p) {
-                        const unsigned a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                        const unsigned b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                        const int pn = (p + 1) & 3, off = p == 3 ? RS : dy * RS; // after the last row: a harmless reload
-                        a0 = t[R.tb0[2 * pn] + off], a1 = t[R.tb1[2 * pn] + off];
-                        b0 = t[R.tb0[2 * pn + 1] + off], b1 = t[R.tb1[2 * pn + 1] + off];
-                        gate_words<8, 8, false>(R.op[p], a, b, g[p]);
+                        const int pn = (p + 1) & 3, dn = p == 3 ? dy + 1 : dy;
+                        if (dn < 2) {
+                            const unsigned tn = t0 + dn * RS * 16;
+                            lds_pair(g[dn][pn], tn + o0[2 * pn], tn + o1[2 * pn]);
+                            lds_pair(b[dn][pn], tn + o0[2 * pn + 1], tn + o1[2 * pn + 1]);
+                        }
+                        gate_words<8>(op[p], g[dy][p], b[dy][p]);
                     }
-                    gate_words<8, 8, false>(R.op[4], g[0], g[1], g[0]);
-                    gate_words<8, 8, false>(R.op[5], g[2], g[3], g[2]);
-                    gate_words<8, 4, true>(R.op[6], g[0], g[2], acc);
+                    gate_words<8>(op[4], g[dy][0], g[dy][1]);
+                    gate_words<8>(op[5], g[dy][2], g[dy][3]);
+                    gate_words<8>(op[6], g[dy][0], g[dy][2]);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) acc[w] |= g[dy][0][w] | g[dy][0][w + 4];
                 }
                 out = make_uint4(acc[0], acc[1], acc[2], acc[3]);
             } else {
@@ -722,16 +754,22 @@ extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const
     s.pwh = (W + 2 * pw + 1) / 2;
     s.CS = s.PH * 2 * s.pwh;
     s.SS = 2 * s.CS;
+    auto smem_of = [&](int ub) { // two buffers + copy offsets
+        const int th = ub * I;
+        return 2 * (size_t)ub * s.SS * 16 + (size_t)((ub * H * W + th - 1) / th) * th * 4;
+    };
+    while (s.UB > 1 && smem_of(s.UB) > 110 * 1024) s.UB = (s.UB + 1) / 2; // small images: the halo doubles the tile; keep two blocks per SM
     const int threads = s.UB * I;
     s.per_thread = (s.UB * H * W + threads - 1) / threads;
-    const size_t smem = 2 * (size_t)s.UB * s.SS * 16 + (size_t)s.per_thread * threads * 4; // two buffers + copy offsets
+    const size_t smem = smem_of(s.UB);
     if (smem > 200 * 1024) return CLB_ERR_SHAPE;
     s.n_ug = (s.U + s.UB - 1) / s.UB;
     s.items = C * s.n_ug;
     auto k = packed_convtree_slab_kernel;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
     int bps = (int)((227 * 1024) / (smem + 1024));
-    if (bps > 2) bps = 2;
+    const int by_regs = 512 / threads < 2 ? 2 : (512 / threads > 8 ? 8 : 512 / threads); // 112 registers per thread
+    if (bps > by_regs) bps = by_regs;
     if (bps < 1) bps = 1;
     int grid = 148 * bps;
     if (grid > s.items) grid = s.items;
