@@ -421,8 +421,13 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_chan_kernel(cons
 // base/A/B, and whatever (dy, dx) the lanes of a warp have, lane px lands in bank (px + const) of its
 // class plane: the data-dependent arg-max costs ~1.7 wavefronts per access instead of ~3 with the
 // forward's row-major layout (which also needs a third more shared memory for its halo).
+// The planes of odd rows start PR floats and those of odd columns PC floats after the even ones, with
+// PR = Wh and PC = 1 modulo 32: for a tap with an odd row (column) offset the two rows (columns) a window can
+// pick then fall into the same bank, so the pick cannot make two lanes collide; taps with an even offset
+// keep the two-way choice.  (No layout serves both parities: the 2x2 blocks of even and odd taps overlap.)
+// With 3x3 kernels and padding 1 two of three offsets are odd.
 // Out-of-image taps are predicated off instead of reading a zero halo.
-constexpr int kBwdChanBuf = 6; // sized so that three blocks (two tiles + records + 1 KiB static) fit one SM
+constexpr int kBwdChanBuf = 4; // sized so that three blocks (two tiles + records + static) fit one SM
 
 struct alignas(16) BwdRec {
     float g[28]; // 7 gates x (k1, ka, kb, kab)
@@ -438,12 +443,13 @@ struct ClsShape {
     int G;          // images per group
     int Hh, Wh;     // class-plane extent
     int PL, CS, IS; // class plane, channel and image stride in floats
+    int PR, PC;     // start of the odd-row / odd-column planes inside a channel
     int wmode;
 };
 
 __device__ __forceinline__ int cls_index(const ClsShape &s, int img, int ch, int row, int col)
 {
-    return img * s.IS + ch * s.CS + ((row & 1) * 2 + (col & 1)) * s.PL + (row >> 1) * s.Wh + (col >> 1);
+    return img * s.IS + ch * s.CS + (row & 1) * s.PR + (col & 1) * s.PC + (row >> 1) * s.Wh + (col >> 1);
 }
 
 // Sum over the 32 lanes of 32 per-lane values at once: lane l returns the warp total of v[l].
@@ -521,7 +527,7 @@ __global__ void __launch_bounds__(kFastThreads / WPT, 3) convtree_bwd_cls_kernel
                 r /= s.H;
                 const int ch = r % s.Ci, im = r / s.Ci;
                 const int b0 = cls_index(s, im, ch, row, col); // col is a multiple of 4: classes alternate
-                xt[b0] = v.x, xt[b0 + s.PL] = v.y, xt[b0 + 1] = v.z, xt[b0 + s.PL + 1] = v.w;
+                xt[b0] = v.x, xt[b0 + s.PC] = v.y, xt[b0 + 1] = v.z, xt[b0 + s.PC + 1] = v.w;
             }
         } else {
             for (int i = tid; i < total; i += TPB) {
@@ -552,8 +558,8 @@ __global__ void __launch_bounds__(kFastThreads / WPT, 3) convtree_bwd_cls_kernel
         for (int i = tid; i < s.G * s.IS; i += TPB) gt[i] = 0.f;
     };
     // f(t): offset of row/col displacement t inside the class layout (t may be negative)
-    auto fy = [&](int t) { return (t & 1) * 2 * s.PL + (t >> 1) * s.Wh; };
-    auto fx = [&](int t) { return (t & 1) * s.PL + (t >> 1); };
+    auto fy = [&](int t) { return (t & 1) * s.PR + (t >> 1) * s.Wh; };
+    auto fx = [&](int t) { return (t & 1) * s.PC + (t >> 1); };
 
     int cur_group = -1;
     for (long long u0 = lo; u0 < hi;) {
@@ -900,7 +906,10 @@ static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int 
     if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return false;
     s.Hh = (H + 1) / 2, s.Wh = (W + 1) / 2;
     s.PL = s.Hh * s.Wh;
-    s.CS = 4 * s.PL;
+    s.PC = s.PL + (((1 - s.PL) % 32) + 32) % 32;              // = 1 (mod 32)
+    s.PR = s.PC + s.PL;
+    s.PR += (((s.Wh - s.PR) % 32) + 32) % 32;                 // = Wh (mod 32)
+    s.CS = (s.PR + s.PC + s.PL + 3) / 4 * 4;
     s.IS = Ci * s.CS;
     const int I = (s.Ho / 2) * (s.Wo / 2);
     int G = kFastThreads / I;
@@ -912,8 +921,9 @@ static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int 
     if (smem > 220 * 1024) return false;
     s.G = G;
     if ((N + G - 1) / G > 65535) return false; // the reduce kernel's grid.y
-    // resident blocks per SM: 233472 bytes of shared memory, 1 KiB reserved per block
-    const int bps = 3 * (smem + 2048) <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
+    // resident blocks per SM: 233472 bytes of shared memory, 1 KiB reserved per block, 128 static bytes per warp
+    const size_t per_block = smem + 1024 + (G * I > kFastThreads / 2 ? kFastThreads / 2 : kFastThreads) / 32 * 128;
+    const int bps = 3 * per_block <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
     const long long units = (long long)((N + G - 1) / G) * C;
     long long g = 148LL * bps;
     if (g > units) g = units;

@@ -82,6 +82,84 @@ __global__ void __launch_bounds__(256) pack_bits_nmajor_kernel(const uint8_t *__
     }
 }
 
+// ---------------------------------------------------------------------------- thermometer + pack
+// Fused input stage of packed inference: pixels [N][P] (P = channels * H * W, fp32 in [0,1] or uint8 that is
+// divided by 255 as torchvision's ToTensor does) -> the L*P thermometer features "pixel > threshold[i]",
+// threshold-major (feature i*P + p), bit-packed along the batch, without the [N, L*P] byte tensor in between.
+// Block: 32 pixel positions (lanes: coalesced 128-byte reads of one sample) x 256 samples (8 warps x 32);
+// a thread builds, for its position, the 32-sample word of every level in registers; the words go through
+// shared memory so that each feature row receives 32 contiguous bytes (rows layout) or each (feature, slab)
+// 512 contiguous bytes (slab layout, one 16-byte unit per position).
+constexpr int kThermoLevels = 32; // levels handled per pass over the pixels
+
+template <typename PIX>
+__device__ __forceinline__ float pixel_value(const PIX *p);
+template <>
+__device__ __forceinline__ float pixel_value<float>(const float *p)
+{
+    return __ldg(p);
+}
+template <>
+__device__ __forceinline__ float pixel_value<uint8_t>(const uint8_t *p)
+{
+    return __fdiv_rn((float)__ldg(p), 255.0f);
+}
+
+template <typename PIX>
+__global__ void __launch_bounds__(256) thermometer_pack_kernel(const PIX *__restrict__ pix, const float *__restrict__ thr, int L,
+                                                               unsigned *__restrict__ out, long long N, int P, int HW,
+                                                               long long words32, int to_slab)
+{
+    __shared__ unsigned sm[kThermoLevels * 32 * 9];
+    const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+    const int p = blockIdx.x * 32 + lane;
+    const long long n0 = (long long)blockIdx.y * 256;
+    for (int l0 = 0; l0 < L; l0 += kThermoLevels) {
+        const int nl = min(kThermoLevels, L - l0);
+        float th[kThermoLevels];
+#pragma unroll
+        for (int i = 0; i < kThermoLevels; ++i) th[i] = i < nl ? __ldg(thr + l0 + i) : 0.f;
+        unsigned word[kThermoLevels];
+#pragma unroll
+        for (int i = 0; i < kThermoLevels; ++i) word[i] = 0u;
+#pragma unroll 4
+        for (int j = 0; j < 32; ++j) {
+            const long long n = n0 + wv * 32 + j;
+            if (n < N && p < P) {
+                const float v = pixel_value<PIX>(pix + n * P + p);
+#pragma unroll
+                for (int i = 0; i < kThermoLevels; ++i) word[i] |= (v > th[i] ? 1u : 0u) << j;
+            }
+        }
+        __syncthreads(); // the previous pass has been written out
+#pragma unroll
+        for (int i = 0; i < kThermoLevels; ++i) sm[(i * 32 + lane) * 9 + wv] = word[i];
+        __syncthreads();
+        const long long w0 = n0 / 32; // first 32-bit word of this block in a row
+        if (!to_slab) {
+            // element e -> (level, position, word): 8 consecutive lanes write the 32 bytes of one row
+            for (int e = threadIdx.x; e < nl * 256; e += 256) {
+                const int w = e & 7, pos = (e >> 3) & 31, i = e >> 8;
+                const int pp = blockIdx.x * 32 + pos;
+                if (pp < P && w0 + w < words32) out[((long long)(l0 + i) * P + pp) * words32 + w0 + w] = sm[(i * 32 + pos) * 9 + w];
+            }
+        } else {
+            // slab layout [feature channel][U][HW] of 16-byte units: 4 consecutive lanes write one unit
+            const long long U = words32 / 4;
+            for (int e = threadIdx.x; e < nl * 256; e += 256) {
+                const int q = e & 3, pos = (e >> 2) & 31, u2 = (e >> 7) & 1, i = e >> 8;
+                const int pp = blockIdx.x * 32 + pos;
+                const long long u = w0 / 4 + u2;
+                if (pp < P && u < U) {
+                    const int c = pp / HW, yx = pp - c * HW;
+                    const long long ch = (long long)(l0 + i) * (P / HW) + c;
+                    out[((ch * U + u) * HW + yx) * 4 + q] = sm[(i * 32 + pos) * 9 + u2 * 4 + q];
+                }
+            }
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------------- flat layer
 // U = transfer unit; units = units per row.  thread <-> (neuron, unit), unit fastest.
 template <typename U>
@@ -630,6 +708,30 @@ extern "C" int clb_pack_bits_nmajor(const uint8_t *t, void *packed, int64_t N, i
     if (gy > 4096) gy = 4096;
     dim3 grid((unsigned)((F + 255) / 256), (unsigned)gy);
     pack_bits_nmajor_kernel<32><<<grid, 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, N, F, rowbytes);
+    return check_launch();
+}
+
+extern "C" int clb_thermometer_pack(const void *pixels, int pixels_u8, const float *thresholds, int levels, void *packed, int64_t N,
+                                    int64_t channels, int64_t HW, int to_slab, void *stream)
+{
+    if (!pixels || !thresholds || !packed || levels <= 0 || N < 0 || channels <= 0 || HW <= 0) return CLB_ERR_ARG;
+    const long long P = channels * HW;
+    if (P > 0x7fffffff || (long long)levels * P > 0x7fffffffLL * 16) return CLB_ERR_SHAPE;
+    if (N == 0) return CLB_OK;
+    long long words32 = (N + 63) / 64 * 2; // rows are made of 64-bit words
+    if (to_slab && (words32 % 4)) return CLB_ERR_SHAPE; // a slab unit is 128 samples
+    if (!aligned_to(packed, 16)) return CLB_ERR_ARG;
+    const long long gy = (N + 255) / 256;
+    if (gy > 65535) return CLB_ERR_SHAPE;
+    dim3 grid((unsigned)((P + 31) / 32), (unsigned)gy);
+    cudaStream_t st = (cudaStream_t)stream;
+    // bits of the last word beyond N stay zero: every word of the output is written
+    if (pixels_u8)
+        thermometer_pack_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P,
+                                                                (int)HW, words32, to_slab);
+    else
+        thermometer_pack_kernel<float><<<grid, 256, 0, st>>>((const float *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P, (int)HW,
+                                                              words32, to_slab);
     return check_launch();
 }
 

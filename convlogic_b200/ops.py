@@ -406,3 +406,25 @@ def packed_convtree_slab(x, ops, sel, geom):
     scratch = torch.empty(max(lib().clb_packed_convtree_slab_scratch_bytes(c), 16), dtype=torch.uint8, device=x.device)
     check(lib().clb_packed_convtree_slab(ptr(x), ptr(ops), ptr(sel), ptr(y), ptr(scratch), ci, h, w, c, *geom, u, stream()))
     return y
+
+
+def thermometer_pack(pixels, thresholds, slab=False):
+    """pixels [N, Cp, H, W] float32 in [0, 1] (or uint8, compared as v / 255) -> the thermometer features
+    ``pixels[:, c] > thresholds[i]`` (channel ``i * Cp + c``) packed 64 samples per int64 word:
+    ``[L*Cp, H, W, words]``, or with ``slab=True`` ``[L*Cp, words // 2, H, W, 2]``.  Returns (packed, pad_len)."""
+    check_input(pixels, thresholds)
+    if pixels.dim() != 4 or pixels.dtype not in (torch.float32, torch.uint8):
+        raise RuntimeError("convlogic_b200: thermometer_pack expects float32 or uint8 pixels [N, C, H, W]")
+    if thresholds.dtype != torch.float32 or thresholds.dim() != 1:
+        raise RuntimeError("convlogic_b200: thresholds must be a float32 vector")
+    n, cp, h, w = pixels.shape
+    levels = thresholds.numel()
+    words = -(-n // 64)
+    if slab and words % 2:
+        raise RuntimeError("convlogic_b200: the slab layout needs the batch padded to a multiple of 128 samples")
+    shape = (levels * cp, words // 2, h, w, 2) if slab else (levels * cp, h, w, words)
+    out = torch.empty(shape, dtype=torch.int64, device=pixels.device)
+    if out.numel():
+        check(lib().clb_thermometer_pack(ptr(pixels), int(pixels.dtype == torch.uint8), ptr(thresholds), levels, ptr(out),
+                                         n, cp, h * w, int(slab), stream()))
+    return out, (64 - n % 64) % 64

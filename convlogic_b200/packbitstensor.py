@@ -36,6 +36,17 @@ class PackBitsTensor:
         self.t, self.pad_len, self.bit_count, self.slab = t, pad_len, t.element_size() * 8, slab
         return self
 
+    @classmethod
+    def from_pixels(cls, pixels, thresholds, slab=None):
+        """Thermometer-encode and pack images in one kernel: ``pixels`` [N, C, H, W] float32 / uint8,
+        ``thresholds`` float32 [L] -> the packed ``[L*C, H, W, words]`` activation of
+        ``cat([(x > t) for t in thresholds], dim=1)`` (the reference's input transform, data.py:46-50).
+        ``slab=None`` picks the slab layout when the batch fills whole 128-sample units."""
+        if slab is None:
+            slab = (-(-pixels.shape[0] // 64)) % 2 == 0
+        t, pad = ops.thermometer_pack(pixels, thresholds, slab)
+        return cls.from_packed(t, pad, slab=slab)
+
     def rows(self):
         """The tensor in the rows layout [..., words] (converts a slab-layout activation)."""
         return ops.packed_to_rows(self.t) if self.slab else self.t

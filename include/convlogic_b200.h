@@ -220,6 +220,19 @@ int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, v
                         int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t words, int bits,
                         void *stream);
 
+/* Fused input stage of packed inference: thermometer encoding + bit packing.  Replaces the reference's
+ * host-side transform `cat([(x > t) for t in thresholds], dim=0)` (src/convlogic/data.py:46-50, thresholds
+ * from :52-71) followed by PackBitsTensor (src/difflogic/packbitstensor.py:12-21) on the device, without the
+ * [N, levels*channels, H, W] byte tensor in between.
+ * pixels [N, channels, HW]: float32 (pixels_u8 == 0) or uint8 (pixels_u8 != 0; compared as v / 255.0f, as
+ * torchvision's ToTensor produces them).  thresholds: `levels` floats on the device.
+ * packed: feature (i*channels + c, yx) holds pixel[n, c, yx] > thresholds[i], sample n in bit n % 64 of
+ * 64-bit word n / 64; bits beyond N are zero.  to_slab == 0: rows layout [levels*channels*HW, ceil(N/64)]
+ * words; to_slab != 0: slab layout [levels*channels, U, HW] of 16-byte units, U = ceil(N/64)/2
+ * (CLB_ERR_SHAPE when ceil(N/64) is odd). */
+int clb_thermometer_pack(const void *pixels, int pixels_u8, const float *thresholds, int levels, void *packed,
+                         int64_t N, int64_t channels, int64_t HW, int to_slab, void *stream);
+
 /* The same block on the SLAB layout [C][U][H][W] of 16-byte units (U = words / 2 for 64-bit words; one unit
  * = 128 samples), in which the image of one (channel, sample slab) is contiguous and can be staged in shared
  * memory.  Stride 1, at most 256 pooled outputs per image (CLB_ERR_SHAPE otherwise: use the rows layout).

@@ -143,3 +143,35 @@ def test_packed_model_equals_float_eval_model():
         counts = net(cb.PackBitsTensor(x, 64))
     assert counts.dtype == torch.int32 and counts.shape == (100, 10)
     assert torch.equal(counts.float(), scores * 8.0)
+
+
+@pytest.mark.parametrize("n,cp,h,w,levels", [(70, 3, 8, 8, 31), (256, 3, 32, 32, 31), (300, 1, 5, 7, 3), (128, 2, 4, 4, 40), (1, 3, 2, 2, 1)])
+@pytest.mark.parametrize("u8", [False, True])
+def test_thermometer_pack_equals_transform_then_pack(n, cp, h, w, levels, u8):
+    """Fused thermometer + pack == the reference's input transform (cat of x > t, threshold-major) followed by
+    PackBitsTensor, bit for bit, in the rows layout and (when the batch fills 128-sample units) the slab layout."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import ops
+
+    rng = np.random.default_rng(n * 7 + levels)
+    th = (np.arange(1, levels + 1, dtype=np.float32) / np.float32(levels + 1))
+    if u8:
+        raw = rng.integers(0, 256, (n, cp, h, w), dtype=np.uint8)
+        # make sure values sitting exactly on a threshold occur (k/255 vs i/(L+1))
+        pix = torch.from_numpy(raw)
+        val = (pix.float() / 255).numpy()  # ToTensor's arithmetic
+    else:
+        val = rng.random((n, cp, h, w), dtype=np.float32)
+        val.reshape(-1)[: levels] = th  # equality with a threshold: strict '>' must give 0
+        pix = torch.from_numpy(val)
+    bits = oracle.thermometer(val, levels)                      # [n, levels*cp, h, w] bool
+    want, pad = oracle.pack_bits(bits.reshape(n, -1).T, 64)     # [F, words]
+    want = want.reshape(levels * cp, h, w, -1)
+    got, pad_g = ops.thermometer_pack(pix.cuda(), torch.from_numpy(th).cuda())
+    assert pad_g == pad and np.array_equal(got.cpu().numpy(), want)
+    p = cb.PackBitsTensor.from_pixels(pix.cuda(), torch.from_numpy(th).cuda())
+    assert p.pad_len == pad and np.array_equal(p.rows().cpu().numpy(), want)
+    assert p.slab == (want.shape[-1] % 2 == 0)
+    if want.shape[-1] % 2:
+        with pytest.raises(RuntimeError):
+            ops.thermometer_pack(pix.cuda(), torch.from_numpy(th).cuda(), slab=True)

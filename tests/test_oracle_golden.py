@@ -197,3 +197,19 @@ def test_mnist_s_stack_matches_reference_scores(golden):
             np.testing.assert_allclose(s, g[key][:n], rtol=1e-5, atol=1e-5)
         else:
             assert np.array_equal(s, g[key][:n])
+
+
+def test_thermometer_restatement_equals_the_transform_expression():
+    """The oracle's thermometer == the reference's input transform written out with torch
+    (`cat([(x > t).float() for t in thresholds], dim=0)` per image, uniform thresholds i / (L + 1))."""
+    import torch
+
+    torch.manual_seed(0)
+    for levels, cp in ((31, 3), (3, 1), (1, 2)):
+        x = torch.rand(6, cp, 5, 4)
+        th = torch.linspace(1, levels, levels, dtype=torch.float32) / (levels + 1)
+        x.view(-1)[:levels] = th  # ties: strict '>'
+        ref = torch.stack([torch.cat([(xi > t).float() for t in th], dim=0) for xi in x])
+        got = oracle.thermometer(x.numpy(), levels)
+        assert got.shape == (6, levels * cp, 5, 4)
+        assert np.array_equal(ref.numpy().astype(bool), got)
