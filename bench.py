@@ -535,6 +535,17 @@ def run_c4(args):
             layer_ms.append(round(e0.elapsed_time(e1), 4))
             h = o
     ms_e2e = _timed(step_e2e, 1, 1, world, dev)
+    # the same stack serialised and run by the library's own runtime (one C call per chunk, no Python per layer)
+    compiled = None
+    if rank == 0:
+        cnet = cb.CompiledLogicNet(net, input_shape=(93, 32, 32)).compile()
+        dev_px[0].copy_(host_px[0])
+        with torch.no_grad():
+            same = bool(torch.equal(cnet.forward_pixels(dev_px[0], th), net(cb.PackBitsTensor.from_pixels(dev_px[0], th))))
+        ms_c = _timed(lambda i: cnet.forward_pixels(dev_px[0], th), 3, 1, 1, dev) / 3
+        compiled = {"ms_per_chunk": round(ms_c, 4), "images_per_s": chunk / (ms_c * 1e-3), "blob_bytes": len(cnet.blob),
+                    "equals_module_path": same, "what": "CompiledLogicNet.forward_pixels on one resident uint8 chunk"}
+        del cnet
     imgs = total * steps
     peak, kind = measured_peaks()
     alg = 1388200.0 * total / world  # layer-by-layer algorithmic bytes per image, per rank and step
@@ -548,7 +559,7 @@ def run_c4(args):
         "e2e": {"value": total / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": 3 * 1024 * (hi - lo),
                 "d2h_bytes_per_step": (hi - lo) * 8,
                 "what": "uint8 pixels from pinned host memory, thermometer + pack on the GPU, class indices back to the host"},
-        "gpu_launches": int(launches), "layer_ms_per_chunk": layer_ms,
+        "gpu_launches": int(launches), "layer_ms_per_chunk": layer_ms, "compiled_net": compiled,
         "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
                      "note": "whole pipeline, 1 388 200 algorithmic bytes per image"},

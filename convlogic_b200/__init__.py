@@ -16,10 +16,11 @@ from .functional import (  # noqa: F401
     TreeLogicFunction,
 )
 from .model import ConvLogicCifarModel, ConvLogicMnistModel  # noqa: F401
+from .compiled_model import CompiledLogicNet  # noqa: F401
 from ._lib import LIB_PATH, W_ARGMAX, W_PROB, W_SOFTMAX  # noqa: F401
 
 __all__ = [
     "ConvLogicLayer", "PoolLogicLayer", "TreeLogicLayer", "LogicLayer", "GroupSum", "PackBitsTensor",
     "ConvLogicFunction", "FullConvLogicFunction", "TreeLogicFunction", "LogicLayerCudaFunction", "GradFactor",
-    "ConvLogicCifarModel", "ConvLogicMnistModel", "get_unique_connections",
+    "ConvLogicCifarModel", "ConvLogicMnistModel", "get_unique_connections", "CompiledLogicNet",
 ]

@@ -54,7 +54,13 @@ _SIGNATURES = {
     "clb_packed_logic": ([_vp] * 5 + [_i64] * 3 + [_i, _vp], _i),
     "clb_group_popcount": ([_vp, _vp, _i64, _i64, _i, _i, _i, _vp], _i),
     "clb_packed_convtree": ([_vp] * 4 + [_i] * 10 + [_i64, _i, _vp], _i),
-    "clb_thermometer_pack": ([_vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp], _i),
+    "clb_thermometer_pack": ([_vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i64, _i, _vp], _i),
+    "clb_net_device_bytes": ([_vp, _sz, _vp], _i),
+    "clb_net_create": ([_vp, _sz, _vp, _vp, _vp], _i),
+    "clb_net_destroy": ([_vp], None),
+    "clb_net_info": ([_vp, _vp, _vp, _vp], _i),
+    "clb_net_workspace_bytes": ([_vp, _i64], _sz),
+    "clb_net_forward": ([_vp, _i, _vp, _vp, _i, _i64, _vp, _vp, _sz, _vp], _i),
     "clb_packed_layout": ([_vp, _vp, _i64, _i64, _i64, _i, _vp], _i),
     "clb_packed_convtree_slab_scratch_bytes": ([_i], _i64),
     "clb_packed_convtree_slab": ([_vp] * 5 + [_i] * 10 + [_i64, _vp], _i),

@@ -1,0 +1,185 @@
+"""CompiledLogicNet: the discretised network as a deployable artefact.
+
+The reference's ``CompiledLogicNet`` (src/difflogic/compiled_model.py:41-361) takes a trained
+``nn.Sequential`` of ``LogicLayer`` s ending in ``GroupSum``, writes every gate out as a line of C,
+compiles that with gcc and calls the resulting ``apply_logic_gate_net(bool*, int*, size_t)`` on the CPU
+through ctypes; fused conv blocks are not supported there.  Here the artefact is a *blob* -- the arg-max
+gate of every neuron plus its connections, for fused ``ConvLogicLayer`` blocks as well as flat layers -- and
+the code is the library's ``clb_net_*`` runtime, which runs the whole stack on the GPU with one C call
+(any host language; no Python or torch needed at deployment).  The class keeps the reference's surface:
+``CompiledLogicNet(model, num_bits=64)``, ``compile(save_lib_path=...)``, ``CompiledLogicNet.load(path, ...)``,
+``forward(x)`` with ``x`` bool ``[B, F]`` (or ``[B, C, H, W]``) returning int32 counts ``[B, num_classes]``.
+"""
+
+import ctypes as C
+import struct
+
+import numpy as np
+import torch
+
+from . import _lib
+from .convlogic_layer import ConvLogicLayer
+from .difflogic import GroupSum, LogicLayer
+
+_MAGIC = b"CLBNET01"
+
+
+def _align16(n):
+    return (n + 15) // 16 * 16
+
+
+def serialise(model, input_shape=None):
+    """``nn.Sequential`` (fused complete ConvLogicLayers, Flatten, LogicLayers, GroupSum last) -> blob bytes.
+
+    ``input_shape`` = (C, H, W) is required when the stack starts with a conv block."""
+    layers = list(model)
+    if not isinstance(layers[-1], GroupSum):
+        raise AssertionError(f"The last layer of the model must be GroupSum, but it is {type(layers[-1])} / {layers[-1]} instead.")
+    num_classes = layers[-1].k
+    recs, arrays = [], []
+    offset = [0]
+
+    def add(arr):
+        data = np.ascontiguousarray(arr).tobytes()
+        off = offset[0]
+        arrays.append((off, data))
+        offset[0] = _align16(off + len(data))
+        return off
+
+    in_features = None
+    for layer in layers[:-1]:
+        if isinstance(layer, ConvLogicLayer):
+            if not layer.complete:
+                raise AssertionError("only complete (fused) ConvLogicLayer blocks can be compiled")
+            if layer.stride[0] != layer.stride[1]:
+                raise AssertionError("compiled conv blocks need equal strides")
+            sel = layer.selection.detach().cpu().numpy().astype(np.int32)
+            ops = layer.weights.detach().argmax(-1).cpu().numpy().astype(np.uint8)
+            recs.append((1, [layer.in_channels, layer.out_channels, layer.kernel[0], layer.kernel[1], layer.stride[0],
+                             layer.padding[0], layer.padding[1]], add(sel), 0, add(ops)))
+        elif isinstance(layer, LogicLayer):
+            if in_features is None and not recs:
+                in_features = layer.in_dim
+            a = layer.indices_0.detach().cpu().numpy().astype(np.int64)
+            b = layer.indices_1.detach().cpu().numpy().astype(np.int64)
+            ops = layer.weights.detach().argmax(-1).cpu().numpy().astype(np.uint8)
+            recs.append((2, [layer.in_dim & 0xFFFFFFFF, layer.out_dim & 0xFFFFFFFF, layer.in_dim >> 32, layer.out_dim >> 32, 0, 0, 0],
+                         add(a), add(b), add(ops)))
+        elif isinstance(layer, torch.nn.Flatten):
+            continue
+        else:
+            raise AssertionError(f"Error: layer {type(layer)} / {layer} unknown.")
+    if not recs:
+        raise AssertionError("the model holds no logic layer")
+    image = recs[0][0] == 1
+    if image and input_shape is None:
+        raise AssertionError("input_shape=(C, H, W) is needed for a stack that starts with a conv block")
+    c, h, w = (int(v) for v in input_shape) if image else (0, 0, 0)
+    base = 64 + 64 * len(recs)
+    total = base + offset[0]
+    out = bytearray(total)
+    struct.pack_into("<8s6IQ", out, 0, _MAGIC, len(recs), num_classes, c, h, w, 0 if image else int(in_features), total)
+    for i, (kind, p, oa, ob, oo) in enumerate(recs):
+        struct.pack_into("<8I3Q", out, 64 + 64 * i, kind, *[int(v) for v in p], base + oa, base + ob, base + oo)
+    for off, data in arrays:
+        out[base + off: base + off + len(data)] = data
+    return bytes(out)
+
+
+class CompiledLogicNet(torch.nn.Module):
+    def __init__(self, model=None, device="cuda", num_bits=64, input_shape=None, verbose=False):
+        super().__init__()
+        assert num_bits == 64, "the GPU runtime packs 64 samples per word"
+        self.model, self.device, self.num_bits, self.input_shape = model, torch.device(device), num_bits, input_shape
+        self.blob = None
+        self._net = None
+        self._params = None
+        self._workspace = None
+        if model is not None:
+            self.num_classes = model[-1].k
+            self.blob = serialise(model, input_shape)
+            if verbose:
+                print(f"blob of {len(self.blob)} bytes created.")
+
+    # ---- the reference's compile / load pair
+    def compile(self, opt_level=1, save_lib_path=None, verbose=False):
+        """Uploads the blob and creates the runtime handle; ``save_lib_path`` also writes the blob to a file
+        (the reference writes the compiled shared object there)."""
+        del opt_level
+        if save_lib_path is not None:
+            with open(save_lib_path, "wb") as f:
+                f.write(self.blob)
+        self._create()
+        if verbose:
+            print(f"network of {len(self.blob)} parameter bytes is on {self.device}.")
+        return self
+
+    @staticmethod
+    def load(save_lib_path, num_classes=None, num_bits=64, device="cuda"):
+        self = CompiledLogicNet(None, device=device, num_bits=num_bits)
+        with open(save_lib_path, "rb") as f:
+            self.blob = f.read()
+        self._create()
+        if num_classes is not None and num_classes != self.num_classes:
+            raise ValueError(f"the file holds a network with {self.num_classes} classes, not {num_classes}")
+        return self
+
+    def _create(self):
+        lib = _lib.lib()
+        need = C.c_size_t()
+        _lib.check(lib.clb_net_device_bytes(self.blob, len(self.blob), C.byref(need)))
+        self._params = torch.empty(max(need.value, 16), dtype=torch.uint8, device=self.device)
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.clb_net_create(self.blob, len(self.blob), _lib.ptr(self._params), _lib.stream(), C.byref(handle)))
+            torch.cuda.current_stream().synchronize()  # the blob is pageable host memory: wait for the copy
+        self._net = handle
+        feats, classes, n = C.c_int64(), C.c_int(), C.c_int()
+        _lib.check(lib.clb_net_info(handle, C.byref(feats), C.byref(classes), C.byref(n)))
+        self.num_inputs, self.num_classes, self.num_layers = feats.value, classes.value, n.value
+
+    def __del__(self):
+        if getattr(self, "_net", None) is not None:
+            try:
+                _lib.lib().clb_net_destroy(self._net)
+            except Exception:
+                pass
+            self._net = None
+
+    # ---- inference
+    def _run(self, kind, x, batch, thresholds=None):
+        if self._net is None:
+            raise RuntimeError("convlogic_b200: call compile() or load() first")
+        lib = _lib.lib()
+        need = lib.clb_net_workspace_bytes(self._net, batch)
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        counts = torch.empty((batch, self.num_classes), dtype=torch.int32, device=self.device)
+        levels = 0 if thresholds is None else thresholds.numel()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.clb_net_forward(self._net, kind, _lib.ptr(x), _lib.ptr(thresholds), levels, batch, _lib.ptr(counts),
+                                           _lib.ptr(self._workspace), self._workspace.numel(), _lib.stream()))
+        return counts
+
+    def forward(self, x, verbose=False):
+        """bool ``[B, F]`` or ``[B, C, H, W]`` (torch tensor or numpy array) -> int32 class counts ``[B, num_classes]``
+        on the device."""
+        del verbose
+        if isinstance(x, np.ndarray):
+            x = torch.from_numpy(x)
+        x = x.to(self.device)
+        if x.dtype not in (torch.bool, torch.uint8):
+            raise RuntimeError("convlogic_b200: CompiledLogicNet.forward expects bool inputs")
+        batch = x.shape[0]
+        x = x.reshape(batch, -1).contiguous()
+        if x.shape[1] != self.num_inputs:
+            raise ValueError(f"expected {self.num_inputs} input bits per sample, got {x.shape[1]}")
+        return self._run(0, x.view(torch.uint8), batch)
+
+    def forward_pixels(self, pixels, thresholds):
+        """float32 / uint8 pixels ``[B, C, H, W]`` + thermometer thresholds -> counts (input stage fused on the GPU)."""
+        pixels = pixels.to(self.device).contiguous()
+        thresholds = thresholds.to(self.device, torch.float32).contiguous()
+        if pixels.dtype not in (torch.float32, torch.uint8):
+            raise RuntimeError("convlogic_b200: pixels must be float32 or uint8")
+        return self._run(2 if pixels.dtype == torch.uint8 else 1, pixels, pixels.shape[0], thresholds)

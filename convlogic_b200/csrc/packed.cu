@@ -712,20 +712,22 @@ extern "C" int clb_pack_bits_nmajor(const uint8_t *t, void *packed, int64_t N, i
 }
 
 extern "C" int clb_thermometer_pack(const void *pixels, int pixels_u8, const float *thresholds, int levels, void *packed, int64_t N,
-                                    int64_t channels, int64_t HW, int to_slab, void *stream)
+                                    int64_t channels, int64_t HW, int64_t words, int to_slab, void *stream)
 {
-    if (!pixels || !thresholds || !packed || levels <= 0 || N < 0 || channels <= 0 || HW <= 0) return CLB_ERR_ARG;
+    if (!pixels || !thresholds || !packed || levels <= 0 || N < 0 || channels <= 0 || HW <= 0 || words < 0) return CLB_ERR_ARG;
     const long long P = channels * HW;
     if (P > 0x7fffffff || (long long)levels * P > 0x7fffffffLL * 16) return CLB_ERR_SHAPE;
-    if (N == 0) return CLB_OK;
-    long long words32 = (N + 63) / 64 * 2; // rows are made of 64-bit words
+    const long long need = (N + 63) / 64;
+    if (words == 0) words = need;
+    if (words < need || words > need + 1) return CLB_ERR_SHAPE; // rows of ceil(N/64) words, or one more to reach an even count
+    if (words == 0) return CLB_OK;
+    const long long words32 = words * 2;
     if (to_slab && (words32 % 4)) return CLB_ERR_SHAPE; // a slab unit is 128 samples
     if (!aligned_to(packed, 16)) return CLB_ERR_ARG;
-    const long long gy = (N + 255) / 256;
+    const long long gy = (words32 + 7) / 8; // a block writes 8 half-words of every row: all of them are written, bits beyond N as zeros
     if (gy > 65535) return CLB_ERR_SHAPE;
     dim3 grid((unsigned)((P + 31) / 32), (unsigned)gy);
     cudaStream_t st = (cudaStream_t)stream;
-    // bits of the last word beyond N stay zero: every word of the output is written
     if (pixels_u8)
         thermometer_pack_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P,
                                                                 (int)HW, words32, to_slab);

@@ -426,5 +426,5 @@ def thermometer_pack(pixels, thresholds, slab=False):
     out = torch.empty(shape, dtype=torch.int64, device=pixels.device)
     if out.numel():
         check(lib().clb_thermometer_pack(ptr(pixels), int(pixels.dtype == torch.uint8), ptr(thresholds), levels, ptr(out),
-                                         n, cp, h * w, int(slab), stream()))
+                                         n, cp, h * w, words, int(slab), stream()))
     return out, (64 - n % 64) % 64

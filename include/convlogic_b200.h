@@ -227,11 +227,11 @@ int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, v
  * pixels [N, channels, HW]: float32 (pixels_u8 == 0) or uint8 (pixels_u8 != 0; compared as v / 255.0f, as
  * torchvision's ToTensor produces them).  thresholds: `levels` floats on the device.
  * packed: feature (i*channels + c, yx) holds pixel[n, c, yx] > thresholds[i], sample n in bit n % 64 of
- * 64-bit word n / 64; bits beyond N are zero.  to_slab == 0: rows layout [levels*channels*HW, ceil(N/64)]
- * words; to_slab != 0: slab layout [levels*channels, U, HW] of 16-byte units, U = ceil(N/64)/2
- * (CLB_ERR_SHAPE when ceil(N/64) is odd). */
+ * 64-bit word n / 64; bits beyond N are zero.  `words`: 64-bit words per row, ceil(N/64) (0 means that) or one
+ * more to make the count even.  to_slab == 0: rows layout [levels*channels*HW, words]; to_slab != 0: slab layout
+ * [levels*channels, U, HW] of 16-byte units, U = words / 2 (CLB_ERR_SHAPE when words is odd). */
 int clb_thermometer_pack(const void *pixels, int pixels_u8, const float *thresholds, int levels, void *packed,
-                         int64_t N, int64_t channels, int64_t HW, int to_slab, void *stream);
+                         int64_t N, int64_t channels, int64_t HW, int64_t words, int to_slab, void *stream);
 
 /* The same block on the SLAB layout [C][U][H][W] of 16-byte units (U = words / 2 for 64-bit words; one unit
  * = 128 samples), in which the image of one (channel, sample slab) is contiguous and can be staged in shared
@@ -245,6 +245,34 @@ int64_t clb_packed_convtree_slab_scratch_bytes(int C);
 int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const int32_t *sel, void *y, void *scratch, int Ci,
                              int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t U,
                              void *stream);
+
+/* ---- Compiled network -----------------------------------------------------------------------------------
+ * A discretised stack (fused ConvLogic blocks, then flat LogicLayers, then GroupSum) serialised into one blob
+ * and run with one call that enqueues the packed kernels above back to back.  It takes the place of the
+ * reference's CompiledLogicNet (src/difflogic/compiled_model.py:41-361: C source generated per network,
+ * compiled with gcc, run on the CPU, flat layers only): the artefact is the blob (written by
+ * convlogic_b200.CompiledLogicNet.save, layout in csrc/net.cu), the code is this library, and fused conv
+ * blocks are included.
+ *   clb_net_device_bytes   validates a blob and returns the device memory the parameters need.
+ *   clb_net_create         copies the parameters into caller-provided device memory (16-byte aligned, one
+ *                          asynchronous copy on `stream`; `blob` must stay valid until it has run) and returns
+ *                          a host-side handle; clb_net_destroy frees the handle (never the device memory).
+ *   clb_net_workspace_bytes  device workspace for a batch (two activation buffers of the widest layer with the
+ *                          batch padded to 128 samples, plus kernel scratch); 256-byte aligned.
+ *   clb_net_forward        input_kind 0: bool / uint8 bits [batch][in_features] (what the reference's
+ *                          `apply_logic_gate_net(bool const *inp, int *out, size_t len)` takes, compiled_model.py:
+ *                          243-330); 1 / 2: float32 / uint8 pixels [batch][in_channels/levels][H*W] with
+ *                          `levels` device thresholds (clb_thermometer_pack); 3: packed rows [in_features]
+ *                          [2*ceil(batch/128)] of 64-bit words.  counts: int32 [batch][num_classes], as
+ *                          clb_group_popcount.  Nothing is allocated and nothing synchronises. */
+typedef struct clb_net clb_net;
+int clb_net_device_bytes(const void *blob, size_t bytes, size_t *device_bytes);
+int clb_net_create(const void *blob, size_t bytes, void *device_mem, void *stream, clb_net **net);
+void clb_net_destroy(clb_net *net);
+int clb_net_info(const clb_net *net, int64_t *in_features, int *num_classes, int *n_layers);
+size_t clb_net_workspace_bytes(const clb_net *net, int64_t batch);
+int clb_net_forward(const clb_net *net, int input_kind, const void *input, const float *thresholds, int levels,
+                    int64_t batch, int32_t *counts, void *workspace, size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -101,3 +101,28 @@ def test_modules_construct_on_cpu_and_refuse_to_run_there():
     m = cb.ConvLogicCifarModel(k_param=2, input_channels=3, tau=5)
     dims = [(l.in_dim, l.out_dim) for l in m.network if isinstance(l, cb.LogicLayer)]
     assert dims == [(256, 2560), (2560, 1280), (1280, 640)]
+
+
+def test_network_blob_is_validated_on_the_host():
+    """clb_net_device_bytes parses a blob without touching the GPU: a well-formed one is accepted, damaged ones
+    (bad magic, truncated, inconsistent layer widths) come back as CLB_ERR_SHAPE."""
+    import ctypes as C
+
+    import torch
+
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib
+    from convlogic_b200.compiled_model import serialise
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(cb.ConvLogicLayer(3, 4, complete=True), torch.nn.Flatten(), cb.LogicLayer(4 * 4 * 4, 40), cb.GroupSum(10))
+    blob = serialise(model, input_shape=(3, 8, 8))
+    lib = _lib.lib()
+    need = C.c_size_t()
+    assert lib.clb_net_device_bytes(blob, len(blob), C.byref(need)) == 0 and need.value == len(blob)
+    assert lib.clb_net_device_bytes(b"XXXXXXXX" + blob[8:], len(blob), C.byref(need)) == _lib.ERR_SHAPE
+    assert lib.clb_net_device_bytes(blob[:-16], len(blob) - 16, C.byref(need)) == _lib.ERR_SHAPE
+    wrong = serialise(model, input_shape=(3, 10, 10))  # the flat layer no longer matches the conv output
+    assert lib.clb_net_device_bytes(wrong, len(wrong), C.byref(need)) == _lib.ERR_SHAPE
+    with pytest.raises(AssertionError):
+        serialise(torch.nn.Sequential(cb.LogicLayer(8, 10)))  # no GroupSum at the end

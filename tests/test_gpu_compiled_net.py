@@ -1,0 +1,99 @@
+"""CompiledLogicNet: the serialised network run by the library's own runtime (one C call) gives the counts of
+the layer-by-layer packed path, of the float eval-mode model, and of the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _randomise(net, seed):
+    g = torch.Generator().manual_seed(seed)
+    for prm in net.parameters():
+        prm.data = torch.randn(*prm.shape, generator=g).to(prm.device)
+
+
+@pytest.mark.parametrize("batch", [1, 60, 64, 100, 128, 300])
+def test_flat_stack_counts_equal_packed_layers_and_oracle(batch):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(cb.LogicLayer(96, 400), cb.LogicLayer(400, 250), cb.LogicLayer(250, 130), cb.GroupSum(10, 4.0)).cuda().eval()
+    _randomise(model, 5)
+    x = torch.rand(batch, 96, device="cuda") < 0.5
+    net = cb.CompiledLogicNet(model).compile()
+    assert (net.num_inputs, net.num_classes, net.num_layers) == (96, 10, 3)
+    got = net(x)
+    assert got.dtype == torch.int32 and got.shape == (batch, 10)
+    with torch.no_grad():
+        want = model(cb.PackBitsTensor(x, 64))
+    assert torch.equal(got, want)
+    # CPU oracle: packed logic per layer, then per-class bit counts
+    h, pad = oracle.pack_bits(x.cpu().numpy().T, 64)
+    for layer in list(model)[:-1]:
+        h = oracle.packed_logic(h, layer.indices_0.cpu().numpy(), layer.indices_1.cpu().numpy(),
+                                layer.weights.argmax(-1).cpu().numpy().astype(np.uint8))
+    assert np.array_equal(got.cpu().numpy(), oracle.packed_group_sum(h, pad, 10))
+    assert np.array_equal(net(x.cpu().numpy()).cpu().numpy(), got.cpu().numpy())  # numpy input, as the reference accepts
+
+
+@pytest.mark.parametrize("batch", [70, 256])
+def test_cifar_shaped_stack_equals_packed_and_float_eval(batch):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    model = cb.ConvLogicCifarModel(k_param=4, input_channels=6, input_size=32, tau=8.0).cuda().eval()
+    _randomise(model, 1)
+    x = torch.rand(batch, 6, 32, 32, device="cuda") < 0.5
+    net = cb.CompiledLogicNet(model.network, input_shape=(6, 32, 32)).compile()
+    got = net(x)
+    with torch.no_grad():
+        assert torch.equal(got, model(cb.PackBitsTensor(x, 64)))
+        assert torch.equal(got.float(), model(x.float()) * 8.0)
+
+
+def test_mnist_shaped_stack_and_strided_block():
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    model = cb.ConvLogicMnistModel(k_param=4, tau=4.0).cuda().eval()
+    _randomise(model, 2)
+    x = torch.rand(130, 1, 28, 28, device="cuda") < 0.3
+    net = cb.CompiledLogicNet(model.network, input_shape=(1, 28, 28)).compile()
+    with torch.no_grad():
+        assert torch.equal(net(x), model(cb.PackBitsTensor(x, 64)))
+    # a stride-2 block (rows-layout kernel) between two stride-1 blocks (slab-layout kernel)
+    seq = torch.nn.Sequential(
+        cb.ConvLogicLayer(3, 8, complete=True), cb.ConvLogicLayer(8, 12, stride=2, padding=1, kernel=3, complete=True),
+        cb.ConvLogicLayer(12, 10, complete=True), torch.nn.Flatten(), cb.LogicLayer(10 * 2 * 2, 60), cb.GroupSum(10, 1.0)).cuda().eval()
+    _randomise(seq, 4)
+    x = torch.rand(200, 3, 32, 32, device="cuda") < 0.5
+    net = cb.CompiledLogicNet(seq, input_shape=(3, 32, 32)).compile()
+    with torch.no_grad():
+        assert torch.equal(net(x), seq(cb.PackBitsTensor(x, 64)))
+
+
+def test_save_load_and_fused_pixel_input(tmp_path):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    model = cb.ConvLogicCifarModel(k_param=2, input_channels=9, input_size=16, tau=1.0).cuda().eval()
+    _randomise(model, 7)
+    path = str(tmp_path / "net.clb")
+    a = cb.CompiledLogicNet(model.network, input_shape=(9, 16, 16)).compile(save_lib_path=path)
+    b = cb.CompiledLogicNet.load(path, num_classes=10)
+    with pytest.raises(ValueError):
+        cb.CompiledLogicNet.load(path, num_classes=7)
+    pixels = torch.rand(90, 3, 16, 16)
+    th = torch.tensor([0.25, 0.5, 0.75])
+    bits = torch.from_numpy(oracle.thermometer(pixels.numpy(), 3))  # [90, 9, 16, 16]
+    want = a(bits)
+    assert torch.equal(b(bits), want)
+    assert torch.equal(b.forward_pixels(pixels, th), want)
+    u8 = torch.randint(0, 256, (90, 3, 16, 16), dtype=torch.uint8)
+    bits8 = torch.from_numpy(oracle.thermometer((u8.float() / 255).numpy(), 3))
+    assert torch.equal(a.forward_pixels(u8, th), a(bits8))
+    with pytest.raises(ValueError):
+        a(torch.zeros(4, 7, dtype=torch.bool))
