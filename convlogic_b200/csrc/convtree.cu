@@ -533,6 +533,115 @@ __global__ void __launch_bounds__(256, 3) convtree_bwd_x_grp_kernel(const float 
     }
 }
 
+// Input gradient from precomputed tap gradients (convtree_bwd_w_win_kernel's `tapgrad`): channel-group tiles and
+// group lists as in the kernel above, but a listed channel costs only its arg-max byte, the tap gradients of the
+// taps that fall into the group and their read-modify-writes; the gate chain is not recomputed and x is not
+// read.  The tile is row-major with a zero-weight halo of the padding's width, so an out-of-image tap needs no
+// test (its cell is never written out) and a cell is  window offset + tap offset + (dy ? row : 0) + dx.
+// Threads of one image only ever touch that image's tile and a warp owns whole images (WPT windows per lane
+// when an image has more than 32), so the ordering between the taps needs __syncwarp only.  Same fixed
+// accumulation order as the kernels above: deterministic, no atomics.
+constexpr int kScatBatch = 16;
+
+template <int WPT>
+__global__ void __launch_bounds__(256, 3) convtree_bwd_x_scatter_kernel(const float *__restrict__ tapgrad, const int32_t *__restrict__ sel,
+                                                                        const uint8_t *__restrict__ amax, float *__restrict__ gx,
+                                                                        const int32_t *__restrict__ grp_start,
+                                                                        const int32_t *__restrict__ grp_list, int cg, int nb, ConvShape s)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int(*cbase)[8] = reinterpret_cast<int(*)[8]>(smem_raw); // [kScatBatch][8]: tap cell offset inside the image's tile, -1 = other group
+    float *tile = reinterpret_cast<float *>(smem_raw + sizeof(int) * 8 * kScatBatch);
+
+    const int HW = s.H * s.W, PW = s.W + 2 * s.pw, PP = (s.H + 2 * s.ph) * PW;
+    const int Wp = s.Wo / 2, I = (s.Ho / 2) * Wp;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.y, n0 = blockIdx.x * nb;
+    const int nimg = min(nb, s.N - n0);
+    const int ch0 = g * cg;
+    const int tile_elems = nb * cg * PP;
+    for (int i = tid; i < tile_elems; i += blockDim.x) tile[i] = 0.f;
+
+    // a lane's WPT slots: slot = lane + 32*j.  Images of 32 or more windows: the warp's image, window = slot.
+    // Smaller images: the warp holds 32*WPT / I of them, image = slot / I, window = slot % I.
+    const int ipw = I >= 32 ? 1 : (32 * WPT) / I;
+    bool live[WPT];
+    int toff[WPT];
+    size_t ob[WPT], tb[WPT]; // index of the slot's arg-max byte / first tap gradient for output channel 0
+#pragma unroll
+    for (int j = 0; j < WPT; ++j) {
+        const int slot = lane + 32 * j;
+        const int img = I >= 32 ? warp : warp * ipw + slot / I;
+        const int win = I >= 32 ? slot : slot % I;
+        live[j] = img < nimg && (I >= 32 ? win < I : slot < ipw * I);
+        const int py = win / Wp, px = win - py * Wp;
+        toff[j] = img * cg * PP + 2 * py * PW + 2 * px;
+        ob[j] = ((size_t)(n0 + img) * s.C) * I + win;
+        tb[j] = (ob[j] - win) * 8 + win;
+    }
+
+    const int lo = grp_start[g], hi = grp_start[g + 1];
+    for (int l0 = lo; l0 < hi; l0 += kScatBatch) {
+        const int cnt = min(kScatBatch, hi - l0);
+        __syncthreads(); // the previous batch's records are no longer read
+        for (int i = tid; i < cnt * 8; i += blockDim.x) {
+            const int e = i >> 3, k = i & 7;
+            const Tap tp = unpack_tap(sel[grp_list[l0 + e] * 8 + k], s.ph, s.pw); // dy, dx: tap offset minus padding
+            const int chl = tp.ch - ch0;
+            cbase[e][k] = (chl >= 0 && chl < cg) ? chl * PP + (tp.dy + s.ph) * PW + tp.dx + s.pw : -1;
+        }
+        __syncthreads();
+        // software pipeline: the arg-max bytes and the in-group tap gradients of the next listed channel are in flight
+        // while this one is added (their addresses do not depend on the arg-max)
+        int bd1[WPT];
+        float v1[WPT][8];
+        auto fetch = [&](int e) {
+            const size_t co = (size_t)grp_list[l0 + e] * I;
+            const int4 c0 = reinterpret_cast<const int4 *>(cbase[e])[0], c1 = reinterpret_cast<const int4 *>(cbase[e])[1];
+            const int cb[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int j = 0; j < WPT; ++j) {
+                bd1[j] = live[j] ? (int)amax[ob[j] + co] : 0;
+                const float *t = tapgrad + tb[j] + co * 8;
+#pragma unroll
+                for (int k = 0; k < 8; ++k, t += I) v1[j][k] = (live[j] && cb[k] >= 0) ? __ldg(t) : 0.f;
+            }
+        };
+        fetch(0);
+        for (int e = 0; e < cnt; ++e) {
+            int woff[WPT];
+            float v[WPT][8];
+#pragma unroll
+            for (int j = 0; j < WPT; ++j) {
+                woff[j] = toff[j] + ((bd1[j] >> 1) ? PW : 0) + (bd1[j] & 1);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[j][k] = v1[j][k];
+            }
+            const int4 c0 = reinterpret_cast<const int4 *>(cbase[e])[0], c1 = reinterpret_cast<const int4 *>(cbase[e])[1];
+            const int cb[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            if (e + 1 < cnt) fetch(e + 1);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (cb[k] < 0) continue; // block-uniform: taps outside the group cost nothing
+#pragma unroll
+                for (int j = 0; j < WPT; ++j)
+                    if (live[j]) tile[woff[j] + cb[k]] += v[j][k];
+                __syncwarp();
+            }
+        }
+    }
+    __syncthreads();
+    const int nch = min(cg, s.Ci - ch0);
+    for (int i = tid; i < nimg * nch * HW; i += blockDim.x) {
+        const int col = i % s.W;
+        int q = i / s.W;
+        const int row = q % s.H;
+        q /= s.H;
+        const int chl = q % nch, im = q / nch;
+        gx[((size_t)(n0 + im) * s.Ci + ch0 + chl) * HW + row * s.W + col] = tile[(im * cg + chl) * PP + (row + s.ph) * PW + col + s.pw];
+    }
+}
+
 // ---------------------------------------------------------------------------- backward: gate grad
 // grid (parts, C).  Block `part` covers items [part*per, (part+1)*per) of the N*items range of channel c.
 template <typename T, bool FUSED>
@@ -580,10 +689,11 @@ __global__ void __launch_bounds__(256) conv_bwd_w_kernel(const T *__restrict__ g
 // in-bounds flags of the 4 x 8 (position, tap) pairs are computed once; per image a tap costs one
 // add, one predicate and one cached global load.  grid (parts, C); block `part` covers images
 // [N*part/parts, N*(part+1)/parts).
-__global__ void __launch_bounds__(256) convtree_bwd_w_win_kernel(const float *__restrict__ gy, const float *__restrict__ x,
+template <bool TAPGRAD>
+__global__ void __launch_bounds__(256, TAPGRAD ? 2 : 1) convtree_bwd_w_win_kernel(const float *__restrict__ gy, const float *__restrict__ x,
                                                                  const float *__restrict__ w, const int32_t *__restrict__ sel,
                                                                  const uint8_t *__restrict__ amax, float *__restrict__ partial,
-                                                                 ConvShape s, int wmode)
+                                                                 float *__restrict__ tapgrad, ConvShape s, int wmode)
 {
     __shared__ BlockGates<float> bg;
     __shared__ float red[8][28];
@@ -649,6 +759,7 @@ __global__ void __launch_bounds__(256) convtree_bwd_w_win_kernel(const float *__
 #pragma unroll
         for (int k = 0; k < 8; ++k) a[k] = a1[k];
         const float dz = dz1;
+        const size_t item_now = item;
         // advance the pipeline
         item += item_step;
         ximg += x_step;
@@ -675,6 +786,16 @@ __global__ void __launch_bounds__(256) convtree_bwd_w_win_kernel(const float *__
             acc[4 * p + 1] = fmaf(dg[p], a[2 * p], acc[4 * p + 1]);
             acc[4 * p + 2] = fmaf(dg[p], a[2 * p + 1], acc[4 * p + 2]);
             acc[4 * p + 3] += dg[p];
+        }
+        if (TAPGRAD) {
+            // gradient w.r.t. each of the 8 taps at the arg-max position, [n][c][tap][window]: the input-gradient
+            // scatter kernel adds them into the pixels without recomputing the gate chain
+            float *t = tapgrad + (item_now - win) * 8 + win;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                t[(2 * p) * I] = dg[p] * gate_da<float>(g[p], a[2 * p + 1]);
+                t[(2 * p + 1) * I] = dg[p] * gate_db<float>(g[p], a[2 * p]);
+            }
         }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -799,7 +920,10 @@ extern "C" int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, vo
 }
 
 // ---- input gradient ---------------------------------------------------------------------------
-static const size_t kTileBudget = 64 * 1024;   // lets three blocks share one SM
+// Shared-memory budget of one block's gradient tile: 4 KiB per warp that works on it, so that about fifty warps
+// stay resident per SM.  A small channel group costs nothing extra: an output channel reads two input channels
+// and therefore appears in at most two groups' lists whatever the group size.
+static const size_t kTileBudgetPerWarp = 4 * 1024;
 static const size_t kTileBudgetMax = 200 * 1024;
 
 extern "C" int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int dtype,
@@ -808,18 +932,25 @@ extern "C" int clb_conv_group_plan(int N, int Ci, int H, int W, int C, int sh, i
     if (!cg || !nb || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
     if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_ARG;
     const size_t esz = dtype == CLB_F32 ? 4 : 8;
-    const size_t hw = (size_t)4 * ((H + 1) / 2) * ((W + 1) / 2); // parity-class planes round odd sizes up
+    // per channel and image: parity-class planes (odd sizes rounded up) or the plane with its padding halo, whichever is larger
+    size_t hw = (size_t)4 * ((H + 1) / 2) * ((W + 1) / 2);
+    const size_t halo = (size_t)(H + 2 * ph) * (W + 2 * pw);
+    if (halo > hw) hw = halo;
     const int Ho = conv_out(H, ph, kh, sh), Wo = conv_out(W, pw, kw, sw);
     if (Ho <= 0 || Wo <= 0) return CLB_ERR_SHAPE;
     if (hw * esz > kTileBudgetMax) return CLB_ERR_SHAPE; // one channel plane must fit in shared memory
-    // images per block: enough (image, window) items for 256 threads when windows are few
     // as many whole images as give at most 256 (image, window) items: a thread then keeps its item
     long long items = (long long)((Ho + 1) / 2) * ((Wo + 1) / 2);
     int n_b = (int)(256 / items);
     if (n_b < 1) n_b = 1;
     if (n_b > (N > 0 ? N : 1)) n_b = N > 0 ? N : 1;
-    while (n_b > 1 && (size_t)n_b * hw * esz > kTileBudget) --n_b;
-    size_t budget = (size_t)n_b * hw * esz > kTileBudget ? kTileBudgetMax : kTileBudget;
+    long long warps = items >= 32 ? n_b : (n_b * items + 63) / 64; // the scatter kernel: a warp per image (or per 64 / items images)
+    if (items > 64) warps = 8;                                     // large images: the 256-thread kernels
+    if (warps < 2) warps = 2;
+    if (warps > 8) warps = 8;
+    size_t budget = kTileBudgetPerWarp * (size_t)warps;
+    while (n_b > 1 && (size_t)n_b * hw * esz > budget) --n_b;
+    if ((size_t)n_b * hw * esz > budget) budget = kTileBudgetMax;
     long long c_g = (long long)(budget / ((size_t)n_b * hw * esz));
     if (c_g < 1) c_g = 1;
     if (c_g > Ci) c_g = Ci;
@@ -985,8 +1116,8 @@ static int launch_bwd_w(const void *gy, const void *x, const void *w, const int3
     const int fb = (int)((ngates + 127) / 128);
     if (dtype == CLB_F32 && FUSED && amax != nullptr && items <= 256 && parts <= N) {
         const int threads = (int)((256 / items) * items); // whole images per block iteration
-        convtree_bwd_w_win_kernel<<<grid, threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
-                                                            (float *)scratch, s, wmode);
+        convtree_bwd_w_win_kernel<false><<<grid, threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
+                                                                   (float *)scratch, nullptr, s, wmode);
         gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
     } else if (dtype == CLB_F32) {
         conv_bwd_w_kernel<float, FUSED><<<grid, 256, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
@@ -1075,12 +1206,28 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
                               float *gw, void *scratch, size_t scratch_bytes, int N, int Ci, int H, int W, int C, int sh, int sw, int ph,
                               int pw, int kh, int kw, int wmode, cudaStream_t st);
 
+// Two-pass backward of the many-channel layers: convtree_bwd_w_win_kernel also writes the tap gradients
+// [N][C][8][I] (after its own partial sums in the scratch), convtree_bwd_x_scatter_kernel adds them into gx.
+// 0 when the shape does not take that path.
+static size_t two_pass_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int want_gx, int dtype)
+{
+    if (!want_gx || dtype != CLB_F32 || sh != 1 || sw != 1 || N <= 0 || C <= 0 || C > 65535) return 0;
+    const int Ho = conv_out(H, ph, kh, 1), Wo = conv_out(W, pw, kw, 1);
+    if (Ho <= 0 || Wo <= 0 || (Ho & 1) || (Wo & 1)) return 0;
+    const long long items = (long long)(Ho / 2) * (Wo / 2);
+    if (items > 256 || bwd_w_parts((long long)N * items, C) > N) return 0;
+    const size_t part = (bwd_w_scratch(N, C, items, 7, CLB_F32) + 255) / 256 * 256;
+    return part + (size_t)N * C * 8 * items * sizeof(float);
+}
+
 extern "C" size_t clb_convtree_bwd_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
                                                  int want_gx, int want_gw, int dtype)
 {
     if (!conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return 0;
     size_t fast = dtype == CLB_F32 ? clb_convtree_bwd_fast_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, want_gx, want_gw) : 0;
     size_t general = want_gw ? clb_convtree_bwd_w_scratch_bytes(N, C, conv_out(H, ph, kh, sh), conv_out(W, pw, kw, sw), dtype) : 0;
+    const size_t two_pass = two_pass_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, want_gx, dtype);
+    if (two_pass > general) general = two_pass;
     return fast > general ? fast : general;
 }
 
@@ -1095,6 +1242,47 @@ extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, co
         const int rc = clb_convtree_bwd_fast_f32((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, (float *)gw,
                                                  scratch, scratch_bytes, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, (cudaStream_t)stream);
         if (rc != CLB_ERR_SHAPE) return rc;
+    }
+    // many input channels, small images: one pass over the windows for the gate sums and the tap gradients, then a scatter
+    const size_t tp = (amax && scratch && grp_start && grp_list && cg > 0 && nb > 0 && !(wmode & CLB_SEL_UNBOUNDED) && (wmode & 0xff) <= 2)
+                          ? two_pass_scratch(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, gx != nullptr, dtype)
+                          : 0;
+    if (tp && scratch_bytes >= tp && gy && x && w && sel && conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) {
+        ConvShape s;
+        if (make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, true) == 0) {
+            const long long items = (long long)(s.Ho / 2) * (s.Wo / 2);
+            const size_t smem = sizeof(int) * 8 * kScatBatch + (size_t)nb * cg * (H + 2 * ph) * (W + 2 * pw) * sizeof(float);
+            const int G = (Ci + cg - 1) / cg;
+            if ((long long)nb * items <= 256 && nb <= 256 && smem <= 227 * 1024 && G <= 65535) {
+                cudaStream_t st = (cudaStream_t)stream;
+                const int parts = bwd_w_parts((long long)N * items, C);
+                float *partial = (float *)scratch;
+                float *tapgrad = (float *)((unsigned char *)scratch + (bwd_w_scratch(N, C, items, 7, CLB_F32) + 255) / 256 * 256);
+                const int threads = (int)((256 / items) * items);
+                convtree_bwd_w_win_kernel<true><<<dim3(parts, C), threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel,
+                                                                                    amax, partial, tapgrad, s, wmode);
+                int launched = 1;
+                if (gw) {
+                    const long long ngates = (long long)C * 7;
+                    gate_grad_finalize_kernel<float><<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, (const float *)w, (float *)gw, parts,
+                                                                                                 ngates, wmode);
+                    ++launched;
+                }
+                const int wpt = items >= 32 ? (int)((items + 31) / 32) : 2;
+                const int ipw = items >= 32 ? 1 : (int)(64 / items);
+                const int sthreads = (nb + ipw - 1) / ipw * 32; // a warp per image (or per 32 / items images)
+                auto go = [&](auto k) {
+                    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+                    k<<<dim3((N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax, (float *)gx, grp_start, grp_list, cg, nb, s);
+                    return true;
+                };
+                const bool ok = wpt == 1 ? go(convtree_bwd_x_scatter_kernel<1>) : wpt == 2 ? go(convtree_bwd_x_scatter_kernel<2>)
+                              : wpt <= 4 ? go(convtree_bwd_x_scatter_kernel<4>) : go(convtree_bwd_x_scatter_kernel<8>);
+                // (wpt == 1: images of exactly 32 windows)
+                if (!ok) return check_launch(0);
+                return check_launch(launched + 1);
+            }
+        }
     }
     if (gx) {
         const int rc = launch_bwd_x<true>(gy, x, w, sel, amax, gx, grp_start, grp_list, cg, nb, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw,

@@ -421,13 +421,11 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_chan_kernel(cons
 // base/A/B, and whatever (dy, dx) the lanes of a warp have, lane px lands in bank (px + const) of its
 // class plane: the data-dependent arg-max costs ~1.7 wavefronts per access instead of ~3 with the
 // forward's row-major layout (which also needs a third more shared memory for its halo).
-// The planes of odd rows start PR floats and those of odd columns PC floats after the even ones, with
-// PR = Wh and PC = 1 modulo 32: for a tap with an odd row (column) offset the two rows (columns) a window can
-// pick then fall into the same bank, so the pick cannot make two lanes collide; taps with an even offset
-// keep the two-way choice.  (No layout serves both parities: the 2x2 blocks of even and odd taps overlap.)
-// With 3x3 kernels and padding 1 two of three offsets are odd.
+// (Skewing the odd-row / odd-column planes by Wh and 1 floats modulo 32 makes taps with odd offsets conflict-free
+// and halves the conflict wavefronts, but it was measured to change nothing in the kernel's time -- the data pipe is
+// not what binds it -- while the padding costs two record slots; the planes are therefore dense.)
 // Out-of-image taps are predicated off instead of reading a zero halo.
-constexpr int kBwdChanBuf = 4; // sized so that three blocks (two tiles + records + static) fit one SM
+constexpr int kBwdChanBuf = 6; // sized so that three blocks (two tiles + records + static) fit one SM
 
 struct alignas(16) BwdRec {
     float g[28]; // 7 gates x (k1, ka, kb, kab)
@@ -906,9 +904,7 @@ static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int 
     if (s.Ho <= 0 || s.Wo <= 0 || (s.Ho & 1) || (s.Wo & 1)) return false;
     s.Hh = (H + 1) / 2, s.Wh = (W + 1) / 2;
     s.PL = s.Hh * s.Wh;
-    s.PC = s.PL + (((1 - s.PL) % 32) + 32) % 32;              // = 1 (mod 32)
-    s.PR = s.PC + s.PL;
-    s.PR += (((s.Wh - s.PR) % 32) + 32) % 32;                 // = Wh (mod 32)
+    s.PC = s.PL, s.PR = 2 * s.PL;
     s.CS = (s.PR + s.PC + s.PL + 3) / 4 * 4;
     s.IS = Ci * s.CS;
     const int I = (s.Ho / 2) * (s.Wo / 2);

@@ -48,12 +48,14 @@ def test_null_arguments_are_rejected_before_any_launch(lib):
 
 def test_group_plan_and_tables(lib):
     cg, nb = C.c_int(), C.c_int()
-    # the microbenchmark block: all 9 channels of one image fit one group
+    # the microbenchmark block: one image per block, a 32 KiB tile of haloed 34x34 planes
     assert lib.clb_conv_group_plan(256, 9, 32, 32, 256, 1, 1, 1, 1, 3, 3, 0, C.byref(cg), C.byref(nb)) == 0
-    assert (cg.value, nb.value) == (9, 1)
-    # tiny images: several images per block, channels split into groups that fit shared memory
+    assert (cg.value, nb.value) == (7, 1)
+    # tiny images: several images per block, small channel groups (a tile of 4 KiB per warp keeps ~50 warps per SM)
     assert lib.clb_conv_group_plan(256, 4096, 4, 4, 8192, 1, 1, 1, 1, 3, 3, 0, C.byref(cg), C.byref(nb)) == 0
-    assert nb.value == 64 and cg.value * nb.value * 16 * 4 <= 96 * 1024 and cg.value >= 1
+    assert nb.value == 64 and cg.value * nb.value * 36 * 4 <= 32 * 1024 and cg.value >= 1
+    assert lib.clb_conv_group_plan(256, 256, 16, 16, 1024, 1, 1, 1, 1, 3, 3, 0, C.byref(cg), C.byref(nb)) == 0
+    assert nb.value == 4 and cg.value * nb.value * 18 * 18 * 4 <= 16 * 1024 and cg.value >= 1
     # a channel plane that cannot fit shared memory is refused
     assert lib.clb_conv_group_plan(1, 1, 512, 512, 1, 1, 1, 1, 1, 3, 3, 0, C.byref(cg), C.byref(nb)) == -2
 

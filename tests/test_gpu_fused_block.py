@@ -333,3 +333,38 @@ def test_many_channel_forward_paths_agree(shape):
         y_gen, amax_gen, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)
         assert torch.equal(y_fast, y_gen)
         assert torch.equal(amax_fast, amax_gen)
+
+
+@pytest.mark.parametrize("shape", [
+    (40, 64, 24, 16, 16, 1, 1, 3, "rand"),     # 64 windows per image: named barriers per image
+    (33, 128, 20, 8, 8, 1, 1, 3, "rand"),      # 16 windows per image: warp-level ordering
+    (130, 600, 10, 4, 4, 1, 1, 3, "rand"),     # 4 windows per image
+    (5, 40, 6, 32, 32, 1, 1, 3, "rand"),       # 256 windows per image: block barrier
+    (20, 70, 12, 12, 12, 1, 1, 3, "rand"),     # 36 windows per image: neither divides a warp nor fills warps
+    (64, 256, 96, 16, 16, 1, 1, 3, "bits"),
+], ids=lambda s: "x".join(str(v) for v in s))
+def test_two_pass_backward_of_many_channel_layers(shape):
+    """Layers whose input does not fit the tiled kernel take the two-pass backward (gate sums + tap gradients in one
+    kernel, then a scatter into gx): equal to the separate kernels to rounding, repeatable bit for bit, and equal
+    to the CPU oracle on small cases.  (The first shape still fits the tiled kernel and is here as a control.)"""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy, geom = _case(shape, seed=21)
+    xd, wd, sd, gd = x.cuda(), logits.cuda(), sel.cuda(), gy.cuda()
+    _, amax, _, _, _ = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX)
+    gx_c, gw_c = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX)
+    gx_s = ops.convtree_bwd_x(gd, xd, wd, sd, amax, geom, W_SOFTMAX)
+    assert_close(gx_c, gx_s, 2e-6)
+    assert_close(gw_c, ops.convtree_bwd_w(gd, xd, wd, sd, amax, geom, W_SOFTMAX), 2e-5)
+    gx_2, gw_2 = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX)
+    assert torch.equal(gx_2, gx_c) and torch.equal(gw_2, gw_c)
+    gx_only, none = ops.convtree_bwd(gd, xd, wd, sd, amax, geom, W_SOFTMAX, need_gw=False)
+    assert none is None and torch.equal(gx_only, gx_c)
+    if x.shape[0] <= 40 and shape[2] <= 64:
+        xo = x.clone().requires_grad_(True)
+        yo, _, _, idxo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])
+        (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
+        idx = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)[4].cpu()
+        if bool((idx == idxo).all()):
+            assert_close(gx_c, gxo, F32_TOL)
