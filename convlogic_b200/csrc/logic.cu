@@ -188,7 +188,13 @@ __global__ void __launch_bounds__(256) logic_bwd_w_kernel(const T *__restrict__ 
 }
 
 // ----------------------------------------------------------------------------------- input grads
-template <typename T, int V>
+// gx[f] = sum over the consumers j of feature f (CSR lists built at construction) of  gy[j] * d op_j / d x_f.
+// A warp owns a (feature, batch split) unit.  The bookkeeping of up to 32 consumers is done lane-parallel --
+// lane l reads consumer lo+l, its two input indices and its 16 logits, takes the soft-max and keeps the two
+// coefficients (k0, kab) of  d op / d x_f = k0 + kab * other  -- and is then handed round by shuffles while all
+// lanes stream the consumer's two rows (gy[j] and the other operand's x row), U consumers' loads in flight
+// at a time.  Consumers are added in list order, so the result does not depend on scheduling.
+template <typename T, int V, int SLOTS>
 __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ x, const int64_t *__restrict__ ia,
                                                           const int64_t *__restrict__ ib, const T *__restrict__ w,
                                                           const T *__restrict__ gy, T *__restrict__ gx,
@@ -196,6 +202,7 @@ __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ 
                                                           long long in_dim, long long out_dim, long long B, int wmode,
                                                           int batch_splits)
 {
+    constexpr int U = 8 / SLOTS; // consumers whose rows are loaded before the first is added
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -205,42 +212,54 @@ __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ 
         const long long f = unit / batch_splits;
         const long long blo = (unit % batch_splits) * span, bhi = min(B, blo + span);
         const long long lo = start[f], hi = start[f + 1];
-        // The running sums of up to MAXV vector slots per lane stay in registers across consumers.
-        constexpr int SLOTS = 4;
         for (long long bb = blo; bb < bhi; bb += (long long)SLOTS * 32 * V) {
             T acc[SLOTS][V];
 #pragma unroll
             for (int q = 0; q < SLOTS; ++q)
 #pragma unroll
                 for (int k = 0; k < V; ++k) acc[q][k] = T(0);
-            for (long long cur = lo; cur < hi; cur += 2) {
-                // two consumers per step: lanes 0-15 prepare the first one's gate, lanes 16-31 the second's
-                const long long mine = cur + (lane >> 4);
-                const long long jm = mine < hi ? cons[mine] : -1;
-                T p;
-                const Gate<T> gh = half_warp_gate<T>(w, jm, out_dim, wmode, lane, p);
-                (void)p;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const long long c2 = cur + h;
-                    if (c2 >= hi) break;
-                    const long long j = cons[c2];
-                    const Gate<T> g = gate_from_lane<T>(gh, h * 16);
+            for (long long c0 = lo; c0 < hi; c0 += 32) {
+                const long long e = c0 + lane;
+                int my_j = 0, my_other = 0;
+                T my_k0 = T(0), my_kab = T(0);
+                if (e < hi) {
+                    const long long j = cons[e];
                     const long long a_j = ia[j], b_j = ib[j];
-                    const bool second = (a_j == f) && (b_j == f) && (c2 > lo) && (cons[c2 - 1] == j);
+                    // a neuron fed twice by f is listed twice in a row: the first entry is w.r.t. a, the second w.r.t. b
+                    const bool second = (a_j == f) && (b_j == f) && (e > lo) && (cons[e - 1] == j);
                     const bool wrt_a = (a_j == f) && !second;
-                    const T *xo = x + (wrt_a ? b_j : a_j) * B; // the other operand's row
-                    const T k0 = wrt_a ? g.ka : g.kb;
-                    const T *gr = gy + j * B;
+                    const Gate<T> g = gate_load<T>(w + j * 16, wmode);
+                    my_j = (int)j, my_other = (int)(wrt_a ? b_j : a_j);
+                    my_k0 = wrt_a ? g.ka : g.kb, my_kab = g.kab;
+                }
+                const int n = (int)min((long long)32, hi - c0);
+                for (int i0 = 0; i0 < n; i0 += U) {
+                    T o[U][SLOTS][V], d[U][SLOTS][V], k0[U], kab[U];
 #pragma unroll
-                    for (int q = 0; q < SLOTS; ++q) {
-                        const long long b0 = bb + ((long long)q * 32 + lane) * V;
-                        if (b0 < bhi) {
-                            T o[V], d[V];
-                            vload<T, V>(xo + b0, o);
-                            vload<T, V>(gr + b0, d);
+                    for (int u = 0; u < U; ++u) {
+                        const int i = min(i0 + u, n - 1); // past the end: a repeated load that is not added
+                        const T *xo = x + (long long)__shfl_sync(0xffffffffu, my_other, i) * B;
+                        const T *gr = gy + (long long)__shfl_sync(0xffffffffu, my_j, i) * B;
+                        k0[u] = __shfl_sync(0xffffffffu, my_k0, i), kab[u] = __shfl_sync(0xffffffffu, my_kab, i);
 #pragma unroll
-                            for (int k = 0; k < V; ++k) acc[q][k] = fma_t<T>(d[k], fma_t<T>(g.kab, o[k], k0), acc[q][k]);
+                        for (int q = 0; q < SLOTS; ++q) {
+                            const long long b0 = bb + ((long long)q * 32 + lane) * V;
+                            if (b0 < bhi) {
+                                vload<T, V>(xo + b0, o[u][q]);
+                                vload<T, V>(gr + b0, d[u][q]);
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < V; ++k) o[u][q][k] = T(0), d[u][q][k] = T(0);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (i0 + u < n) {
+#pragma unroll
+                            for (int q = 0; q < SLOTS; ++q)
+#pragma unroll
+                                for (int k = 0; k < V; ++k) acc[q][k] = fma_t<T>(d[u][q][k], fma_t<T>(kab[u], o[u][q][k], k0[u]), acc[q][k]);
                         }
                     }
                 }
@@ -324,14 +343,29 @@ extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b
     while (in_dim * splits < 148LL * 8 * 8 && splits < max_splits) splits *= 2;
     if (splits > max_splits) splits = max_splits;
     const int grid = logic_grid(in_dim * splits);
+    if (out_dim > 0x7fffffffLL || in_dim > 0x7fffffffLL) return CLB_ERR_SHAPE; // consumer and row indices travel as 32-bit shuffles
+    // vector slots a lane needs for its share of a split: 1, 2 or 4 at a time
+    const long long span = ((B + splits * 32 * V - 1) / (splits * 32 * V));
+    const int slots = span <= 1 ? 1 : span <= 2 ? 2 : 4;
+#define CLB_BWD_X(T, VV, SS)                                                                                                     \
+    logic_bwd_x_kernel<T, VV, SS><<<grid, 256, 0, st>>>((const T *)x, a, b, (const T *)w, (const T *)gy, (T *)gx, start, consumers, \
+                                                        in_dim, out_dim, B, wmode, (int)splits)
     if (dtype == CLB_F32) {
-        if (vec)
-            logic_bwd_x_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
-        else
-            logic_bwd_x_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
+        if (vec) {
+            if (slots == 1) CLB_BWD_X(float, 4, 1);
+            else if (slots == 2) CLB_BWD_X(float, 4, 2);
+            else CLB_BWD_X(float, 4, 4);
+        } else {
+            if (slots == 1) CLB_BWD_X(float, 1, 1);
+            else if (slots == 2) CLB_BWD_X(float, 1, 2);
+            else CLB_BWD_X(float, 1, 4);
+        }
     } else if (dtype == CLB_F64) {
-        logic_bwd_x_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (const double *)gy, (double *)gx, start, consumers, in_dim, out_dim, B, wmode, (int)splits);
+        if (slots == 1) CLB_BWD_X(double, 1, 1);
+        else if (slots == 2) CLB_BWD_X(double, 1, 2);
+        else CLB_BWD_X(double, 1, 4);
     } else
         return CLB_ERR_ARG;
+#undef CLB_BWD_X
     return check_launch();
 }
