@@ -273,6 +273,57 @@ __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ 
     }
 }
 
+// ----------------------------------------------------------------------------------- group sum
+// GroupSum on the feature-major activations the flat layers produce ([F][B]; class c owns rows [c*S, (c+1)*S)):
+// out[b][c] = (sum of the class's rows at sample b) / tau.  Two stages with a fixed order: block (batch tile,
+// class, part) adds its share of the rows warp by warp and combines the eight warps in order; the finalize kernel
+// adds the parts in order.  No transposed copy of the activations, no atomics.
+constexpr int kGroupSumParts = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) group_sum_partial_kernel(const T *__restrict__ y, T *__restrict__ partial, long long S, long long B, int k)
+{
+    __shared__ T red[8][32];
+    const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+    const long long b = (long long)blockIdx.x * 32 + lane;
+    const int c = blockIdx.y, part = blockIdx.z;
+    const long long r0 = S * part / gridDim.z, r1 = S * (part + 1) / gridDim.z;
+    T acc = T(0);
+    if (b < B)
+        for (long long r = r0 + wv; r < r1; r += 8) acc += y[((long long)c * S + r) * B + b];
+    red[wv][lane] = acc;
+    __syncthreads();
+    if (wv == 0 && b < B) {
+        T t = red[0][lane];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) t += red[i][lane];
+        partial[((long long)part * k + c) * B + b] = t;
+    }
+}
+
+template <typename T>
+__global__ void group_sum_finalize_kernel(const T *__restrict__ partial, T *__restrict__ out, long long B, int k, int parts, T tau)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; // (c, b), b fastest
+    if (i >= B * k) return;
+    const long long c = i / B, b = i - c * B;
+    T t = T(0);
+    for (int p = 0; p < parts; ++p) t += partial[((long long)p * k + c) * B + b];
+    out[b * k + c] = t / tau;
+}
+
+// gy[f][b] = gout[b][f / S] / tau
+template <typename T>
+__global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict__ gout, T *__restrict__ gy, long long F, long long S, long long B,
+                                                            int k, T tau)
+{
+    const long long total = F * B;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long f = i / B, b = i - f * B;
+        gy[i] = gout[b * k + f / S] / tau;
+    }
+}
+
 } // namespace clb
 
 using namespace clb;
@@ -367,5 +418,52 @@ extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b
     } else
         return CLB_ERR_ARG;
 #undef CLB_BWD_X
+    return check_launch();
+}
+
+static int group_sum_parts(long long S) { return S >= 8 * kGroupSumParts ? kGroupSumParts : 1; }
+
+extern "C" size_t clb_group_sum_scratch_bytes(int64_t F, int64_t B, int k, int dtype)
+{
+    if (F <= 0 || B <= 0 || k <= 0 || F % k) return 0;
+    return (size_t)group_sum_parts(F / k) * (size_t)k * (size_t)B * (dtype == CLB_F64 ? 8 : 4);
+}
+
+extern "C" int clb_group_sum_fwd(const void *y, void *out, void *scratch, size_t scratch_bytes, int64_t F, int64_t B, int k, double tau,
+                                 int dtype, void *stream)
+{
+    if (!y || !out || F < 0 || B < 0 || k <= 0 || tau == 0.0 || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
+    if (F % k) return CLB_ERR_SHAPE;
+    if (B == 0) return CLB_OK;
+    if (F == 0) return CLB_ERR_SHAPE;
+    if (!scratch || scratch_bytes < clb_group_sum_scratch_bytes(F, B, k, dtype)) return CLB_ERR_SCRATCH;
+    const long long S = F / k;
+    const int parts = group_sum_parts(S);
+    if (k > 65535) return CLB_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)((B + 31) / 32), (unsigned)k, (unsigned)parts);
+    const int fb = (int)((B * k + 255) / 256);
+    if (dtype == CLB_F32) {
+        group_sum_partial_kernel<float><<<grid, 256, 0, st>>>((const float *)y, (float *)scratch, S, B, k);
+        group_sum_finalize_kernel<float><<<fb, 256, 0, st>>>((const float *)scratch, (float *)out, B, k, parts, (float)tau);
+    } else {
+        group_sum_partial_kernel<double><<<grid, 256, 0, st>>>((const double *)y, (double *)scratch, S, B, k);
+        group_sum_finalize_kernel<double><<<fb, 256, 0, st>>>((const double *)scratch, (double *)out, B, k, parts, tau);
+    }
+    return check_launch(2);
+}
+
+extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t B, int k, double tau, int dtype, void *stream)
+{
+    if (!gout || !gy || F < 0 || B < 0 || k <= 0 || tau == 0.0 || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
+    if (F % k) return CLB_ERR_SHAPE;
+    if (B == 0 || F == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    long long blocks = (F * B + 255) / 256;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    if (dtype == CLB_F32)
+        group_sum_bwd_kernel<float><<<(int)blocks, 256, 0, st>>>((const float *)gout, (float *)gy, F, F / k, B, k, (float)tau);
+    else
+        group_sum_bwd_kernel<double><<<(int)blocks, 256, 0, st>>>((const double *)gout, (double *)gy, F, F / k, B, k, tau);
     return check_launch();
 }

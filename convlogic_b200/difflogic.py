@@ -11,7 +11,7 @@ import torch
 
 from . import ops
 from ._lib import W_ARGMAX, W_SOFTMAX
-from .functional import GradFactor, LogicLayerCudaFunction
+from .functional import GradFactor, GroupSumFunction, LogicLayerCudaFunction
 from .packbitstensor import PackBitsTensor
 
 
@@ -141,6 +141,9 @@ class GroupSum(torch.nn.Module):
         if isinstance(x, PackBitsTensor):
             return x.group_sum(self.k)
         assert x.shape[-1] % self.k == 0, (x.shape, self.k)
+        if x.is_cuda and x.dim() == 2 and x.dtype in (torch.float32, torch.float64) and x.numel() and x.t().is_contiguous():
+            # the transposed view a LogicLayer returns: sum its feature-major storage directly
+            return GroupSumFunction.apply(x.t(), self.k, self.tau)
         return x.reshape(*x.shape[:-1], self.k, x.shape[-1] // self.k).sum(-1) / self.tau
 
     def extra_repr(self):

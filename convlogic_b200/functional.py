@@ -131,3 +131,17 @@ class LogicLayerCudaFunction(Function):
         if ctx.needs_input_grad[3] and ctx.wmode != W_ARGMAX:
             gw = ops.logic_bwd_w(x, a, b, w, grad_y, ctx.wmode)
         return gx, None, None, gw, None, None, None
+
+
+class GroupSumFunction(torch.autograd.Function):
+    """GroupSum on the feature-major [F, B] storage a LogicLayer's output is a view of (no transposed copy)."""
+
+    @staticmethod
+    def forward(ctx, y_fm, k, tau):
+        ctx.meta = (y_fm.shape[0], k, tau)
+        return ops.group_sum_fwd(y_fm, k, tau)
+
+    @staticmethod
+    def backward(ctx, gout):
+        f, k, tau = ctx.meta
+        return ops.group_sum_bwd(gout.contiguous(), f, k, tau), None, None

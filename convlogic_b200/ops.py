@@ -428,3 +428,23 @@ def thermometer_pack(pixels, thresholds, slab=False):
         check(lib().clb_thermometer_pack(ptr(pixels), int(pixels.dtype == torch.uint8), ptr(thresholds), levels, ptr(out),
                                          n, cp, h * w, words, int(slab), stream()))
     return out, (64 - n % 64) % 64
+
+
+def group_sum_fwd(y_fm, k, tau):
+    """Feature-major activations [F, B] -> [B, k] class sums / tau."""
+    check_input(y_fm)
+    f, b = y_fm.shape
+    out = torch.empty((b, k), dtype=y_fm.dtype, device=y_fm.device)
+    nbytes = lib().clb_group_sum_scratch_bytes(f, b, k, dtype_code(y_fm))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=y_fm.device)
+    check(lib().clb_group_sum_fwd(ptr(y_fm), ptr(out), ptr(scratch), nbytes, f, b, k, float(tau), dtype_code(y_fm), stream()))
+    return out
+
+
+def group_sum_bwd(gout, f, k, tau):
+    """Gradient of group_sum_fwd: [B, k] -> feature-major [F, B]."""
+    check_input(gout)
+    b = gout.shape[0]
+    gy = torch.empty((f, b), dtype=gout.dtype, device=gout.device)
+    check(lib().clb_group_sum_bwd(ptr(gout), ptr(gy), f, b, k, float(tau), dtype_code(gout), stream()))
+    return gy

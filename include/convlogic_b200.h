@@ -246,6 +246,15 @@ int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const int32_t *s
                              int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t U,
                              void *stream);
 
+/* GroupSum on float activations (src/difflogic/difflogic.py:203-208: `x.reshape(..., k, F/k).sum(-1) / tau`), taken
+ * directly from the feature-major [F, B] output of clb_logic_fwd: out [B, k] = sum over the class's F/k rows / tau.
+ * scratch: clb_group_sum_scratch_bytes(F, B, k, dtype) bytes.  Fixed summation order.  clb_group_sum_bwd is its
+ * gradient: gy [F, B] = gout [B, k][class of f] / tau.  CLB_ERR_SHAPE when F % k != 0 (the reference asserts). */
+size_t clb_group_sum_scratch_bytes(int64_t F, int64_t B, int k, int dtype);
+int clb_group_sum_fwd(const void *y, void *out, void *scratch, size_t scratch_bytes, int64_t F, int64_t B, int k,
+                      double tau, int dtype, void *stream);
+int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t B, int k, double tau, int dtype, void *stream);
+
 /* ---- Compiled network -----------------------------------------------------------------------------------
  * A discretised stack (fused ConvLogic blocks, then flat LogicLayers, then GroupSum) serialised into one blob
  * and run with one call that enqueues the packed kernels above back to back.  It takes the place of the

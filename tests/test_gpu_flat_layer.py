@@ -141,3 +141,29 @@ def test_empty_batch_runs_through_a_small_stack():
         assert prm.grad is not None and float(prm.grad.abs().sum()) == 0.0
     # the context is fine afterwards
     assert net(torch.rand(2, 3, 8, 8, device="cuda")).shape == (2, 10)
+
+
+@pytest.mark.parametrize("f,b,k", [(640, 256, 10), (81920, 64, 10), (30, 7, 3), (1280, 33, 10), (12, 1, 4)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.float64, 1e-13)])
+def test_group_sum_on_feature_major_storage(f, b, k, dtype, tol):
+    """GroupSum fed with the transposed view a LogicLayer returns sums the feature-major storage directly:
+    same values and gradients as the reference expression `x.reshape(B, k, F/k).sum(-1) / tau` (and as the oracle)."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(f + b)
+    y_fm = torch.randn(f, b, dtype=dtype, device="cuda")
+    gs = cb.GroupSum(k, tau=3.5)
+    x = y_fm.t().requires_grad_(True)            # [B, F] view of feature-major storage, as LogicLayer returns it
+    out = gs(x)
+    xr = y_fm.t().contiguous().requires_grad_(True)
+    ref = xr.reshape(b, k, f // k).sum(-1) / 3.5
+    assert out.shape == (b, k)
+    assert_close(out.detach(), ref.detach(), tol)
+    assert_close(out.detach().cpu(), oracle.group_sum(y_fm.t().cpu(), k, 3.5), tol)
+    g = torch.randn(b, k, dtype=dtype, device="cuda")
+    (gx,) = torch.autograd.grad(out, x, g)
+    (gr,) = torch.autograd.grad(ref, xr, g)
+    assert_close(gx, gr, tol)                     # torch multiplies by 1/tau where the kernel divides
+    assert torch.equal(gs(x), out)                # fixed summation order: repeatable
+    with pytest.raises(AssertionError):
+        cb.GroupSum(7)(x)
