@@ -189,58 +189,90 @@ __global__ void __launch_bounds__(256) logic_bwd_w_kernel(const T *__restrict__ 
 
 // ----------------------------------------------------------------------------------- input grads
 // gx[f] = sum over the consumers j of feature f (CSR lists built at construction) of  gy[j] * d op_j / d x_f.
-// A warp owns a (feature, batch split) unit.  The bookkeeping of up to 32 consumers is done lane-parallel --
-// lane l reads consumer lo+l, its two input indices and its 16 logits, takes the soft-max and keeps the two
-// coefficients (k0, kab) of  d op / d x_f = k0 + kab * other  -- and is then handed round by shuffles while all
-// lanes stream the consumer's two rows (gy[j] and the other operand's x row), U consumers' loads in flight
-// at a time.  Consumers are added in list order, so the result does not depend on scheduling.
+// A warp owns a unit = (FPU consecutive features, batch split); the consumer entries of consecutive features are
+// one contiguous range of the CSR list, so the warp walks that range 32 entries at a time whatever the fan-out:
+// lane l reads entry e0+l, finds the feature it belongs to (a 5-step search over the 32 list starts held by the
+// lanes), reads the consumer's two input indices and 16 logits, takes the soft-max and keeps the two coefficients
+// (k0, kab) of  d op / d x_f = k0 + kab * other.  The entries are then handed round by shuffles while all lanes
+// stream each entry's two rows (gy[j] and the other operand's x row), U entries' loads in flight at a time; the
+// running sum is stored and reset whenever the feature changes (features without consumers get zeros).  FPU is 1
+// for wide fan-outs (one feature per warp) and up to 32 when a feature has one or two consumers, where a per-feature
+// chain of dependent loads would otherwise dominate.  Entries are added in list order: no dependence on scheduling.
 template <typename T, int V, int SLOTS>
 __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ x, const int64_t *__restrict__ ia,
                                                           const int64_t *__restrict__ ib, const T *__restrict__ w,
                                                           const T *__restrict__ gy, T *__restrict__ gx,
                                                           const int64_t *__restrict__ start, const int64_t *__restrict__ cons,
                                                           long long in_dim, long long out_dim, long long B, int wmode,
-                                                          int batch_splits)
+                                                          int batch_splits, int fpu)
 {
-    constexpr int U = 8 / SLOTS; // consumers whose rows are loaded before the first is added
+    constexpr int U = 8 / SLOTS; // entries whose rows are loaded before the first is added
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-    // unit = (feature, batch split); a split is a multiple of 32*V elements
+    // a split is a multiple of 32*V elements
     const long long span = ((B + (long long)batch_splits * 32 * V - 1) / ((long long)batch_splits * 32 * V)) * 32 * V;
-    for (long long unit = warp; unit < in_dim * batch_splits; unit += nwarps) {
-        const long long f = unit / batch_splits;
+    const long long funits = (in_dim + fpu - 1) / fpu;
+    for (long long unit = warp; unit < funits * batch_splits; unit += nwarps) {
+        const long long f0 = (unit / batch_splits) * fpu, f1 = min(in_dim, f0 + fpu);
         const long long blo = (unit % batch_splits) * span, bhi = min(B, blo + span);
-        const long long lo = start[f], hi = start[f + 1];
+        const long long my_start = start[min(f0 + lane, f1)]; // lanes past the unit hold its end
+        const long long lo = __shfl_sync(0xffffffffu, my_start, 0), hi = start[f1];
         for (long long bb = blo; bb < bhi; bb += (long long)SLOTS * 32 * V) {
             T acc[SLOTS][V];
 #pragma unroll
             for (int q = 0; q < SLOTS; ++q)
 #pragma unroll
                 for (int k = 0; k < V; ++k) acc[q][k] = T(0);
+            long long cur_f = f0; // the feature `acc` belongs to
+            auto flush_to = [&](long long f_next) {
+                while (cur_f < f_next) {
+#pragma unroll
+                    for (int q = 0; q < SLOTS; ++q) {
+                        const long long b0 = bb + ((long long)q * 32 + lane) * V;
+                        if (b0 < bhi) vstore<T, V>(gx + cur_f * B + b0, acc[q]);
+#pragma unroll
+                        for (int k = 0; k < V; ++k) acc[q][k] = T(0);
+                    }
+                    ++cur_f;
+                }
+            };
             for (long long c0 = lo; c0 < hi; c0 += 32) {
                 const long long e = c0 + lane;
-                int my_j = 0, my_other = 0;
+                int my_j = 0, my_other = 0, my_f = 0;
                 T my_k0 = T(0), my_kab = T(0);
-                if (e < hi) {
-                    const long long j = cons[e];
-                    const long long a_j = ia[j], b_j = ib[j];
-                    // a neuron fed twice by f is listed twice in a row: the first entry is w.r.t. a, the second w.r.t. b
-                    const bool second = (a_j == f) && (b_j == f) && (e > lo) && (cons[e - 1] == j);
-                    const bool wrt_a = (a_j == f) && !second;
-                    const Gate<T> g = gate_load<T>(w + j * 16, wmode);
-                    my_j = (int)j, my_other = (int)(wrt_a ? b_j : a_j);
-                    my_k0 = wrt_a ? g.ka : g.kb, my_kab = g.kab;
+                {
+                    // the feature of entry e: the last lane whose list start is <= e (entries past the range: any)
+                    int sel = 0;
+#pragma unroll
+                    for (int step = 16; step >= 1; step >>= 1) {
+                        const long long sv = __shfl_sync(0xffffffffu, my_start, sel + step);
+                        if (sv <= e) sel += step;
+                    }
+                    const long long fs = __shfl_sync(0xffffffffu, my_start, sel);
+                    if (e < hi) {
+                        const long long f = f0 + sel;
+                        const long long j = cons[e];
+                        const long long a_j = ia[j], b_j = ib[j];
+                        // a neuron fed twice by f is listed twice in a row: the first entry is w.r.t. a, the second w.r.t. b
+                        const bool second = (a_j == f) && (b_j == f) && (e > fs) && (cons[e - 1] == j);
+                        const bool wrt_a = (a_j == f) && !second;
+                        const Gate<T> g = gate_load<T>(w + j * 16, wmode);
+                        my_j = (int)j, my_other = (int)(wrt_a ? b_j : a_j), my_f = sel;
+                        my_k0 = wrt_a ? g.ka : g.kb, my_kab = g.kab;
+                    }
                 }
                 const int n = (int)min((long long)32, hi - c0);
                 for (int i0 = 0; i0 < n; i0 += U) {
                     T o[U][SLOTS][V], d[U][SLOTS][V], k0[U], kab[U];
+                    int fi[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
                         const int i = min(i0 + u, n - 1); // past the end: a repeated load that is not added
                         const T *xo = x + (long long)__shfl_sync(0xffffffffu, my_other, i) * B;
                         const T *gr = gy + (long long)__shfl_sync(0xffffffffu, my_j, i) * B;
                         k0[u] = __shfl_sync(0xffffffffu, my_k0, i), kab[u] = __shfl_sync(0xffffffffu, my_kab, i);
+                        fi[u] = __shfl_sync(0xffffffffu, my_f, i);
 #pragma unroll
                         for (int q = 0; q < SLOTS; ++q) {
                             const long long b0 = bb + ((long long)q * 32 + lane) * V;
@@ -256,6 +288,7 @@ __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ 
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
                         if (i0 + u < n) {
+                            flush_to(f0 + fi[u]);
 #pragma unroll
                             for (int q = 0; q < SLOTS; ++q)
 #pragma unroll
@@ -264,11 +297,7 @@ __global__ void __launch_bounds__(256) logic_bwd_x_kernel(const T *__restrict__ 
                     }
                 }
             }
-#pragma unroll
-            for (int q = 0; q < SLOTS; ++q) {
-                const long long b0 = bb + ((long long)q * 32 + lane) * V;
-                if (b0 < bhi) vstore<T, V>(gx + f * B + b0, acc[q]);
-            }
+            flush_to(f1);
         }
     }
 }
@@ -388,19 +417,25 @@ extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b
     cudaStream_t st = (cudaStream_t)stream;
     const bool vec = dtype == CLB_F32 && B % 4 == 0 && aligned16(x) && aligned16(gy) && aligned16(gx);
     const int V = vec ? 4 : 1;
-    // split the batch when there are too few features to occupy the GPU
+    // features per warp: about 32 consumer entries per unit (one feature when the fan-out 2*out/in is wide)
+    long long fpu = out_dim > 0 ? (16 * in_dim + out_dim - 1) / out_dim : 1;
+    if (fpu > 32) fpu = 32;
+    if (fpu < 1) fpu = 1;
+    while (fpu > 1 && (in_dim + fpu - 1) / fpu < 148LL * 8 * 8) fpu /= 2; // keep enough units to occupy the GPU
+    const long long funits = (in_dim + fpu - 1) / fpu;
+    // split the batch when there are too few units to occupy the GPU
     long long splits = 1;
     const long long max_splits = (B + 32LL * V * 4 - 1) / (32LL * V * 4);
-    while (in_dim * splits < 148LL * 8 * 8 && splits < max_splits) splits *= 2;
+    while (funits * splits < 148LL * 8 * 8 && splits < max_splits) splits *= 2;
     if (splits > max_splits) splits = max_splits;
-    const int grid = logic_grid(in_dim * splits);
+    const int grid = logic_grid(funits * splits);
     if (out_dim > 0x7fffffffLL || in_dim > 0x7fffffffLL) return CLB_ERR_SHAPE; // consumer and row indices travel as 32-bit shuffles
     // vector slots a lane needs for its share of a split: 1, 2 or 4 at a time
     const long long span = ((B + splits * 32 * V - 1) / (splits * 32 * V));
     const int slots = span <= 1 ? 1 : span <= 2 ? 2 : 4;
 #define CLB_BWD_X(T, VV, SS)                                                                                                     \
     logic_bwd_x_kernel<T, VV, SS><<<grid, 256, 0, st>>>((const T *)x, a, b, (const T *)w, (const T *)gy, (T *)gx, start, consumers, \
-                                                        in_dim, out_dim, B, wmode, (int)splits)
+                                                        in_dim, out_dim, B, wmode, (int)splits, (int)fpu)
     if (dtype == CLB_F32) {
         if (vec) {
             if (slots == 1) CLB_BWD_X(float, 4, 1);
