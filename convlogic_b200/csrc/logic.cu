@@ -341,15 +341,29 @@ __global__ void group_sum_finalize_kernel(const T *__restrict__ partial, T *__re
     out[b * k + c] = t / tau;
 }
 
-// gy[f][b] = gout[b][f / S] / tau
+// gy[f][b] = gout[b][f / S] / tau.  grid (row chunks, k): a thread keeps the quotients of its batch positions
+// in registers and writes them to every row of its chunk (coalesced along the batch).
 template <typename T>
-__global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict__ gout, T *__restrict__ gy, long long F, long long S, long long B,
-                                                            int k, T tau)
+__global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict__ gout, T *__restrict__ gy, long long S, long long B, int k,
+                                                            T tau)
 {
-    const long long total = F * B;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long f = i / B, b = i - f * B;
-        gy[i] = gout[b * k + f / S] / tau;
+    const int c = blockIdx.y;
+    const long long r0 = S * blockIdx.x / gridDim.x, r1 = S * (blockIdx.x + 1) / gridDim.x;
+    for (long long b0 = 0; b0 < B; b0 += 4 * 256) {
+        T v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const long long b = b0 + q * 256 + threadIdx.x;
+            v[q] = b < B ? gout[b * k + c] / tau : T(0);
+        }
+        for (long long r = r0; r < r1; ++r) {
+            T *row = gy + ((long long)c * S + r) * B;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const long long b = b0 + q * 256 + threadIdx.x;
+                if (b < B) row[b] = v[q];
+            }
+        }
     }
 }
 
@@ -494,11 +508,14 @@ extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t 
     if (F % k) return CLB_ERR_SHAPE;
     if (B == 0 || F == 0) return CLB_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    long long blocks = (F * B + 255) / 256;
-    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    const long long S = F / k;
+    if (k > 65535) return CLB_ERR_SHAPE;
+    long long chunks = (148LL * 16 + k - 1) / k; // about sixteen blocks per SM in all
+    if (chunks > S) chunks = S;
+    dim3 grid((unsigned)chunks, (unsigned)k);
     if (dtype == CLB_F32)
-        group_sum_bwd_kernel<float><<<(int)blocks, 256, 0, st>>>((const float *)gout, (float *)gy, F, F / k, B, k, (float)tau);
+        group_sum_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)gout, (float *)gy, S, B, k, (float)tau);
     else
-        group_sum_bwd_kernel<double><<<(int)blocks, 256, 0, st>>>((const double *)gout, (double *)gy, F, F / k, B, k, tau);
+        group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (double *)gy, S, B, k, tau);
     return check_launch();
 }
