@@ -72,7 +72,7 @@ class ConvLogicLayer(nn.Module):
         PackBitsTensor ``[C_out, H_out/2, W_out/2, words]``)."""
         assert not self.training, "PackBitsTensor is not supported for the differentiable training mode."
         assert self.complete, "packed inference is defined for the complete block"
-        gate_ids = self.weights.argmax(-1).to(torch.uint8)
+        gate_ids = self._gate_ids()
         geom = (*self.stride, *self.padding, *self.kernel)
         sel = self.selection.contiguous()
         if not x.slab:
@@ -92,6 +92,21 @@ class ConvLogicLayer(nn.Module):
 
     def unpack_selection(self, selection):
         return (selection >> 16) & 0xFFFF, (selection >> 8) & 0xFF, selection & 0xFF
+
+    def _gate_ids(self):
+        """uint8 arg-max gate of every neuron for packed inference, cached until the logits change (in-place
+        updates bump the tensor version, re-assignment changes the storage, ``train()`` drops the cache)."""
+        w = self.weights
+        key = (w._version, w.data_ptr(), w.device)
+        cached = getattr(self, "_gate_cache", None)
+        if cached is None or cached[0] != key:
+            cached = (key, w.detach().argmax(-1).to(torch.uint8))
+            self._gate_cache = cached
+        return cached[1]
+
+    def train(self, mode=True):
+        self._gate_cache = None
+        return super().train(mode)
 
     def extra_repr(self):
         return f"in_channels={self.in_channels}, out_channels={self.out_channels}, groups={self.groups}"

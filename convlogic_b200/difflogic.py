@@ -107,9 +107,24 @@ class LogicLayer(torch.nn.Module):
         t = x.rows()
         t = t.reshape(-1, t.shape[-1])
         assert t.shape[0] == self.in_dim, (tuple(t.shape), self.in_dim)
-        gate_ids = self.weights.argmax(-1).to(torch.uint8)
+        gate_ids = self._gate_ids()
         y = ops.packed_logic(t, self.indices_0, self.indices_1, gate_ids)
         return PackBitsTensor.from_packed(y, x.pad_len)
+
+    def _gate_ids(self):
+        """uint8 arg-max gate of every neuron for packed inference, cached until the logits change (in-place
+        updates bump the tensor version, re-assignment changes the storage, ``train()`` drops the cache)."""
+        w = self.weights
+        key = (w._version, w.data_ptr(), w.device)
+        cached = getattr(self, "_gate_cache", None)
+        if cached is None or cached[0] != key:
+            cached = (key, w.detach().argmax(-1).to(torch.uint8))
+            self._gate_cache = cached
+        return cached[1]
+
+    def train(self, mode=True):
+        self._gate_cache = None
+        return super().train(mode)
 
     def extra_repr(self):
         return "{}, {}, {}".format(self.in_dim, self.out_dim, "train" if self.training else "eval")

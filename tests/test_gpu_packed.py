@@ -175,3 +175,33 @@ def test_thermometer_pack_equals_transform_then_pack(n, cp, h, w, levels, u8):
     if want.shape[-1] % 2:
         with pytest.raises(RuntimeError):
             ops.thermometer_pack(pix.cuda(), torch.from_numpy(th).cuda(), slab=True)
+
+
+def test_cached_gate_ids_follow_the_logits():
+    """Packed inference caches the arg-max gate ids; an in-place update, a re-assignment of .data and a
+    train()/eval() round trip must each be seen."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(1)
+    layer = cb.LogicLayer(64, 80).cuda().eval()
+    x = torch.rand(130, 64, device="cuda") < 0.5
+
+    def run():
+        y = layer(cb.PackBitsTensor(x, 64))
+        with torch.no_grad():
+            want = layer(x.float())
+        got = oracle.unpack_bits(y.t.cpu().numpy(), 130).T.astype(np.float32)
+        assert np.array_equal(got, want.cpu().numpy())
+        return got
+
+    a = run()
+    with torch.no_grad():
+        layer.weights.copy_(torch.randn_like(layer.weights))     # in place: version changes
+    b = run()
+    layer.weights.data = torch.randn_like(layer.weights)          # new storage
+    c = run()
+    layer.train()
+    layer.weights.data.copy_(torch.randn_like(layer.weights))     # invisible to the version counter ...
+    layer.eval()                                                  # ... but train()/eval() drops the cache
+    d = run()
+    assert not np.array_equal(a, b) and not np.array_equal(b, c) and not np.array_equal(c, d)
