@@ -86,7 +86,10 @@ class ConvLogicLayer(nn.Module):
         slab = x.t if x.slab else (ops.packed_to_slab(x.t) if fits else None)
         if slab is not None and fits:
             assert slab.shape[0] == self.in_channels, (tuple(slab.shape), self.in_channels)
-            return PackBitsTensor.from_packed(ops.packed_convtree_slab(slab, gate_ids, sel, geom), x.pad_len, slab=True)
+            try:
+                return PackBitsTensor.from_packed(ops.packed_convtree_slab(slab, gate_ids, sel, geom), x.pad_len, slab=True)
+            except ValueError:
+                pass  # a tile the kernel cannot hold in shared memory: the rows-layout kernel takes any shape
         y = ops.packed_convtree(x.rows(), gate_ids, sel, geom)
         return PackBitsTensor.from_packed(y, x.pad_len)
 

@@ -238,10 +238,16 @@ extern "C" int clb_net_forward(const clb_net *net, int input_kind, const void *i
                 if (st != CLB_OK) return st;
                 cur ^= 1, slab = want_slab;
             }
-            if (slab)
+            if (slab) {
                 st = clb_packed_convtree_slab(buf[cur], P + L.off_ops, (const int32_t *)(P + L.off_a), buf[cur ^ 1], scratch, L.Ci, L.H, L.W,
                                               L.C, 1, 1, L.ph, L.pw, L.kh, L.kw, U, stream);
-            else
+                if (st == CLB_ERR_SHAPE) { // a tile the slab kernel cannot hold: this block runs on the rows layout
+                    st = clb_packed_layout(buf[cur], buf[cur ^ 1], L.Ci, (int64_t)L.H * L.W, U, 0, stream);
+                    if (st != CLB_OK) return st;
+                    cur ^= 1, slab = false;
+                }
+            }
+            if (!slab)
                 st = clb_packed_convtree(buf[cur], P + L.off_ops, (const int32_t *)(P + L.off_a), buf[cur ^ 1], L.Ci, L.H, L.W, L.C,
                                          L.stride, L.stride, L.ph, L.pw, L.kh, L.kw, words, 64, stream);
             if (st != CLB_OK) return st;

@@ -207,8 +207,9 @@ __device__ __forceinline__ void csa(unsigned &hi, unsigned &lo, unsigned a, unsi
     lo = u ^ c;
 }
 
-constexpr int kUpperPlanes = 28; // counts up to 16 * 2^28 rows per class
-
+// PLANES bit planes above the sixteens: a thread can count 16 * 2^PLANES rows (8 planes when its share of the rows
+// allows it: the ripple through the planes is most of the work per 16 rows)
+template <int PLANES>
 __global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__restrict__ x, int *__restrict__ counts, long long S,
                                                              long long units, long long B, int k, int splits)
 {
@@ -221,9 +222,9 @@ __global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__r
         const long long r_lo = per * sp, r_hi = min(S, r_lo + per);
         const unsigned *base = x + ((long long)cls * S) * units + u;
         unsigned ones = 0, twos = 0, fours = 0, eights = 0;
-        unsigned up[kUpperPlanes];
+        unsigned up[PLANES];
 #pragma unroll
-        for (int p = 0; p < kUpperPlanes; ++p) up[p] = 0;
+        for (int p = 0; p < PLANES; ++p) up[p] = 0;
         for (long long r = r_lo; r < r_hi; r += 16) {
             unsigned v[16];
 #pragma unroll
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__r
             // ripple the sixteens into the upper counter
             unsigned carry = t16;
 #pragma unroll
-            for (int p = 0; p < kUpperPlanes; ++p) {
+            for (int p = 0; p < PLANES; ++p) {
                 const unsigned nc = up[p] & carry;
                 up[p] ^= carry;
                 carry = nc;
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__r
             if (s >= B) break;
             int c = ((ones >> bit) & 1) + 2 * ((twos >> bit) & 1) + 4 * ((fours >> bit) & 1) + 8 * ((eights >> bit) & 1);
 #pragma unroll
-            for (int p = 0; p < kUpperPlanes; ++p) c += (int)((up[p] >> bit) & 1u) << (4 + p);
+            for (int p = 0; p < PLANES; ++p) c += (int)((up[p] >> bit) & 1u) << (4 + p);
             if (splits == 1)
                 counts[s * k + cls] = c;
             else if (c)
@@ -771,12 +772,17 @@ extern "C" int clb_group_popcount(const void *x, int32_t *counts, int64_t F, int
     if (rowbytes % 4 == 0 && aligned_to(x, 4)) {
         const long long units = rowbytes / 4;
         long long splits = 1;
-        while ((long long)k * splits * units < 148LL * 128 * 4 && S / (splits * 2) >= 64) splits *= 2;
+        while ((long long)k * splits * units < 148LL * 128 * 16 && S / (splits * 2) >= 64) splits *= 2; // 16 resident blocks per SM: the row loop is latency-bound
         if (splits > 1) {
             if (cudaMemsetAsync(counts, 0, (size_t)B * k * sizeof(int32_t), st) != cudaSuccess) return check_launch();
         }
-        group_popcount_kernel<<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B, k,
-                                                                                             (int)splits);
+        const long long per = ((S + splits - 1) / splits + 15) / 16 * 16; // rows per thread, as the kernel computes it
+        if (per <= 16 * 256)
+            group_popcount_kernel<8><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B, k,
+                                                                                                    (int)splits);
+        else
+            group_popcount_kernel<27><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B,
+                                                                                                     k, (int)splits);
     } else {
         group_popcount_bytes_kernel<<<flat_grid(B * k, 256), 256, 0, st>>>((const uint8_t *)x, counts, S, rowbytes, B, k);
     }

@@ -167,3 +167,38 @@ def test_group_sum_on_feature_major_storage(f, b, k, dtype, tol):
     assert torch.equal(gs(x), out)                # fixed summation order: repeatable
     with pytest.raises(AssertionError):
         cb.GroupSum(7)(x)
+
+
+@pytest.mark.parametrize("in_dim,out_dim,batch", [(50, 40, 64), (500, 60, 20), (33, 700, 256), (2000, 1000, 96), (7, 3, 5)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float64, 1e-12)])
+def test_input_gradient_with_arbitrary_connections(in_dim, out_dim, batch, dtype, tol):
+    """Hand-made connections, drawn uniformly: inputs without any consumer (their gradient is zero), neurons fed
+    twice by the same input, fan-outs from 0 to dozens inside one unit of the segmented kernel -- against autograd
+    through the oracle."""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    rng = np.random.default_rng(in_dim + out_dim)
+    a = torch.from_numpy(rng.integers(0, in_dim, out_dim))
+    b = torch.from_numpy(rng.integers(0, in_dim, out_dim))
+    b[: max(1, out_dim // 10)] = a[: max(1, out_dim // 10)]      # self-paired neurons
+    if in_dim > 20:                                               # a run of inputs nobody reads
+        a[(a >= 5) & (a < 12)] = 0
+        b[(b >= 5) & (b < 12)] = 1
+    start, cons = oracle.inverse_connections(a.numpy(), b.numpy(), in_dim)
+    torch.manual_seed(0)
+    x = torch.rand(batch, in_dim, dtype=dtype)
+    logits = torch.randn(out_dim, 16, dtype=dtype)
+    gy = torch.randn(batch, out_dim, dtype=dtype)
+    xo = x.clone().requires_grad_(True)
+    yo = oracle.logic_layer(xo, a, b, oracle.gate_probabilities(logits, True))
+    (gxo,) = torch.autograd.grad((yo * gy).sum(), (xo,))
+    x_fm, gy_fm = x.t().contiguous().cuda(), gy.t().contiguous().cuda()
+    gx = ops.logic_bwd_x(x_fm, a.cuda(), b.cuda(), logits.cuda(), gy_fm, torch.from_numpy(start).cuda(),
+                         torch.from_numpy(cons).cuda(), W_SOFTMAX)
+    assert_close(gx.t().cpu(), gxo, tol)
+    if in_dim > 20:
+        assert float(gx[5:12].abs().max()) == 0.0
+    again = ops.logic_bwd_x(x_fm, a.cuda(), b.cuda(), logits.cuda(), gy_fm, torch.from_numpy(start).cuda(),
+                            torch.from_numpy(cons).cuda(), W_SOFTMAX)
+    assert torch.equal(gx, again)
