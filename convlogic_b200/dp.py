@@ -28,12 +28,46 @@ class GradBucket:
         self.numel = sum(p.numel() for p in self.params)
         self.flat = torch.zeros(self.numel, dtype=p0.dtype, device=p0.device)
         off = 0
+        self.ranges = []
         for p in self.params:
             p.grad = self.flat[off:off + p.numel()].view_as(p)
+            self.ranges.append((off, off + p.numel()))
             off += p.numel()
+        self._works, self._hooks, self._group, self._average = [], [], None, True
 
     def zero(self):
         self.flat.zero_()
+
+    # ---- all-reduce overlapped with the rest of the backward pass
+    def overlap(self, group=None, average=True):
+        """From now on every layer's slice of the bucket is all-reduced (asynchronously) the moment autograd has
+        accumulated that layer's gradient, i.e. while the layers in front of it are still in their backward
+        kernels; call ``finish()`` after ``backward()`` and before the optimizer step.  The last layers' slices
+        (the large flat layers) go first, as they are ready first."""
+        self.remove_overlap()
+        self._group, self._average = group, average
+        for p, (lo, hi) in zip(self.params, self.ranges):
+            self._hooks.append(p.register_post_accumulate_grad_hook(lambda _p, lo=lo, hi=hi: self._slice_ready(lo, hi)))
+        return self
+
+    def remove_overlap(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks, self._works = [], []
+
+    def _slice_ready(self, lo, hi):
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self._group) == 1:
+            return
+        self._works.append(dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=self._group, async_op=True))
+
+    def finish(self):
+        """Waits for the slices in flight (the waits are stream-side for NCCL) and applies the averaging."""
+        works, self._works = self._works, []
+        for w in works:
+            w.wait()
+        if works and self._average:
+            self.flat.div_(dist.get_world_size(self._group))
+        return len(works)
 
     def allreduce(self, group=None, average=True, async_op=False):
         """Sum (or mean) over ranks.  A no-op without an initialised process group."""

@@ -46,6 +46,19 @@ def _worker(rank, world, port, fail_rank):
         bucket.zero()
         assert float(params[1].grad.abs().max()) == 0.0
 
+        # overlapped variant: a slice is all-reduced from a hook as soon as autograd has accumulated into it
+        bucket.overlap(average=True)
+        bucket.zero()
+        loss = sum((p * float(rank + 1)).sum() for p in params)   # d loss / d p = rank + 1 everywhere
+        loss.backward()
+        assert bucket.finish() == len(params)
+        assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
+        assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
+        bucket.remove_overlap()
+        bucket.zero()
+        sum((p * 2.0).sum() for p in params).backward()
+        assert bucket.finish() == 0 and torch.allclose(bucket.flat, torch.full_like(bucket.flat, 2.0))
+
         # one-shot variant on ordinary .grad tensors
         for p in params:
             p.grad = torch.full_like(p, float(10 * (rank + 1)))
