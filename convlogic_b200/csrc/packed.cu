@@ -560,7 +560,6 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
             cp_async16(reinterpret_cast<uint4 *>(&R) + j, reinterpret_cast<const uint4 *>(recs + c) + j);
     };
     // copies of the planes of an item whose record is already visible
-    // copies of the planes of an item whose record is already visible
     auto stage = [&](int ug, const SlabRec &R, uint4 *dst) {
         const int u0 = ug * s.UB;
         const int n = min(s.UB, s.U - u0) * HW;
