@@ -28,10 +28,33 @@ def _align16(n):
     return (n + 15) // 16 * 16
 
 
-def serialise(model, input_shape=None):
+def fuse_flat_layers(run):
+    """2 or 3 consecutive LogicLayers -> (leaf int32 [out, 2^m], ops uint8 [out, 2^m - 1]): every neuron of the last
+    layer as a gate tree over rows of the first layer's input (``clb_packed_tree``'s tables)."""
+    m = len(run)
+    assert m in (2, 3)
+    idx = [(l.indices_0.detach().cpu().numpy().astype(np.int64), l.indices_1.detach().cpu().numpy().astype(np.int64)) for l in run]
+    gate = [l.weights.detach().argmax(-1).cpu().numpy().astype(np.uint8) for l in run]
+    out = run[-1].out_dim
+    # nodes[level] = neuron ids of layer `level` (0 = first layer) feeding the tree, in tree order, [out, 2^(m-1-level)]
+    nodes = [None] * m
+    nodes[m - 1] = np.arange(out, dtype=np.int64)[:, None]
+    for lvl in range(m - 1, 0, -1):
+        a, b = idx[lvl]
+        cur = nodes[lvl]
+        nodes[lvl - 1] = np.stack([a[cur], b[cur]], axis=-1).reshape(out, -1)  # children of node q at 2q, 2q+1
+    a0, b0 = idx[0]
+    leaf = np.stack([a0[nodes[0]], b0[nodes[0]]], axis=-1).reshape(out, -1).astype(np.int32)
+    ops = np.concatenate([gate[lvl][nodes[lvl]] for lvl in range(m)], axis=1).astype(np.uint8)
+    assert leaf.shape == (out, 1 << m) and ops.shape == (out, (1 << m) - 1)
+    return leaf, ops
+
+
+def serialise(model, input_shape=None, fuse=True):
     """``nn.Sequential`` (fused complete ConvLogicLayers, Flatten, LogicLayers, GroupSum last) -> blob bytes.
 
-    ``input_shape`` = (C, H, W) is required when the stack starts with a conv block."""
+    ``input_shape`` = (C, H, W) is required when the stack starts with a conv block.  ``fuse``: emit runs of flat
+    layers that halve their width as one gate-tree layer (no intermediate activations at run time)."""
     layers = list(model)
     if not isinstance(layers[-1], GroupSum):
         raise AssertionError(f"The last layer of the model must be GroupSum, but it is {type(layers[-1])} / {layers[-1]} instead.")
@@ -47,7 +70,33 @@ def serialise(model, input_shape=None):
         return off
 
     in_features = None
+    flat_run = []  # consecutive LogicLayers, emitted (fused where it pays) when the run ends
+
+    def emit_flat(run):
+        i = 0
+        while i < len(run):
+            # fuse up to three layers while every output of a layer is read at most about once by the next
+            m = 1
+            while fuse and m < 3 and i + m < len(run) and 2 * run[i + m].out_dim <= run[i + m - 1].out_dim:
+                m += 1
+            if m == 1:
+                layer = run[i]
+                a = layer.indices_0.detach().cpu().numpy().astype(np.int64)
+                b = layer.indices_1.detach().cpu().numpy().astype(np.int64)
+                ops = layer.weights.detach().argmax(-1).cpu().numpy().astype(np.uint8)
+                recs.append((2, [layer.in_dim & 0xFFFFFFFF, layer.out_dim & 0xFFFFFFFF, layer.in_dim >> 32, layer.out_dim >> 32, 0, 0, 0],
+                             add(a), add(b), add(ops)))
+            else:
+                leaf, ops = fuse_flat_layers(run[i:i + m])
+                first, last = run[i], run[i + m - 1]
+                recs.append((3, [first.in_dim & 0xFFFFFFFF, last.out_dim & 0xFFFFFFFF, first.in_dim >> 32, last.out_dim >> 32, m, 0, 0],
+                             add(leaf), 0, add(ops)))
+            i += m
+
     for layer in layers[:-1]:
+        if flat_run and not isinstance(layer, LogicLayer):
+            emit_flat(flat_run)
+            flat_run = []
         if isinstance(layer, ConvLogicLayer):
             if not layer.complete:
                 raise AssertionError("only complete (fused) ConvLogicLayer blocks can be compiled")
@@ -60,15 +109,13 @@ def serialise(model, input_shape=None):
         elif isinstance(layer, LogicLayer):
             if in_features is None and not recs:
                 in_features = layer.in_dim
-            a = layer.indices_0.detach().cpu().numpy().astype(np.int64)
-            b = layer.indices_1.detach().cpu().numpy().astype(np.int64)
-            ops = layer.weights.detach().argmax(-1).cpu().numpy().astype(np.uint8)
-            recs.append((2, [layer.in_dim & 0xFFFFFFFF, layer.out_dim & 0xFFFFFFFF, layer.in_dim >> 32, layer.out_dim >> 32, 0, 0, 0],
-                         add(a), add(b), add(ops)))
+            flat_run.append(layer)
         elif isinstance(layer, torch.nn.Flatten):
             continue
         else:
             raise AssertionError(f"Error: layer {type(layer)} / {layer} unknown.")
+    if flat_run:
+        emit_flat(flat_run)
     if not recs:
         raise AssertionError("the model holds no logic layer")
     image = recs[0][0] == 1
@@ -87,7 +134,7 @@ def serialise(model, input_shape=None):
 
 
 class CompiledLogicNet(torch.nn.Module):
-    def __init__(self, model=None, device="cuda", num_bits=64, input_shape=None, verbose=False):
+    def __init__(self, model=None, device="cuda", num_bits=64, input_shape=None, verbose=False, fuse=True):
         super().__init__()
         assert num_bits == 64, "the GPU runtime packs 64 samples per word"
         self.model, self.device, self.num_bits, self.input_shape = model, torch.device(device), num_bits, input_shape
@@ -97,7 +144,7 @@ class CompiledLogicNet(torch.nn.Module):
         self._workspace = None
         if model is not None:
             self.num_classes = model[-1].k
-            self.blob = serialise(model, input_shape)
+            self.blob = serialise(model, input_shape, fuse)
             if verbose:
                 print(f"blob of {len(self.blob)} bytes created.")
 

@@ -11,6 +11,8 @@
 //   layer i (64 bytes): u32 kind (1 fused conv block, 2 flat layer), u32 p[7], u64 off_a, u64 off_b, u64 off_ops, pad
 //       conv: p = {Ci, C, kh, kw, stride, pad_h, pad_w}; off_a -> int32 sel[C][8]; off_ops -> u8 ops[C][7]
 //       flat: p = {in_dim (lo), out_dim (lo), in_dim (hi), out_dim (hi)}; off_a / off_b -> int64 idx[out]; off_ops -> u8 ops[out]
+//       kind 3, two or three flat layers fused into a gate tree (clb_packed_tree): p = {in_dim (lo), out_dim (lo), in_dim (hi),
+//             out_dim (hi), levels}; off_a -> int32 leaf[out][2^levels]; off_ops -> u8 ops[out][2^levels - 1]
 //   arrays
 // The last flat layer's outputs are summed per class (GroupSum): counts[b][k].
 #include "clb_common.cuh"
@@ -41,8 +43,9 @@ struct Layer {
     int kind;
     // conv
     int Ci, C, kh, kw, stride, ph, pw, H, W, Hp, Wp; // input extent and pooled output extent
-    // flat
+    // flat (kind 2) and fused flat tree (kind 3)
     long long in_dim, out_dim;
+    int levels;
     size_t off_a, off_b, off_ops;
 };
 
@@ -100,6 +103,15 @@ static bool parse(const void *blob, size_t bytes, clb_net &net)
             if (L.in_dim != feat || L.out_dim <= 0) return false;
             if (!in_blob(r.off_a, (unsigned long long)L.out_dim * 8) || !in_blob(r.off_b, (unsigned long long)L.out_dim * 8) ||
                 !in_blob(r.off_ops, (unsigned long long)L.out_dim))
+                return false;
+            feat = L.out_dim;
+        } else if (r.kind == 3) {
+            flat_seen = true;
+            L.in_dim = (long long)r.p[0] | ((long long)r.p[2] << 32), L.out_dim = (long long)r.p[1] | ((long long)r.p[3] << 32);
+            L.levels = (int)r.p[4];
+            if (L.in_dim != feat || L.out_dim <= 0 || (L.levels != 2 && L.levels != 3) || L.in_dim > 0x7fffffffLL) return false;
+            const unsigned long long leaves = 1ull << L.levels;
+            if (!in_blob(r.off_a, (unsigned long long)L.out_dim * leaves * 4) || !in_blob(r.off_ops, (unsigned long long)L.out_dim * (leaves - 1)))
                 return false;
             feat = L.out_dim;
         } else {
@@ -259,9 +271,15 @@ extern "C" int clb_net_forward(const clb_net *net, int input_kind, const void *i
                 if (st != CLB_OK) return st;
                 cur ^= 1, slab = false;
             }
-        } else {
+        } else if (L.kind == 2) {
             st = clb_packed_logic(buf[cur], (const int64_t *)(P + L.off_a), (const int64_t *)(P + L.off_b), P + L.off_ops, buf[cur ^ 1],
                                   L.in_dim, L.out_dim, words, 64, stream);
+            if (st != CLB_OK) return st;
+            cur ^= 1;
+            feat = L.out_dim;
+        } else {
+            st = clb_packed_tree(buf[cur], (const int32_t *)(P + L.off_a), P + L.off_ops, buf[cur ^ 1], L.in_dim, L.out_dim, L.levels, words,
+                                 64, stream);
             if (st != CLB_OK) return st;
             cur ^= 1;
             feat = L.out_dim;

@@ -194,6 +194,49 @@ __global__ void __launch_bounds__(256) packed_logic_v4_kernel(const uint4 *__res
     }
 }
 
+// Two or three consecutive flat layers as one pass.  When a layer's outputs are each read about once by the next
+// layer (the stacks halve their width from layer to layer, and `randperm(2*out) % in` then uses every output
+// exactly once), a neuron of the last layer is a gate tree over 2^M rows of the FIRST layer's input: the
+// intermediate activations (the largest tensors of the stack) are never written or read.  leaf [out][2^M] are the
+// input rows in tree order (gate p of the first level reads leaves 2p and 2p+1), ops [out][2^M - 1] the gate ids
+// level by level (first level, ..., root).  Rows move in 8- or 16-byte units like the single layer.
+template <typename V4, int M>
+__global__ void __launch_bounds__(256) packed_tree_kernel(const V4 *__restrict__ x, const int32_t *__restrict__ leaf,
+                                                          const uint8_t *__restrict__ ops, V4 *__restrict__ y, long long out_dim,
+                                                          long long units)
+{
+    constexpr int L = 1 << M, G = L - 1;
+    constexpr int W = sizeof(V4) / 4;
+    const long long total = out_dim * units;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long j = i / units, u = i % units;
+        unsigned v[L][W];
+#pragma unroll
+        for (int k = 0; k < L; ++k) {
+            const V4 q = __ldg(x + (long long)__ldg(leaf + j * L + k) * units + u);
+            const unsigned *qw = reinterpret_cast<const unsigned *>(&q);
+#pragma unroll
+            for (int w = 0; w < W; ++w) v[k][w] = qw[w];
+        }
+        int g = 0;
+#pragma unroll
+        for (int n = L / 2; n >= 1; n /= 2) { // n gates on this level
+#pragma unroll
+            for (int p = 0; p < n; ++p) {
+                const OpMasks<unsigned> m = op_masks<unsigned>(__ldg(ops + j * G + g + p));
+#pragma unroll
+                for (int w = 0; w < W; ++w) v[p][w] = op_apply<unsigned>(m, v[2 * p][w], v[2 * p + 1][w]);
+            }
+            g += n;
+        }
+        V4 r;
+        unsigned *rw = reinterpret_cast<unsigned *>(&r);
+#pragma unroll
+        for (int w = 0; w < W; ++w) rw[w] = v[0][w];
+        y[i] = r;
+    }
+}
+
 // ----------------------------------------------------------------------------------- group sum
 // x rows as 32-bit units (32 samples each).  thread <-> (class, row split, unit).  Rows are added 16 at
 // a time into bit-sliced counters (carry-save adders: ones, twos, fours, eights + ripple counter for
@@ -754,6 +797,35 @@ extern "C" int clb_packed_logic(const void *x, const int64_t *a, const int64_t *
     } else {
         packed_logic_kernel<uint8_t><<<flat_grid(out_dim * rowbytes, 256), 256, 0, st>>>((const uint8_t *)x, a, b, ops, (uint8_t *)y,
                                                                                         out_dim, rowbytes);
+    }
+    return check_launch();
+}
+
+extern "C" int clb_packed_tree(const void *x, const int32_t *leaf, const uint8_t *ops, void *y, int64_t in_dim, int64_t out_dim, int levels,
+                               int64_t words, int bits, void *stream)
+{
+    if (!x || !leaf || !ops || !y || in_dim <= 0 || out_dim < 0 || words < 0 || !bits_ok(bits) || (levels != 2 && levels != 3))
+        return CLB_ERR_ARG;
+    if (in_dim > 0x7fffffffLL) return CLB_ERR_SHAPE;
+    const long long rowbytes = words * (bits / 8);
+    if (out_dim == 0 || rowbytes == 0) return CLB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16)) {
+        const long long units = rowbytes / 16;
+        const int grid = flat_grid(out_dim * units, 256);
+        if (levels == 2)
+            packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units);
+        else
+            packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units);
+    } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
+        const long long units = rowbytes / 8;
+        const int grid = flat_grid(out_dim * units, 256);
+        if (levels == 2)
+            packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units);
+        else
+            packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units);
+    } else {
+        return CLB_ERR_SHAPE; // rows of 64-bit words only
     }
     return check_launch();
 }

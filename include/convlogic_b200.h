@@ -220,6 +220,14 @@ int clb_packed_convtree(const void *x, const uint8_t *ops, const int32_t *sel, v
                         int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t words, int bits,
                         void *stream);
 
+/* Two or three consecutive packed flat layers in one pass (no counterpart in the reference, which runs
+ * difflogic_cuda.eval once per layer): neuron j of the LAST layer as a gate tree over 2^levels rows of the FIRST
+ * layer's input.  leaf int32 [out][2^levels]: input rows in tree order (first-level gate p reads leaves 2p, 2p+1);
+ * ops uint8 [out][2^levels - 1]: gate ids level by level, first level first, root last.  Rows of 8-byte multiples
+ * only (CLB_ERR_SHAPE otherwise).  Worth it when every output of a layer is read about once by the next one. */
+int clb_packed_tree(const void *x, const int32_t *leaf, const uint8_t *ops, void *y, int64_t in_dim, int64_t out_dim,
+                    int levels, int64_t words, int bits, void *stream);
+
 /* Fused input stage of packed inference: thermometer encoding + bit packing.  Replaces the reference's
  * host-side transform `cat([(x > t) for t in thresholds], dim=0)` (src/convlogic/data.py:46-50, thresholds
  * from :52-71) followed by PackBitsTensor (src/difflogic/packbitstensor.py:12-21) on the device, without the

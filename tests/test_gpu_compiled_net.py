@@ -97,3 +97,38 @@ def test_save_load_and_fused_pixel_input(tmp_path):
     assert torch.equal(a.forward_pixels(u8, th), a(bits8))
     with pytest.raises(ValueError):
         a(torch.zeros(4, 7, dtype=torch.bool))
+
+
+@pytest.mark.parametrize("dims", [(64, 320, 160, 150), (96, 640, 320, 160), (50, 400, 200, 100, 50, 30)])
+def test_fused_flat_layers_equal_layer_by_layer(dims):
+    """Runs of flat layers that halve their width are emitted as one gate-tree layer (two or three levels): same
+    counts as the unfused blob and as the module path, for batches that do and do not fill the last word."""
+    import convlogic_b200 as cb
+    from convlogic_b200.compiled_model import fuse_flat_layers
+
+    torch.manual_seed(len(dims))
+    layers = [cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])]
+    model = torch.nn.Sequential(*layers, cb.GroupSum(10, 1.0)).cuda().eval()
+    _randomise(model, 11)
+    fused = cb.CompiledLogicNet(model, fuse=True).compile()
+    plain = cb.CompiledLogicNet(model, fuse=False).compile()
+    assert plain.num_layers == len(layers) and fused.num_layers < plain.num_layers
+    for batch in (1, 64, 200):
+        x = torch.rand(batch, dims[0], device="cuda") < 0.5
+        with torch.no_grad():
+            want = model(cb.PackBitsTensor(x, 64))
+        assert torch.equal(fused(x), want) and torch.equal(plain(x), want)
+    # the tables themselves, against a direct evaluation of the two layers on the CPU oracle
+    leaf, ops = fuse_flat_layers(layers[:2])
+    xb = (np.random.default_rng(0).random((dims[0], 70)) < 0.5)
+    h, _ = oracle.pack_bits(xb, 64)
+    for layer in layers[:2]:
+        h = oracle.packed_logic(h, layer.indices_0.cpu().numpy(), layer.indices_1.cpu().numpy(),
+                                layer.weights.argmax(-1).cpu().numpy().astype(np.uint8))
+    from convlogic_b200 import _lib
+    x_dev = torch.from_numpy(oracle.pack_bits(xb, 64)[0]).cuda()
+    y_dev = torch.empty((dims[2], x_dev.shape[1]), dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().clb_packed_tree(_lib.ptr(x_dev), _lib.ptr(torch.from_numpy(leaf).cuda()), _lib.ptr(torch.from_numpy(ops).cuda()),
+                                          _lib.ptr(y_dev), dims[0], dims[2], 2, x_dev.shape[1], 64, _lib.stream()))
+    torch.cuda.synchronize()
+    assert np.array_equal(y_dev.cpu().numpy(), h)
