@@ -6,7 +6,7 @@ Public names mirror the reference packages ``convlogic`` and ``difflogic``
 
 from .convlogic_layer import ConvLogicLayer, PoolLogicLayer  # noqa: F401
 from .treelogic_layer import TreeLogicLayer  # noqa: F401
-from .difflogic import GroupSum, LogicLayer, get_unique_connections  # noqa: F401
+from .difflogic import FusedLogicLayers, GroupSum, LogicLayer, fuse_logic_layers, get_unique_connections  # noqa: F401
 from .packbitstensor import PackBitsTensor  # noqa: F401
 from .functional import (  # noqa: F401
     ConvLogicFunction,
@@ -22,5 +22,5 @@ from ._lib import LIB_PATH, W_ARGMAX, W_PROB, W_SOFTMAX  # noqa: F401
 __all__ = [
     "ConvLogicLayer", "PoolLogicLayer", "TreeLogicLayer", "LogicLayer", "GroupSum", "PackBitsTensor",
     "ConvLogicFunction", "FullConvLogicFunction", "TreeLogicFunction", "LogicLayerCudaFunction", "GradFactor",
-    "ConvLogicCifarModel", "ConvLogicMnistModel", "get_unique_connections", "CompiledLogicNet",
+    "ConvLogicCifarModel", "ConvLogicMnistModel", "get_unique_connections", "CompiledLogicNet", "FusedLogicLayers", "fuse_logic_layers",
 ]

@@ -56,6 +56,8 @@ _SIGNATURES = {
     "clb_packed_convtree": ([_vp] * 4 + [_i] * 10 + [_i64, _i, _vp], _i),
     "clb_packed_tree": ([_vp, _vp, _vp, _vp, _i64, _i64, _i, _i64, _i, _vp], _i),
     "clb_thermometer_pack": ([_vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i64, _i, _vp], _i),
+    "clb_logic_tree_fwd": ([_vp] * 7 + [_i64, _i64, _i, _vp], _i),
+    "clb_logic_tree_bwd": ([_vp] * 14 + [_i64, _i64, _i64, _i, _vp], _i),
     "clb_group_sum_scratch_bytes": ([_i64, _i64, _i, _i], _sz),
     "clb_group_sum_fwd": ([_vp, _vp, _vp, _sz, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_group_sum_bwd": ([_vp, _vp, _i64, _i64, _i, C.c_double, _i, _vp], _i),

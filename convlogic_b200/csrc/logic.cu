@@ -367,6 +367,170 @@ __global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict_
     }
 }
 
+// ----------------------------------------------------------------------------------- fused flat layers (training)
+// Three consecutive flat layers whose outputs are each read at most once by the next one, as ONE differentiable
+// gate tree per neuron of the last layer: leaf [T][8] are rows of the first layer's input (gate p of the first
+// level reads leaves 2p, 2p+1), node [T][7] the neuron that sits at each tree position (4 of the first layer, 2 of
+// the second, 1 of the third: its logits are the gate's).  The two intermediate activations are never written.
+// Forward: a warp per tree, lanes along the batch.  Backward pass 1: the chain recomputed from the leaves, the
+// gradient w.r.t. each leaf written as a row of `tapgrad` [T*8][B], the 28 basis sums of the 7 gates reduced over
+// the batch and turned into the logit (or mixture) gradients of the 7 neurons.  Pass 2: gx[f] = sum of the
+// tapgrad rows of the leaves that are feature f (CSR by feature, fixed order).
+struct TreeTables {
+    const int32_t *leaf; // [T][8]
+    const int32_t *node; // [T][7]
+    const float *w[3];   // logits (or mixtures) of the three layers
+};
+
+__device__ __forceinline__ Gate<float> tree_gate(const TreeTables &tt, long long t, int g, int wmode)
+{
+    const int layer = g < 4 ? 0 : (g < 6 ? 1 : 2);
+    return gate_load<float>(tt.w[layer] + (long long)__ldg(tt.node + t * 7 + g) * 16, wmode);
+}
+
+// lanes 0..6 hold gate g = lane; everybody gets all seven
+__device__ __forceinline__ void tree_gates_broadcast(const Gate<float> &mine, Gate<float> (&g)[7])
+{
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+        g[i].k1 = __shfl_sync(0xffffffffu, mine.k1, i), g[i].ka = __shfl_sync(0xffffffffu, mine.ka, i);
+        g[i].kb = __shfl_sync(0xffffffffu, mine.kb, i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, i);
+    }
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) logic_tree_fwd_kernel(const float *__restrict__ x, TreeTables tt, float *__restrict__ y, long long T,
+                                                             long long B, int wmode)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long t = warp; t < T; t += nwarps) {
+        Gate<float> mine = {0.f, 0.f, 0.f, 0.f}, g[7];
+        if (lane < 7) mine = tree_gate(tt, t, lane, wmode);
+        tree_gates_broadcast(mine, g);
+        const float *row[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
+        for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
+            float a[8][V], r[V];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vload<float, V>(row[k] + b0, a[k]);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float g0 = gate_eval<float>(g[0], a[0][e], a[1][e]), g1 = gate_eval<float>(g[1], a[2][e], a[3][e]);
+                const float g2 = gate_eval<float>(g[2], a[4][e], a[5][e]), g3 = gate_eval<float>(g[3], a[6][e], a[7][e]);
+                r[e] = gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+            }
+            vstore<float, V>(y + t * B + b0, r);
+        }
+    }
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
+                                                             float *__restrict__ tapgrad, float *__restrict__ gw0, float *__restrict__ gw1,
+                                                             float *__restrict__ gw2, long long T, long long B, int wmode)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long t = warp; t < T; t += nwarps) {
+        Gate<float> mine = {0.f, 0.f, 0.f, 0.f}, g[7];
+        if (lane < 7) mine = tree_gate(tt, t, lane, wmode);
+        tree_gates_broadcast(mine, g);
+        const float *row[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
+        float bs[28];
+#pragma unroll
+        for (int i = 0; i < 28; ++i) bs[i] = 0.f;
+        for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
+            float a[8][V], dz[V], tg[8][V];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vload<float, V>(row[k] + b0, a[k]);
+            vload<float, V>(gy + t * B + b0, dz);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float g0 = gate_eval<float>(g[0], a[0][e], a[1][e]), g1 = gate_eval<float>(g[1], a[2][e], a[3][e]);
+                const float g2 = gate_eval<float>(g[2], a[4][e], a[5][e]), g3 = gate_eval<float>(g[3], a[6][e], a[7][e]);
+                const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+                const float d = dz[e];
+                const float dt0 = d * gate_da<float>(g[6], t1), dt1 = d * gate_db<float>(g[6], t0);
+                const float dg[4] = {dt0 * gate_da<float>(g[4], g1), dt0 * gate_db<float>(g[4], g0), dt1 * gate_da<float>(g[5], g3),
+                                     dt1 * gate_db<float>(g[5], g2)};
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    tg[2 * p][e] = dg[p] * gate_da<float>(g[p], a[2 * p + 1][e]);
+                    tg[2 * p + 1][e] = dg[p] * gate_db<float>(g[p], a[2 * p][e]);
+                    bs[4 * p] = fmaf(dg[p], a[2 * p][e] * a[2 * p + 1][e], bs[4 * p]), bs[4 * p + 1] = fmaf(dg[p], a[2 * p][e], bs[4 * p + 1]);
+                    bs[4 * p + 2] = fmaf(dg[p], a[2 * p + 1][e], bs[4 * p + 2]), bs[4 * p + 3] += dg[p];
+                }
+                bs[16] = fmaf(dt0, g0 * g1, bs[16]), bs[17] = fmaf(dt0, g0, bs[17]), bs[18] = fmaf(dt0, g1, bs[18]), bs[19] += dt0;
+                bs[20] = fmaf(dt1, g2 * g3, bs[20]), bs[21] = fmaf(dt1, g2, bs[21]), bs[22] = fmaf(dt1, g3, bs[22]), bs[23] += dt1;
+                bs[24] = fmaf(d, t0 * t1, bs[24]), bs[25] = fmaf(d, t0, bs[25]), bs[26] = fmaf(d, t1, bs[26]), bs[27] += d;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vstore<float, V>(tapgrad + (t * 8 + k) * B + b0, tg[k]);
+        }
+        // batch totals of the 28 sums (xor butterfly: every lane ends with all of them), then lane g finishes gate g
+#pragma unroll
+        for (int i = 0; i < 28; ++i) bs[i] = warp_sum<float>(bs[i]);
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int gi = 0; gi < 7; ++gi)
+            if (lane == gi) s4[0] = bs[4 * gi], s4[1] = bs[4 * gi + 1], s4[2] = bs[4 * gi + 2], s4[3] = bs[4 * gi + 3];
+        if (lane < 7) {
+            const int layer = lane < 4 ? 0 : (lane < 6 ? 1 : 2);
+            const long long n = __ldg(tt.node + t * 7 + lane);
+            float *out = (layer == 0 ? gw0 : layer == 1 ? gw1 : gw2) + n * 16;
+            gate_grad_store<float>(s4, tt.w[layer] + n * 16, wmode, out);
+        }
+    }
+}
+
+// gx[f][b] = sum over the entries e of feature f of rows[list[e]][b]  (rows = tapgrad, list = leaf slots t*8+k)
+template <int V>
+__global__ void __launch_bounds__(256) row_segment_sum_kernel(const float *__restrict__ rows, const int64_t *__restrict__ start,
+                                                              const int32_t *__restrict__ list, float *__restrict__ gx, long long F,
+                                                              long long B)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long f = warp; f < F; f += nwarps) {
+        const long long lo = start[f], hi = start[f + 1];
+        for (long long bb = 0; bb < B; bb += 32 * V) { // uniform over the warp: the shuffles below need every lane
+            const long long b0 = bb + (long long)lane * V;
+            const bool in = b0 < B;
+            float acc[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = 0.f;
+            for (long long c0 = lo; c0 < hi; c0 += 32) {
+                const int mine = c0 + lane < hi ? __ldg(list + c0 + lane) : 0;
+                const int n = (int)min((long long)32, hi - c0);
+                for (int i0 = 0; i0 < n; i0 += 4) {
+                    float v[4][V];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int r = __shfl_sync(0xffffffffu, mine, min(i0 + u, n - 1));
+                        if (in) {
+                            vload<float, V>(rows + (long long)r * B + b0, v[u]);
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < V; ++k) v[u][k] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (i0 + u < n)
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc[k] += v[u][k];
+                }
+            }
+            if (in)
+                vstore<float, V>(gx + f * B + b0, acc);
+        }
+    }
+}
+
 } // namespace clb
 
 using namespace clb;
@@ -518,4 +682,57 @@ extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t 
     else
         group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (double *)gy, S, B, k, tau);
     return check_launch();
+}
+
+// ---- fused flat layers (training) ------------------------------------------------------------------
+static bool tree_args_ok(const void *x, const int32_t *leaf, const int32_t *node, const void *w0, const void *w1, const void *w2, int64_t T,
+                         int64_t B, int wmode)
+{
+    return x && leaf && node && w0 && w1 && w2 && T >= 0 && B >= 0 && wmode >= 0 && wmode <= 2;
+}
+
+extern "C" int clb_logic_tree_fwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
+                                  float *y, int64_t T, int64_t B, int wmode, void *stream)
+{
+    if (!tree_args_ok(x, leaf, node, w0, w1, w2, T, B, wmode) || !y) return CLB_ERR_ARG;
+    if (T == 0 || B == 0) return CLB_OK;
+    TreeTables tt{leaf, node, {w0, w1, w2}};
+    const int grid = logic_grid(T);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B % 4 == 0 && aligned16(x) && aligned16(y))
+        logic_tree_fwd_kernel<4><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode);
+    else
+        logic_tree_fwd_kernel<1><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode);
+    return check_launch();
+}
+
+// tapgrad: scratch of T*8*B floats.  gw0/gw1/gw2 must be zeroed by the caller: neurons no tree uses keep zero.
+// start int64 [in_dim + 1], list int32 [T*8]: the leaf slots (t*8 + k) grouped by the input feature they read.
+extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
+                                  const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2, float *gx, const int64_t *start,
+                                  const int32_t *list, int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)
+{
+    if (!tree_args_ok(x, leaf, node, w0, w1, w2, T, B, wmode) || !gy || !tapgrad || !gw0 || !gw1 || !gw2 || in_dim <= 0) return CLB_ERR_ARG;
+    if (gx && (!start || !list)) return CLB_ERR_ARG;
+    if (T * 8 > 0x7fffffffLL) return CLB_ERR_SHAPE;
+    if (B == 0) return CLB_OK;
+    TreeTables tt{leaf, node, {w0, w1, w2}};
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = B % 4 == 0 && aligned16(x) && aligned16(gy) && aligned16(tapgrad) && (!gx || aligned16(gx));
+    int launched = 0;
+    if (T > 0) {
+        if (vec)
+            logic_tree_bwd_kernel<4><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode);
+        else
+            logic_tree_bwd_kernel<1><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode);
+        ++launched;
+    }
+    if (gx) {
+        if (vec)
+            row_segment_sum_kernel<4><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B);
+        else
+            row_segment_sum_kernel<1><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B);
+        ++launched;
+    }
+    return check_launch(launched);
 }

@@ -11,7 +11,7 @@ import torch
 
 from . import ops
 from ._lib import W_ARGMAX, W_SOFTMAX
-from .functional import GradFactor, GroupSumFunction, LogicLayerCudaFunction
+from .functional import GradFactor, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction
 from .packbitstensor import PackBitsTensor
 
 
@@ -163,3 +163,88 @@ class GroupSum(torch.nn.Module):
 
     def extra_repr(self):
         return f"k={self.k}, tau={self.tau}"
+
+
+class FusedLogicLayers(torch.nn.Module):
+    """Three consecutive ``LogicLayer`` s run as one kernel per pass in training (float) mode.
+
+    When every output of a layer is read at most once by the next one -- the stacks of the reference's models halve
+    their width, and ``randperm(2 * out) % in`` then uses every output exactly once -- a neuron of the last layer
+    is a gate tree over 8 features of the first layer's input, and the two intermediate activations (the largest
+    tensors of the flat stack) need not exist.  The three layers stay what they are (same parameters and buffers,
+    reachable as ``self.layers``); packed inference and any input the fused path does not cover run through them
+    one after the other.  Opt-in: see ``fuse_logic_layers``."""
+
+    def __init__(self, layers):
+        super().__init__()
+        layers = list(layers)
+        if len(layers) != 3 or not all(isinstance(l, LogicLayer) for l in layers):
+            raise ValueError("FusedLogicLayers takes exactly three LogicLayers")
+        for prev, nxt in zip(layers[:-1], layers[1:]):
+            if prev.out_dim != nxt.in_dim:
+                raise ValueError("the layers do not follow each other")
+            used = torch.cat([nxt.indices_0, nxt.indices_1])
+            if used.unique().numel() != used.numel():
+                raise ValueError("a layer's output is read more than once by the next layer: fusing would recompute it")
+        self.layers = torch.nn.ModuleList(layers)
+        self.in_dim, self.out_dim = layers[0].in_dim, layers[-1].out_dim
+        idx = [(l.indices_0.long().cpu(), l.indices_1.long().cpu()) for l in layers]
+        n2 = torch.arange(self.out_dim)[:, None]                                  # third-layer neuron of every tree
+        n1 = torch.stack([idx[2][0][n2], idx[2][1][n2]], -1).reshape(self.out_dim, 2)   # its two second-layer neurons
+        n0 = torch.stack([idx[1][0][n1], idx[1][1][n1]], -1).reshape(self.out_dim, 4)   # their four first-layer neurons
+        leaf = torch.stack([idx[0][0][n0], idx[0][1][n0]], -1).reshape(self.out_dim, 8)
+        node = torch.cat([n0, n1, n2], 1)
+        order = torch.sort(leaf.reshape(-1), stable=True)                          # leaf slots grouped by feature
+        start = torch.zeros(self.in_dim + 1, dtype=torch.int64)
+        start[1:] = torch.cumsum(torch.bincount(leaf.reshape(-1), minlength=self.in_dim), 0)
+        dev = layers[0].indices_0.device
+        self.register_buffer("leaf", leaf.to(torch.int32).to(dev), persistent=False)
+        self.register_buffer("node", node.to(torch.int32).to(dev), persistent=False)
+        self.register_buffer("leaf_start", start.to(dev), persistent=False)
+        self.register_buffer("leaf_slots", order.indices.to(torch.int32).to(dev), persistent=False)
+
+    def forward(self, x):
+        first = self.layers[0]
+        fused = (not isinstance(x, PackBitsTensor) and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
+                 and all(l.grad_factor == 1.0 for l in self.layers) and x.shape[0] > 0)
+        if not fused:
+            for layer in self.layers:
+                x = layer(x)
+            return x
+        assert x.shape[1] == first.in_dim, (x.shape, first.in_dim)
+        x_fm = x.transpose(0, 1).contiguous()
+        w = [l.weights for l in self.layers]
+        if self.training:
+            y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_SOFTMAX)
+        else:
+            with torch.no_grad():
+                y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_ARGMAX)
+        return y.transpose(0, 1)
+
+    def extra_repr(self):
+        return f"{self.in_dim} -> {' -> '.join(str(l.out_dim) for l in self.layers)}"
+
+
+def fuse_logic_layers(model):
+    """A copy of an ``nn.Sequential`` in which every run of three LogicLayers that can be fused is replaced by a
+    ``FusedLogicLayers`` over the SAME layer objects (parameters are shared with ``model``)."""
+    out, run = [], []
+
+    def flush():
+        while len(run) >= 3:
+            try:
+                out.append(FusedLogicLayers(run[:3]))
+                del run[:3]
+            except ValueError:
+                out.append(run.pop(0))
+        out.extend(run)
+        run.clear()
+
+    for m in model:
+        if isinstance(m, LogicLayer):
+            run.append(m)
+        else:
+            flush()
+            out.append(m)
+    flush()
+    return torch.nn.Sequential(*out)

@@ -145,3 +145,23 @@ class GroupSumFunction(torch.autograd.Function):
     def backward(ctx, gout):
         f, k, tau = ctx.meta
         return ops.group_sum_bwd(gout.contiguous(), f, k, tau), None, None
+
+
+class LogicTreeFunction(torch.autograd.Function):
+    """Three flat layers fused into one gate tree per neuron of the last one (feature-major in and out)."""
+
+    @staticmethod
+    def forward(ctx, x_fm, w0, w1, w2, leaf, node, start, slots, wmode):
+        x_fm, w0, w1, w2 = x_fm.contiguous(), w0.contiguous(), w1.contiguous(), w2.contiguous()
+        ctx.save_for_backward(x_fm, w0, w1, w2, leaf, node, start, slots)
+        ctx.wmode = wmode
+        return ops.logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x_fm, w0, w1, w2, leaf, node, start, slots = ctx.saved_tensors
+        gx, g0, g1, g2 = ops.logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy.contiguous(), start, slots, ctx.wmode,
+                                            need_gx=ctx.needs_input_grad[0])
+        if ctx.wmode == W_ARGMAX:
+            g0 = g1 = g2 = None
+        return gx, g0, g1, g2, None, None, None, None, None

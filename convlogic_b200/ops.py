@@ -448,3 +448,24 @@ def group_sum_bwd(gout, f, k, tau):
     gy = torch.empty((f, b), dtype=gout.dtype, device=gout.device)
     check(lib().clb_group_sum_bwd(ptr(gout), ptr(gy), f, b, k, float(tau), dtype_code(gout), stream()))
     return gy
+
+
+def logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode):
+    """Three fused flat layers, forward: x [in, B] -> y [T, B] (see ``clb_logic_tree_fwd``)."""
+    check_input(x_fm, leaf, node, w0, w1, w2)
+    t, b = leaf.shape[0], x_fm.shape[1]
+    y = torch.empty((t, b), dtype=torch.float32, device=x_fm.device)
+    check(lib().clb_logic_tree_fwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(y), t, b, wmode, stream()))
+    return y
+
+
+def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True):
+    """Gradients of ``logic_tree_fwd``: (gx [in, B] or None, gw0, gw1, gw2)."""
+    check_input(x_fm, leaf, node, w0, w1, w2, gy, start, slots)
+    t, b, in_dim = leaf.shape[0], x_fm.shape[1], x_fm.shape[0]
+    tapgrad = torch.empty((max(t * 8, 1), b), dtype=torch.float32, device=x_fm.device)
+    gws = [torch.zeros_like(w) for w in (w0, w1, w2)]
+    gx = torch.empty_like(x_fm) if need_gx else None
+    check(lib().clb_logic_tree_bwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(gy), ptr(tapgrad), ptr(gws[0]),
+                                   ptr(gws[1]), ptr(gws[2]), ptr(gx), ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))
+    return gx, gws[0], gws[1], gws[2]

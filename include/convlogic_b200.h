@@ -254,6 +254,22 @@ int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const int32_t *s
                              int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int64_t U,
                              void *stream);
 
+/* Three consecutive flat layers as one differentiable gate tree per neuron of the last layer (no counterpart in
+ * the reference, which calls difflogic_cuda.forward / backward_w / backward_x once per layer).  Valid when every
+ * output of a layer is read at most once by the next one (layer widths halving with `randperm(2*out) % in`
+ * connections).  leaf int32 [T][8]: rows of the first layer's feature-major input x [in, B] in tree order; node
+ * int32 [T][7]: the neuron at each tree position (4 of the first layer, 2 of the second, 1 of the third); w0/w1/w2:
+ * the three layers' gate tensors [out_l][16] (wmode as elsewhere).  y [T][B].
+ * Backward: tapgrad is scratch of T*8*B floats; gw0/gw1/gw2 [out_l][16] must be zero on entry (neurons no tree
+ * uses keep zero); gx [in][B] may be NULL; start int64 [in+1], list int32 [T*8]: leaf slots t*8+k grouped by the
+ * feature they read, in increasing slot order.  Fixed summation order. */
+int clb_logic_tree_fwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                       const float *w2, float *y, int64_t T, int64_t B, int wmode, void *stream);
+int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                       const float *w2, const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2,
+                       float *gx, const int64_t *start, const int32_t *list, int64_t in_dim, int64_t T, int64_t B,
+                       int wmode, void *stream);
+
 /* GroupSum on float activations (src/difflogic/difflogic.py:203-208: `x.reshape(..., k, F/k).sum(-1) / tau`), taken
  * directly from the feature-major [F, B] output of clb_logic_fwd: out [B, k] = sum over the class's F/k rows / tau.
  * scratch: clb_group_sum_scratch_bytes(F, B, k, dtype) bytes.  Fixed summation order.  clb_group_sum_bwd is its

@@ -202,3 +202,61 @@ def test_input_gradient_with_arbitrary_connections(in_dim, out_dim, batch, dtype
     again = ops.logic_bwd_x(x_fm, a.cuda(), b.cuda(), logits.cuda(), gy_fm, torch.from_numpy(start).cuda(),
                             torch.from_numpy(cons).cuda(), W_SOFTMAX)
     assert torch.equal(gx, again)
+
+
+@pytest.mark.parametrize("dims,batch", [((40, 320, 160, 80), 64), ((96, 640, 320, 160), 256), ((30, 200, 100, 50), 37), ((64, 480, 240, 120), 4)])
+def test_three_fused_layers_equal_the_layers_one_by_one(dims, batch):
+    """FusedLogicLayers (one gate tree per neuron of the last layer) against the same three LogicLayers run in
+    sequence: soft and hard forward, input gradient and the logit gradients of all three layers; repeatable."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(sum(dims))
+    seq = torch.nn.Sequential(*[cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])], cb.GroupSum(10, 2.0)).cuda()
+    g = torch.Generator().manual_seed(3)
+    for prm in seq.parameters():
+        prm.data = torch.randn(*prm.shape, generator=g).cuda()
+    fused = cb.fuse_logic_layers(seq)
+    assert isinstance(fused[0], cb.FusedLogicLayers) and len(fused) == 2
+    assert fused[0].layers[0].weights is seq[0].weights          # shared parameters
+    x = torch.rand(batch, dims[0], device="cuda")
+    gy = torch.randn(batch, 10, device="cuda")
+
+    def run(model):
+        model.train()
+        for prm in model.parameters():
+            prm.grad = None
+        xi = x.clone().requires_grad_(True)
+        out = model(xi)
+        out.backward(gy)
+        grads = [seq[i].weights.grad.clone() for i in range(3)]
+        model.eval()
+        with torch.no_grad():
+            hard = model(x)
+        return out.detach(), xi.grad.clone(), grads, hard
+
+    y_s, gx_s, gw_s, h_s = run(seq)
+    y_f, gx_f, gw_f, h_f = run(fused)
+    assert_close(y_f, y_s, 1e-5)
+    assert_close(gx_f, gx_s, 1e-5)
+    for a, b in zip(gw_f, gw_s):
+        assert_close(a, b, 2e-5)
+    assert torch.equal(h_f, h_s)                                   # one-hot gates on the same inputs: exact
+    y_2, gx_2, gw_2, _ = run(fused)
+    assert torch.equal(y_2, y_f) and torch.equal(gx_2, gx_f) and all(torch.equal(a, b) for a, b in zip(gw_2, gw_f))
+    # packed input goes through the three layers themselves
+    xb = torch.rand(batch, dims[0], device="cuda") < 0.5
+    fused.eval()
+    seq.eval()
+    with torch.no_grad():
+        assert torch.equal(fused(cb.PackBitsTensor(xb, 64)), seq(cb.PackBitsTensor(xb, 64)))
+
+
+def test_fusing_is_refused_when_outputs_are_read_twice():
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    layers = [cb.LogicLayer(40, 100), cb.LogicLayer(100, 90), cb.LogicLayer(90, 60)]   # 2 * 90 > 100: outputs reused
+    with pytest.raises(ValueError):
+        cb.FusedLogicLayers(layers)
+    model = cb.fuse_logic_layers(torch.nn.Sequential(*layers, cb.GroupSum(10)))
+    assert all(isinstance(m, cb.LogicLayer) for m in list(model)[:3])
