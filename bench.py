@@ -447,7 +447,7 @@ def run_c3(args):
     g = torch.Generator().manual_seed(1)
     for prm in net.parameters():
         prm.data = torch.randn(*prm.shape, generator=g)
-    net = net.to(dev).train()
+    net = cb.fuse_logic_layers(net.to(dev)).train()  # the three flat layers run as one gate tree per output neuron (same parameters)
     bucket = dp.GradBucket(net).overlap(average=True)  # a layer's slice is all-reduced while the layers in front of it run backward
     opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
     sets = 4

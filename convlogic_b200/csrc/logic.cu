@@ -427,7 +427,7 @@ __global__ void __launch_bounds__(256) logic_tree_fwd_kernel(const float *__rest
 }
 
 template <int V>
-__global__ void __launch_bounds__(256) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
+__global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
                                                              float *__restrict__ tapgrad, float *__restrict__ gw0, float *__restrict__ gw1,
                                                              float *__restrict__ gw2, long long T, long long B, int wmode)
 {
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(256) logic_tree_bwd_kernel(const float *__rest
 #pragma unroll
         for (int i = 0; i < 28; ++i) bs[i] = 0.f;
         for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
-            float a[8][V], dz[V], tg[8][V];
+            float a[8][V], dz[V], dg[4][V];
 #pragma unroll
             for (int k = 0; k < 8; ++k) vload<float, V>(row[k] + b0, a[k]);
             vload<float, V>(gy + t * B + b0, dz);
@@ -455,21 +455,26 @@ __global__ void __launch_bounds__(256) logic_tree_bwd_kernel(const float *__rest
                 const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
                 const float d = dz[e];
                 const float dt0 = d * gate_da<float>(g[6], t1), dt1 = d * gate_db<float>(g[6], t0);
-                const float dg[4] = {dt0 * gate_da<float>(g[4], g1), dt0 * gate_db<float>(g[4], g0), dt1 * gate_da<float>(g[5], g3),
-                                     dt1 * gate_db<float>(g[5], g2)};
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    tg[2 * p][e] = dg[p] * gate_da<float>(g[p], a[2 * p + 1][e]);
-                    tg[2 * p + 1][e] = dg[p] * gate_db<float>(g[p], a[2 * p][e]);
-                    bs[4 * p] = fmaf(dg[p], a[2 * p][e] * a[2 * p + 1][e], bs[4 * p]), bs[4 * p + 1] = fmaf(dg[p], a[2 * p][e], bs[4 * p + 1]);
-                    bs[4 * p + 2] = fmaf(dg[p], a[2 * p + 1][e], bs[4 * p + 2]), bs[4 * p + 3] += dg[p];
-                }
+                dg[0][e] = dt0 * gate_da<float>(g[4], g1), dg[1][e] = dt0 * gate_db<float>(g[4], g0);
+                dg[2][e] = dt1 * gate_da<float>(g[5], g3), dg[3][e] = dt1 * gate_db<float>(g[5], g2);
                 bs[16] = fmaf(dt0, g0 * g1, bs[16]), bs[17] = fmaf(dt0, g0, bs[17]), bs[18] = fmaf(dt0, g1, bs[18]), bs[19] += dt0;
                 bs[20] = fmaf(dt1, g2 * g3, bs[20]), bs[21] = fmaf(dt1, g2, bs[21]), bs[22] = fmaf(dt1, g3, bs[22]), bs[23] += dt1;
                 bs[24] = fmaf(d, t0 * t1, bs[24]), bs[25] = fmaf(d, t0, bs[25]), bs[26] = fmaf(d, t1, bs[26]), bs[27] += d;
             }
+            // leaf gradients pair by pair, stored at once so that they do not occupy registers
 #pragma unroll
-            for (int k = 0; k < 8; ++k) vstore<float, V>(tapgrad + (t * 8 + k) * B + b0, tg[k]);
+            for (int p = 0; p < 4; ++p) {
+                float ta[V], tb[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    const float x0 = a[2 * p][e], x1 = a[2 * p + 1][e], d = dg[p][e];
+                    ta[e] = d * gate_da<float>(g[p], x1), tb[e] = d * gate_db<float>(g[p], x0);
+                    bs[4 * p] = fmaf(d, x0 * x1, bs[4 * p]), bs[4 * p + 1] = fmaf(d, x0, bs[4 * p + 1]);
+                    bs[4 * p + 2] = fmaf(d, x1, bs[4 * p + 2]), bs[4 * p + 3] += d;
+                }
+                vstore<float, V>(tapgrad + (t * 8 + 2 * p) * B + b0, ta);
+                vstore<float, V>(tapgrad + (t * 8 + 2 * p + 1) * B + b0, tb);
+            }
         }
         // batch totals of the 28 sums (xor butterfly: every lane ends with all of them), then lane g finishes gate g
 #pragma unroll
