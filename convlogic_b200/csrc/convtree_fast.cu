@@ -718,12 +718,12 @@ __global__ void __launch_bounds__(kFastThreads / WPT, 3) convtree_bwd_cls_kernel
 // Adds the per-group basis sums and turns them into the 16 gradients of every gate.  Eight threads share a
 // gate: each adds a contiguous eighth of the groups in order, then the eight partial sums are added in
 // order -- a fixed summation tree, so the result does not depend on scheduling.
-__global__ void __launch_bounds__(256) convtree_gw_finalize_kernel(const float *__restrict__ wpartial, const float *__restrict__ w,
-                                                                   float *__restrict__ gw, int groups, int ngates, int wmode)
+__device__ __forceinline__ void gw_finalize_block(const float *__restrict__ wpartial, const float *__restrict__ w, float *__restrict__ gw,
+                                                  int groups, int ngates, int wmode, int block)
 {
     __shared__ float4 part[32][8];
     const int local = threadIdx.x >> 3, sub = threadIdx.x & 7;
-    const int gi = blockIdx.x * 32 + local;
+    const int gi = block * 32 + local;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (gi < ngates) {
         const int per = (groups + 7) / 8;
@@ -745,15 +745,21 @@ __global__ void __launch_bounds__(256) convtree_gw_finalize_kernel(const float *
     }
 }
 
+__global__ void __launch_bounds__(256) convtree_gw_finalize_kernel(const float *__restrict__ wpartial, const float *__restrict__ w,
+                                                                   float *__restrict__ gw, int groups, int ngates, int wmode)
+{
+    gw_finalize_block(wpartial, w, gw, groups, ngates, wmode, blockIdx.x);
+}
+
 // gx of every group that no single block covered = sum of that group's partial tiles, in block order.
 // grid (chunks, groups): the owners of a group's first and last channel are found once per thread.
-__global__ void convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gx, ClsShape s, int grid)
+__device__ __forceinline__ void bwd_x_reduce_block(const float *__restrict__ partial, float *__restrict__ gx, const ClsShape &s, int grid,
+                                                   int bx, int grp, int chunks)
 {
     const int HW = s.H * s.W;
     const int per_group = s.G * s.Ci * HW;
     const int NG = (s.N + s.G - 1) / s.G;
     const long long units = (long long)NG * s.C;
-    const int grp = blockIdx.y;
     // owner(u): the block b with units*b/grid <= u < units*(b+1)/grid
     auto owner = [&](long long u) {
         long long b = u * grid / units;
@@ -766,12 +772,31 @@ __global__ void convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, 
     const int live = min(s.G, s.N - grp * s.G) * s.Ci * HW; // the last group may hold fewer images
     const float *p1 = partial + ((size_t)b1 * 2 + ((int)((units * b1 / grid) / s.C) == grp ? 0 : 1)) * per_group;
     float *out = gx + (size_t)grp * per_group;
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < live; e += gridDim.x * blockDim.x) {
+    for (int e = bx * blockDim.x + threadIdx.x; e < live; e += chunks * blockDim.x) {
         float acc = p1[e];
         // every later block starts inside this group, so the group is its first: slot 0
         for (int b = b1 + 1; b <= b2; ++b) acc += partial[(size_t)b * 2 * per_group + e];
         out[e] = acc;
     }
+}
+
+__global__ void __launch_bounds__(256) convtree_bwd_x_reduce_kernel(const float *__restrict__ partial, float *__restrict__ gx, ClsShape s,
+                                                                    int grid)
+{
+    bwd_x_reduce_block(partial, gx, s, grid, blockIdx.x, blockIdx.y, gridDim.x);
+}
+
+// Both of the above in one launch (they do not depend on each other): blocks [0, chunks*groups) reduce the partial
+// gradient tiles, the rest finish the gate gradients.
+__global__ void __launch_bounds__(256) convtree_bwd_post_kernel(const float *__restrict__ partial, float *__restrict__ gx, ClsShape s, int grid,
+                                                                int chunks, int ngroups, const float *__restrict__ wpartial,
+                                                                const float *__restrict__ w, float *__restrict__ gw, int ngates, int wmode)
+{
+    const int rb = chunks * ngroups;
+    if ((int)blockIdx.x < rb)
+        bwd_x_reduce_block(partial, gx, s, grid, blockIdx.x % chunks, blockIdx.x / chunks, chunks);
+    else
+        gw_finalize_block(wpartial, w, gw, ngroups, ngates, wmode, blockIdx.x - rb);
 }
 
 } // namespace clb
@@ -981,18 +1006,23 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
         ok = two ? launch(convtree_bwd_cls_kernel<false, true, 2>, kFastThreads / 2) : launch(convtree_bwd_cls_kernel<false, true, 1>, kFastThreads);
     if (!ok) return check_launch(0);
     int launched = 1;
-    if (gx) {
-        const int per_group = s.G * s.Ci * s.H * s.W;
-        int chunks = (per_group + 1023) / 1024;
-        if (chunks > 32) chunks = 32;
-        dim3 rgrid(chunks, NG);
-        convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, gx, s, grid);
+    const int per_group = s.G * s.Ci * s.H * s.W;
+    int chunks = (per_group + 1023) / 1024;
+    if (chunks > 32) chunks = 32;
+    const int ngates = C * 7;
+    if (gx && gw && (long long)chunks * NG + (ngates + 31) / 32 < 0x7fffffffLL) {
+        convtree_bwd_post_kernel<<<chunks * NG + (ngates + 31) / 32, 256, 0, st>>>(tiles, gx, s, grid, chunks, NG, wpartial, w, gw, ngates, wmode);
         ++launched;
-    }
-    if (gw) {
-        const int ngates = C * 7;
-        convtree_gw_finalize_kernel<<<(ngates + 31) / 32, 256, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
-        ++launched;
+    } else {
+        if (gx) {
+            dim3 rgrid(chunks, NG);
+            convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, gx, s, grid);
+            ++launched;
+        }
+        if (gw) {
+            convtree_gw_finalize_kernel<<<(ngates + 31) / 32, 256, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
+            ++launched;
+        }
     }
     return check_launch(launched);
 }
