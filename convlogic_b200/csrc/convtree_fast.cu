@@ -226,6 +226,162 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
     }
 }
 
+// ---- forward on image pairs -----------------------------------------------------------------------------
+// The same kernel with the two images a thread works on interleaved in the tile: element (channel, row, column)
+// holds the float2 {image 2p, image 2p+1}, so one 64-bit shared load fetches a tap for both images and the gate
+// polynomials run as packed two-float FMAs (fma.rn.f32x2: two independent IEEE fused multiply-adds, so the results
+// are the scalar kernel's bit for bit) on operands that are pairs to begin with -- no packing moves.  Per pair of
+// windows: 32 loads and 84 FMAs instead of 64 and 168.  Coefficients are stored duplicated, {k, k}, in the record.
+struct alignas(16) PairRec {
+    float g[56]; // 7 gates x (k1, ka, kb, kab), each twice
+    int tb0[8];  // BYTE offset in the pair tile of tap k for the dx = 0 positions
+    int tb1[8];
+};
+
+typedef unsigned long long f32x2; // two floats in one 64-bit register
+
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
+{
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+struct Gate2 {
+    f32x2 k1, ka, kb, kab;
+};
+__device__ __forceinline__ f32x2 gate_eval2(const Gate2 &g, f32x2 a, f32x2 b) { return fma2(a, fma2(g.kab, b, g.ka), fma2(g.kb, b, g.k1)); }
+
+template <int PWH>
+__global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_pair_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                                           const int32_t *__restrict__ sel, float *__restrict__ y,
+                                                                           uint8_t *__restrict__ amax, FastShape s)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    PairRec *chan = reinterpret_cast<PairRec *>(smem_raw);
+    float *tile = reinterpret_cast<float *>(smem_raw + sizeof(PairRec) * kChanBuf); // [pair][IS] float2
+    const unsigned char *tileb = reinterpret_cast<const unsigned char *>(tile);
+
+    const int pwh = PWH > 0 ? PWH : s.pwh;
+    const int RSB = 16 * pwh; // row stride in bytes
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp;
+    const int tid = threadIdx.x;
+    const int P = s.G / 2; // image pairs per group (G is even)
+
+    const int NG = (s.N + s.G - 1) / s.G;
+    const long long units = (long long)NG * s.C;
+    const long long lo = units * blockIdx.x / gridDim.x, hi = units * (blockIdx.x + 1) / gridDim.x;
+    if (lo >= hi) return;
+
+    const int pair = tid / I, win = tid - pair * I;
+    const int py = win / Wp, px = win - py * Wp;
+    const bool mine = pair < P;
+    const int toff = 8 * (pair * s.IS + 2 * py * 2 * pwh + px);
+
+    for (int i = tid; i < 2 * P * s.IS; i += kFastThreads) tile[i] = 0.f; // halo (and everything else) starts at zero
+
+    int cur_group = -1;
+    for (long long u0 = lo; u0 < hi;) {
+        const int grp = (int)(u0 / s.C);
+        const int c0 = (int)(u0 - (long long)grp * s.C);
+        int cnt = s.C - c0;
+        if (cnt > kChanBuf) cnt = kChanBuf;
+        if (cnt > hi - u0) cnt = (int)(hi - u0);
+        const int n0 = grp * s.G;
+        __syncthreads(); // previous chunk's readers are done with chan[] (and with the tile, if it changes)
+        if (grp != cur_group) {
+            cur_group = grp;
+            const int nimg = min(s.G, s.N - n0);
+            if (nimg < s.G) // a last, incomplete group: the slots of the missing images must not keep older data
+                for (int i = tid; i < 2 * P * s.IS; i += kFastThreads) tile[i] = 0.f;
+            if (nimg < s.G) __syncthreads();
+            const int q = s.W >> 2; // W % 4 == 0 and x 16-byte aligned: launch conditions
+            const int total = nimg * s.Ci * s.H * q;
+            for (int i = tid; i < total; i += kFastThreads) {
+                const int xq = i % q;
+                int r = i / q;
+                const int row = r % s.H;
+                r /= s.H;
+                const int ch = r % s.Ci, img = r / s.Ci;
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (((size_t)(n0 + img) * s.Ci + ch) * s.H + row) * s.W) + xq);
+                float *t = tile + 2 * (img >> 1) * s.IS + (img & 1);
+                const int e0 = ch * s.CS + (row + s.ph) * 2 * pwh;
+                const int c = xq * 4 + s.pw;
+                t[2 * (e0 + (c & 1) * pwh + (c >> 1))] = v.x;
+                t[2 * (e0 + ((c + 1) & 1) * pwh + ((c + 1) >> 1))] = v.y;
+                t[2 * (e0 + ((c + 2) & 1) * pwh + ((c + 2) >> 1))] = v.z;
+                t[2 * (e0 + ((c + 3) & 1) * pwh + ((c + 3) >> 1))] = v.w;
+            }
+        }
+        for (int i = tid; i < cnt * 7; i += kFastThreads) {
+            const int cc = i / 7, gi = i - cc * 7;
+            const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
+            float *o = chan[cc].g + gi * 8;
+            o[0] = o[1] = g.k1, o[2] = o[3] = g.ka, o[4] = o[5] = g.kb, o[6] = o[7] = g.kab;
+        }
+        for (int i = tid; i < cnt * 8; i += kFastThreads) {
+            const int cc = i >> 3, k = i & 7;
+            const int word = sel[(c0 + cc) * 8 + k];
+            const int ch = min((word >> 16) & 0xFFFF, s.Ci - 1), r = min((word >> 8) & 0xFF, s.kh - 1), sx = min(word & 0xFF, s.kw - 1);
+            const int base = ch * s.CS + r * 2 * pwh;
+            chan[cc].tb0[k] = 8 * (base + (sx & 1) * pwh + (sx >> 1));
+            chan[cc].tb1[k] = 8 * (base + ((sx + 1) & 1) * pwh + ((sx + 1) >> 1));
+        }
+        __syncthreads();
+
+        const int na = n0 + 2 * pair, nb = na + 1; // the thread's two images
+        for (int cc = 0; cc < cnt; ++cc) {
+            if (!mine || na >= s.N) continue;
+            const PairRec &rec = chan[cc];
+            Gate2 g[7];
+            {
+                const ulonglong2 *gp = reinterpret_cast<const ulonglong2 *>(rec.g);
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const ulonglong2 q0 = gp[2 * i], q1 = gp[2 * i + 1];
+                    g[i].k1 = q0.x, g[i].ka = q0.y, g[i].kb = q1.x, g[i].kab = q1.y;
+                }
+            }
+            int tb0[8], tb1[8];
+            {
+                const int4 *t0 = reinterpret_cast<const int4 *>(rec.tb0), *t1 = reinterpret_cast<const int4 *>(rec.tb1);
+                const int4 a0 = t0[0], a1 = t0[1], b0 = t1[0], b1 = t1[1];
+                tb0[0] = a0.x, tb0[1] = a0.y, tb0[2] = a0.z, tb0[3] = a0.w, tb0[4] = a1.x, tb0[5] = a1.y, tb0[6] = a1.z, tb0[7] = a1.w;
+                tb1[0] = b0.x, tb1[1] = b0.y, tb1[2] = b0.z, tb1[3] = b0.w, tb1[4] = b1.x, tb1[5] = b1.y, tb1[6] = b1.z, tb1[7] = b1.w;
+            }
+            f32x2 z[4];
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                f32x2 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    v[k] = *reinterpret_cast<const f32x2 *>(tileb + toff + ((d & 1) ? tb1[k] : tb0[k]) + ((d >> 1) ? RSB : 0));
+                const f32x2 g0 = gate_eval2(g[0], v[0], v[1]), g1 = gate_eval2(g[1], v[2], v[3]);
+                const f32x2 g2 = gate_eval2(g[2], v[4], v[5]), g3 = gate_eval2(g[3], v[6], v[7]);
+                z[d] = gate_eval2(g[6], gate_eval2(g[4], g0, g1), gate_eval2(g[5], g2, g3));
+            }
+            float best[2];
+            int bd[2] = {0, 0};
+            best[0] = __uint_as_float((unsigned)z[0]), best[1] = __uint_as_float((unsigned)(z[0] >> 32));
+#pragma unroll
+            for (int d = 1; d < 4; ++d) {
+                const float z0 = __uint_as_float((unsigned)z[d]), z1 = __uint_as_float((unsigned)(z[d] >> 32));
+                if (z0 > best[0]) best[0] = z0, bd[0] = d; // strict '>' in scan order keeps the first maximum
+                if (z1 > best[1]) best[1] = z1, bd[1] = d;
+            }
+            const int c = c0 + cc;
+            const size_t oa = ((size_t)na * s.C + c) * I + win;
+            y[oa] = best[0];
+            if (amax != nullptr) amax[oa] = (uint8_t)bd[0];
+            if (nb < s.N) {
+                const size_t ob = oa + (size_t)s.C * I;
+                y[ob] = best[1];
+                if (amax != nullptr) amax[ob] = (uint8_t)bd[1];
+            }
+        }
+        u0 += cnt;
+    }
+}
+
 // ======================================================================== forward, many input channels
 // Layers behind the first one have hundreds of input channels and small images; an output channel
 // reads only the channels its 8 taps name (two, by the reference's construction).  grid (parts, C): a
@@ -834,6 +990,19 @@ static bool make_fast_shape(FastShape &s, int N, int Ci, int H, int W, int C, in
     return (size_t)s.IS * 4 <= 200 * 1024;
 }
 
+template <int PWH>
+static int launch_fwd_pair(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, FastShape s, size_t smem,
+                           int blocks_per_sm, cudaStream_t st)
+{
+    auto k = convtree_fwd_pair_kernel<PWH>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
+    long long grid = 148LL * blocks_per_sm;
+    if (grid > units) grid = units;
+    k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s);
+    return check_launch();
+}
+
 template <int WPT, int PWH>
 static int launch_fwd(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, FastShape s, size_t smem,
                       int blocks_per_sm, cudaStream_t st)
@@ -906,6 +1075,15 @@ int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel
         if (smem > 220 * 1024) return CLB_ERR_SHAPE;
         s.G = G;
         const int bps = smem <= 110 * 1024 ? 2 : 1;
+        if (wpt == 2 && G % 2 == 0 && (W & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            // two images per thread, interleaved in the tile: packed two-float FMAs
+            const size_t smem2 = smem - fixed + sizeof(PairRec) * kChanBuf;
+            if (smem2 <= 110 * 1024) {
+                if (s.pwh == 20) return launch_fwd_pair<20>(x, w, sel, y, amax, s, smem2, 2, st);
+                if (s.pwh == 10) return launch_fwd_pair<10>(x, w, sel, y, amax, s, smem2, 2, st);
+                return launch_fwd_pair<0>(x, w, sel, y, amax, s, smem2, 2, st);
+            }
+        }
         if (wpt == 2) {
             if (s.pwh == 20) return launch_fwd<2, 20>(x, w, sel, y, amax, s, smem, bps, st);
             if (s.pwh == 10) return launch_fwd<2, 10>(x, w, sel, y, amax, s, smem, bps, st);
