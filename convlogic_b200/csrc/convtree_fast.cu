@@ -231,9 +231,9 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_tile_kernel(cons
 // holds the float2 {image 2p, image 2p+1}, so one 64-bit shared load fetches a tap for both images and the gate
 // polynomials run as packed two-float FMAs (fma.rn.f32x2: two independent IEEE fused multiply-adds, so the results
 // are the scalar kernel's bit for bit) on operands that are pairs to begin with -- no packing moves.  Per pair of
-// windows: 32 loads and 84 FMAs instead of 64 and 168.  Coefficients are stored duplicated, {k, k}, in the record.
+// windows: 32 loads and 84 FMAs instead of 64 and 168.
 struct alignas(16) PairRec {
-    float g[56]; // 7 gates x (k1, ka, kb, kab), each twice
+    float g[28]; // 7 gates x (k1, ka, kb, kab)
     int tb0[8];  // BYTE offset in the pair tile of tap k for the dx = 0 positions
     int tb1[8];
 };
@@ -244,6 +244,12 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
 {
     f32x2 d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 dup2(unsigned bits)
+{
+    f32x2 d;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "r"(bits));
     return d;
 }
 struct Gate2 {
@@ -315,8 +321,8 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_pair_kernel(cons
         for (int i = tid; i < cnt * 7; i += kFastThreads) {
             const int cc = i / 7, gi = i - cc * 7;
             const Gate<float> g = gate_load<float>(w + ((size_t)(c0 + cc) * 7 + gi) * 16, s.wmode);
-            float *o = chan[cc].g + gi * 8;
-            o[0] = o[1] = g.k1, o[2] = o[3] = g.ka, o[4] = o[5] = g.kb, o[6] = o[7] = g.kab;
+            float *o = chan[cc].g + gi * 4;
+            o[0] = g.k1, o[1] = g.ka, o[2] = g.kb, o[3] = g.kab;
         }
         for (int i = tid; i < cnt * 8; i += kFastThreads) {
             const int cc = i >> 3, k = i & 7;
@@ -334,11 +340,12 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_pair_kernel(cons
             const PairRec &rec = chan[cc];
             Gate2 g[7];
             {
-                const ulonglong2 *gp = reinterpret_cast<const ulonglong2 *>(rec.g);
+                // a coefficient is read once and doubled in registers: the shared-memory pipe, not the issue slots, binds
+                const uint4 *gp = reinterpret_cast<const uint4 *>(rec.g);
 #pragma unroll
                 for (int i = 0; i < 7; ++i) {
-                    const ulonglong2 q0 = gp[2 * i], q1 = gp[2 * i + 1];
-                    g[i].k1 = q0.x, g[i].ka = q0.y, g[i].kb = q1.x, g[i].kab = q1.y;
+                    const uint4 q = gp[i];
+                    g[i].k1 = dup2(q.x), g[i].ka = dup2(q.y), g[i].kb = dup2(q.z), g[i].kab = dup2(q.w);
                 }
             }
             int tb0[8], tb1[8];
