@@ -576,6 +576,185 @@ __global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_chan_kernel(cons
     }
 }
 
+// Image-pair variant of the kernel above (see convtree_fwd_pair_kernel): the slice holds G/2 pairs of images interleaved
+// as float2, a thread owns one window of one pair, taps are 64-bit loads and the gates packed two-float FMAs.
+__global__ void __launch_bounds__(kFastThreads, 2) convtree_fwd_chan_pair_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                                           const int32_t *__restrict__ sel, float *__restrict__ y,
+                                                                           uint8_t *__restrict__ amax, FastShape s, int q4 /* float4 per thread per slice */)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *tile = reinterpret_cast<float *>(smem_raw);
+    const unsigned char *tileb = smem_raw;
+    __shared__ Gate<float> sg[7];
+    __shared__ int sslot[8], sch[kChanSlots], snslot;
+    __shared__ Tap stap[8];
+
+    const int c = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int pwh = s.pwh, RSB = 16 * pwh;
+    const int Hp = s.Ho / 2, Wp = s.Wo / 2, I = Hp * Wp, HW = s.H * s.W;
+    if (tid < 7) sg[tid] = gate_load<float>(w + ((size_t)c * 7 + tid) * 16, s.wmode);
+    if (tid >= 64 && tid < 72) stap[tid - 64] = unpack_tap(sel[c * 8 + tid - 64], s.ph, s.pw);
+    if (tid == 32) { // channel -> slot map of this output channel's taps
+        int n = 0;
+        int chs[8];
+        bool inside = true;
+        for (int k = 0; k < 8; ++k) {
+            const int word = sel[c * 8 + k];
+            const int ch = (word >> 16) & 0xFFFF;
+            inside = inside && ch < s.Ci && ((word >> 8) & 0xFF) < s.kh && (word & 0xFF) < s.kw;
+            int slot = -1;
+            for (int j = 0; j < n; ++j)
+                if (chs[j] == ch) slot = j;
+            if (slot < 0) {
+                slot = n;
+                chs[n++] = ch;
+            }
+            sslot[k] = slot;
+        }
+        for (int j = 0; j < kChanSlots; ++j) sch[j] = min(chs[j < n ? j : 0], s.Ci - 1);
+        snslot = inside ? n : kChanSlots + 1;
+    }
+    for (int i = tid; i < s.G * s.IS; i += kFastThreads) tile[i] = 0.f; // halo stays zero
+    __syncthreads();
+
+    Gate<float> g[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g[i] = sg[i];
+    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+
+    if (snslot > kChanSlots) {
+        // Hand-made selection (more than two channels, or taps outside the window): no staging, every tap is a
+        // bounds-checked global load.  Block-uniform branch.
+        for (int f = tid; f < (n_hi - n_lo) * I; f += kFastThreads) {
+            const int img = f / I, win = f - img * I;
+            const int py = win / Wp, px = win - py * Wp;
+            const float *ximg = x + (size_t)(n_lo + img) * s.Ci * HW;
+            float best = 0.f;
+            int bd = 0;
+            for (int d = 0; d < 4; ++d) {
+                float a[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int iy = 2 * py + (d >> 1) + stap[k].dy, ix = 2 * px + (d & 1) + stap[k].dx;
+                    a[k] = ((unsigned)iy < (unsigned)s.H && (unsigned)ix < (unsigned)s.W) ? __ldg(ximg + stap[k].ch * HW + iy * s.W + ix) : 0.f;
+                }
+                const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+                const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+                const float z = gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+                if (d == 0 || z > best) {
+                    best = z;
+                    bd = d;
+                }
+            }
+            const size_t o = ((size_t)(n_lo + img) * s.C + c) * I + win;
+            y[o] = best;
+            if (amax != nullptr) amax[o] = (uint8_t)bd;
+        }
+        return;
+    }
+
+    int tb0[8], tb1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int word = sel[c * 8 + k];
+        const int r = (word >> 8) & 0xFF, sx = word & 0xFF;
+        const int base = sslot[k] * s.CS + r * 2 * pwh;
+        tb0[k] = 8 * (base + (sx & 1) * pwh + (sx >> 1));
+        tb1[k] = 8 * (base + ((sx + 1) & 1) * pwh + ((sx + 1) >> 1));
+    }
+    Gate2 g2[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i)
+        g2[i].k1 = dup2(__float_as_uint(g[i].k1)), g2[i].ka = dup2(__float_as_uint(g[i].ka)), g2[i].kb = dup2(__float_as_uint(g[i].kb)),
+        g2[i].kab = dup2(__float_as_uint(g[i].kab));
+    const int nstage = snslot;
+    const int ch_a = sch[0], ch_b = sch[1];
+
+    // a thread owns window `win` of the image pair (2*pair, 2*pair + 1) of every slice
+    const int pair = tid / I, win = tid - pair * I;
+    const int wpy = win / Wp, wpx = win - wpy * Wp;
+    const bool mine = 2 * pair < s.G;
+    const int toff = 8 * (pair * s.IS + 2 * wpy * 2 * pwh + wpx);
+
+    // one float4 = 4 consecutive pixels of one row of plane (img, slot); W % 4 == 0 is a launch condition.
+    // Which float4s a thread moves, and where they land in the tile, is the same for every slice.
+    const int w4 = s.W >> 2, per_plane = s.H * w4, per_slice = s.G * nstage * per_plane;
+    int src[kChanPrefetch], dst[kChanPrefetch], simg[kChanPrefetch];
+#pragma unroll
+    for (int q = 0; q < kChanPrefetch; ++q) {
+        const int i = tid + q * kFastThreads;
+        simg[q] = -1;
+        src[q] = dst[q] = 0;
+        if (q < q4 && i < per_slice) {
+            const int pl = i / per_plane, e = i - pl * per_plane;
+            const int img = pl / nstage, slot = pl - img * nstage;
+            const int row = e / w4, col = (e - row * w4) * 4;
+            simg[q] = img;
+            src[q] = (img * s.Ci + (slot ? ch_b : ch_a)) * HW + e * 4;
+            dst[q] = 2 * ((img >> 1) * s.IS + slot * s.CS + (row + s.ph) * 2 * pwh + ((col + s.pw) >> 1)) + (img & 1);
+        }
+    }
+    // the 4 pixels of a float4 alternate between the two column-parity planes (col is a multiple of 4)
+    const int p0 = 2 * ((s.pw & 1) * pwh), p1 = 2 * (((s.pw + 1) & 1) * pwh + ((s.pw & 1) ? 1 : 0));
+    const int p2 = p0 + 2, p3 = p1 + 2;
+    float4 pre[kChanPrefetch];
+    auto fetch = [&](int n0) {
+        const float *xs = x + (size_t)n0 * s.Ci * HW;
+#pragma unroll
+        for (int q = 0; q < kChanPrefetch; ++q)
+            if (simg[q] >= 0)
+                pre[q] = n0 + simg[q] < n_hi ? __ldg(reinterpret_cast<const float4 *>(xs + src[q])) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto deposit = [&]() {
+#pragma unroll
+        for (int q = 0; q < kChanPrefetch; ++q)
+            if (simg[q] >= 0) {
+                float *d = tile + dst[q];
+                d[p0] = pre[q].x, d[p1] = pre[q].y, d[p2] = pre[q].z, d[p3] = pre[q].w;
+            }
+    };
+
+    fetch(n_lo);
+    for (int n0 = n_lo; n0 < n_hi; n0 += s.G) {
+        __syncthreads(); // the previous slice has been read
+        deposit();
+        __syncthreads();
+        if (n0 + s.G < n_hi) fetch(n0 + s.G);
+        const int na = n0 + 2 * pair, nb = na + 1;
+        if (mine && na < n_hi) {
+            f32x2 z[4];
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                f32x2 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    v[k] = *reinterpret_cast<const f32x2 *>(tileb + toff + ((d & 1) ? tb1[k] : tb0[k]) + ((d >> 1) ? RSB : 0));
+                const f32x2 g0 = gate_eval2(g2[0], v[0], v[1]), g1 = gate_eval2(g2[1], v[2], v[3]);
+                const f32x2 q2 = gate_eval2(g2[2], v[4], v[5]), q3 = gate_eval2(g2[3], v[6], v[7]);
+                z[d] = gate_eval2(g2[6], gate_eval2(g2[4], g0, g1), gate_eval2(g2[5], q2, q3));
+            }
+            float best[2];
+            int bd[2] = {0, 0};
+            best[0] = __uint_as_float((unsigned)z[0]), best[1] = __uint_as_float((unsigned)(z[0] >> 32));
+#pragma unroll
+            for (int d = 1; d < 4; ++d) {
+                const float z0 = __uint_as_float((unsigned)z[d]), z1 = __uint_as_float((unsigned)(z[d] >> 32));
+                if (z0 > best[0]) best[0] = z0, bd[0] = d; // strict '>' in scan order keeps the first maximum
+                if (z1 > best[1]) best[1] = z1, bd[1] = d;
+            }
+            const size_t oa = ((size_t)na * s.C + c) * I + win;
+            y[oa] = best[0];
+            if (amax != nullptr) amax[oa] = (uint8_t)bd[0];
+            if (nb < n_hi) {
+                const size_t ob = oa + (size_t)s.C * I;
+                y[ob] = best[1];
+                if (amax != nullptr) amax[ob] = (uint8_t)bd[1];
+            }
+        }
+    }
+}
+
 // ==================================================================================== input gradient
 // Layout of the two backward tiles (x and its gradient): NO halo; a channel plane is split into the four
 // parity classes of (row, column) -- class = 2*(row & 1) + (col & 1) -- each stored as a dense
@@ -1049,6 +1228,12 @@ static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, f
     int parts = (int)((148LL * 3 * 8 + C - 1) / C); // about eight waves of three resident blocks per SM
     if (parts > (N + G - 1) / G) parts = (N + G - 1) / G;
     if (parts < 1) parts = 1;
+    if (G % 2 == 0 && (G / 2) * I <= kFastThreads) { // image pairs: 64-bit tap loads, packed two-float FMAs
+        auto k2 = convtree_fwd_chan_pair_kernel;
+        if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+        k2<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4);
+        return check_launch();
+    }
     auto k = convtree_fwd_chan_kernel<WPT>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
     k<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4);
