@@ -39,7 +39,7 @@ import torch  # noqa: E402
 
 C2 = dict(batch=256, cin=9, cout=256, size=32)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two c2 kernels, from the ncu captures
-# summarised in profiles/convtree_fwd_tile_c2.md and profiles/convtree_bwd_cls_c2.md
+# summarised in profiles/convtree_fwd_pair_c2.md and profiles/convtree_bwd_cls_c2.md
 NCU_TRAFFIC = {"fwd": 38.0e6, "bwd": 105.5e6}
 
 
