@@ -423,6 +423,9 @@ def run_c1(args):
     launches = (lib.clb_kernel_launches() - l0) * args.steps // (args.steps + args.warmup)
     ms_p = _timed(fwd_packed, args.steps, 3, world, dev)
     ms_c = _timed(lambda i: cnet(xb), args.steps, 3, world, dev)
+    replay = cnet.capture(xb)
+    graph_ok = bool(torch.equal(replay(xb), counts))
+    ms_g = _timed(lambda i: replay(xb), args.steps, 3, world, dev)
     clocks = sampler.stop() if rank == 0 else None
     _finish({
         "metric": "eval imgs/sec, mnist_s-shaped LogicTreeNet (float eval forward)", "value": 256 * world * args.steps / (ms * 1e-3),
@@ -430,7 +433,8 @@ def run_c1(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "c1: mnist_s-shaped stack (k=16, tau=6.5), eval mode, batch 256 of 1x28x28 Bernoulli(0.2) bits",
                    "l2": "launch-bound: every tensor fits the L2", "parallelism": f"{world} independent replicas"},
-        "packed_ms": ms_p / args.steps, "compiled_net_ms": ms_c / args.steps, "paths_agree": agree,
+        "packed_ms": ms_p / args.steps, "compiled_net_ms": ms_c / args.steps, "compiled_net_graph_ms": ms_g / args.steps,
+        "paths_agree": agree and graph_ok,
         "gpu_launches": int(launches), "clocks": clocks}, world)
 
 

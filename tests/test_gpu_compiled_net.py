@@ -132,3 +132,26 @@ def test_fused_flat_layers_equal_layer_by_layer(dims):
                                           _lib.ptr(y_dev), dims[0], dims[2], 2, x_dev.shape[1], 64, _lib.stream()))
     torch.cuda.synchronize()
     assert np.array_equal(y_dev.cpu().numpy(), h)
+
+
+def test_graph_replay_equals_direct_calls():
+    """A captured CUDA graph of one forward call replays to the same counts, for bit input and for pixel input."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    model = cb.ConvLogicMnistModel(k_param=4, tau=4.0).cuda().eval()
+    _randomise(model, 9)
+    net = cb.CompiledLogicNet(model.network, input_shape=(1, 28, 28)).compile()
+    xs = [torch.rand(130, 1, 28, 28, device="cuda") < 0.3 for _ in range(3)]
+    replay = net.capture(xs[0])
+    for x in xs:
+        want = net(x).clone()
+        assert torch.equal(replay(x), want)
+    pix_model = cb.ConvLogicCifarModel(k_param=2, input_channels=9, input_size=16, tau=1.0).cuda().eval()
+    _randomise(pix_model, 10)
+    pnet = cb.CompiledLogicNet(pix_model.network, input_shape=(9, 16, 16)).compile()
+    th = torch.tensor([0.25, 0.5, 0.75])
+    ps = [torch.randint(0, 256, (256, 3, 16, 16), dtype=torch.uint8) for _ in range(2)]
+    preplay = pnet.capture(ps[0], th)
+    for p_ in ps:
+        assert torch.equal(preplay(p_), pnet.forward_pixels(p_, th))
