@@ -257,6 +257,15 @@ class CompiledLogicNet(torch.nn.Module):
             raise ValueError(f"expected {self.num_inputs} input bits per sample, got {x.shape[1]}")
         return self._run(0, x.view(torch.uint8), batch)
 
+    def forward_packed(self, rows, batch):
+        """Bit-packed input rows ``[in_features, 2 * ceil(batch / 128)]`` int64 (64 samples per word, the batch padded
+        to whole 128-sample units with zero bits) -> counts for the first ``batch`` samples."""
+        rows = rows.to(self.device).contiguous()
+        words = 2 * (-(-batch // 128))
+        if rows.dtype != torch.int64 or rows.dim() != 2 or rows.shape[0] != self.num_inputs or rows.shape[1] != words:
+            raise ValueError(f"expected int64 rows [{self.num_inputs}, {words}], got {tuple(rows.shape)} {rows.dtype}")
+        return self._run(3, rows, batch)
+
     def forward_pixels(self, pixels, thresholds):
         """float32 / uint8 pixels ``[B, C, H, W]`` + thermometer thresholds -> counts (input stage fused on the GPU)."""
         pixels = pixels.to(self.device).contiguous()

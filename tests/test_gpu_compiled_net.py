@@ -155,3 +155,22 @@ def test_graph_replay_equals_direct_calls():
     preplay = pnet.capture(ps[0], th)
     for p_ in ps:
         assert torch.equal(preplay(p_), pnet.forward_pixels(p_, th))
+
+
+@pytest.mark.parametrize("batch", [70, 128, 300])
+def test_packed_rows_input(batch):
+    """The runtime also takes already packed rows (padded to whole 128-sample units)."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(0)
+    model = cb.ConvLogicCifarModel(k_param=2, input_channels=3, input_size=16, tau=1.0).cuda().eval()
+    _randomise(model, 12)
+    net = cb.CompiledLogicNet(model.network, input_shape=(3, 16, 16)).compile()
+    x = torch.rand(batch, 3, 16, 16) < 0.5
+    rows, _ = oracle.pack_bits(x.reshape(batch, -1).T.numpy(), 64)          # [F, ceil(batch/64)]
+    words = 2 * (-(-batch // 128))
+    padded = np.zeros((rows.shape[0], words), dtype=np.int64)
+    padded[:, : rows.shape[1]] = rows
+    assert torch.equal(net.forward_packed(torch.from_numpy(padded), batch), net(x))
+    with pytest.raises(ValueError):
+        net.forward_packed(torch.from_numpy(padded[:, :1].copy()), batch)
