@@ -27,6 +27,8 @@ _SIGNATURES = {
     "clb_status_string": ([_i], C.c_char_p),
     "clb_last_cuda_error": ([], _i),
     "clb_kernel_launches": ([], C.c_longlong),
+    "clb_trace": ([_i], _i),
+    "clb_trace_report": ([C.c_char_p, _sz], C.c_longlong),
     "clb_convtree_fwd": ([_vp] * 8 + _conv + [_i, _i, _vp], _i),
     "clb_convtree_bwd_x_scratch_bytes": (_conv + [_i], _sz),
     "clb_convtree_bwd_x": ([_vp] * 8 + [_i, _i, _vp, _sz] + _conv + [_i, _i, _vp], _i),
@@ -89,6 +91,22 @@ def lib():
             fn.argtypes, fn.restype = args, res
         _lib = handle
     return _lib
+
+
+def trace(on):
+    """Turn the library's launch tracing on (dropping earlier records) or off."""
+    check(lib().clb_trace(int(bool(on))))
+
+
+def trace_report():
+    """{kernel name: (launches, total ms)} of the launches traced since ``trace(True)``; clears the records."""
+    buf = C.create_string_buffer(1 << 16)
+    lib().clb_trace_report(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, launches, ms = line.split("\t")
+        out[name] = (int(launches), float(ms))
+    return out
 
 
 def check(status):

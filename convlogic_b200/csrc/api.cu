@@ -2,6 +2,11 @@
 #include "clb_common.cuh"
 
 #include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
 
 static thread_local int g_last_cuda_error = 0;
 static std::atomic<long long> g_launches{0};
@@ -9,6 +14,92 @@ namespace clb_host {
 void set_last_cuda_error(int e) { g_last_cuda_error = e; }
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 } // namespace clb_host
+
+// ---- launch tracing: CUDA events around the launches that CLB_TRACED marks -------------------------
+namespace {
+struct TraceRec {
+    const char *name;
+    cudaEvent_t e0, e1;
+};
+std::atomic<int> g_trace_on{0};
+std::mutex g_trace_mutex;
+std::vector<TraceRec> g_trace;
+void trace_drop_locked()
+{
+    for (TraceRec &r : g_trace) {
+        if (r.e0) cudaEventDestroy(r.e0);
+        if (r.e1) cudaEventDestroy(r.e1);
+    }
+    g_trace.clear();
+}
+} // namespace
+
+namespace clb_host {
+bool trace_enabled() { return g_trace_on.load(std::memory_order_relaxed) != 0; }
+int trace_begin(const char *name, cudaStream_t st)
+{
+    TraceRec r{name, nullptr, nullptr};
+    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) {
+        cudaGetLastError();
+        if (r.e0) cudaEventDestroy(r.e0);
+        return -1;
+    }
+    cudaEventRecord(r.e0, st);
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    g_trace.push_back(r);
+    return (int)g_trace.size() - 1;
+}
+void trace_end(int slot, cudaStream_t st)
+{
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    if (slot >= 0 && slot < (int)g_trace.size()) cudaEventRecord(g_trace[slot].e1, st);
+}
+} // namespace clb_host
+
+extern "C" int clb_trace(int on)
+{
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    trace_drop_locked();
+    g_trace_on.store(on ? 1 : 0, std::memory_order_relaxed);
+    return CLB_OK;
+}
+
+extern "C" long long clb_trace_report(char *buf, size_t cap)
+{
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    struct Row {
+        const char *name;
+        long long launches;
+        double ms;
+    };
+    std::vector<Row> rows;
+    for (TraceRec &r : g_trace) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(r.e1) != cudaSuccess || cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+        }
+        size_t i = 0;
+        for (; i < rows.size(); ++i)
+            if (rows[i].name == r.name || std::strcmp(rows[i].name, r.name) == 0) break;
+        if (i == rows.size()) rows.push_back(Row{r.name, 0, 0.0});
+        rows[i].launches += 1;
+        rows[i].ms += ms;
+    }
+    std::string out;
+    char line[256];
+    for (const Row &r : rows) {
+        std::snprintf(line, sizeof line, "%s\t%lld\t%.6f\n", r.name, r.launches, r.ms);
+        out += line;
+    }
+    trace_drop_locked();
+    if (buf && cap > 0) {
+        const size_t n = out.size() < cap - 1 ? out.size() : cap - 1;
+        std::memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return (long long)out.size() + 1;
+}
 
 extern "C" long long clb_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -154,6 +154,26 @@ inline int check_launch(int n = 1)
     count_launches(n);
     return CLB_OK;
 }
+// Launch tracing (clb_trace / clb_trace_report): while it is on, a traced launch is bracketed by two CUDA
+// events on its stream; off, the cost is one relaxed atomic load.
+bool trace_enabled();
+int trace_begin(const char *name, cudaStream_t st);
+void trace_end(int slot, cudaStream_t st);
+struct TraceScope {
+    int slot;
+    cudaStream_t st;
+    TraceScope(const char *name, cudaStream_t s) : slot(trace_enabled() ? trace_begin(name, s) : -1), st(s) {}
+    ~TraceScope()
+    {
+        if (slot >= 0) trace_end(slot, st);
+    }
+};
+// CLB_TRACED("kernel name", stream, kernel<<<grid, block, smem, stream>>>(args...));
+#define CLB_TRACED(name, st, ...)                                                                                       \
+    do {                                                                                                                \
+        clb_host::TraceScope clb_trace_scope_(name, st);                                                                \
+        __VA_ARGS__;                                                                                                    \
+    } while (0)
 inline int conv_out(int in, int pad, int k, int stride) { return (in + 2 * pad - k) / stride + 1; }
 inline bool conv_args_ok(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw)
 {

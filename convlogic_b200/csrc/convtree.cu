@@ -883,16 +883,16 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
         const int ipb = threads / items;
         if (parts > (N + ipb - 1) / ipb) parts = (N + ipb - 1) / ipb;
         if (parts < 1) parts = 1;
-        convtree_fwd_win_kernel<<<dim3(parts, C), threads, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, s, wmode);
+        CLB_TRACED("convtree_fwd_win_kernel", st, convtree_fwd_win_kernel<<<dim3(parts, C), threads, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, s, wmode));
         return check_launch();
     }
     dim3 grid(grid_x_for(total, C), C);
     if (dtype == CLB_F32)
-        convtree_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, (float *)x2,
-                                                          (float *)x3, idx, s, wmode);
+        CLB_TRACED("convtree_fwd_kernel", st, convtree_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, amax, (float *)x2,
+                                                          (float *)x3, idx, s, wmode));
     else if (dtype == CLB_F64)
-        convtree_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, amax,
-                                                           (double *)x2, (double *)x3, idx, s, wmode);
+        CLB_TRACED("convtree_fwd_kernel", st, convtree_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, amax,
+                                                           (double *)x2, (double *)x3, idx, s, wmode));
     else
         return CLB_ERR_ARG;
     return check_launch();
@@ -911,9 +911,9 @@ extern "C" int clb_conv_fwd(const void *x, const void *w, const int32_t *sel, vo
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(grid_x_for((long long)N * s.Ho * s.Wo, C), C);
     if (dtype == CLB_F32)
-        conv_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, s, wmode);
+        CLB_TRACED("conv_fwd_kernel", st, conv_fwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, sel, (float *)y, s, wmode));
     else if (dtype == CLB_F64)
-        conv_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, s, wmode);
+        CLB_TRACED("conv_fwd_kernel", st, conv_fwd_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, sel, (double *)y, s, wmode));
     else
         return CLB_ERR_ARG;
     return check_launch();
@@ -1012,21 +1012,21 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
         if (smem2 <= 227 * 1024) {
             auto k = convtree_bwd_x_grp_kernel;
             if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess) return check_launch(0);
-            k<<<grid, 256, smem2, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start, grp_list,
-                                        cg, nb, s, wmode);
+            CLB_TRACED("convtree_bwd_x_grp_kernel", st, k<<<grid, 256, smem2, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx,
+                                                                                     grp_start, grp_list, cg, nb, s, wmode));
             return check_launch();
         }
     }
     if (dtype == CLB_F32) {
         auto k = conv_bwd_x_kernel<float, FUSED>;
         if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
-        k<<<grid, 256, smem, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start, grp_list,
-                                   cg, nb, s, wmode);
+        CLB_TRACED("conv_bwd_x_kernel", st, k<<<grid, 256, smem, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start,
+                                                                        grp_list, cg, nb, s, wmode));
     } else {
         auto k = conv_bwd_x_kernel<double, FUSED>;
         if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
-        k<<<grid, 256, smem, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax, (double *)gx, grp_start,
-                                   grp_list, cg, nb, s, wmode);
+        CLB_TRACED("conv_bwd_x_kernel", st, k<<<grid, 256, smem, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax, (double *)gx,
+                                                                        grp_start, grp_list, cg, nb, s, wmode));
     }
     return check_launch();
 }
@@ -1116,18 +1116,18 @@ static int launch_bwd_w(const void *gy, const void *x, const void *w, const int3
     const int fb = (int)((ngates + 127) / 128);
     if (dtype == CLB_F32 && FUSED && amax != nullptr && items <= 256 && parts <= N) {
         const int threads = (int)((256 / items) * items); // whole images per block iteration
-        convtree_bwd_w_win_kernel<false><<<grid, threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
-                                                                   (float *)scratch, nullptr, s, wmode);
-        gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
+        CLB_TRACED("convtree_bwd_w_win_kernel", st, convtree_bwd_w_win_kernel<false><<<grid, threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
+                                                                   (float *)scratch, nullptr, s, wmode));
+        CLB_TRACED("gate_grad_finalize_kernel", st, gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode));
     } else if (dtype == CLB_F32) {
-        conv_bwd_w_kernel<float, FUSED><<<grid, 256, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
-                                                               (float *)scratch, s, wmode);
-        gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
+        CLB_TRACED("conv_bwd_w_kernel", st, conv_bwd_w_kernel<float, FUSED><<<grid, 256, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax,
+                                                               (float *)scratch, s, wmode));
+        CLB_TRACED("gate_grad_finalize_kernel", st, gate_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode));
     } else {
-        conv_bwd_w_kernel<double, FUSED><<<grid, 256, 0, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax,
-                                                                (double *)scratch, s, wmode);
-        gate_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates,
-                                                              wmode);
+        CLB_TRACED("conv_bwd_w_kernel", st, conv_bwd_w_kernel<double, FUSED><<<grid, 256, 0, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax,
+                                                                (double *)scratch, s, wmode));
+        CLB_TRACED("gate_grad_finalize_kernel", st, gate_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates,
+                                                              wmode));
     }
     return check_launch(2);
 }
@@ -1259,13 +1259,13 @@ extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, co
                 float *partial = (float *)scratch;
                 float *tapgrad = (float *)((unsigned char *)scratch + (bwd_w_scratch(N, C, items, 7, CLB_F32) + 255) / 256 * 256);
                 const int threads = (int)((256 / items) * items);
-                convtree_bwd_w_win_kernel<true><<<dim3(parts, C), threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel,
-                                                                                    amax, partial, tapgrad, s, wmode);
+                CLB_TRACED("convtree_bwd_w_win_kernel", st, convtree_bwd_w_win_kernel<true><<<dim3(parts, C), threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel,
+                                                                                    amax, partial, tapgrad, s, wmode));
                 int launched = 1;
                 if (gw) {
                     const long long ngates = (long long)C * 7;
-                    gate_grad_finalize_kernel<float><<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, (const float *)w, (float *)gw, parts,
-                                                                                                 ngates, wmode);
+                    CLB_TRACED("gate_grad_finalize_kernel", st, gate_grad_finalize_kernel<float><<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, (const float *)w, (float *)gw, parts,
+                                                                                                 ngates, wmode));
                     ++launched;
                 }
                 const int wpt = items >= 32 ? (int)((items + 31) / 32) : 2;
@@ -1273,7 +1273,8 @@ extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, co
                 const int sthreads = (nb + ipw - 1) / ipw * 32; // a warp per image (or per 32 / items images)
                 auto go = [&](auto k) {
                     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-                    k<<<dim3((N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax, (float *)gx, grp_start, grp_list, cg, nb, s);
+                    CLB_TRACED("convtree_bwd_x_scatter_kernel", st,
+                               k<<<dim3((N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax, (float *)gx, grp_start, grp_list, cg, nb, s));
                     return true;
                 };
                 const bool ok = wpt == 1 ? go(convtree_bwd_x_scatter_kernel<1>) : wpt == 2 ? go(convtree_bwd_x_scatter_kernel<2>)

@@ -1185,7 +1185,7 @@ static int launch_fwd_pair(const float *x, const float *w, const int32_t *sel, f
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
     long long grid = 148LL * blocks_per_sm;
     if (grid > units) grid = units;
-    k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s);
+    CLB_TRACED("convtree_fwd_pair_kernel", st, k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s));
     return check_launch();
 }
 
@@ -1198,7 +1198,7 @@ static int launch_fwd(const float *x, const float *w, const int32_t *sel, float 
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
     long long grid = 148LL * blocks_per_sm;
     if (grid > units) grid = units;
-    k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s);
+    CLB_TRACED("convtree_fwd_tile_kernel", st, k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s));
     return check_launch();
 }
 
@@ -1231,12 +1231,12 @@ static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, f
     if (G % 2 == 0 && (G / 2) * I <= kFastThreads) { // image pairs: 64-bit tap loads, packed two-float FMAs
         auto k2 = convtree_fwd_chan_pair_kernel;
         if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
-        k2<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4);
+        CLB_TRACED("convtree_fwd_chan_pair_kernel", st, k2<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4));
         return check_launch();
     }
     auto k = convtree_fwd_chan_kernel<WPT>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
-    k<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4);
+    CLB_TRACED("convtree_fwd_chan_kernel", st, k<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4));
     return check_launch();
 }
 
@@ -1362,7 +1362,7 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
     float *wpartial = tiles + ((tile_floats + 3) / 4) * 4;
     auto launch = [&](auto kern, int threads) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-        kern<<<grid, threads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s);
+        CLB_TRACED("convtree_bwd_cls_kernel", st, kern<<<grid, threads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s));
         return true;
     };
     // two windows per thread once a group has more than 128 of them
@@ -1381,16 +1381,16 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
     if (chunks > 32) chunks = 32;
     const int ngates = C * 7;
     if (gx && gw && (long long)chunks * NG + (ngates + 31) / 32 < 0x7fffffffLL) {
-        convtree_bwd_post_kernel<<<chunks * NG + (ngates + 31) / 32, 256, 0, st>>>(tiles, gx, s, grid, chunks, NG, wpartial, w, gw, ngates, wmode);
+        CLB_TRACED("convtree_bwd_post_kernel", st, convtree_bwd_post_kernel<<<chunks * NG + (ngates + 31) / 32, 256, 0, st>>>(tiles, gx, s, grid, chunks, NG, wpartial, w, gw, ngates, wmode));
         ++launched;
     } else {
         if (gx) {
             dim3 rgrid(chunks, NG);
-            convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, gx, s, grid);
+            CLB_TRACED("convtree_bwd_x_reduce_kernel", st, convtree_bwd_x_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, gx, s, grid));
             ++launched;
         }
         if (gw) {
-            convtree_gw_finalize_kernel<<<(ngates + 31) / 32, 256, 0, st>>>(wpartial, w, gw, NG, ngates, wmode);
+            CLB_TRACED("convtree_gw_finalize_kernel", st, convtree_gw_finalize_kernel<<<(ngates + 31) / 32, 256, 0, st>>>(wpartial, w, gw, NG, ngates, wmode));
             ++launched;
         }
     }

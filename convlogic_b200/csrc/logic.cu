@@ -561,11 +561,11 @@ extern "C" int clb_logic_fwd(const void *x, const int64_t *a, const int64_t *b, 
     const int grid = logic_grid((out_dim + 1) / 2);
     if (dtype == CLB_F32) {
         if (B % 4 == 0 && aligned16(x) && aligned16(y))
-            logic_fwd_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode);
+            CLB_TRACED("logic_fwd_kernel", st, logic_fwd_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode));
         else
-            logic_fwd_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode);
+            CLB_TRACED("logic_fwd_kernel", st, logic_fwd_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (float *)y, out_dim, B, wmode));
     } else if (dtype == CLB_F64) {
-        logic_fwd_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (double *)y, out_dim, B, wmode);
+        CLB_TRACED("logic_fwd_kernel", st, logic_fwd_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (double *)y, out_dim, B, wmode));
     } else
         return CLB_ERR_ARG;
     return check_launch();
@@ -580,11 +580,11 @@ extern "C" int clb_logic_bwd_w(const void *x, const int64_t *a, const int64_t *b
     const int grid = logic_grid((out_dim + 1) / 2);
     if (dtype == CLB_F32) {
         if (B % 4 == 0 && aligned16(x) && aligned16(gy))
-            logic_bwd_w_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode);
+            CLB_TRACED("logic_bwd_w_kernel", st, logic_bwd_w_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode));
         else
-            logic_bwd_w_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode);
+            CLB_TRACED("logic_bwd_w_kernel", st, logic_bwd_w_kernel<float, 1><<<grid, 256, 0, st>>>((const float *)x, a, b, (const float *)w, (const float *)gy, (float *)gw, out_dim, B, wmode));
     } else if (dtype == CLB_F64) {
-        logic_bwd_w_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (const double *)gy, (double *)gw, out_dim, B, wmode);
+        CLB_TRACED("logic_bwd_w_kernel", st, logic_bwd_w_kernel<double, 1><<<grid, 256, 0, st>>>((const double *)x, a, b, (const double *)w, (const double *)gy, (double *)gw, out_dim, B, wmode));
     } else
         return CLB_ERR_ARG;
     return check_launch();
@@ -619,6 +619,7 @@ extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b
 #define CLB_BWD_X(T, VV, SS)                                                                                                     \
     logic_bwd_x_kernel<T, VV, SS><<<grid, 256, 0, st>>>((const T *)x, a, b, (const T *)w, (const T *)gy, (T *)gx, start, consumers, \
                                                         in_dim, out_dim, B, wmode, (int)splits, (int)fpu)
+    clb_host::TraceScope trace_scope("logic_bwd_x_kernel", st);
     if (dtype == CLB_F32) {
         if (vec) {
             if (slots == 1) CLB_BWD_X(float, 4, 1);
@@ -662,11 +663,11 @@ extern "C" int clb_group_sum_fwd(const void *y, void *out, void *scratch, size_t
     dim3 grid((unsigned)((B + 31) / 32), (unsigned)k, (unsigned)parts);
     const int fb = (int)((B * k + 255) / 256);
     if (dtype == CLB_F32) {
-        group_sum_partial_kernel<float><<<grid, 256, 0, st>>>((const float *)y, (float *)scratch, S, B, k);
-        group_sum_finalize_kernel<float><<<fb, 256, 0, st>>>((const float *)scratch, (float *)out, B, k, parts, (float)tau);
+        CLB_TRACED("group_sum_partial_kernel", st, group_sum_partial_kernel<float><<<grid, 256, 0, st>>>((const float *)y, (float *)scratch, S, B, k));
+        CLB_TRACED("group_sum_finalize_kernel", st, group_sum_finalize_kernel<float><<<fb, 256, 0, st>>>((const float *)scratch, (float *)out, B, k, parts, (float)tau));
     } else {
-        group_sum_partial_kernel<double><<<grid, 256, 0, st>>>((const double *)y, (double *)scratch, S, B, k);
-        group_sum_finalize_kernel<double><<<fb, 256, 0, st>>>((const double *)scratch, (double *)out, B, k, parts, tau);
+        CLB_TRACED("group_sum_partial_kernel", st, group_sum_partial_kernel<double><<<grid, 256, 0, st>>>((const double *)y, (double *)scratch, S, B, k));
+        CLB_TRACED("group_sum_finalize_kernel", st, group_sum_finalize_kernel<double><<<fb, 256, 0, st>>>((const double *)scratch, (double *)out, B, k, parts, tau));
     }
     return check_launch(2);
 }
@@ -683,9 +684,9 @@ extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t 
     if (chunks > S) chunks = S;
     dim3 grid((unsigned)chunks, (unsigned)k);
     if (dtype == CLB_F32)
-        group_sum_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)gout, (float *)gy, S, B, k, (float)tau);
+        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)gout, (float *)gy, S, B, k, (float)tau));
     else
-        group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (double *)gy, S, B, k, tau);
+        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (double *)gy, S, B, k, tau));
     return check_launch();
 }
 
@@ -705,9 +706,9 @@ extern "C" int clb_logic_tree_fwd(const float *x, const int32_t *leaf, const int
     const int grid = logic_grid(T);
     cudaStream_t st = (cudaStream_t)stream;
     if (B % 4 == 0 && aligned16(x) && aligned16(y))
-        logic_tree_fwd_kernel<4><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode);
+        CLB_TRACED("logic_tree_fwd_kernel", st, logic_tree_fwd_kernel<4><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode));
     else
-        logic_tree_fwd_kernel<1><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode);
+        CLB_TRACED("logic_tree_fwd_kernel", st, logic_tree_fwd_kernel<1><<<grid, 256, 0, st>>>(x, tt, y, T, B, wmode));
     return check_launch();
 }
 
@@ -727,16 +728,16 @@ extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int
     int launched = 0;
     if (T > 0) {
         if (vec)
-            logic_tree_bwd_kernel<4><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode);
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
         else
-            logic_tree_bwd_kernel<1><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode);
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
         ++launched;
     }
     if (gx) {
         if (vec)
-            row_segment_sum_kernel<4><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B);
+            CLB_TRACED("row_segment_sum_kernel", st, row_segment_sum_kernel<4><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B));
         else
-            row_segment_sum_kernel<1><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B);
+            CLB_TRACED("row_segment_sum_kernel", st, row_segment_sum_kernel<1><<<logic_grid(in_dim), 256, 0, st>>>(tapgrad, start, list, gx, in_dim, B));
         ++launched;
     }
     return check_launch(launched);

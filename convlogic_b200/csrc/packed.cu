@@ -738,7 +738,7 @@ extern "C" int clb_pack_bits(const uint8_t *t, void *packed, int64_t F, int64_t 
     if (!t || !packed || F < 0 || B < 0 || !bits_ok(bits)) return CLB_ERR_ARG;
     const long long words = (B + bits - 1) / bits, rowbytes = words * (bits / 8);
     if (F == 0 || rowbytes == 0) return CLB_OK;
-    pack_bits_kernel<<<flat_grid(F * rowbytes, 256), 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, F, B, rowbytes);
+    CLB_TRACED("pack_bits_kernel", (cudaStream_t)stream, pack_bits_kernel<<<flat_grid(F * rowbytes, 256), 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, F, B, rowbytes));
     return check_launch();
 }
 
@@ -750,7 +750,7 @@ extern "C" int clb_pack_bits_nmajor(const uint8_t *t, void *packed, int64_t N, i
     long long gy = (rowbytes + 31) / 32;
     if (gy > 4096) gy = 4096;
     dim3 grid((unsigned)((F + 255) / 256), (unsigned)gy);
-    pack_bits_nmajor_kernel<32><<<grid, 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, N, F, rowbytes);
+    CLB_TRACED("pack_bits_nmajor_kernel", (cudaStream_t)stream, pack_bits_nmajor_kernel<32><<<grid, 256, 0, (cudaStream_t)stream>>>(t, (uint8_t *)packed, N, F, rowbytes));
     return check_launch();
 }
 
@@ -772,11 +772,11 @@ extern "C" int clb_thermometer_pack(const void *pixels, int pixels_u8, const flo
     dim3 grid((unsigned)((P + 31) / 32), (unsigned)gy);
     cudaStream_t st = (cudaStream_t)stream;
     if (pixels_u8)
-        thermometer_pack_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P,
-                                                                (int)HW, words32, to_slab);
+        CLB_TRACED("thermometer_pack_kernel", st, thermometer_pack_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P,
+                                                                (int)HW, words32, to_slab));
     else
-        thermometer_pack_kernel<float><<<grid, 256, 0, st>>>((const float *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P, (int)HW,
-                                                              words32, to_slab);
+        CLB_TRACED("thermometer_pack_kernel", st, thermometer_pack_kernel<float><<<grid, 256, 0, st>>>((const float *)pixels, thresholds, levels, (unsigned *)packed, N, (int)P, (int)HW,
+                                                              words32, to_slab));
     return check_launch();
 }
 
@@ -789,14 +789,14 @@ extern "C" int clb_packed_logic(const void *x, const int64_t *a, const int64_t *
     cudaStream_t st = (cudaStream_t)stream;
     if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16)) {
         const long long units = rowbytes / 16;
-        packed_logic_v4_kernel<<<flat_grid(out_dim * units, 256), 256, 0, st>>>((const uint4 *)x, a, b, ops, (uint4 *)y, out_dim, units);
+        CLB_TRACED("packed_logic_v4_kernel", st, packed_logic_v4_kernel<<<flat_grid(out_dim * units, 256), 256, 0, st>>>((const uint4 *)x, a, b, ops, (uint4 *)y, out_dim, units));
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
-        packed_logic_kernel<unsigned long long><<<flat_grid(out_dim * units, 256), 256, 0, st>>>(
-            (const unsigned long long *)x, a, b, ops, (unsigned long long *)y, out_dim, units);
+        CLB_TRACED("packed_logic_kernel", st, packed_logic_kernel<unsigned long long><<<flat_grid(out_dim * units, 256), 256, 0, st>>>(
+            (const unsigned long long *)x, a, b, ops, (unsigned long long *)y, out_dim, units));
     } else {
-        packed_logic_kernel<uint8_t><<<flat_grid(out_dim * rowbytes, 256), 256, 0, st>>>((const uint8_t *)x, a, b, ops, (uint8_t *)y,
-                                                                                        out_dim, rowbytes);
+        CLB_TRACED("packed_logic_kernel", st, packed_logic_kernel<uint8_t><<<flat_grid(out_dim * rowbytes, 256), 256, 0, st>>>((const uint8_t *)x, a, b, ops, (uint8_t *)y,
+                                                                                        out_dim, rowbytes));
     }
     return check_launch();
 }
@@ -814,16 +814,16 @@ extern "C" int clb_packed_tree(const void *x, const int32_t *leaf, const uint8_t
         const long long units = rowbytes / 16;
         const int grid = flat_grid(out_dim * units, 256);
         if (levels == 2)
-            packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units);
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units));
         else
-            packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units);
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units));
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         const int grid = flat_grid(out_dim * units, 256);
         if (levels == 2)
-            packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units);
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units));
         else
-            packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units);
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units));
     } else {
         return CLB_ERR_SHAPE; // rows of 64-bit words only
     }
@@ -849,13 +849,13 @@ extern "C" int clb_group_popcount(const void *x, int32_t *counts, int64_t F, int
         }
         const long long per = ((S + splits - 1) / splits + 15) / 16 * 16; // rows per thread, as the kernel computes it
         if (per <= 16 * 256)
-            group_popcount_kernel<8><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B, k,
-                                                                                                    (int)splits);
+            CLB_TRACED("group_popcount_kernel", st, group_popcount_kernel<8><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B, k,
+                                                                                                    (int)splits));
         else
-            group_popcount_kernel<27><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B,
-                                                                                                     k, (int)splits);
+            CLB_TRACED("group_popcount_kernel", st, group_popcount_kernel<27><<<flat_grid((long long)k * splits * units, 128), 128, 0, st>>>((const unsigned *)x, counts, S, units, B,
+                                                                                                     k, (int)splits));
     } else {
-        group_popcount_bytes_kernel<<<flat_grid(B * k, 256), 256, 0, st>>>((const uint8_t *)x, counts, S, rowbytes, B, k);
+        CLB_TRACED("group_popcount_bytes_kernel", st, group_popcount_bytes_kernel<<<flat_grid(B * k, 256), 256, 0, st>>>((const uint8_t *)x, counts, S, rowbytes, B, k));
     }
     return check_launch();
 }
@@ -880,21 +880,21 @@ extern "C" int clb_packed_convtree(const void *x, const uint8_t *ops, const int3
         const long long cap = (148LL * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
-        packed_convtree_v4_kernel<<<grid, 256, 0, st>>>((const uint4 *)x, ops, sel, (uint4 *)y, s, units);
+        CLB_TRACED("packed_convtree_v4_kernel", st, packed_convtree_v4_kernel<<<grid, 256, 0, st>>>((const uint4 *)x, ops, sel, (uint4 *)y, s, units));
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         long long gx = (wins * units + 255) / 256;
         const long long cap = (148LL * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
-        packed_convtree_kernel<unsigned long long><<<grid, 256, 0, st>>>((const unsigned long long *)x, ops, sel,
-                                                                         (unsigned long long *)y, s, units);
+        CLB_TRACED("packed_convtree_kernel", st, packed_convtree_kernel<unsigned long long><<<grid, 256, 0, st>>>((const unsigned long long *)x, ops, sel,
+                                                                         (unsigned long long *)y, s, units));
     } else {
         long long gx = (wins * rowbytes + 255) / 256;
         const long long cap = (148LL * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
-        packed_convtree_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)x, ops, sel, (uint8_t *)y, s, rowbytes);
+        CLB_TRACED("packed_convtree_kernel", st, packed_convtree_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)x, ops, sel, (uint8_t *)y, s, rowbytes));
     }
     return check_launch();
 }
@@ -906,8 +906,8 @@ extern "C" int clb_packed_layout(const void *src, void *dst, int64_t C, int64_t 
     if (C > 0x7fffffff || HW > 0x7fffffff || U > 0x7fffffff) return CLB_ERR_SHAPE;
     const long long total = C * HW * U;
     if (total == 0) return CLB_OK;
-    packed_rows_to_slab_kernel<<<flat_grid(total, 256), 256, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, (int)C, (int)HW,
-                                                                                        (int)U, to_slab);
+    CLB_TRACED("packed_rows_to_slab_kernel", (cudaStream_t)stream, packed_rows_to_slab_kernel<<<flat_grid(total, 256), 256, 0, (cudaStream_t)stream>>>((const uint4 *)src, (uint4 *)dst, (int)C, (int)HW,
+                                                                                        (int)U, to_slab));
     return check_launch();
 }
 
@@ -954,7 +954,7 @@ extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const
     if (bps < 1) bps = 1;
     int grid = 148 * bps;
     if (grid > s.items) grid = s.items;
-    packed_slab_records_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ops, sel, (SlabRec *)scratch, s);
-    k<<<grid, threads, smem, (cudaStream_t)stream>>>((const uint4 *)x, (const SlabRec *)scratch, (uint4 *)y, s);
+    CLB_TRACED("packed_slab_records_kernel", (cudaStream_t)stream, packed_slab_records_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ops, sel, (SlabRec *)scratch, s));
+    CLB_TRACED("packed_convtree_slab_kernel", (cudaStream_t)stream, k<<<grid, threads, smem, (cudaStream_t)stream>>>((const uint4 *)x, (const SlabRec *)scratch, (uint4 *)y, s));
     return check_launch();
 }

@@ -109,9 +109,9 @@ static int launch_tree_map(const void *x, const void *w, const void *gy, void *o
     dim3 grid((unsigned)chunks, C, N);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == CLB_F32)
-        tree_map_kernel<float, MODE><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, (const float *)gy, (float *)out, C, HW, X, wmode);
+        CLB_TRACED("tree_map_kernel", st, tree_map_kernel<float, MODE><<<grid, 256, 0, st>>>((const float *)x, (const float *)w, (const float *)gy, (float *)out, C, HW, X, wmode));
     else if (dtype == CLB_F64)
-        tree_map_kernel<double, MODE><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, (const double *)gy, (double *)out, C, HW, X, wmode);
+        CLB_TRACED("tree_map_kernel", st, tree_map_kernel<double, MODE><<<grid, 256, 0, st>>>((const double *)x, (const double *)w, (const double *)gy, (double *)out, C, HW, X, wmode));
     else
         return CLB_ERR_ARG;
     return check_launch();
@@ -157,11 +157,11 @@ extern "C" int clb_tree_bwd_w(const void *gy, const void *x, const void *w, void
     const int fb = (int)((ngates + 127) / 128);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == CLB_F32) {
-        tree_bwd_w_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)gy, (float *)scratch, N, C, HW, X, threads_used);
-        tree_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode);
+        CLB_TRACED("tree_bwd_w_kernel", st, tree_bwd_w_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)gy, (float *)scratch, N, C, HW, X, threads_used));
+        CLB_TRACED("tree_grad_finalize_kernel", st, tree_grad_finalize_kernel<float><<<fb, 128, 0, st>>>((const float *)scratch, (const float *)w, (float *)gw, parts, ngates, wmode));
     } else {
-        tree_bwd_w_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)gy, (double *)scratch, N, C, HW, X, threads_used);
-        tree_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates, wmode);
+        CLB_TRACED("tree_bwd_w_kernel", st, tree_bwd_w_kernel<double><<<grid, 256, 0, st>>>((const double *)x, (const double *)gy, (double *)scratch, N, C, HW, X, threads_used));
+        CLB_TRACED("tree_grad_finalize_kernel", st, tree_grad_finalize_kernel<double><<<fb, 128, 0, st>>>((const double *)scratch, (const double *)w, (double *)gw, parts, ngates, wmode));
     }
     return check_launch(2);
 }

@@ -60,6 +60,15 @@ const char *clb_status_string(int status);
 int clb_last_cuda_error(void);
 /* Number of kernels this library has launched in the calling process since it was loaded. */
 long long clb_kernel_launches(void);
+/* Launch tracing, for benchmarks (no counterpart in the reference, which device-synchronises after every
+ * launch instead).  clb_trace(1) drops earlier records and turns tracing on: from then on the library
+ * brackets each of its main kernels' launches with two CUDA events on the launch's stream (a few
+ * microseconds of host time per launch, nothing on the device).  clb_trace_report waits for the recorded
+ * events, writes one line per kernel, "name<TAB>launches<TAB>total milliseconds", into buf (NUL-terminated,
+ * truncated to cap), drops the records and returns the number of bytes the full text needs.
+ * clb_trace(0) turns tracing off.  Not for use during stream capture. */
+int clb_trace(int on);
+long long clb_trace_report(char *buf, size_t cap);
 
 /* ------------------------------------------------------------------------------------------------
  * Fused ConvLogic block: 8-tap gather -> 4 gates -> 2 gates -> 1 gate -> 2x2 max pool.

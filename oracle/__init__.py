@@ -21,6 +21,7 @@ from .conv_oracle import (  # noqa: F401
     conv_stage,
     tree_stage,
     pool_first_max,
+    pool_at,
     full_convlogic,
     gate_probabilities,
 )

@@ -90,13 +90,25 @@ def pool_first_max(z):
     return y, idx.reshape(n, c, hp * wp).to(torch.int32)
 
 
-def full_convlogic(x, w_prob, sel, stride=1, padding=1, kernel=3):
-    """Fused block: returns (y [N,C,Ho/2,Wo/2], x2 [N,C,Ho,Wo,4], x3 [N,C,Ho,Wo,2], idx)."""
+def pool_at(z, idx):
+    """The pooled output taken at GIVEN flat positions ``idx`` [N, C, I] (``in_y * W_out + in_x``) instead of at
+    the maximum: the gradient then flows through exactly those positions, which is what the reference's backward
+    kernels do with the ``indices`` tensor they are handed (full_convlogic_kernel.cu:365-461)."""
+    n, c, ho, wo = z.shape
+    y = z.reshape(n, c, ho * wo).gather(2, idx.to(torch.int64))
+    return y.reshape(n, c, ho // 2, wo // 2)
+
+
+def full_convlogic(x, w_prob, sel, stride=1, padding=1, kernel=3, forced_idx=None):
+    """Fused block: returns (y [N,C,Ho/2,Wo/2], x2 [N,C,Ho,Wo,4], x3 [N,C,Ho,Wo,2], idx).
+    With ``forced_idx`` the pool keeps those positions (see ``pool_at``) and returns them as idx."""
     ho, wo = out_size(x.shape[2], x.shape[3], stride, padding, kernel)
     if ho <= 0 or wo <= 0 or ho % 2 or wo % 2:
         raise ValueError(f"conv output {ho}x{wo} must be positive and even for the 2x2 pool")
     x2 = conv_stage(x, w_prob[:, 0:4], sel, stride, padding, kernel)
     x3 = tree_stage(x2, w_prob[:, 4:6])
     z = tree_stage(x3, w_prob[:, 6:7])[..., 0]
+    if forced_idx is not None:
+        return pool_at(z, forced_idx), x2, x3, forced_idx
     y, idx = pool_first_max(z)
     return y, x2, x3, idx
