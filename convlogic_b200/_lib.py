@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libconvlogic_b200.so")
 F32, F64 = 0, 1
 W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
 SEL_UNBOUNDED = 0x100
+TUNE_TAPGRAD_SLICE_BYTES = 1
 ERR_SHAPE, ERR_ODD_OUTPUT, ERR_TOO_LARGE = -2, -5, -6
 
 _lib = None
@@ -27,6 +28,8 @@ _SIGNATURES = {
     "clb_status_string": ([_i], C.c_char_p),
     "clb_last_cuda_error": ([], _i),
     "clb_kernel_launches": ([], C.c_longlong),
+    "clb_tune": ([_i, C.c_longlong], _i),
+    "clb_tune_get": ([_i], C.c_longlong),
     "clb_trace": ([_i], _i),
     "clb_trace_report": ([C.c_char_p, _sz], C.c_longlong),
     "clb_convtree_fwd": ([_vp] * 8 + _conv + [_i, _i, _vp], _i),

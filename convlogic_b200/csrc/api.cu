@@ -56,6 +56,43 @@ void trace_end(int slot, cudaStream_t st)
 }
 } // namespace clb_host
 
+// ---- tuning knobs and per-device facts ---------------------------------------------------------------
+namespace {
+std::atomic<long long> g_tapgrad_slice_bytes{48ll << 20};
+std::atomic<int> g_sm_count[64];
+} // namespace
+
+namespace clb_host {
+long long tune_get(int key) { return key == CLB_TUNE_TAPGRAD_SLICE_BYTES ? g_tapgrad_slice_bytes.load(std::memory_order_relaxed) : -1; }
+int sm_count()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return 148;
+    }
+    int n = g_sm_count[dev].load(std::memory_order_relaxed);
+    if (n <= 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 148; // B200; also what a query without a device (size planning on the host) assumes
+        }
+        g_sm_count[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+} // namespace clb_host
+
+extern "C" int clb_tune(int key, long long value)
+{
+    if (key == CLB_TUNE_TAPGRAD_SLICE_BYTES && value >= 0) {
+        g_tapgrad_slice_bytes.store(value, std::memory_order_relaxed);
+        return CLB_OK;
+    }
+    return CLB_ERR_ARG;
+}
+extern "C" long long clb_tune_get(int key) { return clb_host::tune_get(key); }
+
 extern "C" int clb_trace(int on)
 {
     std::lock_guard<std::mutex> lock(g_trace_mutex);

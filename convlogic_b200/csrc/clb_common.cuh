@@ -154,6 +154,8 @@ inline int check_launch(int n = 1)
     count_launches(n);
     return CLB_OK;
 }
+long long tune_get(int key); // clb_tune's current value
+int sm_count();              // multiprocessors of the current device, asked once per device
 // Launch tracing (clb_trace / clb_trace_report): while it is on, a traced launch is bracketed by two CUDA
 // events on its stream; off, the cost is one relaxed atomic load.
 bool trace_enabled();

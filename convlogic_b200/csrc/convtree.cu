@@ -846,7 +846,7 @@ static int grid_x_for(long long total_items, int C)
 {
     long long want = (total_items + 255) / 256;
     // enough blocks to fill 148 SMs several times over, without starving each block of work
-    long long cap = (148LL * 16 + C - 1) / (C > 0 ? C : 1);
+    long long cap = ((long long)sm_count() * 16 + C - 1) / (C > 0 ? C : 1);
     if (cap < 1) cap = 1;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
@@ -879,7 +879,7 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
     const int items = (s.Ho / 2) * (s.Wo / 2);
     if (dtype == CLB_F32 && !x2 && !idx && items <= 256) {
         const int threads = (256 / items) * items;
-        int parts = (int)((148LL * 20 + C - 1) / C); // about ten waves of two resident blocks per SM
+        int parts = (int)(((long long)sm_count() * 20 + C - 1) / C); // about ten waves of two resident blocks per SM
         const int ipb = threads / items;
         if (parts > (N + ipb - 1) / ipb) parts = (N + ipb - 1) / ipb;
         if (parts < 1) parts = 1;
@@ -1069,7 +1069,7 @@ extern "C" int clb_conv_bwd_x(const void *gy, const void *x, const void *w, cons
 // ---- gate gradient ----------------------------------------------------------------------------
 static int bwd_w_parts(long long total_items, int C)
 {
-    long long parts = (148LL * 20 + C - 1) / (C > 0 ? C : 1); // about ten waves of two resident blocks per SM
+    long long parts = ((long long)sm_count() * 20 + C - 1) / (C > 0 ? C : 1); // about ten waves of two resident blocks per SM
     long long most = total_items / 2048;
     if (parts > most) parts = most;
     if (parts < 1) parts = 1;
@@ -1209,15 +1209,45 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
 // Two-pass backward of the many-channel layers: convtree_bwd_w_win_kernel also writes the tap gradients
 // [N][C][8][I] (after its own partial sums in the scratch), convtree_bwd_x_scatter_kernel adds them into gx.
 // 0 when the shape does not take that path.
+// The batch is walked in slices of S images, pass 1 and pass 2 alternating on ONE tap-gradient buffer of a slice's
+// size: when that buffer fits the L2 cache (CLB_TUNE_TAPGRAD_SLICE_BYTES) the second pass finds the tap gradients
+// there, and the next slice overwrites them before they were ever written back to HBM.
+struct TwoPassPlan {
+    int S;        // images per slice
+    int slices;
+    int parts;    // blocks per output channel and slice in pass 1
+    size_t partial_bytes, tapgrad_bytes;
+};
+static bool two_pass_plan(TwoPassPlan &p, int N, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int want_gx, int dtype)
+{
+    if (!want_gx || dtype != CLB_F32 || sh != 1 || sw != 1 || N <= 0 || C <= 0 || C > 65535) return false;
+    const int Ho = conv_out(H, ph, kh, 1), Wo = conv_out(W, pw, kw, 1);
+    if (Ho <= 0 || Wo <= 0 || (Ho & 1) || (Wo & 1)) return false;
+    const long long items = (long long)(Ho / 2) * (Wo / 2);
+    if (items > 256) return false;
+    const long long per_image = (long long)C * 8 * items * (long long)sizeof(float);
+    const long long budget = tune_get(CLB_TUNE_TAPGRAD_SLICE_BYTES);
+    long long S = N;
+    if (budget > 0 && per_image * N > budget) {
+        const long long ipb = 256 / items; // images per block iteration of pass 1
+        S = budget / per_image / ipb * ipb;
+        if (S < ipb) S = ipb;
+        if (S > N) S = N;
+    }
+    p.S = (int)S;
+    p.slices = (int)((N + S - 1) / S);
+    p.parts = bwd_w_parts(S * items, C);
+    if (p.parts > S) return false;
+    p.partial_bytes = ((size_t)p.slices * p.parts * C * 28 * sizeof(float) + 255) / 256 * 256;
+    p.tapgrad_bytes = (size_t)S * C * 8 * items * sizeof(float);
+    return true;
+}
 static size_t two_pass_scratch(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int want_gx, int dtype)
 {
-    if (!want_gx || dtype != CLB_F32 || sh != 1 || sw != 1 || N <= 0 || C <= 0 || C > 65535) return 0;
-    const int Ho = conv_out(H, ph, kh, 1), Wo = conv_out(W, pw, kw, 1);
-    if (Ho <= 0 || Wo <= 0 || (Ho & 1) || (Wo & 1)) return 0;
-    const long long items = (long long)(Ho / 2) * (Wo / 2);
-    if (items > 256 || bwd_w_parts((long long)N * items, C) > N) return 0;
-    const size_t part = (bwd_w_scratch(N, C, items, 7, CLB_F32) + 255) / 256 * 256;
-    return part + (size_t)N * C * 8 * items * sizeof(float);
+    (void)Ci;
+    TwoPassPlan p;
+    if (!two_pass_plan(p, N, H, W, C, sh, sw, ph, pw, kh, kw, want_gx, dtype)) return 0;
+    return p.partial_bytes + p.tapgrad_bytes;
 }
 
 extern "C" size_t clb_convtree_bwd_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
@@ -1253,35 +1283,50 @@ extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, co
             const long long items = (long long)(s.Ho / 2) * (s.Wo / 2);
             const size_t smem = sizeof(int) * 8 * kScatBatch + (size_t)nb * cg * (H + 2 * ph) * (W + 2 * pw) * sizeof(float);
             const int G = (Ci + cg - 1) / cg;
-            if ((long long)nb * items <= 256 && nb <= 256 && smem <= 227 * 1024 && G <= 65535) {
+            TwoPassPlan plan;
+            if ((long long)nb * items <= 256 && nb <= 256 && smem <= 227 * 1024 && G <= 65535 &&
+                two_pass_plan(plan, N, H, W, C, sh, sw, ph, pw, kh, kw, 1, dtype)) {
                 cudaStream_t st = (cudaStream_t)stream;
-                const int parts = bwd_w_parts((long long)N * items, C);
                 float *partial = (float *)scratch;
-                float *tapgrad = (float *)((unsigned char *)scratch + (bwd_w_scratch(N, C, items, 7, CLB_F32) + 255) / 256 * 256);
+                float *tapgrad = (float *)((unsigned char *)scratch + plan.partial_bytes);
                 const int threads = (int)((256 / items) * items);
-                CLB_TRACED("convtree_bwd_w_win_kernel", st, convtree_bwd_w_win_kernel<true><<<dim3(parts, C), threads, 0, st>>>((const float *)gy, (const float *)x, (const float *)w, sel,
-                                                                                    amax, partial, tapgrad, s, wmode));
-                int launched = 1;
-                if (gw) {
-                    const long long ngates = (long long)C * 7;
-                    CLB_TRACED("gate_grad_finalize_kernel", st, gate_grad_finalize_kernel<float><<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, (const float *)w, (float *)gw, parts,
-                                                                                                 ngates, wmode));
-                    ++launched;
-                }
                 const int wpt = items >= 32 ? (int)((items + 31) / 32) : 2;
                 const int ipw = items >= 32 ? 1 : (int)(64 / items);
-                const int sthreads = (nb + ipw - 1) / ipw * 32; // a warp per image (or per 32 / items images)
-                auto go = [&](auto k) {
-                    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-                    CLB_TRACED("convtree_bwd_x_scatter_kernel", st,
-                               k<<<dim3((N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax, (float *)gx, grp_start, grp_list, cg, nb, s));
-                    return true;
-                };
-                const bool ok = wpt == 1 ? go(convtree_bwd_x_scatter_kernel<1>) : wpt == 2 ? go(convtree_bwd_x_scatter_kernel<2>)
-                              : wpt <= 4 ? go(convtree_bwd_x_scatter_kernel<4>) : go(convtree_bwd_x_scatter_kernel<8>);
-                // (wpt == 1: images of exactly 32 windows)
+                const int sthreads = (nb + ipw - 1) / ipw * 32; // a warp per image (or per 64 / items images)
+                const size_t HW = (size_t)H * W;
+                int launched = 0;
+                bool ok = true;
+                for (int sl = 0; sl < plan.slices && ok; ++sl) {
+                    const int n0 = sl * plan.S;
+                    ConvShape ss = s;
+                    ss.N = N - n0 < plan.S ? N - n0 : plan.S;
+                    const float *gy_s = (const float *)gy + (size_t)n0 * C * items, *x_s = (const float *)x + (size_t)n0 * Ci * HW;
+                    const uint8_t *amax_s = amax + (size_t)n0 * C * items;
+                    float *gx_s = (float *)gx + (size_t)n0 * Ci * HW;
+                    CLB_TRACED("convtree_bwd_w_win_kernel<tapgrad>", st,
+                               convtree_bwd_w_win_kernel<true><<<dim3(plan.parts, C), threads, 0, st>>>(
+                                   gy_s, x_s, (const float *)w, sel, amax_s, partial + (size_t)sl * plan.parts * C * 28, tapgrad, ss, wmode));
+                    ++launched;
+                    auto go = [&](auto k) {
+                        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+                        CLB_TRACED("convtree_bwd_x_scatter_kernel", st,
+                                   k<<<dim3((ss.N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax_s, gx_s, grp_start, grp_list, cg, nb, ss));
+                        return true;
+                    };
+                    ok = wpt == 1 ? go(convtree_bwd_x_scatter_kernel<1>) : wpt == 2 ? go(convtree_bwd_x_scatter_kernel<2>)
+                       : wpt <= 4 ? go(convtree_bwd_x_scatter_kernel<4>) : go(convtree_bwd_x_scatter_kernel<8>);
+                    // (wpt == 1: images of exactly 32 windows)
+                    ++launched;
+                }
                 if (!ok) return check_launch(0);
-                return check_launch(launched + 1);
+                if (gw) {
+                    const long long ngates = (long long)C * 7;
+                    CLB_TRACED("gate_grad_finalize_kernel", st,
+                               gate_grad_finalize_kernel<float><<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, (const float *)w, (float *)gw,
+                                                                                                            plan.slices * plan.parts, ngates, wmode));
+                    ++launched;
+                }
+                return check_launch(launched);
             }
         }
     }

@@ -1183,7 +1183,7 @@ static int launch_fwd_pair(const float *x, const float *w, const int32_t *sel, f
     auto k = convtree_fwd_pair_kernel<PWH>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
-    long long grid = 148LL * blocks_per_sm;
+    long long grid = (long long)sm_count() * blocks_per_sm;
     if (grid > units) grid = units;
     CLB_TRACED("convtree_fwd_pair_kernel", st, k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s));
     return check_launch();
@@ -1196,7 +1196,7 @@ static int launch_fwd(const float *x, const float *w, const int32_t *sel, float 
     auto k = convtree_fwd_tile_kernel<WPT, PWH>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
-    long long grid = 148LL * blocks_per_sm;
+    long long grid = (long long)sm_count() * blocks_per_sm;
     if (grid > units) grid = units;
     CLB_TRACED("convtree_fwd_tile_kernel", st, k<<<(unsigned)grid, kFastThreads, smem, st>>>(x, w, sel, y, amax, s));
     return check_launch();
@@ -1225,7 +1225,7 @@ static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, f
     if (smem > 72 * 1024) return CLB_ERR_SHAPE;
     const int q4 = (G * kChanSlots * H * (W / 4) + kFastThreads - 1) / kFastThreads;
     if (q4 > kChanPrefetch) return CLB_ERR_SHAPE;
-    int parts = (int)((148LL * 3 * 8 + C - 1) / C); // about eight waves of three resident blocks per SM
+    int parts = (int)(((long long)sm_count() * 3 * 8 + C - 1) / C); // about eight waves of three resident blocks per SM
     if (parts > (N + G - 1) / G) parts = (N + G - 1) / G;
     if (parts < 1) parts = 1;
     if (G % 2 == 0 && (G / 2) * I <= kFastThreads) { // image pairs: 64-bit tap loads, packed two-float FMAs
@@ -1316,7 +1316,7 @@ static bool plan_bwd_x(ClsShape &s, size_t &smem, int &grid, int N, int Ci, int 
     const size_t per_block = smem + 1024 + (G * I > kFastThreads / 2 ? kFastThreads / 2 : kFastThreads) / 32 * 128;
     const int bps = 3 * per_block <= 233472 ? 3 : smem <= 110 * 1024 ? 2 : 1;
     const long long units = (long long)((N + G - 1) / G) * C;
-    long long g = 148LL * bps;
+    long long g = (long long)sm_count() * bps;
     if (g > units) g = units;
     grid = (int)g;
     return true;

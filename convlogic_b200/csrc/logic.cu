@@ -546,7 +546,7 @@ static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int logic_grid(long long units_of_warps)
 {
     long long blocks = (units_of_warps + 7) / 8; // 8 warps per block
-    const long long cap = 148LL * 8 * 4;
+    const long long cap = (long long)sm_count() * 8 * 4;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (int)blocks;
@@ -604,12 +604,12 @@ extern "C" int clb_logic_bwd_x(const void *x, const int64_t *a, const int64_t *b
     long long fpu = out_dim > 0 ? (16 * in_dim + out_dim - 1) / out_dim : 1;
     if (fpu > 32) fpu = 32;
     if (fpu < 1) fpu = 1;
-    while (fpu > 1 && (in_dim + fpu - 1) / fpu < 148LL * 8 * 8) fpu /= 2; // keep enough units to occupy the GPU
+    while (fpu > 1 && (in_dim + fpu - 1) / fpu < (long long)sm_count() * 8 * 8) fpu /= 2; // keep enough units to occupy the GPU
     const long long funits = (in_dim + fpu - 1) / fpu;
     // split the batch when there are too few units to occupy the GPU
     long long splits = 1;
     const long long max_splits = (B + 32LL * V * 4 - 1) / (32LL * V * 4);
-    while (funits * splits < 148LL * 8 * 8 && splits < max_splits) splits *= 2;
+    while (funits * splits < (long long)sm_count() * 8 * 8 && splits < max_splits) splits *= 2;
     if (splits > max_splits) splits = max_splits;
     const int grid = logic_grid(funits * splits);
     if (out_dim > 0x7fffffffLL || in_dim > 0x7fffffffLL) return CLB_ERR_SHAPE; // consumer and row indices travel as 32-bit shuffles
@@ -680,7 +680,7 @@ extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t 
     cudaStream_t st = (cudaStream_t)stream;
     const long long S = F / k;
     if (k > 65535) return CLB_ERR_SHAPE;
-    long long chunks = (148LL * 16 + k - 1) / k; // about sixteen blocks per SM in all
+    long long chunks = ((long long)sm_count() * 16 + k - 1) / k; // about sixteen blocks per SM in all
     if (chunks > S) chunks = S;
     dim3 grid((unsigned)chunks, (unsigned)k);
     if (dtype == CLB_F32)

@@ -727,7 +727,7 @@ static bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintp
 static int flat_grid(long long items, int threads)
 {
     long long blocks = (items + threads - 1) / threads;
-    const long long cap = 148LL * 32;
+    const long long cap = (long long)sm_count() * 32;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (int)blocks;
@@ -843,7 +843,7 @@ extern "C" int clb_group_popcount(const void *x, int32_t *counts, int64_t F, int
     if (rowbytes % 4 == 0 && aligned_to(x, 4)) {
         const long long units = rowbytes / 4;
         long long splits = 1;
-        while ((long long)k * splits * units < 148LL * 128 * 16 && S / (splits * 2) >= 64) splits *= 2; // 16 resident blocks per SM: the row loop is latency-bound
+        while ((long long)k * splits * units < (long long)sm_count() * 128 * 16 && S / (splits * 2) >= 64) splits *= 2; // 16 resident blocks per SM: the row loop is latency-bound
         if (splits > 1) {
             if (cudaMemsetAsync(counts, 0, (size_t)B * k * sizeof(int32_t), st) != cudaSuccess) return check_launch();
         }
@@ -877,21 +877,21 @@ extern "C" int clb_packed_convtree(const void *x, const uint8_t *ops, const int3
     if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16) && in_units16 < (1LL << 30) && out_units16 < (1LL << 30)) {
         const int units = (int)(rowbytes / 16);
         long long gx = (wins * units + 255) / 256;
-        const long long cap = (148LL * 32 + C - 1) / C;
+        const long long cap = ((long long)sm_count() * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
         CLB_TRACED("packed_convtree_v4_kernel", st, packed_convtree_v4_kernel<<<grid, 256, 0, st>>>((const uint4 *)x, ops, sel, (uint4 *)y, s, units));
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         long long gx = (wins * units + 255) / 256;
-        const long long cap = (148LL * 32 + C - 1) / C;
+        const long long cap = ((long long)sm_count() * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
         CLB_TRACED("packed_convtree_kernel", st, packed_convtree_kernel<unsigned long long><<<grid, 256, 0, st>>>((const unsigned long long *)x, ops, sel,
                                                                          (unsigned long long *)y, s, units));
     } else {
         long long gx = (wins * rowbytes + 255) / 256;
-        const long long cap = (148LL * 32 + C - 1) / C;
+        const long long cap = ((long long)sm_count() * 32 + C - 1) / C;
         if (gx > cap) gx = cap;
         dim3 grid((unsigned)(gx < 1 ? 1 : gx), C);
         CLB_TRACED("packed_convtree_kernel", st, packed_convtree_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *)x, ops, sel, (uint8_t *)y, s, rowbytes));
@@ -952,7 +952,7 @@ extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const
     const int by_regs = 512 / threads < 2 ? 2 : (512 / threads > 8 ? 8 : 512 / threads); // 112 registers per thread
     if (bps > by_regs) bps = by_regs;
     if (bps < 1) bps = 1;
-    int grid = 148 * bps;
+    int grid = sm_count() * bps;
     if (grid > s.items) grid = s.items;
     CLB_TRACED("packed_slab_records_kernel", (cudaStream_t)stream, packed_slab_records_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ops, sel, (SlabRec *)scratch, s));
     CLB_TRACED("packed_convtree_slab_kernel", (cudaStream_t)stream, k<<<grid, threads, smem, (cudaStream_t)stream>>>((const uint4 *)x, (const SlabRec *)scratch, (uint4 *)y, s));

@@ -129,7 +129,7 @@ extern "C" int clb_tree_bwd_x(const void *gy, const void *x, const void *w, void
 
 static int tree_parts(long long positions, int C)
 {
-    long long parts = (148LL * 8 + C - 1) / (C > 0 ? C : 1);
+    long long parts = ((long long)sm_count() * 8 + C - 1) / (C > 0 ? C : 1);
     long long most = positions / 1024;
     if (parts > most) parts = most;
     if (parts < 1) parts = 1;

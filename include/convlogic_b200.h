@@ -69,6 +69,14 @@ long long clb_kernel_launches(void);
  * clb_trace(0) turns tracing off.  Not for use during stream capture. */
 int clb_trace(int on);
 long long clb_trace_report(char *buf, size_t cap);
+/* Process-wide tuning knobs (no counterpart in the reference).  Set them before querying scratch sizes: the
+ * *_scratch_bytes functions and the launches read the same values.  Returns CLB_ERR_ARG for an unknown key.
+ *   CLB_TUNE_TAPGRAD_SLICE_BYTES  the two-pass backward of many-channel blocks (clb_convtree_bwd) walks the batch
+ *       in slices whose tap gradients ([slice][C][8][windows] fp32) fit this many bytes, so that they are still
+ *       in the L2 cache when the second pass reads them; 0 = one slice (the whole batch).  Default 48 MiB. */
+#define CLB_TUNE_TAPGRAD_SLICE_BYTES 1
+int clb_tune(int key, long long value);
+long long clb_tune_get(int key);
 
 /* ------------------------------------------------------------------------------------------------
  * Fused ConvLogic block: 8-tap gather -> 4 gates -> 2 gates -> 1 gate -> 2x2 max pool.
