@@ -855,12 +855,18 @@ def main():
     ap.add_argument("--chunk", type=int, default=8192, help="c4: images per streamed chunk")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images per step of the CPU port")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tapgrad-slice-mb", type=int, default=None,
+                    help="override the library's slice size of the two-pass conv backward (0 = whole batch in one slice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
         return
     ctx = Ctx()
+    if args.tapgrad_slice_mb is not None:
+        from convlogic_b200 import _lib
+
+        _lib.check(_lib.lib().clb_tune(_lib.TUNE_TAPGRAD_SLICE_BYTES, args.tapgrad_slice_mb << 20))
     if args.workload == "all":
         rec = run_c3(ctx, args)
         rec["packed_inference"] = run_c4(ctx, args)

@@ -78,6 +78,7 @@ static bool parse(const void *blob, size_t bytes, clb_net &net)
     long long feat = net.in_features;
     bool flat_seen = false;
     auto in_blob = [&](uint64_t off, unsigned long long n) { return off % 16 == 0 && off <= bytes && n <= bytes - off; };
+    const unsigned char *base = (const unsigned char *)blob; // arrays sit at 16-byte aligned offsets of a caller buffer
     for (uint32_t i = 0; i < h.n_layers; ++i) {
         LayerRec r;
         std::memcpy(&r, (const unsigned char *)blob + kHeaderBytes + (size_t)i * kLayerBytes, sizeof(LayerRec));
@@ -94,6 +95,16 @@ static bool parse(const void *blob, size_t bytes, clb_net &net)
             if (Ho <= 0 || Wo <= 0 || (Ho & 1) || (Wo & 1)) return false;
             L.H = H, L.W = W, L.Hp = Ho / 2, L.Wp = Wo / 2;
             if (!in_blob(r.off_a, (unsigned long long)L.C * 32) || !in_blob(r.off_ops, (unsigned long long)L.C * 7)) return false;
+            { // every tap must name a channel of the input and a cell of the window, every gate id one of the 16 gates
+                const int32_t *selw = reinterpret_cast<const int32_t *>(base + r.off_a);
+                for (long long t = 0; t < (long long)L.C * 8; ++t) {
+                    const int32_t word = selw[t];
+                    if (word < 0 || ((word >> 16) & 0xFFFF) >= L.Ci || ((word >> 8) & 0xFF) >= L.kh || (word & 0xFF) >= L.kw) return false;
+                }
+                const uint8_t *opsb = base + r.off_ops;
+                for (long long t = 0; t < (long long)L.C * 7; ++t)
+                    if (opsb[t] > 15) return false;
+            }
             C = L.C, H = L.Hp, W = L.Wp;
             feat = (long long)C * H * W;
             if ((size_t)L.C > net.max_conv_channels) net.max_conv_channels = (size_t)L.C;
@@ -104,6 +115,12 @@ static bool parse(const void *blob, size_t bytes, clb_net &net)
             if (!in_blob(r.off_a, (unsigned long long)L.out_dim * 8) || !in_blob(r.off_b, (unsigned long long)L.out_dim * 8) ||
                 !in_blob(r.off_ops, (unsigned long long)L.out_dim))
                 return false;
+            { // connection indices must name input features, gate ids one of the 16 gates
+                const int64_t *ia = reinterpret_cast<const int64_t *>(base + r.off_a), *ib = reinterpret_cast<const int64_t *>(base + r.off_b);
+                const uint8_t *opsb = base + r.off_ops;
+                for (long long t = 0; t < L.out_dim; ++t)
+                    if (ia[t] < 0 || ia[t] >= L.in_dim || ib[t] < 0 || ib[t] >= L.in_dim || opsb[t] > 15) return false;
+            }
             feat = L.out_dim;
         } else if (r.kind == 3) {
             flat_seen = true;
@@ -113,6 +130,14 @@ static bool parse(const void *blob, size_t bytes, clb_net &net)
             const unsigned long long leaves = 1ull << L.levels;
             if (!in_blob(r.off_a, (unsigned long long)L.out_dim * leaves * 4) || !in_blob(r.off_ops, (unsigned long long)L.out_dim * (leaves - 1)))
                 return false;
+            {
+                const int32_t *leaf = reinterpret_cast<const int32_t *>(base + r.off_a);
+                for (unsigned long long t = 0; t < (unsigned long long)L.out_dim * leaves; ++t)
+                    if (leaf[t] < 0 || leaf[t] >= L.in_dim) return false;
+                const uint8_t *opsb = base + r.off_ops;
+                for (unsigned long long t = 0; t < (unsigned long long)L.out_dim * (leaves - 1); ++t)
+                    if (opsb[t] > 15) return false;
+            }
             feat = L.out_dim;
         } else {
             return false;

@@ -77,10 +77,6 @@ class LogicLayer(torch.nn.Module):
         start = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)])
         return start.to(a.device), neuron[order].to(a.device)
 
-    def load_state_dict(self, state_dict, strict=True, assign=False):
-        res = super().load_state_dict(state_dict, strict=strict, assign=assign)
-        return res
-
     def forward(self, x):
         if isinstance(x, PackBitsTensor):
             assert not self.training, "PackBitsTensor is not supported for the differentiable training mode."

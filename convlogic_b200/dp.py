@@ -18,7 +18,12 @@ def gate_parameters(model):
 
 class GradBucket:
     """Keeps all gate-logit gradients in ONE flat buffer (each ``weights.grad`` is a view into it),
-    so that the data-parallel exchange is a single all-reduce with no packing copies."""
+    so that the data-parallel exchange is a single all-reduce with no packing copies.
+
+    ``zero()`` replaces ``optimizer.zero_grad()``.  If something drops the views all the same
+    (``zero_grad(set_to_none=True)`` is torch's default and makes autograd allocate fresh ``.grad`` tensors),
+    the bucket notices before it exchanges anything: the stray gradient is copied into its slice and
+    ``.grad`` is bound to the slice again, so ranks never exchange a stale buffer."""
 
     def __init__(self, model):
         self.params = gate_parameters(model)
@@ -34,9 +39,29 @@ class GradBucket:
             self.ranges.append((off, off + p.numel()))
             off += p.numel()
         self._works, self._hooks, self._group, self._average = [], [], None, True
+        self.rebinds = 0
 
     def zero(self):
+        self._rebind_all(copy=False)
         self.flat.zero_()
+
+    def _rebind(self, p, lo, hi, copy=True):
+        """Make ``p.grad`` the bucket's slice again if it is not (any longer); returns True when it had to."""
+        view = self.flat[lo:hi].view_as(p)
+        g = p.grad
+        if g is not None and g.data_ptr() == view.data_ptr() and g.shape == view.shape:
+            return False
+        if g is not None and copy:
+            view.copy_(g)
+        elif g is None and copy:
+            view.zero_()  # no gradient arrived for this layer in this step
+        p.grad = view
+        self.rebinds += 1
+        return True
+
+    def _rebind_all(self, copy=True):
+        for p, (lo, hi) in zip(self.params, self.ranges):
+            self._rebind(p, lo, hi, copy)
 
     # ---- all-reduce overlapped with the rest of the backward pass
     def overlap(self, group=None, average=True):
@@ -47,7 +72,7 @@ class GradBucket:
         self.remove_overlap()
         self._group, self._average = group, average
         for p, (lo, hi) in zip(self.params, self.ranges):
-            self._hooks.append(p.register_post_accumulate_grad_hook(lambda _p, lo=lo, hi=hi: self._slice_ready(lo, hi)))
+            self._hooks.append(p.register_post_accumulate_grad_hook(lambda _p, lo=lo, hi=hi: self._slice_ready(lo, hi, _p)))
         return self
 
     def remove_overlap(self):
@@ -55,7 +80,9 @@ class GradBucket:
             h.remove()
         self._hooks, self._works = [], []
 
-    def _slice_ready(self, lo, hi):
+    def _slice_ready(self, lo, hi, p=None):
+        if p is not None:
+            self._rebind(p, lo, hi)
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self._group) == 1:
             return
         self._works.append(dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=self._group, async_op=True))
@@ -71,6 +98,7 @@ class GradBucket:
 
     def allreduce(self, group=None, average=True, async_op=False):
         """Sum (or mean) over ranks.  A no-op without an initialised process group."""
+        self._rebind_all()
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
             return None
         work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)

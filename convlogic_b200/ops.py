@@ -25,16 +25,22 @@ def _sel_ok(sel, c):
         raise RuntimeError(f"convlogic_b200: selection must be int32 [{c}, 8], got {sel.dtype} {tuple(sel.shape)}")
 
 
-def _sel_flag(sel, geom):
-    """SEL_UNBOUNDED when some tap lies outside the kh x kw window (checked once per selection
-    tensor and in-place version; the result is cached on the tensor object)."""
-    key = (sel._version, geom[4], geom[5])
+def _sel_flag(sel, geom, ci):
+    """SEL_UNBOUNDED when some tap lies outside the kh x kw window; raises when a tap names a channel the input
+    does not have (the kernels index with it).  Checked once per selection tensor, in-place version and channel
+    count; the result is cached on the tensor object."""
+    key = (sel._version, geom[4], geom[5], ci)
     cache = getattr(sel, "_clb_window", None)
     if cache is None or cache[0] != key:
-        rows, cols = (sel >> 8) & 0xFF, sel & 0xFF
-        inside = bool((rows.max() < geom[4]) & (cols.max() < geom[5])) if sel.numel() else True
-        cache = (key, 0 if inside else _lib.SEL_UNBOUNDED)
+        inside, ch_ok = True, True
+        if sel.numel():
+            rows, cols, chans = (sel >> 8) & 0xFF, sel & 0xFF, (sel >> 16) & 0xFFFF
+            flags = torch.stack([rows.max() < geom[4], cols.max() < geom[5], (chans.max() < ci) & (sel.min() >= 0)]).tolist()
+            inside, ch_ok = flags[0] and flags[1], flags[2]
+        cache = (key, 0 if inside else _lib.SEL_UNBOUNDED, ch_ok)
         sel._clb_window = cache
+    if not cache[2]:
+        raise RuntimeError("convlogic_b200: selection refers to a channel the input does not have")
     return cache[1]
 
 
@@ -64,7 +70,7 @@ def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False
     if n == 0 or c == 0:  # empty batch: nothing to launch
         return y, amax, x2, x3, idx
     check(lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), ptr(amax), ptr(x2), ptr(x3), ptr(idx),
-                                 n, ci, h, wd, c, *geom, wmode | _sel_flag(sel, geom), dtype_code(x), stream()))
+                                 n, ci, h, wd, c, *geom, wmode | _sel_flag(sel, geom, ci), dtype_code(x), stream()))
     return y, amax, x2, x3, idx
 
 
@@ -104,12 +110,28 @@ def conv_groups(sel, x_shape, geom, dtype):
     return out
 
 
+def _bwd_args_ok(gy, x, w, sel, amax, geom):
+    """Shapes and dtypes of the fused block's backward inputs (the C ABI receives bare pointers)."""
+    n, ci, h, wd = x.shape
+    c = w.shape[0]
+    _sel_ok(sel, c)
+    ho, wo = _out_hw(h, wd, *geom)
+    want = (n, c, ho // 2, wo // 2)
+    if w.shape != (c, 7, 16) or w.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: gate tensor must be [{c}, 7, 16] {x.dtype}")
+    if tuple(gy.shape) != want or gy.dtype != x.dtype:
+        raise RuntimeError(f"convlogic_b200: upstream gradient must be {want} {x.dtype}, got {tuple(gy.shape)} {gy.dtype}")
+    if amax is not None and (tuple(amax.shape) != want or amax.dtype != torch.uint8):
+        raise RuntimeError(f"convlogic_b200: arg-max tensor must be uint8 {want}, got {tuple(amax.shape)} {amax.dtype}")
+
+
 def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
     check_input(gy, x, w, sel)
+    _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
     c = w.shape[0]
     gx = torch.empty_like(x)
-    flag = _sel_flag(sel, geom)
+    flag = _sel_flag(sel, geom, ci)
     nbytes = lib().clb_convtree_bwd_x_scratch_bytes(n, ci, h, wd, c, *geom, dtype_code(x)) if (use_scratch and not flag) else 0
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
     start, lst, cg, nb = conv_groups(sel, tuple(x.shape), geom, x.dtype)
@@ -122,13 +144,14 @@ def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
 def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
     """Both gradients of the fused block in one C-ABI call; returns (gx or None, gw or None)."""
     check_input(gy, x, w, sel)
+    _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
     c = w.shape[0]
     gx = torch.empty_like(x) if need_gx else None
     gw = torch.empty_like(w) if need_gw else None
     if n == 0 or c == 0:  # empty batch: the gate gradient is an empty sum
         return gx, (gw.zero_() if gw is not None else None)
-    flag = _sel_flag(sel, geom)
+    flag = _sel_flag(sel, geom, ci)
     nbytes = lib().clb_convtree_bwd_scratch_bytes(n, ci, h, wd, c, *geom, int(need_gx), int(need_gw), dtype_code(x))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
     if need_gx:
@@ -143,7 +166,9 @@ def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
 
 def convtree_bwd_w(gy, x, w, sel, amax, geom, wmode):
     check_input(gy, x, w, sel)
+    _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
+    _sel_flag(sel, geom, ci)
     c = w.shape[0]
     ho, wo = _out_hw(h, wd, *geom)
     gw = torch.empty_like(w)
@@ -162,7 +187,9 @@ def convtree_bwd_w_noalloc(gy, x, w, sel, amax, geom, wmode, out):
     All calls on a device share the array, so do not let two of them overlap on the GPU; make the
     first call on a device outside any stream capture (it looks the array's address up once)."""
     check_input(gy, x, w, sel, out)
+    _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
+    _sel_flag(sel, geom, ci)
     c = w.shape[0]
     if out.shape != w.shape or out.dtype != w.dtype:
         raise RuntimeError("convlogic_b200: `out` must have the gate tensor's shape and dtype")
@@ -182,6 +209,7 @@ def conv_fwd(x, w, sel, geom, wmode):
     ho, wo = _out_hw(h, wd, *geom)
     if ho <= 0 or wo <= 0:
         raise RuntimeError(f"Invalid output shape: H_out={ho}, W_out={wo}")
+    _sel_flag(sel, geom, ci)
     y = torch.empty((n, c, ho, wo, 4), dtype=x.dtype, device=x.device)
     check(lib().clb_conv_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream()))
     return y

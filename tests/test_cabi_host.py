@@ -128,3 +128,48 @@ def test_network_blob_is_validated_on_the_host():
     assert lib.clb_net_device_bytes(wrong, len(wrong), C.byref(need)) == _lib.ERR_SHAPE
     with pytest.raises(AssertionError):
         serialise(torch.nn.Sequential(cb.LogicLayer(8, 10)))  # no GroupSum at the end
+
+
+def test_network_blob_with_an_index_out_of_range_is_rejected():
+    """A blob whose offsets and widths are fine but whose index VALUES are not (a flat connection beyond the input
+    width, a conv tap naming a missing channel or a cell outside the window, a gate id above 15, a leaf of a fused
+    gate tree beyond the input) must come back as CLB_ERR_SHAPE: the kernels index with these values unclamped."""
+    import ctypes as C
+    import struct
+
+    import torch
+
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib
+    from convlogic_b200.compiled_model import serialise
+
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(cb.ConvLogicLayer(3, 4, complete=True), torch.nn.Flatten(), cb.LogicLayer(4 * 4 * 4, 40), cb.GroupSum(10))
+    blob = serialise(model, input_shape=(3, 8, 8))
+    lib = _lib.lib()
+    need = C.c_size_t()
+
+    def status(b):
+        return lib.clb_net_device_bytes(bytes(b), len(b), C.byref(need))
+
+    def layer_offsets(b, i):
+        return struct.unpack_from("<3Q", b, 64 + 64 * i + 32)   # off_a, off_b, off_ops
+
+    assert status(blob) == 0
+    conv_sel, _, conv_ops = layer_offsets(blob, 0)
+    flat_a, flat_b, flat_ops = layer_offsets(blob, 1)
+    for off, fmt, bad in ((flat_a, "<q", 64), (flat_b, "<q", -1), (flat_a + 8 * 39, "<q", 1 << 40), (flat_ops, "<B", 16),
+                          (conv_ops + 5, "<B", 200), (conv_sel, "<i", (3 << 16) | (1 << 8) | 1),      # channel 3 of 3
+                          (conv_sel + 4, "<i", (0 << 16) | (3 << 8) | 0), (conv_sel + 8, "<i", (0 << 16) | (0 << 8) | 3)):
+        damaged = bytearray(blob)
+        struct.pack_into(fmt, damaged, off, bad)
+        assert status(damaged) == _lib.ERR_SHAPE, (off, fmt, bad)
+    # a fused gate tree (three flat layers halving their width)
+    tree = torch.nn.Sequential(cb.LogicLayer(16, 80), cb.LogicLayer(80, 40), cb.LogicLayer(40, 20), cb.GroupSum(10))
+    tb = serialise(tree)
+    assert status(tb) == 0 and struct.unpack_from("<I", tb, 64)[0] == 3
+    leaf, _, ops = layer_offsets(tb, 0)
+    for off, fmt, bad in ((leaf + 4 * 7, "<i", 16), (leaf, "<i", -2), (ops + 3, "<B", 99)):
+        damaged = bytearray(tb)
+        struct.pack_into(fmt, damaged, off, bad)
+        assert status(damaged) == _lib.ERR_SHAPE, (off, fmt, bad)

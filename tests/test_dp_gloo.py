@@ -59,6 +59,27 @@ def _worker(rank, world, port, fail_rank):
         sum((p * 2.0).sum() for p in params).backward()
         assert bucket.finish() == 0 and torch.allclose(bucket.flat, torch.full_like(bucket.flat, 2.0))
 
+        # zero_grad(set_to_none=True), torch's default, drops the views: the bucket must notice and exchange the
+        # real gradients, in the overlapped variant (hooks) and in the one-call variant
+        bucket.overlap(average=True)
+        opt = torch.optim.SGD(params, lr=0.0)
+        opt.zero_grad(set_to_none=True)
+        assert all(p.grad is None for p in params)
+        sum((p * float(rank + 1)).sum() for p in params).backward()      # autograd allocates fresh .grad tensors
+        assert bucket.finish() == len(params)
+        assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5)), "stale bucket was exchanged"
+        assert all(torch.allclose(p.grad, torch.full_like(p, 1.5)) for p in params)
+        assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
+        assert bucket.rebinds >= len(params)
+        bucket.remove_overlap()
+        model.zero_grad(set_to_none=True)
+        sum((p * float(3 * (rank + 1))).sum() for p in params).backward()
+        bucket.allreduce(average=True)
+        assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 4.5))
+        assert all(torch.allclose(p.grad, torch.full_like(p, 4.5)) for p in params)
+        bucket.zero()   # also re-binds (nothing to copy)
+        assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
+
         # one-shot variant on ordinary .grad tensors
         for p in params:
             p.grad = torch.full_like(p, float(10 * (rank + 1)))
