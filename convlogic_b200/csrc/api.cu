@@ -58,7 +58,7 @@ void trace_end(int slot, cudaStream_t st)
 
 // ---- tuning knobs and per-device facts ---------------------------------------------------------------
 namespace {
-std::atomic<long long> g_tapgrad_slice_bytes{48ll << 20};
+std::atomic<long long> g_tapgrad_slice_bytes{0};
 std::atomic<int> g_sm_count[64];
 } // namespace
 

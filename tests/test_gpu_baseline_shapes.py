@@ -106,14 +106,23 @@ def test_fused_block_at_benchmark_shape_against_reference_kernels(ref_conv, name
     assert_same_argmax_up_to_ties(idx, idx_d, 1e-3)
     assert_close(gx, gx_d, TOL, "gx vs reference fp64")
     assert_close(gl, _softmax_jacobian(p, gp_d), TOL, "gw vs reference fp64")
-    # the reference-style Function call (mixture in, gradient w.r.t. the mixture out)
-    pd = p.float().requires_grad_(True)
+    del gx_d, gp_d
+    # the reference-style Function call (mixture in, gradient w.r.t. the mixture out).  Its mixture is the fp64
+    # soft-max rounded to fp32, not the kernels' own fp32 soft-max, so near-tied windows may pool elsewhere than
+    # above: the reference's backward is run again at the positions THIS call pooled.
+    from convlogic_b200._lib import W_PROB
+
+    pf = p.float()
+    pd = pf.clone().requires_grad_(True)
     xd2 = x.clone().requires_grad_(True)
     y2 = cb.FullConvLogicFunction.apply(xd2, pd, sel, 1, 1, 1, 1, 3, 3)
     gx2, gp2 = torch.autograd.grad((y2 * gy).sum(), (xd2, pd))
+    idx2 = ops.convtree_fwd(x, pf, sel, (1, 1, 1, 1, 3, 3), W_PROB, want_indices=True)[4]
     assert_close(y2, y_d, TOL, "Function y")
-    assert_close(gx2, gx_d, TOL, "Function gx")
-    assert_close(gp2, gp_d, TOL, "Function gw (mixture)")
+    assert_same_argmax_up_to_ties(idx2, idx_d, 1e-3)
+    _, _, gx_f, gp_f = _reference_block(ref_conv, x, pf, sel, idx2, gy, torch.float64)
+    assert_close(gx2, gx_f, TOL, "Function gx")
+    assert_close(gp2, gp_f, TOL, "Function gw (mixture)")
 
 
 @pytest.mark.parametrize("ci,c,side", [(1024, 4096, 8), (256, 1024, 16)])

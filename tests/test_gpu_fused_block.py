@@ -297,7 +297,7 @@ def test_tiled_input_gradient_equals_general(shape):
         xo = x.clone().requires_grad_(True)
         yo, _, _, idxo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])
         idx = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)[4].cpu()
-        assert_same_argmax_up_to_ties(idx, idxo, 1e-4)
+        assert_same_argmax_up_to_ties(idx, idxo, 1e-3)
         wo = logits.clone().requires_grad_(True)
         yf = oracle.full_convlogic(xo, oracle.gate_probabilities(wo, True), sel, geom[0:2], geom[2:4], geom[4:6], forced_idx=idx)[0]
         gxf, gwf = torch.autograd.grad((yf * gy).sum(), (xo, wo))
@@ -362,7 +362,7 @@ def test_two_pass_backward_of_many_channel_layers(shape):
         xo = x.clone().requires_grad_(True)
         yo, _, _, idxo = oracle.full_convlogic(xo, oracle.gate_probabilities(logits, True), sel, geom[0:2], geom[2:4], geom[4:6])
         idx = ops.convtree_fwd(xd, wd, sd, geom, W_SOFTMAX, want_indices=True)[4].cpu()
-        assert_same_argmax_up_to_ties(idx, idxo, 1e-4)
+        assert_same_argmax_up_to_ties(idx, idxo, 1e-3)
         wo = logits.clone().requires_grad_(True)
         yf = oracle.full_convlogic(xo, oracle.gate_probabilities(wo, True), sel, geom[0:2], geom[2:4], geom[4:6], forced_idx=idx)[0]
         gxf, gwf = torch.autograd.grad((yf * gy).sum(), (xo, wo))
