@@ -16,6 +16,7 @@ F32, F64 = 0, 1
 W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
 SEL_UNBOUNDED = 0x100
 TUNE_TAPGRAD_SLICE_BYTES = 1
+TUNE_PLANE_KERNELS = 2
 ERR_SHAPE, ERR_ODD_OUTPUT, ERR_TOO_LARGE = -2, -5, -6
 
 _lib = None
@@ -37,6 +38,10 @@ _SIGNATURES = {
     "clb_convtree_bwd_x": ([_vp] * 8 + [_i, _i, _vp, _sz] + _conv + [_i, _i, _vp], _i),
     "clb_convtree_bwd_scratch_bytes": (_conv + [_i, _i, _i], _sz),
     "clb_convtree_bwd": ([_vp] * 9 + [_i, _i, _vp, _sz] + _conv + [_i, _i, _vp], _i),
+    "clb_conv_channel_lists": ([_vp, _i, _i, _i, _i, _vp, _vp, _i], _i),
+    "clb_convtree_bwd_plane_scratch_bytes": (_conv + [_i], _sz),
+    "clb_convtree_bwd_plane": ([_vp] * 10 + [_sz] + _conv + [_i, _i, _vp], _i),
+    "clb_plane_error": ([_vp], _i),
     "clb_conv_group_plan": (_conv + [_i, C.POINTER(_i), C.POINTER(_i)], _i),
     "clb_conv_build_groups": ([_vp, _i, _i, _i, _vp, _vp, _i], _i),
     "clb_convtree_bwd_w_scratch_bytes": ([_i, _i, _i, _i, _i], _sz),

@@ -59,11 +59,17 @@ void trace_end(int slot, cudaStream_t st)
 // ---- tuning knobs and per-device facts ---------------------------------------------------------------
 namespace {
 std::atomic<long long> g_tapgrad_slice_bytes{0};
+std::atomic<long long> g_plane_kernels{1};
 std::atomic<int> g_sm_count[64];
 } // namespace
 
 namespace clb_host {
-long long tune_get(int key) { return key == CLB_TUNE_TAPGRAD_SLICE_BYTES ? g_tapgrad_slice_bytes.load(std::memory_order_relaxed) : -1; }
+long long tune_get(int key)
+{
+    if (key == CLB_TUNE_TAPGRAD_SLICE_BYTES) return g_tapgrad_slice_bytes.load(std::memory_order_relaxed);
+    if (key == CLB_TUNE_PLANE_KERNELS) return g_plane_kernels.load(std::memory_order_relaxed);
+    return -1;
+}
 int sm_count()
 {
     int dev = 0;
@@ -87,6 +93,10 @@ extern "C" int clb_tune(int key, long long value)
 {
     if (key == CLB_TUNE_TAPGRAD_SLICE_BYTES && value >= 0) {
         g_tapgrad_slice_bytes.store(value, std::memory_order_relaxed);
+        return CLB_OK;
+    }
+    if (key == CLB_TUNE_PLANE_KERNELS && (value == 0 || value == 1)) {
+        g_plane_kernels.store(value, std::memory_order_relaxed);
         return CLB_OK;
     }
     return CLB_ERR_ARG;

@@ -1,0 +1,93 @@
+// Tensor-memory-accelerator (TMA) helpers: tiled tensor maps built on the host, bulk tensor loads into shared
+// memory that complete on an mbarrier, and bounded mbarrier waits.  sm_100a.
+//
+// Rules this code keeps: the innermost coordinate of every load is a multiple of 16 bytes (a negative start is
+// fine for a load and reads the fill value, zero); box inner extents and global strides are multiples of 16 bytes;
+// every shared-memory destination is 128-byte aligned; every wait has an iteration limit, after which the caller
+// records an error and leaves without touching the tile.  Loads only ever read this GPU's own memory and go to the
+// issuing block's own shared memory.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace clb_tma {
+
+// ---- host: cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda) ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// fp32 tensor [N][Ci][H][W] seen as 4-D (W, H, Ci, N); a box is (box_w, box_h, 1, box_n) elements, out-of-range
+// elements read as zero.  False when the driver refuses (alignment, extents) or the entry point is missing.
+inline bool make_plane_map(CUtensorMap *map, const float *base, int N, int Ci, int H, int W, int box_w, int box_h, int box_n)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (W & 3) || (box_w & 3) || box_w > 256 || box_h > 256 || box_n > 256) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)Ci, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4, (cuuint64_t)Ci * H * W * 4};
+    const cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)box_h, 1u, (cuuint32_t)box_n};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ---- device ----
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+// makes the initialised barriers visible to the asynchronous proxy (the copy engine)
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_addr(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with the given parity; gives up after `limit` polls (each poll may itself block for a
+// hardware time slice) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = 1u << 20)
+{
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// One box of the 4-D map to shared memory; completion (bytes) is signalled on `bar`.
+__device__ __forceinline__ void load_box_4d(void *dst, const CUtensorMap *map, int x, int y, int z, int w, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+} // namespace clb_tma

@@ -1240,14 +1240,20 @@ static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, f
     return check_launch();
 }
 
+int clb_convtree_fwd_plane_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W, int C,
+                               int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st); // convtree_plane.cu
+
 int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W,
                               int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st)
 {
     FastShape s;
     if (sh != 1 || sw != 1) return CLB_ERR_SHAPE;
     // many input channels: an image's channels do not fit shared memory (or barely one image does)
-    if ((size_t)Ci * (H + 2 * ph) * (W + 2 * pw) * 4 > 48 * 1024)
+    if ((size_t)Ci * (H + 2 * ph) * (W + 2 * pw) * 4 > 48 * 1024) {
+        const int rc = clb_convtree_fwd_plane_f32(x, w, sel, y, amax, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode, st);
+        if (rc != CLB_ERR_SHAPE) return rc;
         return launch_fwd_chan(x, w, sel, y, amax, N, Ci, H, W, C, ph, pw, kh, kw, wmode, st);
+    }
     if (!make_fast_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, wmode)) return CLB_ERR_SHAPE;
     const int I = (s.Ho / 2) * (s.Wo / 2);
     const size_t img_bytes = (size_t)s.IS * 4;

@@ -110,6 +110,29 @@ def conv_groups(sel, x_shape, geom, dtype):
     return out
 
 
+def plane_lists(sel, ci, geom):
+    """Per input channel, the (output channel, slot) gradient planes that belong to it -- the tables of
+    ``clb_convtree_bwd_plane`` -- or None when the selection does not fit those kernels (an output channel with more
+    than two input channels, or taps outside the window).  Cached on the selection tensor like ``conv_groups``."""
+    key = (sel._version, ci, geom[4], geom[5])
+    cache = getattr(sel, "_clb_planes", None)
+    if cache is not None and cache[0] == key:
+        return cache[1]
+    c = sel.shape[0]
+    sel_host = np.ascontiguousarray(sel.detach().cpu().numpy(), dtype=np.int32)
+    start = np.zeros(ci + 1, dtype=np.int32)
+    entry = np.zeros(max(2 * c, 1), dtype=np.int32)
+    cnt = lib().clb_conv_channel_lists(sel_host.ctypes.data_as(C.c_void_p), c, ci, geom[4], geom[5],
+                                       start.ctypes.data_as(C.c_void_p), entry.ctypes.data_as(C.c_void_p), entry.size)
+    out = None
+    if cnt >= 0:
+        out = (torch.from_numpy(start).to(sel.device), torch.from_numpy(entry[:max(cnt, 1)].copy()).to(sel.device))
+    elif cnt != _lib.ERR_SHAPE:
+        check(cnt)
+    sel._clb_planes = (key, out)
+    return out
+
+
 def _bwd_args_ok(gy, x, w, sel, amax, geom):
     """Shapes and dtypes of the fused block's backward inputs (the C ABI receives bare pointers)."""
     n, ci, h, wd = x.shape
@@ -152,6 +175,17 @@ def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
     if n == 0 or c == 0:  # empty batch: the gate gradient is an empty sum
         return gx, (gw.zero_() if gw is not None else None)
     flag = _sel_flag(sel, geom, ci)
+    if need_gx and not flag and x.dtype == torch.float32 and amax is not None:
+        # many-channel layers: the plane kernels (two channel planes per output channel streamed through shared memory)
+        nbytes = lib().clb_convtree_bwd_plane_scratch_bytes(n, ci, h, wd, c, *geom, dtype_code(x))
+        lists = plane_lists(sel, ci, geom) if nbytes else None
+        if lists is not None:
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            rc = lib().clb_convtree_bwd_plane(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(gw), ptr(lists[0]), ptr(lists[1]),
+                                              ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream())
+            if rc != _lib.ERR_SHAPE:
+                check(rc)
+                return gx, gw
     nbytes = lib().clb_convtree_bwd_scratch_bytes(n, ci, h, wd, c, *geom, int(need_gx), int(need_gw), dtype_code(x))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
     if need_gx:

@@ -78,6 +78,10 @@ long long clb_trace_report(char *buf, size_t cap);
  *       saved HBM traffic returns (measured: 3.47 ms per cifar10_m step unsliced, 4.4 ms with 80 MiB slices,
  *       5.0 ms with 48 MiB). */
 #define CLB_TUNE_TAPGRAD_SLICE_BYTES 1
+/*   CLB_TUNE_PLANE_KERNELS  1 (default): many-channel fused blocks (fp32, stride 1, image width a multiple of 4) run on
+ *       the kernels that stream two channel planes per output channel through shared memory with TMA loads
+ *       (clb_convtree_fwd picks them by itself; clb_convtree_bwd_plane is their backward); 0: never. */
+#define CLB_TUNE_PLANE_KERNELS 2
 int clb_tune(int key, long long value);
 long long clb_tune_get(int key);
 
@@ -93,6 +97,25 @@ long long clb_tune_get(int key);
 int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel, void *y, uint8_t *amax, void *x2, void *x3,
                      int32_t *idx, int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh,
                      int kw, int wmode, int dtype, void *stream);
+
+/* Backward of a fused block with many input channels (both gradients, fp32, stride 1), on the kernels that stream the
+ * two channel planes of an output channel through shared memory; stands in for full_convlogic_backward_x +
+ * full_convlogic_backward_weight (src/convlogic/cuda/convlogic.cpp:40-44; full_convlogic_kernel.cu:365-461, 616-701)
+ * on the layers behind the first one of a stack.  Pass 1 recomputes the gate chain at the saved arg-max, keeps the gate
+ * sums and writes, per (image, output channel), the gradient of its two input planes; pass 2 adds, per input channel,
+ * the planes of the output channels that read it (lists from clb_conv_channel_lists, built once per selection).
+ * Deterministic, no floating-point atomics.  gw may be NULL.  Returns CLB_ERR_SHAPE when the shape is outside these
+ * kernels' domain (use clb_convtree_bwd then); clb_convtree_bwd_plane_scratch_bytes returns 0 in that case.
+ *   clb_conv_channel_lists: host function; start int32 [Ci + 1], entry int32 [<= 2 * C]; returns the entry count, or
+ *   CLB_ERR_SHAPE when an output channel names more than two input channels or a tap outside the kh x kw window. */
+int clb_conv_channel_lists(const int32_t *sel_host, int C, int Ci, int kh, int kw, int32_t *start, int32_t *entry, int entry_cap);
+size_t clb_convtree_bwd_plane_scratch_bytes(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw,
+                                            int dtype);
+int clb_convtree_bwd_plane(const void *gy, const void *x, const void *w, const int32_t *sel, const uint8_t *amax, void *gx, void *gw,
+                           const int32_t *ch_start, const int32_t *ch_entry, void *scratch, size_t scratch_bytes, int N, int Ci,
+                           int H, int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream);
+/* Diagnostic (synchronises the device): *flag = 0 unless a bounded wait inside one of the plane kernels ever ran out. */
+int clb_plane_error(int *flag);
 
 /* Input gradient of the fused block; deterministic (no floating-point atomics).
  * Replaces convlogic_cuda.full_convlogic_backward_x (convlogic.cpp:40-41;
