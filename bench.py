@@ -219,6 +219,9 @@ def c3_algorithmic_bytes(batch):
         "convtree_fwd_chan_pair_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
         "convtree_fwd_chan_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
         "convtree_bwd_cls_kernel": y1 + x1,
+        "convtree_fwd_plane_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
+        "convtree_bwd_plane_kernel": (y2 + y1) + (y3 + y2) + (y4 + y3),            # upstream gradient + input
+        "plane_sum_kernel": y1 + y2 + y3,                                           # the input gradients
         "convtree_bwd_w_win_kernel<tapgrad>": (y2 + y1) + (y3 + y2) + (y4 + y3),   # upstream gradient + input
         "convtree_bwd_x_scatter_kernel": y1 + y2 + y3,                              # the input gradients
         "logic_tree_fwd_kernel": fin + fout,
@@ -857,6 +860,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--tapgrad-slice-mb", type=int, default=None,
                     help="override the library's slice size of the two-pass conv backward (0 = whole batch in one slice)")
+    ap.add_argument("--plane-kernels", type=int, default=None, choices=[0, 1],
+                    help="override the library's choice of the TMA-staged many-channel conv kernels (0 = the older staged kernels)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -867,6 +872,10 @@ def main():
         from convlogic_b200 import _lib
 
         _lib.check(_lib.lib().clb_tune(_lib.TUNE_TAPGRAD_SLICE_BYTES, args.tapgrad_slice_mb << 20))
+    if args.plane_kernels is not None:
+        from convlogic_b200 import _lib
+
+        _lib.check(_lib.lib().clb_tune(_lib.TUNE_PLANE_KERNELS, args.plane_kernels))
     if args.workload == "all":
         rec = run_c3(ctx, args)
         rec["packed_inference"] = run_c4(ctx, args)

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(kPlaneThreads) convtree_fwd_plane_kernel(const
     __shared__ __align__(8) uint64_t full[4][kPlaneStages];
     __shared__ Gate<float> sg[7];
     __shared__ SlotInfo si;
+    __shared__ int sabort;
 
     const int c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int HW = s.H * s.W, I = s.Hp * s.Wp;
@@ -92,8 +93,10 @@ __global__ void __launch_bounds__(kPlaneThreads) convtree_fwd_plane_kernel(const
         for (int g = 0; g < 4; ++g)
             for (int st = 0; st < kPlaneStages; ++st) clb_tma::mbar_init(&full[g][st], 1);
         clb_tma::mbar_init_fence();
+        sabort = *reinterpret_cast<volatile int *>(&g_plane_error);
     }
     __syncthreads();
+    if (sabort) return; // an earlier block's wait ran out: do not queue more work behind a copy engine that does not answer
 
     Gate<float> g[7];
 #pragma unroll
@@ -230,6 +233,7 @@ __global__ void __launch_bounds__(kPlaneThreads) convtree_bwd_plane_kernel(const
     __shared__ Gate<float> sg[7];
     __shared__ SlotInfo si;
     __shared__ float red[4][28];
+    __shared__ int sabort;
 
     const int c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int HW = s.H * s.W, I = s.Hp * s.Wp;
@@ -239,8 +243,10 @@ __global__ void __launch_bounds__(kPlaneThreads) convtree_bwd_plane_kernel(const
         for (int g = 0; g < 4; ++g)
             for (int st = 0; st < ST; ++st) clb_tma::mbar_init(&full[g][st], 1);
         clb_tma::mbar_init_fence();
+        sabort = *reinterpret_cast<volatile int *>(&g_plane_error);
     }
     __syncthreads();
+    if (sabort) return;
     Gate<float> g[7];
 #pragma unroll
     for (int i = 0; i < 7; ++i) g[i] = sg[i];
