@@ -47,6 +47,7 @@ template <> struct Geo<4> {
 
 struct Args {
     int N, Ci, C, wmode;
+    int parts; // the batch is split into this many contiguous parts; a (channel, part) pair is one task
 };
 
 __device__ int g_plane_error; // set when a bounded wait gave up (never expected); read by clb_plane_error()
@@ -87,10 +88,11 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+// volatile: computed once and kept, never re-materialised in front of every use
 __device__ __forceinline__ f32x2 dup2(float v)
 {
     f32x2 d;
-    asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "r"(__float_as_uint(v)));
+    asm volatile("mov.b64 %0, {%1, %1};" : "=l"(d) : "r"(__float_as_uint(v)));
     return d;
 }
 struct Gate2 {
@@ -167,27 +169,42 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     using Cf = FwdCfg<S>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full[Cf::GROUPS][Cf::STAGES];
-    __shared__ Gate<float> sg[7];
-    __shared__ SlotInfo si;
-    __shared__ int sabort;
+    __shared__ Gate<float> sgs[Cf::GROUPS][7];
+    __shared__ SlotInfo sis[Cf::GROUPS];
+    __shared__ int saborts[Cf::GROUPS];
 
-    const int c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // A group is the unit that shares a ring of staged planes: the whole block (16x16 images: 128 threads per image
+    // pair) or one warp (smaller images).  Every group works on its own task = (output channel, part of the batch),
+    // so with warp groups nothing in this kernel synchronises the block.
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int HW = S * S, I = Cf::I;
     const int gid = Cf::WIDE ? 0 : warp;
-    const bool leader = Cf::WIDE ? tid == 0 : lane == 0;
+    const int gt = Cf::WIDE ? tid : lane;                 // thread index inside the group
+    constexpr int GSIZE = Cf::WIDE ? kThreads : 32;
+    const bool leader = gt == 0;
+    const long long task = (long long)blockIdx.x * Cf::GROUPS + gid;
+    if (task >= (long long)s.C * s.parts) return;         // a whole group leaves together
+    const int c = (int)(task % s.C), part = (int)(task / s.C);
+    auto group_sync = [&]() {
+        if (Cf::WIDE)
+            __syncthreads();
+        else
+            __syncwarp();
+    };
+    Gate<float> *sg = sgs[gid];
+    SlotInfo &si = sis[gid];
 
-    if (tid < 7) sg[tid] = gate_load<float>(w + ((size_t)c * 7 + tid) * 16, s.wmode);
-    if (tid == 32) fill_slots(si, sel, c, s.Ci);
-    if (tid == 64) {
-        for (int g = 0; g < Cf::GROUPS; ++g)
-            for (int st = 0; st < Cf::STAGES; ++st) clb_tma::mbar_init(&full[g][st], 1);
+    if (gt < 7) sg[gt] = gate_load<float>(w + ((size_t)c * 7 + gt) * 16, s.wmode);
+    if (gt == (Cf::WIDE ? 32 : 8)) fill_slots(si, sel, c, s.Ci);
+    if (gt == (Cf::WIDE ? 64 : 9)) {
+        for (int st = 0; st < Cf::STAGES; ++st) clb_tma::mbar_init(&full[gid][st], 1);
         clb_tma::mbar_init_fence();
-        sabort = *reinterpret_cast<volatile int *>(&g_plane_error);
+        saborts[gid] = *reinterpret_cast<volatile int *>(&g_plane_error);
     }
-    __syncthreads();
-    if (sabort) return; // an earlier block's wait ran out: do not queue more work behind a copy engine that does not answer
+    group_sync();
+    if (saborts[gid]) return; // an earlier wait ran out: do not queue more work behind a copy engine that does not answer
 
-    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+    const int n_lo = (int)((long long)s.N * part / s.parts), n_hi = (int)((long long)s.N * (part + 1) / s.parts);
 
     if (si.nslot > 2) {
         // Hand-made selection (more than two channels, or taps outside the window): every tap is a bounds-checked
@@ -195,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         Gate<float> g[7];
 #pragma unroll
         for (int i = 0; i < 7; ++i) g[i] = sg[i];
-        for (int f = tid; f < (n_hi - n_lo) * I; f += kThreads) {
+        for (int f = gt; f < (n_hi - n_lo) * I; f += GSIZE) {
             const int img = f / I, win = f - img * I;
             const int py = win / Cf::WP, px = win - py * Cf::WP;
             const float *ximg = x + (size_t)(n_lo + img) * s.Ci * HW;
@@ -229,7 +246,6 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     for (int i = 0; i < 7; ++i) g[i].k1 = dup2(sg[i].k1), g[i].ka = dup2(sg[i].ka), g[i].kb = dup2(sg[i].kb), g[i].kab = dup2(sg[i].kab);
 
     // this thread's place: pair `pair_local` of the group's batch, pooled row py, column position ox
-    const int gt = Cf::WIDE ? tid : lane;
     const int pair_local = gt / Cf::TPI;
     const int t = gt - pair_local * Cf::TPI;
     const int py = t / Cf::WO, ox = t - py * Cf::WO;
@@ -243,12 +259,11 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     }
     const int ch_a = si.ch[0], ch_b = si.ch[1];
 
-    const int nbatch = (n_hi - n_lo + Cf::NIMG - 1) / Cf::NIMG;
-    const int iters = nbatch > gid ? (nbatch - gid + Cf::GROUPS - 1) / Cf::GROUPS : 0;
+    const int iters = (n_hi - n_lo + Cf::NIMG - 1) / Cf::NIMG;
     constexpr uint32_t tx_bytes = 2u * (uint32_t)(Cf::NIMG * Cf::IMG * 4);
     auto issue = [&](int it) {
         const int st = it % Cf::STAGES;
-        const int n0 = n_lo + (it * Cf::GROUPS + gid) * Cf::NIMG;
+        const int n0 = n_lo + it * Cf::NIMG;
         unsigned char *dst = gbase + (size_t)st * Cf::STAGE_BYTES;
         clb_tma::mbar_expect_tx(&full[gid][st], tx_bytes);
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[gid][st]);
@@ -277,7 +292,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         if (hi_of(d2) > best[1]) best[1] = hi_of(d2), bd[1] = 2;
         if (lo_of(d3) > best[0]) best[0] = lo_of(d3), bd[0] = 3;
         if (hi_of(d3) > best[1]) best[1] = hi_of(d3), bd[1] = 3;
-        const int na = n_lo + (it * Cf::GROUPS + gid) * Cf::NIMG + 2 * pair_local;
+        const int na = n_lo + it * Cf::NIMG + 2 * pair_local;
         const size_t o = ((size_t)na * s.C + c) * I + py * Cf::WP + (ox >> 1);
         // even lanes store the values, odd lanes the arg-max bytes, of both images of the pair
         if (na < n_hi) {
@@ -322,9 +337,10 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
 }
 
 // ================================================================================== backward, pass 1
-// grid (parts, C), 4 warps per block, every warp with its own ring of staged planes.  A warp works on NIMG whole
-// images per iteration (32 / I of them when an image has I < 32 pooled windows, else one image with WPT = I / 32
-// windows per lane).  Per warp: [XST stages x (2 slots of x planes)] + [2 slots of gradient planes].
+// 4 warps per block, every warp with its own task = (output channel, part of the batch), its own ring of staged
+// planes and its own gradient tile: nothing synchronises the block.  A warp works on NIMG whole images per iteration
+// (32 / I of them when an image has I < 32 pooled windows, else one image with WPT = I / 32 windows per lane).
+// Per warp: [XST stages x (2 slots of x planes)] + [2 slots of gradient planes].
 template <int S> struct BwdCfg {
     using G = Geo<S>;
     static constexpr int P = G::P, R = G::R, NIMG = G::BWD_NIMG, WPT = G::BWD_WPT;
@@ -341,44 +357,54 @@ template <int S> struct BwdCfg {
     static_assert(UNITS % 32 == 0, "write-out units per lane");
 };
 
-// One window at its arg-max position: gate chain, basis sums, tap gradients added into the gradient tile.
-template <int S, int ST>
-__device__ __forceinline__ void bwd_window(uint32_t base, const uint32_t (&toff)[8], const Gate<float> (&g)[7], float d, float (&acc)[28])
+// The lane's WPT windows at their arg-max positions: gate chain, basis sums, tap gradients added into the gradient tile.
+template <int S, int ST, int WPT>
+__device__ __forceinline__ void bwd_windows(const uint32_t (&base)[WPT], const uint32_t (&toff)[8], const Gate<float> (&g)[7],
+                                            const float (&dz)[WPT], float (&acc)[28])
 {
     using Cf = BwdCfg<S>;
     constexpr int B = ST * Cf::STAGE_BYTES, GT = Cf::GT_BYTES;
-    uint32_t cell[8];
-    float a[8];
+    uint32_t cell[WPT][8];
+    float tg[WPT][8];
+#pragma unroll
+    for (int j = 0; j < WPT; ++j) {
+        float a[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            cell[j][k] = base[j] + toff[k];
+            a[k] = lds_f32<B>(cell[j][k]);
+        }
+        const float d = dz[j];
+        const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+        const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+        const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+        const float dt0 = d * gate_da<float>(g[6], t1), dt1 = d * gate_db<float>(g[6], t0);
+        float dg[4];
+        dg[0] = dt0 * gate_da<float>(g[4], g1), dg[1] = dt0 * gate_db<float>(g[4], g0);
+        dg[2] = dt1 * gate_da<float>(g[5], g3), dg[3] = dt1 * gate_db<float>(g[5], g2);
+        acc[24] = fmaf(d, t0 * t1, acc[24]), acc[25] = fmaf(d, t0, acc[25]), acc[26] = fmaf(d, t1, acc[26]), acc[27] += d;
+        acc[16] = fmaf(dt0, g0 * g1, acc[16]), acc[17] = fmaf(dt0, g0, acc[17]), acc[18] = fmaf(dt0, g1, acc[18]), acc[19] += dt0;
+        acc[20] = fmaf(dt1, g2 * g3, acc[20]), acc[21] = fmaf(dt1, g2, acc[21]), acc[22] = fmaf(dt1, g3, acc[22]), acc[23] += dt1;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            acc[4 * p] = fmaf(dg[p], a[2 * p] * a[2 * p + 1], acc[4 * p]);
+            acc[4 * p + 1] = fmaf(dg[p], a[2 * p], acc[4 * p + 1]);
+            acc[4 * p + 2] = fmaf(dg[p], a[2 * p + 1], acc[4 * p + 2]);
+            acc[4 * p + 3] += dg[p];
+            tg[j][2 * p] = dg[p] * gate_da<float>(g[p], a[2 * p + 1]);
+            tg[j][2 * p + 1] = dg[p] * gate_db<float>(g[p], a[2 * p]);
+        }
+    }
+    // One tap at a time: all windows of a warp (both of a lane included) hit distinct pixels within one tap -- the map
+    // window -> pixel is a translation of the window grid -- and a pixel outside the image is a halo cell that is never
+    // written out.  The order of additions into a pixel is the tap order: fixed.
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        cell[k] = base + toff[k];
-        a[k] = lds_f32<B>(cell[k]);
-    }
-    const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
-    const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
-    const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
-    const float dt0 = d * gate_da<float>(g[6], t1), dt1 = d * gate_db<float>(g[6], t0);
-    float dg[4];
-    dg[0] = dt0 * gate_da<float>(g[4], g1), dg[1] = dt0 * gate_db<float>(g[4], g0);
-    dg[2] = dt1 * gate_da<float>(g[5], g3), dg[3] = dt1 * gate_db<float>(g[5], g2);
-    acc[24] = fmaf(d, t0 * t1, acc[24]), acc[25] = fmaf(d, t0, acc[25]), acc[26] = fmaf(d, t1, acc[26]), acc[27] += d;
-    acc[16] = fmaf(dt0, g0 * g1, acc[16]), acc[17] = fmaf(dt0, g0, acc[17]), acc[18] = fmaf(dt0, g1, acc[18]), acc[19] += dt0;
-    acc[20] = fmaf(dt1, g2 * g3, acc[20]), acc[21] = fmaf(dt1, g2, acc[21]), acc[22] = fmaf(dt1, g3, acc[22]), acc[23] += dt1;
-    float tg[8];
+        float cur[WPT];
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-        acc[4 * p] = fmaf(dg[p], a[2 * p] * a[2 * p + 1], acc[4 * p]);
-        acc[4 * p + 1] = fmaf(dg[p], a[2 * p], acc[4 * p + 1]);
-        acc[4 * p + 2] = fmaf(dg[p], a[2 * p + 1], acc[4 * p + 2]);
-        acc[4 * p + 3] += dg[p];
-        tg[2 * p] = dg[p] * gate_da<float>(g[p], a[2 * p + 1]);
-        tg[2 * p + 1] = dg[p] * gate_db<float>(g[p], a[2 * p]);
-    }
-    // One tap at a time: the windows of a warp hit distinct pixels within one tap (a translation of the window grid),
-    // and a pixel outside the image is a halo cell that is never written out.
+        for (int j = 0; j < WPT; ++j) cur[j] = lds_f32<GT>(cell[j][k]);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        sts_f32<GT>(cell[k], lds_f32<GT>(cell[k]) + tg[k]);
+        for (int j = 0; j < WPT; ++j) sts_f32<GT>(cell[j][k], cur[j] + tg[j][k]);
         __syncwarp();
     }
 }
@@ -393,22 +419,25 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     constexpr int XST = Cf::XST, WPT = Cf::WPT, I = Cf::I, HW = S * S;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full[4][XST];
-    __shared__ Gate<float> sg[7];
-    __shared__ SlotInfo si;
-    __shared__ float red[4][28];
-    __shared__ int sabort;
+    __shared__ Gate<float> sgs[4][7];
+    __shared__ SlotInfo sis[4];
+    __shared__ int saborts[4];
 
-    const int c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid < 7) sg[tid] = gate_load<float>(w + ((size_t)c * 7 + tid) * 16, s.wmode);
-    if (tid == 32) fill_slots(si, sel, c, s.Ci);
-    if (tid == 64) {
-        for (int g = 0; g < 4; ++g)
-            for (int st = 0; st < XST; ++st) clb_tma::mbar_init(&full[g][st], 1);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long task = (long long)blockIdx.x * 4 + warp;
+    if (task >= (long long)s.C * s.parts) return;
+    const int c = (int)(task % s.C), part = (int)(task / s.C);
+    Gate<float> *sg = sgs[warp];
+    SlotInfo &si = sis[warp];
+    if (lane < 7) sg[lane] = gate_load<float>(w + ((size_t)c * 7 + lane) * 16, s.wmode);
+    if (lane == 8) fill_slots(si, sel, c, s.Ci);
+    if (lane == 9) {
+        for (int st = 0; st < XST; ++st) clb_tma::mbar_init(&full[warp][st], 1);
         clb_tma::mbar_init_fence();
-        sabort = *reinterpret_cast<volatile int *>(&g_plane_error);
+        saborts[warp] = *reinterpret_cast<volatile int *>(&g_plane_error);
     }
-    __syncthreads();
-    if (sabort) return;
+    __syncwarp();
+    if (saborts[warp]) return;
     Gate<float> g[7];
 #pragma unroll
     for (int i = 0; i < 7; ++i) g[i] = sg[i];
@@ -416,7 +445,7 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
 #pragma unroll
     for (int i = 0; i < 28; ++i) acc[i] = 0.f;
 
-    const int n_lo = (int)((long long)s.N * blockIdx.x / gridDim.x), n_hi = (int)((long long)s.N * (blockIdx.x + 1) / gridDim.x);
+    const int n_lo = (int)((long long)s.N * part / s.parts), n_hi = (int)((long long)s.N * (part + 1) / s.parts);
     unsigned char *wbase = smem_raw + (size_t)warp * Cf::WARP_BYTES;
     float *gt = reinterpret_cast<float *>(wbase + Cf::GT_BYTES);
     for (int i = lane * 4; i < Cf::STAGE_FLOATS; i += 128) *reinterpret_cast<float4 *>(gt + i) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -441,12 +470,11 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     const int ch_a = si.ch[0], ch_b = si.ch[1];
     const bool usable = si.nslot <= 2; // the host only routes selections here that fit two planes
 
-    const int nbatch = (n_hi - n_lo + Cf::NIMG - 1) / Cf::NIMG;
-    const int iters = (usable && nbatch > warp) ? (nbatch - warp + 3) / 4 : 0;
+    const int iters = usable ? (n_hi - n_lo + Cf::NIMG - 1) / Cf::NIMG : 0;
     constexpr uint32_t tx_bytes = 2u * (uint32_t)(Cf::NIMG * Cf::IMG * 4);
     auto issue = [&](int it) {
         const int st = it % XST;
-        const int n0 = n_lo + (it * 4 + warp) * Cf::NIMG;
+        const int n0 = n_lo + it * Cf::NIMG;
         unsigned char *dst = wbase + (size_t)st * Cf::STAGE_BYTES;
         clb_tma::mbar_expect_tx(&full[warp][st], tx_bytes);
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[warp][st]);
@@ -461,7 +489,7 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     auto fetch = [&](int it) {
 #pragma unroll
         for (int j = 0; j < WPT; ++j) {
-            const int n = n_lo + (it * 4 + warp) * Cf::NIMG + img_local[j];
+            const int n = n_lo + it * Cf::NIMG + img_local[j];
             const bool live = it < iters && n < n_hi;
             const size_t o = ((size_t)n * s.C + c) * I + win[j];
             dz_next[j] = live ? __ldg(gy + o) : 0.f;
@@ -475,7 +503,7 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     __syncwarp();
     auto finish = [&]() {
         // write the interior of the gradient planes out and clear it for the next iteration
-        const int nb0 = n_lo + (it * 4 + warp) * Cf::NIMG;
+        const int nb0 = n_lo + it * Cf::NIMG;
 #pragma unroll
         for (int q = 0; q < Cf::UNITS / 32; ++q) {
             const int u = lane + 32 * q;
@@ -502,8 +530,9 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         if (!ok) {                                                                                                        \
             failed = true;                                                                                                \
         } else {                                                                                                          \
-            _Pragma("unroll") for (int j = 0; j < WPT; ++j)                                                                \
-                bwd_window<S, ST>(woff[j] + 4u * (uint32_t)(((bd[j] >> 1) ? Cf::P : 0) + (bd[j] & 1)), toff, g, dz[j], acc); \
+            uint32_t base[WPT];                                                                                           \
+            _Pragma("unroll") for (int j = 0; j < WPT; ++j) base[j] = woff[j] + 4u * (uint32_t)(((bd[j] >> 1) ? Cf::P : 0) + (bd[j] & 1)); \
+            bwd_windows<S, ST, WPT>(base, toff, g, dz, acc);                                                              \
             /* the input planes of this stage have been read by every lane (the taps' __syncwarp): refill it */           \
             if (lane == 0 && it + XST < iters) issue(it + XST);                                                           \
             finish();                                                                                                     \
@@ -519,15 +548,23 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         g_plane_error = 1;
         for (int j = it + 1; j < iters && j < it + XST; ++j) clb_tma::mbar_wait(&full[warp][j % XST], (j / XST) & 1);
     }
-    if (!usable && tid == 0) g_plane_error = 2;
+    if (!usable && lane == 0) g_plane_error = 2;
 
+    // the warp's 28 basis sums: lane i ends up with sum i (a transposed butterfly over the 32 lanes)
+    float v[32];
 #pragma unroll
-    for (int i = 0; i < 28; ++i) {
-        const float v = warp_sum<float>(acc[i]);
-        if (lane == 0) red[warp][i] = v;
+    for (int i = 0; i < 32; ++i) v[i] = i < 28 ? acc[i] : 0.f;
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
     }
-    __syncthreads();
-    if (tid < 28) partial[((size_t)blockIdx.x * s.C + c) * 28 + tid] = (red[0][tid] + red[1][tid]) + (red[2][tid] + red[3][tid]);
+    if (lane < 28) partial[((size_t)part * s.C + c) * 28 + lane] = v[0];
 }
 
 // Pass 2: gx[n][ch] = sum of the gradient planes (c, slot) that belong to input channel ch, in list order.
@@ -593,10 +630,12 @@ int plane_side(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int p
     return (H == 16 || H == 8 || H == 4) ? H : 0;
 }
 
-int plane_parts(int N, int C, int images_per_block_iteration)
+// Parts of the batch per output channel: enough (channel, part) tasks for about three waves of resident groups, but
+// at least eight iterations per task so that a task's set-up (soft-max of 7 gates, tap table) stays a small share.
+int plane_parts(int N, int C, int images_per_iteration, int resident_groups_per_sm)
 {
-    long long parts = ((long long)sm_count() * 16 + C - 1) / C;
-    const long long most = N / (4LL * images_per_block_iteration); // at least four iterations per group
+    long long parts = ((long long)sm_count() * resident_groups_per_sm * 3 + C - 1) / C;
+    const long long most = N / (8LL * images_per_iteration);
     if (parts > most) parts = most;
     if (parts < 1) parts = 1;
     return (int)parts;
@@ -610,13 +649,15 @@ int launch_fwd(const float *x, const float *w, const int32_t *sel, float *y, uin
     if (!clb_tma::make_plane_map(&map, x, N, Ci, S, S, Cf::P, Cf::R, Cf::NIMG)) return CLB_ERR_SHAPE;
     auto k = convtree_fwd_plane_kernel<S>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM) != cudaSuccess) return check_launch(0);
-    const int parts = plane_parts(N, C, Cf::GROUPS * Cf::NIMG);
-    const Args a{N, Ci, C, wmode};
-    CLB_TRACED("convtree_fwd_plane_kernel", st, k<<<dim3(parts, C), kThreads, Cf::SMEM, st>>>(map, x, w, sel, y, amax, a));
+    const int parts = plane_parts(N, C, Cf::NIMG, Cf::WIDE ? 6 : 12);
+    const Args a{N, Ci, C, wmode, parts};
+    const long long tasks = (long long)C * parts;
+    CLB_TRACED("convtree_fwd_plane_kernel", st,
+               k<<<(unsigned)((tasks + Cf::GROUPS - 1) / Cf::GROUPS), kThreads, Cf::SMEM, st>>>(map, x, w, sel, y, amax, a));
     return check_launch();
 }
 
-template <int S> int bwd_parts(int N, int C) { return plane_parts(N, C, (kThreads / 32) * BwdCfg<S>::NIMG); }
+template <int S> int bwd_parts(int N, int C) { return plane_parts(N, C, BwdCfg<S>::NIMG, 12); }
 
 template <int S>
 int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *sel, const uint8_t *amax, float *partial, float *planes, int N,
@@ -627,8 +668,10 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     if (!clb_tma::make_plane_map(&map, x, N, Ci, S, S, Cf::P, Cf::R, Cf::NIMG)) return CLB_ERR_SHAPE;
     auto k = convtree_bwd_plane_kernel<S>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM) != cudaSuccess) return check_launch(0);
-    const Args a{N, Ci, C, wmode};
-    CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<dim3(bwd_parts<S>(N, C), C), kThreads, Cf::SMEM, st>>>(map, gy, w, sel, amax, partial, planes, a));
+    const int parts = bwd_parts<S>(N, C);
+    const Args a{N, Ci, C, wmode, parts};
+    const long long tasks = (long long)C * parts;
+    CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<(unsigned)((tasks + 3) / 4), kThreads, Cf::SMEM, st>>>(map, gy, w, sel, amax, partial, planes, a));
     return CLB_OK;
 }
 
