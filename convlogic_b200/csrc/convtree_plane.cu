@@ -122,6 +122,23 @@ template <int OFF> __device__ __forceinline__ void sts_f32(uint32_t addr, float 
     asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "f"(v) : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (L2 only), commit / wait of the calling thread's copy groups
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// How the planes reach shared memory.  16x16 images: TMA box loads (one elected thread, halo zero-filled by the copy
+// engine).  8x8 and 4x4 images: the copy engine handles a box row by row at a few cycles per row, and rows of 32 or 16
+// useful bytes make it the bottleneck (measured: 290-300 us per layer against 230-240 us for register staging); there
+// every thread of the group issues two 16-byte cp.async copies per iteration into the interior of a tile whose halo was
+// zeroed once.
+template <int S> struct UseTma {
+    static constexpr bool value = S >= 16;
+};
+
 // =========================================================================================== forward
 template <int S> struct FwdCfg {
     using G = Geo<S>;
@@ -135,7 +152,11 @@ template <int S> struct FwdCfg {
     static constexpr int STAGE_BYTES = 2 * SLOT * 4;
     static constexpr int STAGES = 4;
     static constexpr int SMEM = GROUPS * STAGES * STAGE_BYTES;
+    static constexpr bool TMA = UseTma<S>::value;
+    static constexpr int GSIZE = WIDE ? kThreads : 32;
+    static constexpr int CPQ = NIMG * 2 * S * (S / 4) / GSIZE;   // 16-byte copies per thread and iteration (cp.async staging)
     static_assert(WIDE ? (TPI == kThreads && NIMG == 2) : (32 % TPI == 0 && NIMG == 2 * (32 / TPI)), "thread mapping");
+    static_assert(NIMG * 2 * S * (S / 4) % GSIZE == 0, "copies per thread");
 };
 
 // One stage of the ring: both conv rows of both images of the thread's pair.
@@ -269,8 +290,40 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[gid][st]);
         clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n0, &full[gid][st]);
     };
-    if (leader)
-        for (int it = 0; it < Cf::STAGES && it < iters; ++it) issue(it);
+    // cp.async staging: which 16-byte pieces this thread moves is the same for every iteration
+    int coff[Cf::CPQ], cimg[Cf::CPQ];
+    uint32_t cdst[Cf::CPQ];
+#pragma unroll
+    for (int q = 0; q < Cf::CPQ; ++q) {
+        const int u = gt + q * Cf::GSIZE;
+        constexpr int W4 = S / 4;
+        const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
+        coff[q] = (slot ? ch_b : ch_a) * HW + row * S + col4 * 4;
+        cimg[q] = img;
+        cdst[q] = clb_tma::smem_addr(gbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
+    }
+    auto issue_cp = [&](int it) {   // every thread of the group; always commits, so that the group counts stay aligned
+        if (it < iters) {
+            const int st = it % Cf::STAGES;
+            const int n0 = n_lo + it * Cf::NIMG;
+#pragma unroll
+            for (int q = 0; q < Cf::CPQ; ++q) {
+                const int n = min(n0 + cimg[q], s.N - 1); // images past the end: any valid plane, the results are not stored
+                cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), x + (size_t)n * s.Ci * HW + coff[q]);
+            }
+        }
+        cp_async_commit();
+    };
+    if (Cf::TMA) {
+        if (leader)
+            for (int it = 0; it < Cf::STAGES && it < iters; ++it) issue(it);
+    } else {
+        // the halo is zeroed once; the copies only ever write the interior
+        for (int i = gt * 4; i < Cf::STAGES * Cf::STAGE_BYTES / 4; i += Cf::GSIZE * 4)
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(gbase) + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        group_sync();
+        for (int it = 0; it < Cf::STAGES; ++it) issue_cp(it);
+    }
 
     const bool odd = ox & 1;
     bool failed = false;
@@ -280,7 +333,11 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         // thread whether anyone's wait ran out (never expected): then nothing of this iteration is stored.
         const bool ok = Cf::WIDE ? (__syncthreads_and(ok_in ? 1 : 0) != 0) : (__all_sync(0xffffffffu, ok_in ? 1 : 0) != 0);
         if (!ok) return false;
-        if (leader && it + Cf::STAGES < iters) issue(it + Cf::STAGES);
+        if (Cf::TMA) {
+            if (leader && it + Cf::STAGES < iters) issue(it + Cf::STAGES);
+        } else {
+            issue_cp(it + Cf::STAGES);
+        }
         // 2x2 pool: lanes ox and ox^1 hold the two columns; candidates in scan order (0,0),(0,1),(1,0),(1,1)
         const f32x2 q0 = __shfl_xor_sync(0xffffffffu, z[0], 1), q1 = __shfl_xor_sync(0xffffffffu, z[1], 1);
         const f32x2 d0 = odd ? q0 : z[0], d1 = odd ? z[0] : q0, d2 = odd ? q1 : z[1], d3 = odd ? z[1] : q1;
@@ -314,7 +371,13 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         const uint32_t parity = (it / Cf::STAGES) & 1;
 #define CLB_FWD_STAGE(ST)                                                                                                 \
     if (it < iters && !failed) {                                                                                          \
-        const bool ok = clb_tma::mbar_wait(&full[gid][ST], parity);                                                       \
+        bool ok = true;                                                                                                   \
+        if (Cf::TMA) {                                                                                                    \
+            ok = clb_tma::mbar_wait(&full[gid][ST], parity);                                                              \
+        } else {                                                                                                          \
+            cp_async_wait<Cf::STAGES - 1>();                                                                              \
+            group_sync(); /* the other threads' pieces of this stage are visible */                                      \
+        }                                                                                                                 \
         f32x2 z[2];                                                                                                       \
         fwd_stage<S, ST>(toff, g, z);                                                                                     \
         if (finish(z, ok))                                                                                                \
@@ -352,7 +415,8 @@ template <int S> struct BwdCfg {
     static constexpr int GT_BYTES = XST * STAGE_BYTES;  // byte distance from stage 0 to the gradient tile: the same cell offsets
     static constexpr int WARP_BYTES = (XST + 1) * STAGE_BYTES;
     static constexpr int SMEM = (kThreads / 32) * WARP_BYTES;
-    static constexpr int UNITS = NIMG * 2 * S * (S / 4); // float4 units of the interior of the gradient tile
+    static constexpr int UNITS = NIMG * 2 * S * (S / 4); // float4 units of the interior of the gradient tile (and of a stage)
+    static constexpr bool TMA = UseTma<S>::value;
     static_assert(I >= 32 ? (NIMG == 1 && WPT * 32 == I) : (WPT == 1 && NIMG * I == 32), "thread mapping");
     static_assert(UNITS % 32 == 0, "write-out units per lane");
 };
@@ -411,9 +475,9 @@ __device__ __forceinline__ void bwd_windows(const uint32_t (&base)[WPT], const u
 
 template <int S>
 __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __grid_constant__ CUtensorMap xmap, const float *__restrict__ gy,
-                                                                      const float *__restrict__ w, const int32_t *__restrict__ sel,
-                                                                      const uint8_t *__restrict__ amax, float *__restrict__ partial,
-                                                                      float *__restrict__ planes, Args s)
+                                                                      const float *__restrict__ x, const float *__restrict__ w,
+                                                                      const int32_t *__restrict__ sel, const uint8_t *__restrict__ amax,
+                                                                      float *__restrict__ partial, float *__restrict__ planes, Args s)
 {
     using Cf = BwdCfg<S>;
     constexpr int XST = Cf::XST, WPT = Cf::WPT, I = Cf::I, HW = S * S;
@@ -480,8 +544,40 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[warp][st]);
         clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n0, &full[warp][st]);
     };
-    if (lane == 0)
-        for (int it = 0; it < XST && it < iters; ++it) issue(it);
+    // cp.async staging (small images): the 16-byte pieces this lane moves, the same for every iteration
+    constexpr int CPQ = Cf::UNITS / 32;
+    int coff[CPQ], cimg[CPQ];
+    uint32_t cdst[CPQ];
+#pragma unroll
+    for (int q = 0; q < CPQ; ++q) {
+        const int u = lane + 32 * q;
+        constexpr int W4 = S / 4;
+        const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
+        coff[q] = (slot ? ch_b : ch_a) * HW + row * S + col4 * 4;
+        cimg[q] = img;
+        cdst[q] = clb_tma::smem_addr(wbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
+    }
+    auto issue_cp = [&](int it) {   // every lane; always commits, so that the group counts stay aligned
+        if (it < iters) {
+            const int st = it % XST;
+            const int n0 = n_lo + it * Cf::NIMG;
+#pragma unroll
+            for (int q = 0; q < CPQ; ++q) {
+                const int n = min(n0 + cimg[q], s.N - 1);
+                cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), x + (size_t)n * s.Ci * HW + coff[q]);
+            }
+        }
+        cp_async_commit();
+    };
+    if (Cf::TMA) {
+        if (lane == 0)
+            for (int it = 0; it < XST && it < iters; ++it) issue(it);
+    } else {
+        for (int i = lane * 4; i < XST * Cf::STAGE_FLOATS; i += 128)   // the halo is zeroed once; copies write the interior
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(wbase) + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncwarp();
+        for (int it = 0; it < XST; ++it) issue_cp(it);
+    }
 
     // upstream gradient and arg-max: fetched one iteration ahead
     float dz_next[WPT];
@@ -525,8 +621,13 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         int bd[WPT];                                                                                                      \
         _Pragma("unroll") for (int j = 0; j < WPT; ++j) dz[j] = dz_next[j], bd[j] = bd_next[j];                            \
         fetch(it + 1);                                                                                                    \
-        bool ok = clb_tma::mbar_wait(&full[warp][ST], parity);                                                            \
-        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;                                                                    \
+        bool ok = true;                                                                                                   \
+        if (Cf::TMA) {                                                                                                    \
+            ok = clb_tma::mbar_wait(&full[warp][ST], parity);                                                             \
+        } else {                                                                                                          \
+            cp_async_wait<XST - 1>();                                                                                     \
+        }                                                                                                                 \
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0; /* also: the other lanes' pieces of this stage are visible */     \
         if (!ok) {                                                                                                        \
             failed = true;                                                                                                \
         } else {                                                                                                          \
@@ -534,7 +635,11 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
             _Pragma("unroll") for (int j = 0; j < WPT; ++j) base[j] = woff[j] + 4u * (uint32_t)(((bd[j] >> 1) ? Cf::P : 0) + (bd[j] & 1)); \
             bwd_windows<S, ST, WPT>(base, toff, g, dz, acc);                                                              \
             /* the input planes of this stage have been read by every lane (the taps' __syncwarp): refill it */           \
-            if (lane == 0 && it + XST < iters) issue(it + XST);                                                           \
+            if (Cf::TMA) {                                                                                                \
+                if (lane == 0 && it + XST < iters) issue(it + XST);                                                       \
+            } else {                                                                                                      \
+                issue_cp(it + XST);                                                                                       \
+            }                                                                                                             \
             finish();                                                                                                     \
             ++it;                                                                                                         \
         }                                                                                                                 \
@@ -671,7 +776,7 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     const int parts = bwd_parts<S>(N, C);
     const Args a{N, Ci, C, wmode, parts};
     const long long tasks = (long long)C * parts;
-    CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<(unsigned)((tasks + 3) / 4), kThreads, Cf::SMEM, st>>>(map, gy, w, sel, amax, partial, planes, a));
+    CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<(unsigned)((tasks + 3) / 4), kThreads, Cf::SMEM, st>>>(map, gy, x, w, sel, amax, partial, planes, a));
     return CLB_OK;
 }
 
