@@ -219,6 +219,7 @@ def c3_algorithmic_bytes(batch):
         "convtree_fwd_chan_pair_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
         "convtree_fwd_chan_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
         "convtree_bwd_cls_kernel": y1 + x1,
+        "convtree_bwd_w_plane32_kernel": y1 + x1,
         "convtree_fwd_plane_kernel": (y1 + y2) + (y2 + y3) + (y3 + y4),
         "convtree_bwd_plane_kernel": (y2 + y1) + (y3 + y2) + (y4 + y3),            # upstream gradient + input
         "plane_sum_kernel": y1 + y2 + y3,                                           # the input gradients
@@ -613,11 +614,12 @@ def run_c5(ctx, args):
 
     dev, world, rank = ctx.dev, ctx.world, ctx.rank
     torch.manual_seed(0)
-    dims = [3072] + [256000] * 8
+    width, depth, batch = args.flat_width, args.flat_layers, 1024   # 256000 x 8 is the configuration; smaller ones are for profiling
+    dims = [3072] + [width] * depth
     net = torch.nn.Sequential(*[cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])], cb.GroupSum(10, 100.0)).to(dev).train()
     gi = torch.Generator().manual_seed(100 + rank)
-    x = (torch.rand(1024, 3072, generator=gi) < 0.5).float().to(dev)
-    gy = torch.randn(1024, 10, generator=gi).to(dev)
+    x = (torch.rand(batch, 3072, generator=gi) < 0.5).float().to(dev)
+    gy = torch.randn(batch, 10, generator=gi).to(dev)
 
     def step(i):
         for prm in net.parameters():
@@ -636,32 +638,34 @@ def run_c5(ctx, args):
     trace = traced(step, 3)
     clocks = sampler.stop()
     peak, kind = measured_peaks()
-    row = 256000 * 1024 * 4          # one activation [256000, 1024] fp32
-    xin = 3072 * 1024 * 4
+    row = width * batch * 4          # one activation [width, batch] fp32
+    xin = 3072 * batch * 4
     names = {
-        "logic_fwd_kernel": (xin + row) + 7 * 2 * row,          # layer 1: x + y; layers 2-8: x + y
-        "logic_bwd_w_kernel": (xin + row) + 7 * 2 * row,        # gy + x per layer
-        "logic_bwd_x_kernel": 7 * 3 * row,                      # layers 2-8: gy + x + gx
+        "logic_fwd_kernel": (xin + row) + (depth - 1) * 2 * row,    # layer 1: x + y; the others: x + y
+        "logic_bwd_w_kernel": (xin + row) + (depth - 1) * 2 * row,  # gy + x per layer
+        "logic_bwd_x_kernel": (depth - 1) * 3 * row,                # all but the first layer: gy + x + gx
         "group_sum_partial_kernel": row, "group_sum_bwd_kernel": row,
     }
     kernels = kernel_table(trace, names, peak)
     top = kernels[0] if kernels else {}
-    alg = 39.9e9
+    # forward: layer 1 in + out, the others 2 rows each, GroupSum read; backward: 3 rows per layer, the first gy + x
+    # (the GroupSum gradient counted as fused into the last layer): 39.9 GB at 256000 x 8
+    alg = (xin + row) + (depth - 1) * 2 * row + row + (depth - 1) * 3 * row + (row + xin)
     rec = {
         "metric": "train samples/sec (fwd+bwd), flat difflogic stack", "value": 1024 * world * steps / (ms * 1e-3), "unit": "samples/s",
         "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "c5: 8 LogicLayers 3072->256000x8 + GroupSum(10, tau=100), batch 1024, fwd+bwd",
-                   "l2": "every activation is 1.05 GB (> 126 MB L2)"},
+        "config": {"workload": f"c5: {depth} LogicLayers 3072->{width}x{depth} + GroupSum(10, tau=100), batch {batch}, fwd+bwd",
+                   "l2": f"every activation is {row / 1e9:.2f} GB (> 126 MB L2)"},
         "gpu_launches": int(launches) * steps,
         "roofline": {"bound": "hbm", "kernel": top.get("kernel"), "achieved": top.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
                      "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": None,
                      "step_frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "kernels": kernels,
-                     "note": "whole step 39.9 GB algorithmic; per kernel: gathered rows counted once per use (12 B in + 4 B out per neuron "
-                             "and sample in the forward)"},
+                     "note": f"whole step {alg / 1e9:.1f} GB algorithmic; per kernel: gathered rows counted once per use (12 B in + 4 B out per "
+                             "neuron and sample in the forward)"},
         "clocks": clocks}
     # one 256000 -> 256000 layer, ours and (when built) the reference's CUDA kernels, same tensors
-    if world == 1:
+    if world == 1 and width == 256000 and depth > 1:
         lay = net[1]
         xf = torch.rand(256000, 1024, device=dev)
         gyf = torch.randn(256000, 1024, device=dev)
@@ -856,6 +860,8 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--images", type=int, default=1 << 20, help="c4: total images")
     ap.add_argument("--chunk", type=int, default=8192, help="c4: images per streamed chunk")
+    ap.add_argument("--flat-width", type=int, default=256000, help="c5: neurons per layer (smaller values: profiling cases)")
+    ap.add_argument("--flat-layers", type=int, default=8, help="c5: number of LogicLayers")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images per step of the CPU port")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--tapgrad-slice-mb", type=int, default=None,

@@ -672,6 +672,166 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     if (lane < 28) partial[((size_t)part * s.C + c) * 28 + lane] = v[0];
 }
 
+// ======================================================================= gate gradient alone, 32x32 images
+// The first block of a stack needs no input gradient.  A block of 128 threads owns one (output channel, batch part)
+// task and walks its images one at a time through a ring of TMA-staged planes (32x32 planes are 4 KB: rows of 160
+// bytes suit the copy engine); a thread owns two pooled windows of the image, recomputes the gate chain at the saved
+// arg-max and keeps the 28 basis sums in registers for ALL its images: one block reduction at the very end instead of
+// one per (image group, channel).
+struct BwdW32 {
+    static constexpr int S = 32, P = 40, R = 34, WP = 16, I = 256, WPT = 2;
+    static constexpr int IMG = R * P, SLOT = (IMG + 31) / 32 * 32, STAGE_BYTES = 2 * SLOT * 4, STAGES = 3;
+    static constexpr int SMEM = STAGES * STAGE_BYTES;
+};
+
+template <int ST> __device__ __forceinline__ void bww_window(uint32_t base, const uint32_t (&toff)[8], const Gate<float> (&g)[7], float d, float (&acc)[28])
+{
+    constexpr int B = ST * BwdW32::STAGE_BYTES;
+    float a[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = lds_f32<B>(base + toff[k]);
+    const float g0 = gate_eval<float>(g[0], a[0], a[1]), g1 = gate_eval<float>(g[1], a[2], a[3]);
+    const float g2 = gate_eval<float>(g[2], a[4], a[5]), g3 = gate_eval<float>(g[3], a[6], a[7]);
+    const float t0 = gate_eval<float>(g[4], g0, g1), t1 = gate_eval<float>(g[5], g2, g3);
+    const float dt0 = d * gate_da<float>(g[6], t1), dt1 = d * gate_db<float>(g[6], t0);
+    float dg[4];
+    dg[0] = dt0 * gate_da<float>(g[4], g1), dg[1] = dt0 * gate_db<float>(g[4], g0);
+    dg[2] = dt1 * gate_da<float>(g[5], g3), dg[3] = dt1 * gate_db<float>(g[5], g2);
+    acc[24] = fmaf(d, t0 * t1, acc[24]), acc[25] = fmaf(d, t0, acc[25]), acc[26] = fmaf(d, t1, acc[26]), acc[27] += d;
+    acc[16] = fmaf(dt0, g0 * g1, acc[16]), acc[17] = fmaf(dt0, g0, acc[17]), acc[18] = fmaf(dt0, g1, acc[18]), acc[19] += dt0;
+    acc[20] = fmaf(dt1, g2 * g3, acc[20]), acc[21] = fmaf(dt1, g2, acc[21]), acc[22] = fmaf(dt1, g3, acc[22]), acc[23] += dt1;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        acc[4 * p] = fmaf(dg[p], a[2 * p] * a[2 * p + 1], acc[4 * p]);
+        acc[4 * p + 1] = fmaf(dg[p], a[2 * p], acc[4 * p + 1]);
+        acc[4 * p + 2] = fmaf(dg[p], a[2 * p + 1], acc[4 * p + 2]);
+        acc[4 * p + 3] += dg[p];
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) convtree_bwd_w_plane32_kernel(const __grid_constant__ CUtensorMap xmap, const float *__restrict__ gy,
+                                                                          const float *__restrict__ w, const int32_t *__restrict__ sel,
+                                                                          const uint8_t *__restrict__ amax, float *__restrict__ partial, Args s)
+{
+    using Cf = BwdW32;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full[Cf::STAGES];
+    __shared__ Gate<float> sg[7];
+    __shared__ SlotInfo si;
+    __shared__ float red[4][28];
+    __shared__ int sabort;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = blockIdx.x % s.C, part = blockIdx.x / s.C;
+    if (tid < 7) sg[tid] = gate_load<float>(w + ((size_t)c * 7 + tid) * 16, s.wmode);
+    if (tid == 32) fill_slots(si, sel, c, s.Ci);
+    if (tid == 64) {
+        for (int st = 0; st < Cf::STAGES; ++st) clb_tma::mbar_init(&full[st], 1);
+        clb_tma::mbar_init_fence();
+        sabort = *reinterpret_cast<volatile int *>(&g_plane_error);
+    }
+    __syncthreads();
+    if (sabort) return;
+    Gate<float> g[7];
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g[i] = sg[i];
+    float acc[28];
+#pragma unroll
+    for (int i = 0; i < 28; ++i) acc[i] = 0.f;
+    const int n_lo = (int)((long long)s.N * part / s.parts), n_hi = (int)((long long)s.N * (part + 1) / s.parts);
+    const bool usable = si.nslot <= 2; // the host only routes selections here that fit two planes
+
+    int win[Cf::WPT];
+    uint32_t woff[Cf::WPT];
+#pragma unroll
+    for (int j = 0; j < Cf::WPT; ++j) {
+        win[j] = tid + kThreads * j;
+        const int py = win[j] / Cf::WP, px = win[j] - py * Cf::WP;
+        woff[j] = clb_tma::smem_addr(smem_raw) + 4u * (uint32_t)(2 * py * Cf::P + 2 * px);
+    }
+    uint32_t toff[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int word = sel[c * 8 + k];
+        toff[k] = 4u * (uint32_t)(si.slot[k] * Cf::SLOT + ((word >> 8) & 0xFF) * Cf::P + (word & 0xFF) + kLead - 1);
+    }
+    const int ch_a = si.ch[0], ch_b = si.ch[1];
+    const int iters = usable ? n_hi - n_lo : 0;
+    constexpr uint32_t tx_bytes = 2u * (uint32_t)(Cf::IMG * 4);
+    auto issue = [&](int it) {
+        const int st = it % Cf::STAGES;
+        unsigned char *dst = smem_raw + (size_t)st * Cf::STAGE_BYTES;
+        clb_tma::mbar_expect_tx(&full[st], tx_bytes);
+        clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n_lo + it, &full[st]);
+        clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n_lo + it, &full[st]);
+    };
+    if (tid == 0)
+        for (int it = 0; it < Cf::STAGES && it < iters; ++it) issue(it);
+
+    float dz_next[Cf::WPT];
+    int bd_next[Cf::WPT];
+    auto fetch = [&](int it) {
+#pragma unroll
+        for (int j = 0; j < Cf::WPT; ++j) {
+            const bool live = it < iters;
+            const size_t o = ((size_t)(n_lo + it) * s.C + c) * Cf::I + win[j];
+            dz_next[j] = live ? __ldg(gy + o) : 0.f;
+            bd_next[j] = live ? (int)__ldg(amax + o) : 0;
+        }
+    };
+    fetch(0);
+    bool failed = false;
+    int it = 0;
+    while (it < iters && !failed) {
+        const uint32_t parity = (it / Cf::STAGES) & 1;
+#define CLB_BWW_STAGE(ST)                                                                                                 \
+    if (it < iters && !failed) {                                                                                          \
+        float dz[Cf::WPT];                                                                                                \
+        int bd[Cf::WPT];                                                                                                  \
+        _Pragma("unroll") for (int j = 0; j < Cf::WPT; ++j) dz[j] = dz_next[j], bd[j] = bd_next[j];                        \
+        fetch(it + 1);                                                                                                    \
+        bool ok = clb_tma::mbar_wait(&full[ST], parity);                                                                  \
+        if (ok) {                                                                                                         \
+            _Pragma("unroll") for (int j = 0; j < Cf::WPT; ++j)                                                            \
+                bww_window<ST>(woff[j] + 4u * (uint32_t)(((bd[j] >> 1) ? Cf::P : 0) + (bd[j] & 1)), toff, g, dz[j], acc);  \
+        }                                                                                                                 \
+        ok = __syncthreads_and(ok ? 1 : 0) != 0; /* the stage has been read by the whole block */                        \
+        if (!ok) {                                                                                                        \
+            failed = true;                                                                                                \
+        } else {                                                                                                          \
+            if (tid == 0 && it + Cf::STAGES < iters) issue(it + Cf::STAGES);                                              \
+            ++it;                                                                                                         \
+        }                                                                                                                 \
+    }
+        CLB_BWW_STAGE(0)
+        CLB_BWW_STAGE(1)
+        CLB_BWW_STAGE(2)
+#undef CLB_BWW_STAGE
+    }
+    if (failed && tid == 0) {
+        g_plane_error = 1;
+        for (int j = it + 1; j < iters && j < it + Cf::STAGES; ++j) clb_tma::mbar_wait(&full[j % Cf::STAGES], (j / Cf::STAGES) & 1);
+    }
+    if (!usable && tid == 0) g_plane_error = 2;
+
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = i < 28 ? acc[i] : 0.f;
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    if (lane < 28) red[warp][lane] = v[0];
+    __syncthreads();
+    if (tid < 28) partial[((size_t)part * s.C + c) * 28 + tid] = (red[0][tid] + red[1][tid]) + (red[2][tid] + red[3][tid]);
+}
+
 // Pass 2: gx[n][ch] = sum of the gradient planes (c, slot) that belong to input channel ch, in list order.
 // `start` [Ci + 1], `entry` [..] = 2*c + slot.  One float4 per thread; grid-stride over N * Ci * HW / 4.
 __global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict__ planes, const int32_t *__restrict__ start,
@@ -732,7 +892,7 @@ int plane_side(int N, int Ci, int H, int W, int C, int sh, int sw, int ph, int p
 {
     if (sh != 1 || sw != 1 || ph != 1 || pw != 1 || kh != 3 || kw != 3 || H != W || N <= 0 || C <= 0 || C > 65535 || Ci > 65535) return 0;
     if (tune_get(CLB_TUNE_PLANE_KERNELS) == 0 || clb_tma::encode_tiled_fn() == nullptr) return 0;
-    return (H == 16 || H == 8 || H == 4) ? H : 0;
+    return (H == 32 || H == 16 || H == 8 || H == 4) ? H : 0; // 32: the gate gradient alone (clb_convtree_bwd_plane without gx)
 }
 
 // Parts of the batch per output channel: enough (channel, part) tasks for about three waves of resident groups, but
@@ -780,7 +940,11 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     return CLB_OK;
 }
 
-int bwd_parts_for(int side, int N, int C) { return side == 16 ? bwd_parts<16>(N, C) : side == 8 ? bwd_parts<8>(N, C) : bwd_parts<4>(N, C); }
+int bwd_parts_for(int side, int N, int C)
+{
+    if (side == 32) return plane_parts(N, C, 1, 5);
+    return side == 16 ? bwd_parts<16>(N, C) : side == 8 ? bwd_parts<8>(N, C) : bwd_parts<4>(N, C);
+}
 
 } // namespace
 
@@ -844,6 +1008,7 @@ extern "C" size_t clb_convtree_bwd_plane_scratch_bytes(int N, int Ci, int H, int
     const int side = plane_side(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw);
     if (!side) return 0;
     const size_t partial = ((size_t)bwd_parts_for(side, N, C) * C * 28 * sizeof(float) + 255) / 256 * 256;
+    if (side == 32) return partial; // gate gradient alone: no gradient planes
     return partial + (size_t)N * C * 2 * H * W * sizeof(float);
 }
 
@@ -851,10 +1016,29 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
                                       const int32_t *ch_start, const int32_t *ch_entry, void *scratch, size_t scratch_bytes, int N, int Ci, int H,
                                       int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
 {
-    if (!gy || !x || !w || !sel || !amax || !gx || !ch_start || !ch_entry || !scratch || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (!gy || !x || !w || !sel || !amax || (!gx && !gw) || !scratch || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
+    if (gx && (!ch_start || !ch_entry)) return CLB_ERR_ARG;
     if (dtype != CLB_F32 || !conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_SHAPE;
     const int side = plane_side(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw);
-    if (!side) return CLB_ERR_SHAPE;
+    if (!side || (side == 32) != (gx == nullptr)) return CLB_ERR_SHAPE; // 32x32: gate gradient alone; smaller: both gradients
+    if (side == 32) {
+        const int parts32 = bwd_parts_for(32, N, C);
+        if (scratch_bytes < (size_t)parts32 * C * 28 * sizeof(float) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return CLB_ERR_SCRATCH;
+        CUtensorMap map32;
+        if (!clb_tma::make_plane_map(&map32, (const float *)x, N, Ci, 32, 32, BwdW32::P, BwdW32::R, 1)) return CLB_ERR_SHAPE;
+        auto k32 = convtree_bwd_w_plane32_kernel;
+        if (cudaFuncSetAttribute(k32, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdW32::SMEM) != cudaSuccess) return check_launch(0);
+        cudaStream_t st32 = (cudaStream_t)stream;
+        const Args a32{N, Ci, C, wmode, parts32};
+        CLB_TRACED("convtree_bwd_w_plane32_kernel", st32,
+                   k32<<<(unsigned)((long long)C * parts32), kThreads, BwdW32::SMEM, st32>>>(map32, (const float *)gy, (const float *)w, sel, amax,
+                                                                                           (float *)scratch, a32));
+        const long long ngates32 = (long long)C * 7;
+        CLB_TRACED("plane_gate_finalize_kernel", st32,
+                   plane_gate_finalize_kernel<<<(int)((ngates32 + 127) / 128), 128, 0, st32>>>((const float *)scratch, (const float *)w, (float *)gw,
+                                                                                              parts32, ngates32, wmode));
+        return check_launch(2);
+    }
     const size_t need = clb_convtree_bwd_plane_scratch_bytes(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, dtype);
     if (scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 15) || (reinterpret_cast<uintptr_t>(gx) & 15)) return CLB_ERR_SCRATCH;
     cudaStream_t st = (cudaStream_t)stream;

@@ -666,28 +666,29 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
                 const int o1[8] = {o1a.x, o1a.y, o1a.z, o1a.w, o1b.x, o1b.y, o1b.z, o1b.w};
                 const int op[7] = {opa.x, opa.y, opa.z, opa.w, opb.x, opb.y, opb.z};
                 unsigned acc[4] = {0u, 0u, 0u, 0u};
-                // the taps of the next gate are fetched before the current gate's switch so that the
-                // shared-memory latency runs under it
-                unsigned g[2][4][8], b[2][4][8];
-                lds_pair(g[0][0], t0 + o0[0], t0 + o1[0]);
-                lds_pair(b[0][0], t0 + o0[1], t0 + o1[1]);
-#pragma unroll
+                // The two conv rows of the window run through ONE copy of the code (the loop is not unrolled): the seven
+                // 16-way gate switches are about 150 instructions each, and with fourteen of them the kernel did not fit
+                // the instruction cache (stall reason "no instruction").  Inside a row the taps of the next gate are
+                // fetched before the current gate's switch, so that the shared-memory latency runs under it.
+#pragma unroll 1
                 for (int dy = 0; dy < 2; ++dy) {
+                    const unsigned tn = t0 + dy * RS * 16;
+                    unsigned g[4][8], b[4][8];
+                    lds_pair(g[0], tn + o0[0], tn + o1[0]);
+                    lds_pair(b[0], tn + o0[1], tn + o1[1]);
 #pragma unroll
                     for (int p = 0; p < 4; ++p) {
-                        const int pn = (p + 1) & 3, dn = p == 3 ? dy + 1 : dy;
-                        if (dn < 2) {
-                            const unsigned tn = t0 + dn * RS * 16;
-                            lds_pair(g[dn][pn], tn + o0[2 * pn], tn + o1[2 * pn]);
-                            lds_pair(b[dn][pn], tn + o0[2 * pn + 1], tn + o1[2 * pn + 1]);
+                        if (p < 3) {
+                            lds_pair(g[p + 1], tn + o0[2 * p + 2], tn + o1[2 * p + 2]);
+                            lds_pair(b[p + 1], tn + o0[2 * p + 3], tn + o1[2 * p + 3]);
                         }
-                        gate_words<8>(op[p], g[dy][p], b[dy][p]);
+                        gate_words<8>(op[p], g[p], b[p]);
                     }
-                    gate_words<8>(op[4], g[dy][0], g[dy][1]);
-                    gate_words<8>(op[5], g[dy][2], g[dy][3]);
-                    gate_words<8>(op[6], g[dy][0], g[dy][2]);
+                    gate_words<8>(op[4], g[0], g[1]);
+                    gate_words<8>(op[5], g[2], g[3]);
+                    gate_words<8>(op[6], g[0], g[2]);
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) acc[w] |= g[dy][0][w] | g[dy][0][w + 4];
+                    for (int w = 0; w < 4; ++w) acc[w] |= g[0][w] | g[0][w + 4];
                 }
                 out = make_uint4(acc[0], acc[1], acc[2], acc[3]);
             } else {

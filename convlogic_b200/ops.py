@@ -175,12 +175,13 @@ def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
     if n == 0 or c == 0:  # empty batch: the gate gradient is an empty sum
         return gx, (gw.zero_() if gw is not None else None)
     flag = _sel_flag(sel, geom, ci)
-    if need_gx and not flag and x.dtype == torch.float32 and amax is not None:
-        # many-channel layers: the plane kernels (two channel planes per output channel streamed through shared memory)
+    if not flag and x.dtype == torch.float32 and amax is not None:
+        # The plane kernels (two channel planes per output channel streamed through shared memory): both gradients of the
+        # many-channel layers (16x16 .. 4x4 images), the gate gradient alone of a 32x32 first block.
         nbytes = lib().clb_convtree_bwd_plane_scratch_bytes(n, ci, h, wd, c, *geom, dtype_code(x))
         lists = plane_lists(sel, ci, geom) if nbytes else None
         if lists is not None:
-            scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
             rc = lib().clb_convtree_bwd_plane(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(gw), ptr(lists[0]), ptr(lists[1]),
                                               ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream())
             if rc != _lib.ERR_SHAPE:

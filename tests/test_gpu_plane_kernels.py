@@ -137,3 +137,30 @@ def test_selection_with_one_channel_and_with_many_channels():
         assert_close(gx, gxo, 1e-5)
         assert_close(gw, gwo, 1e-5)
     assert _plane_error() == 0
+
+
+@pytest.mark.parametrize("n,ci,c", [(20, 9, 24), (3, 3, 5), (67, 9, 8)])
+def test_gate_gradient_alone_of_a_32x32_block(n, ci, c):
+    """A first block (32x32 images) whose input needs no gradient: the gate gradient on the plane kernel against the CPU
+    oracle at the kernels' own pooled positions, against the combined tiled kernel, and bit-identical when repeated."""
+    from convlogic_b200 import _lib, ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy = _case((n, ci, c, 32), 7)
+    x = (x < 0.5).float()
+    xd, wd, sd, gd = x.cuda(), logits.cuda(), sel.cuda(), gy.cuda()
+    _, amax, _, _, idx = ops.convtree_fwd(xd, wd, sd, GEOM, W_SOFTMAX, want_indices=True)
+    _lib.trace(True)
+    none, gw = ops.convtree_bwd(gd, xd, wd, sd, amax, GEOM, W_SOFTMAX, need_gx=False)
+    torch.cuda.synchronize()
+    rep = _lib.trace_report()
+    _lib.trace(False)
+    assert none is None and "convtree_bwd_w_plane32_kernel" in rep, rep
+    assert _plane_error() == 0
+    assert torch.equal(gw, ops.convtree_bwd(gd, xd, wd, sd, amax, GEOM, W_SOFTMAX, need_gx=False)[1])
+    _, gw_both = ops.convtree_bwd(gd, xd, wd, sd, amax, GEOM, W_SOFTMAX)   # the tiled kernel that also gives gx
+    assert_close(gw, gw_both, 2e-5, "gw vs combined kernel")
+    wo = logits.clone().requires_grad_(True)
+    yf = oracle.full_convlogic(x, oracle.gate_probabilities(wo, True), sel, forced_idx=idx.cpu())[0]
+    (gwo,) = torch.autograd.grad((yf * gy).sum(), (wo,))
+    assert_close(gw, gwo, 1e-5, "gw vs oracle")
