@@ -484,36 +484,34 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// a[w] = gate(a[w], b[w]) for N words, in place so that every case leaves its result in the registers the
-// operand came in; `op` is uniform over the block, so the switch does not diverge
+// a[w] = gate(a[w], b[w]) for N words; `op` is uniform over the block, so the switch does not diverge.  Every case is
+// ONE lop3 per word written IN PLACE (the "+r" constraint): with plain C expressions the sixteen cases of a switch end
+// in different registers and the compiler reconciles them with moves at the join -- more moves than logic operations.
+// Truth-table immediates for (A, B) = (0xF0, 0xCC); the third operand is unused (every table is symmetric in it).
 template <int N>
 __device__ __forceinline__ void gate_words(int op, unsigned (&a)[N], const unsigned (&b)[N])
 {
-#define CLB_GATE_CASE(i, expr)                                                                                                   \
+#define CLB_GATE_CASE(i, lut)                                                                                                    \
     case i:                                                                                                                      \
-        _Pragma("unroll") for (int w = 0; w < N; ++w)                                                                            \
-        {                                                                                                                        \
-            const unsigned A = a[w], B = b[w];                                                                                   \
-            a[w] = (expr);                                                                                                       \
-        }                                                                                                                        \
+        _Pragma("unroll") for (int w = 0; w < N; ++w) asm("lop3.b32 %0, %0, %1, %1, " #lut ";" : "+r"(a[w]) : "r"(b[w]));        \
         break;
     switch (op & 15) {
-        CLB_GATE_CASE(0, (A & 0u) & B)
-        CLB_GATE_CASE(1, A & B)
-        CLB_GATE_CASE(2, A & ~B)
-        CLB_GATE_CASE(3, A | (B & 0u))
-        CLB_GATE_CASE(4, ~A & B)
-        CLB_GATE_CASE(5, B | (A & 0u))
-        CLB_GATE_CASE(6, A ^ B)
-        CLB_GATE_CASE(7, A | B)
-        CLB_GATE_CASE(8, ~(A | B))
-        CLB_GATE_CASE(9, ~(A ^ B))
-        CLB_GATE_CASE(10, ~B | (A & 0u))
-        CLB_GATE_CASE(11, A | ~B)
-        CLB_GATE_CASE(12, ~A | (B & 0u))
-        CLB_GATE_CASE(13, ~A | B)
-        CLB_GATE_CASE(14, ~(A & B))
-        CLB_GATE_CASE(15, ~(A & 0u) | B)
+        CLB_GATE_CASE(0, 0x00)  // 0
+        CLB_GATE_CASE(1, 0xC0)  // A & B
+        CLB_GATE_CASE(2, 0x30)  // A & ~B
+        CLB_GATE_CASE(3, 0xF0)  // A
+        CLB_GATE_CASE(4, 0x0C)  // ~A & B
+        CLB_GATE_CASE(5, 0xCC)  // B
+        CLB_GATE_CASE(6, 0x3C)  // A ^ B
+        CLB_GATE_CASE(7, 0xFC)  // A | B
+        CLB_GATE_CASE(8, 0x03)  // ~(A | B)
+        CLB_GATE_CASE(9, 0xC3)  // ~(A ^ B)
+        CLB_GATE_CASE(10, 0x33) // ~B
+        CLB_GATE_CASE(11, 0xF3) // A | ~B
+        CLB_GATE_CASE(12, 0x0F) // ~A
+        CLB_GATE_CASE(13, 0xCF) // ~A | B
+        CLB_GATE_CASE(14, 0x3F) // ~(A & B)
+        CLB_GATE_CASE(15, 0xFF) // 1
     }
 #undef CLB_GATE_CASE
 }
