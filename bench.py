@@ -225,6 +225,7 @@ def c3_algorithmic_bytes(batch):
         "plane_sum_kernel": y1 + y2 + y3,                                           # the input gradients
         "convtree_bwd_w_win_kernel<tapgrad>": (y2 + y1) + (y3 + y2) + (y4 + y3),   # upstream gradient + input
         "convtree_bwd_x_scatter_kernel": y1 + y2 + y3,                              # the input gradients
+        "adam_step_kernel": 7 * 4 * 10694656 // batch,   # p, g, m, v read; p, m, v written (per step, not per image)
         "logic_tree_fwd_kernel": fin + fout,
         "logic_tree_bwd_kernel": fout + fin,
         "row_segment_sum_kernel": fin,
@@ -252,8 +253,13 @@ def run_c3(ctx, args, with_cpu=True):
 
     dev, world, rank = ctx.dev, ctx.world, ctx.rank
     net = cb.fuse_logic_layers(build_c3(dev)).train()   # the three flat layers run as one gate tree per output neuron
-    bucket = dp.GradBucket(net).overlap(average=True)
-    opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
+    if args.torch_tail:   # torch's cross-entropy, gradient accumulation and fused Adam behind the library's layers
+        bucket = dp.GradBucket(net).overlap(average=True)
+        opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
+    else:                 # the library's own tail: GroupSum + cross-entropy kernel, gradients written into the bucket, flat Adam
+        body, head = net[:-1], cb.GroupSumCrossEntropy(net[-1].k, net[-1].tau)
+        bucket = dp.GradBucket(net).direct().overlap(average=True)
+        opt = cb.FlatAdam(bucket, lr=0.01)
     sets = 4
     gi = torch.Generator().manual_seed(100 + rank)
     bits_h = [(torch.rand(C3_BATCH, 9, 32, 32, generator=gi) < 0.5).to(torch.uint8).pin_memory() for _ in range(sets)]
@@ -262,8 +268,11 @@ def run_c3(ctx, args, with_cpu=True):
     loss_host = torch.zeros(1).pin_memory()
 
     def train_step(x, lab):
-        bucket.zero()
-        loss = torch.nn.functional.cross_entropy(net(x), lab)
+        if args.torch_tail:
+            bucket.zero()
+            loss = torch.nn.functional.cross_entropy(net(x), lab)
+        else:
+            loss = head(body(x), lab)
         loss.backward()
         bucket.finish()
         opt.step()
@@ -868,6 +877,9 @@ def main():
                     help="override the library's slice size of the two-pass conv backward (0 = whole batch in one slice)")
     ap.add_argument("--plane-kernels", type=int, default=None, choices=[0, 1],
                     help="override the library's choice of the TMA-staged many-channel conv kernels (0 = the older staged kernels)")
+    ap.add_argument("--torch-tail", action="store_true",
+                    help="c3: torch's cross-entropy, .grad accumulation and fused Adam instead of the library's fused tail")
+    ap.add_argument("--slab-mux", type=int, default=None, choices=[0, 1], help="override how the packed slab kernel applies gates")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -882,6 +894,10 @@ def main():
         from convlogic_b200 import _lib
 
         _lib.check(_lib.lib().clb_tune(_lib.TUNE_PLANE_KERNELS, args.plane_kernels))
+    if args.slab_mux is not None:
+        from convlogic_b200 import _lib
+
+        _lib.check(_lib.lib().clb_tune(_lib.TUNE_SLAB_MUX, args.slab_mux))
     if args.workload == "all":
         rec = run_c3(ctx, args)
         rec["packed_inference"] = run_c4(ctx, args)

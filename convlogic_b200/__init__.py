@@ -6,7 +6,15 @@ Public names mirror the reference packages ``convlogic`` and ``difflogic``
 
 from .convlogic_layer import ConvLogicLayer, PoolLogicLayer  # noqa: F401
 from .treelogic_layer import TreeLogicLayer  # noqa: F401
-from .difflogic import FusedLogicLayers, GroupSum, LogicLayer, fuse_logic_layers, get_unique_connections  # noqa: F401
+from .difflogic import (  # noqa: F401
+    FusedLogicLayers,
+    GroupSum,
+    GroupSumCrossEntropy,
+    LogicLayer,
+    fuse_logic_layers,
+    get_unique_connections,
+)
+from .dp import FlatAdam, GradBucket  # noqa: F401
 from .packbitstensor import PackBitsTensor  # noqa: F401
 from .functional import (  # noqa: F401
     ConvLogicFunction,
@@ -23,4 +31,5 @@ __all__ = [
     "ConvLogicLayer", "PoolLogicLayer", "TreeLogicLayer", "LogicLayer", "GroupSum", "PackBitsTensor",
     "ConvLogicFunction", "FullConvLogicFunction", "TreeLogicFunction", "LogicLayerCudaFunction", "GradFactor",
     "ConvLogicCifarModel", "ConvLogicMnistModel", "get_unique_connections", "CompiledLogicNet", "FusedLogicLayers", "fuse_logic_layers",
+    "GroupSumCrossEntropy", "FlatAdam", "GradBucket",
 ]

@@ -17,6 +17,7 @@ W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
 SEL_UNBOUNDED = 0x100
 TUNE_TAPGRAD_SLICE_BYTES = 1
 TUNE_PLANE_KERNELS = 2
+TUNE_SLAB_MUX = 3
 ERR_SHAPE, ERR_ODD_OUTPUT, ERR_TOO_LARGE = -2, -5, -6
 
 _lib = None
@@ -70,6 +71,9 @@ _SIGNATURES = {
     "clb_logic_tree_bwd": ([_vp] * 14 + [_i64, _i64, _i64, _i, _vp], _i),
     "clb_group_sum_scratch_bytes": ([_i64, _i64, _i, _i], _sz),
     "clb_group_sum_fwd": ([_vp, _vp, _vp, _sz, _i64, _i64, _i, C.c_double, _i, _vp], _i),
+    "clb_group_sum_ce": ([_vp] * 6 + [_sz, _i64, _i64, _i, C.c_double, _vp], _i),
+    "clb_adam_step": ([_vp] * 4 + [_i64] + [C.c_double] * 5 + [_i64, _i, _vp], _i),
+    "clb_group_sum_bwd_scaled": ([_vp, _vp, _vp, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_group_sum_bwd": ([_vp, _vp, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_net_device_bytes": ([_vp, _sz, _vp], _i),
     "clb_net_create": ([_vp, _sz, _vp, _vp, _vp], _i),

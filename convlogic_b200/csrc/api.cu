@@ -60,6 +60,7 @@ void trace_end(int slot, cudaStream_t st)
 namespace {
 std::atomic<long long> g_tapgrad_slice_bytes{0};
 std::atomic<long long> g_plane_kernels{1};
+std::atomic<long long> g_slab_mux{0};
 std::atomic<int> g_sm_count[64];
 } // namespace
 
@@ -68,6 +69,7 @@ long long tune_get(int key)
 {
     if (key == CLB_TUNE_TAPGRAD_SLICE_BYTES) return g_tapgrad_slice_bytes.load(std::memory_order_relaxed);
     if (key == CLB_TUNE_PLANE_KERNELS) return g_plane_kernels.load(std::memory_order_relaxed);
+    if (key == CLB_TUNE_SLAB_MUX) return g_slab_mux.load(std::memory_order_relaxed);
     return -1;
 }
 int sm_count()
@@ -93,6 +95,10 @@ extern "C" int clb_tune(int key, long long value)
 {
     if (key == CLB_TUNE_TAPGRAD_SLICE_BYTES && value >= 0) {
         g_tapgrad_slice_bytes.store(value, std::memory_order_relaxed);
+        return CLB_OK;
+    }
+    if (key == CLB_TUNE_SLAB_MUX && (value == 0 || value == 1)) {
+        g_slab_mux.store(value, std::memory_order_relaxed);
         return CLB_OK;
     }
     if (key == CLB_TUNE_PLANE_KERNELS && (value == 0 || value == 1)) {

@@ -14,6 +14,8 @@
 // first-input derivative twice in that case; its CPU path gives the sum used here).
 #include "clb_common.cuh"
 
+#include <cmath>
+
 namespace clb {
 
 // Each half-warp reduces the 16 values of one neuron: the lane handles value (lane & 15) of neuron
@@ -341,13 +343,86 @@ __global__ void group_sum_finalize_kernel(const T *__restrict__ partial, T *__re
     out[b * k + c] = t / tau;
 }
 
+// GroupSum + cross-entropy in one finish (src/convlogic/model.py:137-152: CrossEntropyLoss on the GroupSum scores):
+// scores[b][c] = (sum of the parts) / tau, loss = mean_b (logsumexp(scores[b]) - scores[b][label_b]), and
+// dscore[b][c] = (softmax(scores[b])[c] - [c == label_b]) / B, the gradient of the mean loss w.r.t. the scores.
+// ONE block: a thread owns samples b = tid, tid + 256, ...; the per-sample losses are added in a fixed tree.  k <= 32.
+__global__ void __launch_bounds__(256) group_sum_ce_finalize_kernel(const float *__restrict__ partial, const int64_t *__restrict__ labels,
+                                                                    float *__restrict__ scores, float *__restrict__ dscore,
+                                                                    float *__restrict__ loss, long long B, int k, int parts, float tau)
+{
+    __shared__ float red[256];
+    float mine = 0.f;
+    for (long long b = threadIdx.x; b < B; b += 256) {
+        float sc[32];
+        float mx = -3.0e38f;
+#pragma unroll 1
+        for (int c = 0; c < k; ++c) {
+            float t = 0.f;
+            for (int p = 0; p < parts; ++p) t += partial[((long long)p * k + c) * B + b];
+            sc[c] = t / tau;
+            mx = fmaxf(mx, sc[c]);
+        }
+        float sum = 0.f;
+        for (int c = 0; c < k; ++c) sum += expf(sc[c] - mx);
+        const float lse = mx + logf(sum);
+        const int lab = (int)labels[b];
+        const float inv = 1.f / sum, invB = 1.f / (float)B;
+        for (int c = 0; c < k; ++c) {
+            const float pr = expf(sc[c] - mx) * inv;
+            if (scores != nullptr) scores[b * k + c] = sc[c];
+            dscore[b * k + c] = (pr - (c == lab ? 1.f : 0.f)) * invB;
+        }
+        mine += lse - ((lab >= 0 && lab < k) ? sc[lab] : 0.f);
+    }
+    red[threadIdx.x] = mine;
+    __syncthreads();
+    for (int half = 128; half >= 1; half >>= 1) {
+        if ((int)threadIdx.x < half) red[threadIdx.x] += red[threadIdx.x + half];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *loss = red[0] / (float)B;
+}
+
+// Adam / AdamW over one flat parameter buffer (src/convlogic/model.py:179-180 uses torch.optim.AdamW): one thread per
+// four elements, 128-bit accesses.  step_size = lr / (1 - beta1^t), bc2_sqrt = sqrt(1 - beta2^t).
+__global__ void __launch_bounds__(256) adam_step_kernel(float *__restrict__ p, const float *__restrict__ g, float *__restrict__ m,
+                                                        float *__restrict__ v, long long n, float lr, float beta1, float beta2, float eps,
+                                                        float weight_decay, float step_size, float bc2_sqrt, int decoupled)
+{
+    auto one = [&](float &pp, float gg, float &mm, float &vv) {
+        if (weight_decay != 0.f) {
+            if (decoupled)
+                pp *= 1.f - lr * weight_decay;
+            else
+                gg = fmaf(weight_decay, pp, gg);
+        }
+        mm = fmaf(1.f - beta1, gg - mm, mm);           // exp_avg.lerp_(grad, 1 - beta1)
+        vv = fmaf(1.f - beta2, gg * gg, beta2 * vv);   // exp_avg_sq.mul_(beta2).addcmul_(grad, grad, 1 - beta2)
+        const float denom = sqrtf(vv) / bc2_sqrt + eps;
+        pp -= step_size * (mm / denom);
+    };
+    const long long n4 = n >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        float4 pp = reinterpret_cast<float4 *>(p)[i], mm = reinterpret_cast<float4 *>(m)[i], vv = reinterpret_cast<float4 *>(v)[i];
+        const float4 gg = reinterpret_cast<const float4 *>(g)[i];
+        one(pp.x, gg.x, mm.x, vv.x), one(pp.y, gg.y, mm.y, vv.y), one(pp.z, gg.z, mm.z, vv.z), one(pp.w, gg.w, mm.w, vv.w);
+        reinterpret_cast<float4 *>(p)[i] = pp, reinterpret_cast<float4 *>(m)[i] = mm, reinterpret_cast<float4 *>(v)[i] = vv;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+        const long long i = (n4 << 2) + threadIdx.x;
+        one(p[i], g[i], m[i], v[i]);
+    }
+}
+
 // gy[f][b] = gout[b][f / S] / tau.  grid (row chunks, k): a thread keeps the quotients of its batch positions
 // in registers and writes them to every row of its chunk (coalesced along the batch).
 template <typename T>
-__global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict__ gout, T *__restrict__ gy, long long S, long long B, int k,
-                                                            T tau)
+__global__ void __launch_bounds__(256) group_sum_bwd_kernel(const T *__restrict__ gout, const T *__restrict__ scale, T *__restrict__ gy,
+                                                            long long S, long long B, int k, T tau)
 {
     const int c = blockIdx.y;
+    if (scale != nullptr) tau = tau / scale[0]; // an upstream scalar gradient, read on the device
     const long long r0 = S * blockIdx.x / gridDim.x, r1 = S * (blockIdx.x + 1) / gridDim.x;
     for (long long b0 = 0; b0 < B; b0 += 4 * 256) {
         T v[4];
@@ -672,7 +747,50 @@ extern "C" int clb_group_sum_fwd(const void *y, void *out, void *scratch, size_t
     return check_launch(2);
 }
 
+extern "C" int clb_group_sum_ce(const float *y, const int64_t *labels, float *scores, float *dscore, float *loss, void *scratch,
+                                size_t scratch_bytes, int64_t F, int64_t B, int k, double tau, void *stream)
+{
+    if (!y || !labels || !dscore || !loss || F <= 0 || B <= 0 || k <= 0 || tau == 0.0) return CLB_ERR_ARG;
+    if (F % k || k > 32) return CLB_ERR_SHAPE;
+    if (!scratch || scratch_bytes < clb_group_sum_scratch_bytes(F, B, k, CLB_F32)) return CLB_ERR_SCRATCH;
+    const long long S = F / k;
+    const int parts = group_sum_parts(S);
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)((B + 31) / 32), (unsigned)k, (unsigned)parts);
+    CLB_TRACED("group_sum_partial_kernel", st, group_sum_partial_kernel<float><<<grid, 256, 0, st>>>(y, (float *)scratch, S, B, k));
+    CLB_TRACED("group_sum_ce_finalize_kernel", st,
+               group_sum_ce_finalize_kernel<<<1, 256, 0, st>>>((const float *)scratch, labels, scores, dscore, loss, B, k, parts, (float)tau));
+    return check_launch(2);
+}
+
+extern "C" int clb_adam_step(float *p, const float *g, float *m, float *v, int64_t n, double lr, double beta1, double beta2, double eps,
+                             double weight_decay, int64_t step, int decoupled, void *stream)
+{
+    if (!p || !g || !m || !v || n < 0 || step < 1 || beta1 < 0 || beta1 >= 1 || beta2 < 0 || beta2 >= 1) return CLB_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15)
+        return CLB_ERR_ARG;
+    if (n == 0) return CLB_OK;
+    const double bc1 = 1.0 - std::pow(beta1, (double)step), bc2 = 1.0 - std::pow(beta2, (double)step);
+    cudaStream_t st = (cudaStream_t)stream;
+    long long blocks = ((n >> 2) + 255) / 256;
+    const long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    CLB_TRACED("adam_step_kernel", st,
+               adam_step_kernel<<<(unsigned)blocks, 256, 0, st>>>(p, g, m, v, n, (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay,
+                                                                  (float)(lr / bc1), (float)std::sqrt(bc2), decoupled));
+    return check_launch();
+}
+
+extern "C" int clb_group_sum_bwd_scaled(const void *gout, const void *scale, void *gy, int64_t F, int64_t B, int k, double tau, int dtype,
+                                        void *stream);
 extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t B, int k, double tau, int dtype, void *stream)
+{
+    return clb_group_sum_bwd_scaled(gout, nullptr, gy, F, B, k, tau, dtype, stream);
+}
+
+extern "C" int clb_group_sum_bwd_scaled(const void *gout, const void *scale, void *gy, int64_t F, int64_t B, int k, double tau, int dtype,
+                                        void *stream)
 {
     if (!gout || !gy || F < 0 || B < 0 || k <= 0 || tau == 0.0 || (dtype != CLB_F32 && dtype != CLB_F64)) return CLB_ERR_ARG;
     if (F % k) return CLB_ERR_SHAPE;
@@ -684,9 +802,9 @@ extern "C" int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t 
     if (chunks > S) chunks = S;
     dim3 grid((unsigned)chunks, (unsigned)k);
     if (dtype == CLB_F32)
-        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)gout, (float *)gy, S, B, k, (float)tau));
+        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)gout, (const float *)scale, (float *)gy, S, B, k, (float)tau));
     else
-        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (double *)gy, S, B, k, tau));
+        CLB_TRACED("group_sum_bwd_kernel", st, group_sum_bwd_kernel<double><<<grid, 256, 0, st>>>((const double *)gout, (const double *)scale, (double *)gy, S, B, k, tau));
     return check_launch();
 }
 

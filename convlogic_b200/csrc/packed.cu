@@ -516,6 +516,58 @@ __device__ __forceinline__ void gate_words(int op, unsigned (&a)[N], const unsig
 #undef CLB_GATE_CASE
 }
 
+// The same sixteen cases behind ONE indexed branch (brx.idx over a table of the sixteen case labels) instead of the
+// compare-and-branch tree a C switch compiles to (13 control instructions per gate, more than its 8 lop3).  `op` is uniform
+// over the block, so the branch is declared uniform.  Eight words, in place.
+__device__ __forceinline__ void gate_words_brx(int op, unsigned (&a)[8], const unsigned (&b)[8])
+{
+    asm(
+        "{\n\t.reg .u32 gi;\n\tand.b32 gi, %16, 15;\n\t"
+        "gtab: .branchtargets G0, G1, G2, G3, G4, G5, G6, G7, G8, G9, G10, G11, G12, G13, G14, G15;\n\t"
+        "brx.idx.uni gi, gtab;\n"
+        "G0: lop3.b32 %0, %0, %8, %8, 0x00; lop3.b32 %1, %1, %9, %9, 0x00; lop3.b32 %2, %2, %10, %10, 0x00; lop3.b32 %3, %3, %11, %11, 0x00; lop3.b32 %4, %4, %12, %12, 0x00; lop3.b32 %5, %5, %13, %13, 0x00; lop3.b32 %6, %6, %14, %14, 0x00; lop3.b32 %7, %7, %15, %15, 0x00; bra.uni GDONE;\n"
+        "G1: lop3.b32 %0, %0, %8, %8, 0xC0; lop3.b32 %1, %1, %9, %9, 0xC0; lop3.b32 %2, %2, %10, %10, 0xC0; lop3.b32 %3, %3, %11, %11, 0xC0; lop3.b32 %4, %4, %12, %12, 0xC0; lop3.b32 %5, %5, %13, %13, 0xC0; lop3.b32 %6, %6, %14, %14, 0xC0; lop3.b32 %7, %7, %15, %15, 0xC0; bra.uni GDONE;\n"
+        "G2: lop3.b32 %0, %0, %8, %8, 0x30; lop3.b32 %1, %1, %9, %9, 0x30; lop3.b32 %2, %2, %10, %10, 0x30; lop3.b32 %3, %3, %11, %11, 0x30; lop3.b32 %4, %4, %12, %12, 0x30; lop3.b32 %5, %5, %13, %13, 0x30; lop3.b32 %6, %6, %14, %14, 0x30; lop3.b32 %7, %7, %15, %15, 0x30; bra.uni GDONE;\n"
+        "G3: lop3.b32 %0, %0, %8, %8, 0xF0; lop3.b32 %1, %1, %9, %9, 0xF0; lop3.b32 %2, %2, %10, %10, 0xF0; lop3.b32 %3, %3, %11, %11, 0xF0; lop3.b32 %4, %4, %12, %12, 0xF0; lop3.b32 %5, %5, %13, %13, 0xF0; lop3.b32 %6, %6, %14, %14, 0xF0; lop3.b32 %7, %7, %15, %15, 0xF0; bra.uni GDONE;\n"
+        "G4: lop3.b32 %0, %0, %8, %8, 0x0C; lop3.b32 %1, %1, %9, %9, 0x0C; lop3.b32 %2, %2, %10, %10, 0x0C; lop3.b32 %3, %3, %11, %11, 0x0C; lop3.b32 %4, %4, %12, %12, 0x0C; lop3.b32 %5, %5, %13, %13, 0x0C; lop3.b32 %6, %6, %14, %14, 0x0C; lop3.b32 %7, %7, %15, %15, 0x0C; bra.uni GDONE;\n"
+        "G5: lop3.b32 %0, %0, %8, %8, 0xCC; lop3.b32 %1, %1, %9, %9, 0xCC; lop3.b32 %2, %2, %10, %10, 0xCC; lop3.b32 %3, %3, %11, %11, 0xCC; lop3.b32 %4, %4, %12, %12, 0xCC; lop3.b32 %5, %5, %13, %13, 0xCC; lop3.b32 %6, %6, %14, %14, 0xCC; lop3.b32 %7, %7, %15, %15, 0xCC; bra.uni GDONE;\n"
+        "G6: lop3.b32 %0, %0, %8, %8, 0x3C; lop3.b32 %1, %1, %9, %9, 0x3C; lop3.b32 %2, %2, %10, %10, 0x3C; lop3.b32 %3, %3, %11, %11, 0x3C; lop3.b32 %4, %4, %12, %12, 0x3C; lop3.b32 %5, %5, %13, %13, 0x3C; lop3.b32 %6, %6, %14, %14, 0x3C; lop3.b32 %7, %7, %15, %15, 0x3C; bra.uni GDONE;\n"
+        "G7: lop3.b32 %0, %0, %8, %8, 0xFC; lop3.b32 %1, %1, %9, %9, 0xFC; lop3.b32 %2, %2, %10, %10, 0xFC; lop3.b32 %3, %3, %11, %11, 0xFC; lop3.b32 %4, %4, %12, %12, 0xFC; lop3.b32 %5, %5, %13, %13, 0xFC; lop3.b32 %6, %6, %14, %14, 0xFC; lop3.b32 %7, %7, %15, %15, 0xFC; bra.uni GDONE;\n"
+        "G8: lop3.b32 %0, %0, %8, %8, 0x03; lop3.b32 %1, %1, %9, %9, 0x03; lop3.b32 %2, %2, %10, %10, 0x03; lop3.b32 %3, %3, %11, %11, 0x03; lop3.b32 %4, %4, %12, %12, 0x03; lop3.b32 %5, %5, %13, %13, 0x03; lop3.b32 %6, %6, %14, %14, 0x03; lop3.b32 %7, %7, %15, %15, 0x03; bra.uni GDONE;\n"
+        "G9: lop3.b32 %0, %0, %8, %8, 0xC3; lop3.b32 %1, %1, %9, %9, 0xC3; lop3.b32 %2, %2, %10, %10, 0xC3; lop3.b32 %3, %3, %11, %11, 0xC3; lop3.b32 %4, %4, %12, %12, 0xC3; lop3.b32 %5, %5, %13, %13, 0xC3; lop3.b32 %6, %6, %14, %14, 0xC3; lop3.b32 %7, %7, %15, %15, 0xC3; bra.uni GDONE;\n"
+        "G10: lop3.b32 %0, %0, %8, %8, 0x33; lop3.b32 %1, %1, %9, %9, 0x33; lop3.b32 %2, %2, %10, %10, 0x33; lop3.b32 %3, %3, %11, %11, 0x33; lop3.b32 %4, %4, %12, %12, 0x33; lop3.b32 %5, %5, %13, %13, 0x33; lop3.b32 %6, %6, %14, %14, 0x33; lop3.b32 %7, %7, %15, %15, 0x33; bra.uni GDONE;\n"
+        "G11: lop3.b32 %0, %0, %8, %8, 0xF3; lop3.b32 %1, %1, %9, %9, 0xF3; lop3.b32 %2, %2, %10, %10, 0xF3; lop3.b32 %3, %3, %11, %11, 0xF3; lop3.b32 %4, %4, %12, %12, 0xF3; lop3.b32 %5, %5, %13, %13, 0xF3; lop3.b32 %6, %6, %14, %14, 0xF3; lop3.b32 %7, %7, %15, %15, 0xF3; bra.uni GDONE;\n"
+        "G12: lop3.b32 %0, %0, %8, %8, 0x0F; lop3.b32 %1, %1, %9, %9, 0x0F; lop3.b32 %2, %2, %10, %10, 0x0F; lop3.b32 %3, %3, %11, %11, 0x0F; lop3.b32 %4, %4, %12, %12, 0x0F; lop3.b32 %5, %5, %13, %13, 0x0F; lop3.b32 %6, %6, %14, %14, 0x0F; lop3.b32 %7, %7, %15, %15, 0x0F; bra.uni GDONE;\n"
+        "G13: lop3.b32 %0, %0, %8, %8, 0xCF; lop3.b32 %1, %1, %9, %9, 0xCF; lop3.b32 %2, %2, %10, %10, 0xCF; lop3.b32 %3, %3, %11, %11, 0xCF; lop3.b32 %4, %4, %12, %12, 0xCF; lop3.b32 %5, %5, %13, %13, 0xCF; lop3.b32 %6, %6, %14, %14, 0xCF; lop3.b32 %7, %7, %15, %15, 0xCF; bra.uni GDONE;\n"
+        "G14: lop3.b32 %0, %0, %8, %8, 0x3F; lop3.b32 %1, %1, %9, %9, 0x3F; lop3.b32 %2, %2, %10, %10, 0x3F; lop3.b32 %3, %3, %11, %11, 0x3F; lop3.b32 %4, %4, %12, %12, 0x3F; lop3.b32 %5, %5, %13, %13, 0x3F; lop3.b32 %6, %6, %14, %14, 0x3F; lop3.b32 %7, %7, %15, %15, 0x3F; bra.uni GDONE;\n"
+        "G15: lop3.b32 %0, %0, %8, %8, 0xFF; lop3.b32 %1, %1, %9, %9, 0xFF; lop3.b32 %2, %2, %10, %10, 0xFF; lop3.b32 %3, %3, %11, %11, 0xFF; lop3.b32 %4, %4, %12, %12, 0xFF; lop3.b32 %5, %5, %13, %13, 0xFF; lop3.b32 %6, %6, %14, %14, 0xFF; lop3.b32 %7, %7, %15, %15, 0xFF; bra.uni GDONE;\n"
+        "GDONE:\n\t}"
+        : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7])
+        : "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]), "r"(op));
+}
+
+// Branch-free form of the same: the gate as a two-level multiplexer over four block-uniform masks, three lop3 per word
+// (0xCA = a ? b : c) and no switch.  MUX selects it at compile time.
+template <int N>
+__device__ __forceinline__ void gate_words_mux(int op, unsigned (&a)[N], const unsigned (&b)[N])
+{
+    const unsigned m00 = (op & 8) ? ~0u : 0u, m01 = (op & 4) ? ~0u : 0u, m10 = (op & 2) ? ~0u : 0u, m11 = (op & 1) ? ~0u : 0u;
+#pragma unroll
+    for (int w = 0; w < N; ++w) {
+        unsigned r1, r0;
+        asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(r1) : "r"(b[w]), "r"(m11), "r"(m10));
+        asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(r0) : "r"(b[w]), "r"(m01), "r"(m00));
+        asm("lop3.b32 %0, %0, %1, %2, 0xCA;" : "+r"(a[w]) : "r"(r1), "r"(r0));
+    }
+}
+template <bool MUX, int N> __device__ __forceinline__ void gate_apply(int op, unsigned (&a)[N], const unsigned (&b)[N])
+{
+    if (MUX)
+        gate_words_mux<N>(op, a, b);
+    else
+        gate_words_brx(op, a, b);
+}
+
 // two 16-byte shared-memory loads (left and right conv column of a tap) into eight words
 __device__ __forceinline__ void lds_pair(unsigned (&d)[8], unsigned addr0, unsigned addr1)
 {
@@ -578,6 +630,7 @@ __global__ void packed_slab_records_kernel(const uint8_t *__restrict__ ops, cons
     recs[c] = R;
 }
 
+template <bool MUX>
 __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint4 *__restrict__ x,
                                                                       const SlabRec *__restrict__ recs, uint4 *__restrict__ y,
                                                                       SlabShape s)
@@ -680,11 +733,11 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
                             lds_pair(g[p + 1], tn + o0[2 * p + 2], tn + o1[2 * p + 2]);
                             lds_pair(b[p + 1], tn + o0[2 * p + 3], tn + o1[2 * p + 3]);
                         }
-                        gate_words<8>(op[p], g[p], b[p]);
+                        gate_apply<MUX, 8>(op[p], g[p], b[p]);
                     }
-                    gate_words<8>(op[4], g[0], g[1]);
-                    gate_words<8>(op[5], g[2], g[3]);
-                    gate_words<8>(op[6], g[0], g[2]);
+                    gate_apply<MUX, 8>(op[4], g[0], g[1]);
+                    gate_apply<MUX, 8>(op[5], g[2], g[3]);
+                    gate_apply<MUX, 8>(op[6], g[0], g[2]);
 #pragma unroll
                     for (int w = 0; w < 4; ++w) acc[w] |= g[0][w] | g[0][w + 4];
                 }
@@ -945,7 +998,8 @@ extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const
     if (smem > 200 * 1024) return CLB_ERR_SHAPE;
     s.n_ug = (s.U + s.UB - 1) / s.UB;
     s.items = C * s.n_ug;
-    auto k = packed_convtree_slab_kernel;
+    const bool mux = tune_get(CLB_TUNE_SLAB_MUX) != 0;
+    auto k = mux ? packed_convtree_slab_kernel<true> : packed_convtree_slab_kernel<false>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
     int bps = (int)((227 * 1024) / (smem + 1024));
     const int by_regs = 512 / threads < 2 ? 2 : (512 / threads > 8 ? 8 : 512 / threads); // 112 registers per thread

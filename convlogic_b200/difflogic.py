@@ -11,7 +11,7 @@ import torch
 
 from . import ops
 from ._lib import W_ARGMAX, W_SOFTMAX
-from .functional import GradFactor, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction
+from .functional import GradFactor, GroupSumCrossEntropyFunction, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction
 from .packbitstensor import PackBitsTensor
 
 
@@ -156,6 +156,28 @@ class GroupSum(torch.nn.Module):
             # the transposed view a LogicLayer returns: sum its feature-major storage directly
             return GroupSumFunction.apply(x.t(), self.k, self.tau)
         return x.reshape(*x.shape[:-1], self.k, x.shape[-1] // self.k).sum(-1) / self.tau
+
+    def extra_repr(self):
+        return f"k={self.k}, tau={self.tau}"
+
+
+class GroupSumCrossEntropy(torch.nn.Module):
+    """``cross_entropy(GroupSum(k, tau)(x), labels)`` (mean reduction) as one module -- the tail of the reference's
+    training step (src/convlogic/model.py:137-152).  On the transposed view a ``LogicLayer`` returns, the class sums, the
+    loss and the gradient w.r.t. the scores come from two kernels and the backward is one broadcast kernel; any other
+    input takes the torch expression."""
+
+    def __init__(self, k: int, tau: float = 1.0):
+        super().__init__()
+        self.k, self.tau = k, tau
+
+    def forward(self, x, labels):
+        assert x.shape[-1] % self.k == 0, (x.shape, self.k)
+        if (x.is_cuda and x.dim() == 2 and x.dtype == torch.float32 and x.numel() and x.t().is_contiguous() and self.k <= 32
+                and labels.dtype == torch.int64):
+            return GroupSumCrossEntropyFunction.apply(x.t(), labels, self.k, self.tau)
+        scores = x.reshape(*x.shape[:-1], self.k, x.shape[-1] // self.k).sum(-1) / self.tau
+        return torch.nn.functional.cross_entropy(scores, labels)
 
     def extra_repr(self):
         return f"k={self.k}, tau={self.tau}"

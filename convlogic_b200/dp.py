@@ -40,6 +40,7 @@ class GradBucket:
             off += p.numel()
         self._works, self._hooks, self._group, self._average = [], [], None, True
         self.rebinds = 0
+        self._direct = False
 
     def zero(self):
         self._rebind_all(copy=False)
@@ -82,10 +83,27 @@ class GradBucket:
 
     def _slice_ready(self, lo, hi, p=None):
         if p is not None:
+            if self._direct:
+                return  # direct mode: the kernels' own ready() calls drive the exchange, not autograd's hooks
             self._rebind(p, lo, hi)
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self._group) == 1:
             return
         self._works.append(dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=self._group, async_op=True))
+
+    # ---- kernels write their gate gradients straight into the bucket
+    def direct(self, on=True):
+        """From now on the backward kernels of this library write each layer's gate gradient straight into its slice
+        of the bucket (no ``.grad`` accumulation kernels, no clearing between steps): every parameter carries a
+        ``(slice, ready)`` pair the autograd Functions look for.  A parameter must then be used ONCE per backward pass
+        (its slice is overwritten, not added to) -- true of the layer stacks this library models.  With ``overlap()``
+        active the slice is all-reduced the moment its kernel has been enqueued, as the hooks would do."""
+        for p, (lo, hi) in zip(self.params, self.ranges):
+            if on:
+                p._clb_grad_sink = (self.flat[lo:hi].view_as(p), lambda lo=lo, hi=hi: self._slice_ready(lo, hi) if self._hooks else None)
+            elif hasattr(p, "_clb_grad_sink"):
+                del p._clb_grad_sink
+        self._direct = bool(on)
+        return self
 
     def finish(self):
         """Waits for the slices in flight (the waits are stream-side for NCCL) and applies the averaging."""
@@ -141,3 +159,38 @@ def shard_range(n_items, rank=None, world=None):
     if world is None:
         world = dist.get_world_size() if dist.is_initialized() else 1
     return n_items * rank // world, n_items * (rank + 1) // world
+
+
+class FlatAdam:
+    """Adam / AdamW over ALL gate logits of a model in one kernel launch (``clb_adam_step``).
+
+    The parameters become views into one flat buffer (their names, shapes and values are unchanged, so state dicts
+    interchange), the gradients are the flat buffer of a ``GradBucket``; ``step()`` is one launch over both.  Matches
+    ``torch.optim.Adam(lr, betas, eps, weight_decay)`` / ``torch.optim.AdamW`` (``decoupled=True``, what the reference
+    trains with: src/convlogic/model.py:179-180) to fp32 rounding."""
+
+    def __init__(self, bucket, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, decoupled=False):
+        from . import ops  # noqa: F401  (needs the CUDA library)
+
+        self.bucket, self.lr, self.betas, self.eps, self.weight_decay, self.decoupled = bucket, lr, betas, eps, weight_decay, decoupled
+        self.params = torch.empty_like(bucket.flat)
+        for p, (lo, hi) in zip(bucket.params, bucket.ranges):
+            self.params[lo:hi].copy_(p.data.reshape(-1))
+            p.data = self.params[lo:hi].view_as(p)
+        self.exp_avg = torch.zeros_like(bucket.flat)
+        self.exp_avg_sq = torch.zeros_like(bucket.flat)
+        self.steps = 0
+
+    def zero_grad(self, set_to_none=False):
+        """Clears the bucket (the gradients are views of it and stay bound)."""
+        del set_to_none
+        self.bucket.zero()
+
+    def step(self):
+        from . import ops
+
+        if not self.bucket._direct:
+            self.bucket._rebind_all()  # gradients that autograd re-allocated are copied into the bucket first
+        self.steps += 1
+        ops.adam_step(self.params, self.bucket.flat, self.exp_avg, self.exp_avg_sq, self.lr, self.betas[0], self.betas[1], self.eps,
+                      self.weight_decay, self.steps, self.decoupled)

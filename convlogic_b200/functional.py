@@ -20,6 +20,13 @@ from . import ops
 from ._lib import W_ARGMAX, W_PROB, W_SOFTMAX  # noqa: F401
 
 
+def _grad_sink(w):
+    """(slice, ready-callback) when a gradient bucket (``dp.GradBucket.direct``) wants this parameter's gradient written
+    straight into its slice of the flat buffer, else None.  Backward passes then hand the slice to the kernel as its
+    output, call ``ready()`` and return no gradient for the parameter: no ``.grad`` accumulation kernel runs."""
+    return getattr(w, "_clb_grad_sink", None)
+
+
 class GradFactor(Function):
     @staticmethod
     def forward(ctx, x, f):
@@ -61,7 +68,12 @@ class FullConvLogicFunction(Function):
         need_gw = ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX
         gx = gw = None
         if need_gx or need_gw:
-            gx, gw = ops.convtree_bwd(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode, need_gx, need_gw)
+            sink = _grad_sink(w) if need_gw else None
+            gx, gw = ops.convtree_bwd(grad_y, x, w, sel, amax, ctx.geom, ctx.wmode, need_gx, need_gw,
+                                      gw_out=None if sink is None else sink[0])
+            if sink is not None:
+                sink[1]()
+                gw = None
         return (gx, gw) + (None,) * 10
 
 
@@ -129,7 +141,11 @@ class LogicLayerCudaFunction(Function):
         if ctx.needs_input_grad[0]:
             gx = ops.logic_bwd_x(x, a, b, w, grad_y, start, cons, ctx.wmode)
         if ctx.needs_input_grad[3] and ctx.wmode != W_ARGMAX:
-            gw = ops.logic_bwd_w(x, a, b, w, grad_y, ctx.wmode)
+            sink = _grad_sink(w)
+            gw = ops.logic_bwd_w(x, a, b, w, grad_y, ctx.wmode, gw_out=None if sink is None else sink[0])
+            if sink is not None:
+                sink[1]()
+                gw = None
         return gx, None, None, gw, None, None, None
 
 
@@ -160,8 +176,31 @@ class LogicTreeFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gy):
         x_fm, w0, w1, w2, leaf, node, start, slots = ctx.saved_tensors
+        sinks = [_grad_sink(w) for w in (w0, w1, w2)]
+        direct = ctx.wmode != W_ARGMAX and all(s is not None for s in sinks)
         gx, g0, g1, g2 = ops.logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy.contiguous(), start, slots, ctx.wmode,
-                                            need_gx=ctx.needs_input_grad[0])
-        if ctx.wmode == W_ARGMAX:
+                                            need_gx=ctx.needs_input_grad[0], gw_out=[s[0] for s in sinks] if direct else None)
+        if direct:
+            for s in sinks:
+                s[1]()
+        if ctx.wmode == W_ARGMAX or direct:
             g0 = g1 = g2 = None
         return gx, g0, g1, g2, None, None, None, None, None
+
+
+class GroupSumCrossEntropyFunction(torch.autograd.Function):
+    """GroupSum(k, tau) followed by the mean cross-entropy, on the feature-major [F, B] storage of a LogicLayer's output:
+    the scores are never materialised for autograd, and the backward is one broadcast kernel."""
+
+    @staticmethod
+    def forward(ctx, y_fm, labels, k, tau):
+        loss, dscore, _ = ops.group_sum_ce(y_fm.contiguous(), labels.contiguous(), k, tau)
+        ctx.save_for_backward(dscore)
+        ctx.meta = (y_fm.shape[0], k, tau)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, gloss):
+        (dscore,) = ctx.saved_tensors
+        f, k, tau = ctx.meta
+        return ops.group_sum_bwd(dscore, f, k, tau, scale=gloss.reshape(1).to(dscore.dtype).contiguous()), None, None, None

@@ -164,14 +164,19 @@ def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
     return gx
 
 
-def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True):
-    """Both gradients of the fused block in one C-ABI call; returns (gx or None, gw or None)."""
+def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True, gw_out=None):
+    """Both gradients of the fused block in one C-ABI call; returns (gx or None, gw or None).  ``gw_out``: a contiguous
+    tensor of the gate tensor's shape to receive the gate gradient (e.g. a slice of a flat gradient bucket)."""
     check_input(gy, x, w, sel)
     _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
     c = w.shape[0]
     gx = torch.empty_like(x) if need_gx else None
-    gw = torch.empty_like(w) if need_gw else None
+    gw = None
+    if need_gw:
+        gw = torch.empty_like(w) if gw_out is None else gw_out
+        if gw.shape != w.shape or gw.dtype != w.dtype or not gw.is_contiguous():
+            raise RuntimeError("convlogic_b200: `gw_out` must be contiguous with the gate tensor's shape and dtype")
     if n == 0 or c == 0:  # empty batch: the gate gradient is an empty sum
         return gx, (gw.zero_() if gw is not None else None)
     flag = _sel_flag(sel, geom, ci)
@@ -336,10 +341,10 @@ def logic_fwd(x, a, b, w, wmode):
     return y
 
 
-def logic_bwd_w(x, a, b, w, gy, wmode):
+def logic_bwd_w(x, a, b, w, gy, wmode, gw_out=None):
     check_input(x, a, b, w, gy)
     i, o, bsz = _logic_dims(x, a, b, w)
-    gw = torch.empty_like(w)
+    gw = torch.empty_like(w) if gw_out is None else gw_out
     if bsz == 0 or o == 0:
         return gw.zero_()
     check(lib().clb_logic_bwd_w(ptr(x), ptr(a), ptr(b), ptr(w), ptr(gy), ptr(gw), i, o, bsz, wmode, dtype_code(x),
@@ -504,12 +509,17 @@ def group_sum_fwd(y_fm, k, tau):
     return out
 
 
-def group_sum_bwd(gout, f, k, tau):
-    """Gradient of group_sum_fwd: [B, k] -> feature-major [F, B]."""
+def group_sum_bwd(gout, f, k, tau, scale=None):
+    """Gradient of group_sum_fwd: [B, k] -> feature-major [F, B]; ``scale``: a one-element device tensor every value is
+    multiplied by (the upstream gradient of a scalar loss), read by the kernel."""
     check_input(gout)
     b = gout.shape[0]
     gy = torch.empty((f, b), dtype=gout.dtype, device=gout.device)
-    check(lib().clb_group_sum_bwd(ptr(gout), ptr(gy), f, b, k, float(tau), dtype_code(gout), stream()))
+    if scale is not None:
+        check_input(scale)
+        if scale.numel() != 1 or scale.dtype != gout.dtype:
+            raise RuntimeError("convlogic_b200: `scale` must be a one-element tensor of the gradient's dtype")
+    check(lib().clb_group_sum_bwd_scaled(ptr(gout), ptr(scale), ptr(gy), f, b, k, float(tau), dtype_code(gout), stream()))
     return gy
 
 
@@ -522,13 +532,41 @@ def logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode):
     return y
 
 
-def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True):
-    """Gradients of ``logic_tree_fwd``: (gx [in, B] or None, gw0, gw1, gw2)."""
+def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True, gw_out=None):
+    """Gradients of ``logic_tree_fwd``: (gx [in, B] or None, gw0, gw1, gw2).  ``gw_out``: three contiguous tensors to
+    receive the gate gradients (cleared first: a neuron no tree reads keeps a zero gradient)."""
     check_input(x_fm, leaf, node, w0, w1, w2, gy, start, slots)
     t, b, in_dim = leaf.shape[0], x_fm.shape[1], x_fm.shape[0]
     tapgrad = torch.empty((max(t * 8, 1), b), dtype=torch.float32, device=x_fm.device)
-    gws = [torch.zeros_like(w) for w in (w0, w1, w2)]
+    gws = [torch.zeros_like(w) for w in (w0, w1, w2)] if gw_out is None else [g.zero_() for g in gw_out]
     gx = torch.empty_like(x_fm) if need_gx else None
     check(lib().clb_logic_tree_bwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(gy), ptr(tapgrad), ptr(gws[0]),
                                    ptr(gws[1]), ptr(gws[2]), ptr(gx), ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))
     return gx, gws[0], gws[1], gws[2]
+
+
+def group_sum_ce(y_fm, labels, k, tau, want_scores=False):
+    """GroupSum + mean cross-entropy on feature-major activations [F, B]: (loss [1], dscore [B, k], scores or None)."""
+    check_input(y_fm, labels)
+    if y_fm.dtype != torch.float32 or labels.dtype != torch.int64 or labels.shape != (y_fm.shape[1],):
+        raise RuntimeError("convlogic_b200: group_sum_ce expects float32 [F, B] activations and int64 [B] labels")
+    f, b = y_fm.shape
+    if f % k:
+        raise ValueError(f"in_dim ({f}) has to be divisible by k ({k}) but it is not")
+    loss = torch.empty(1, dtype=torch.float32, device=y_fm.device)
+    dscore = torch.empty((b, k), dtype=torch.float32, device=y_fm.device)
+    scores = torch.empty((b, k), dtype=torch.float32, device=y_fm.device) if want_scores else None
+    nbytes = lib().clb_group_sum_scratch_bytes(f, b, k, dtype_code(y_fm))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=y_fm.device)
+    check(lib().clb_group_sum_ce(ptr(y_fm), ptr(labels), ptr(scores), ptr(dscore), ptr(loss), ptr(scratch), nbytes, f, b, k, float(tau), stream()))
+    return loss, dscore, scores
+
+
+def adam_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, decoupled):
+    """One Adam / AdamW step over flat fp32 buffers, in place."""
+    check_input(p, g, m, v)
+    n = p.numel()
+    if not (g.numel() == m.numel() == v.numel() == n) or any(t.dtype != torch.float32 for t in (p, g, m, v)):
+        raise RuntimeError("convlogic_b200: adam_step expects four float32 buffers of equal size")
+    check(lib().clb_adam_step(ptr(p), ptr(g), ptr(m), ptr(v), n, float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
+                              int(step), int(bool(decoupled)), stream()))

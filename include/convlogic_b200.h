@@ -82,6 +82,9 @@ long long clb_trace_report(char *buf, size_t cap);
  *       the kernels that stream two channel planes per output channel through shared memory with TMA loads
  *       (clb_convtree_fwd picks them by itself; clb_convtree_bwd_plane is their backward); 0: never. */
 #define CLB_TUNE_PLANE_KERNELS 2
+/*   CLB_TUNE_SLAB_MUX  how the packed ConvLogic block on the slab layout applies a gate to its words: 0 = a block-uniform
+ *       16-way switch with one lop3 per word, 1 = a branch-free multiplexer over four masks, three lop3 per word. */
+#define CLB_TUNE_SLAB_MUX 3
 int clb_tune(int key, long long value);
 long long clb_tune_get(int key);
 
@@ -321,6 +324,25 @@ size_t clb_group_sum_scratch_bytes(int64_t F, int64_t B, int k, int dtype);
 int clb_group_sum_fwd(const void *y, void *out, void *scratch, size_t scratch_bytes, int64_t F, int64_t B, int k,
                       double tau, int dtype, void *stream);
 int clb_group_sum_bwd(const void *gout, void *gy, int64_t F, int64_t B, int k, double tau, int dtype, void *stream);
+/* The same with every value multiplied by *scale, a one-element device array of the gradient's dtype (the upstream
+ * gradient of a scalar loss); scale may be NULL. */
+int clb_group_sum_bwd_scaled(const void *gout, const void *scale, void *gy, int64_t F, int64_t B, int k, double tau, int dtype,
+                             void *stream);
+
+/* GroupSum followed by the mean cross-entropy loss, forward and the gradient w.r.t. the scores in one pass; stands in for
+ * GroupSum.forward (src/difflogic/difflogic.py:203-208) + torch.nn.CrossEntropyLoss as the training step applies them
+ * (src/convlogic/model.py:137-152).  y feature-major [F, B] fp32, labels int64 [B];
+ * scores [B, k] (may be NULL) = class sums / tau, dscore [B, k] = (softmax(scores) - one_hot(labels)) / B, loss [1].
+ * scratch as for clb_group_sum_fwd.  k <= 32.  Feed dscore (times the upstream scalar) to clb_group_sum_bwd. */
+int clb_group_sum_ce(const float *y, const int64_t *labels, float *scores, float *dscore, float *loss, void *scratch,
+                     size_t scratch_bytes, int64_t F, int64_t B, int k, double tau, void *stream);
+
+/* One Adam / AdamW step over a flat fp32 parameter buffer (all gate logits of a model in one array, their gradients in
+ * another); stands in for torch.optim.AdamW as configured at src/convlogic/model.py:179-180.  step counts from 1;
+ * decoupled != 0: AdamW (p *= 1 - lr * weight_decay), else the weight decay is added to the gradient.  All four arrays
+ * 16-byte aligned.  m and v are the running moments (zero before the first step). */
+int clb_adam_step(float *p, const float *g, float *m, float *v, int64_t n, double lr, double beta1, double beta2, double eps,
+                  double weight_decay, int64_t step, int decoupled, void *stream);
 
 /* ---- Compiled network -----------------------------------------------------------------------------------
  * A discretised stack (fused ConvLogic blocks, then flat LogicLayers, then GroupSum) serialised into one blob

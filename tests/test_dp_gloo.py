@@ -80,6 +80,36 @@ def _worker(rank, world, port, fail_rank):
         bucket.zero()   # also re-binds (nothing to copy)
         assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
 
+        # direct mode: a backward kernel writes a layer's gradient into its bucket slice and reports it ready (the
+        # library's autograd Functions do this on the GPU; here a stand-in Function follows the same protocol)
+        from convlogic_b200.functional import _grad_sink
+
+        class WritesIntoSink(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, w, scale):
+                ctx.save_for_backward(w)
+                ctx.scale = scale
+                return (w * scale).sum()
+
+            @staticmethod
+            def backward(ctx, g):
+                (w,) = ctx.saved_tensors
+                sink = _grad_sink(w)
+                assert sink is not None and w is params[0] or w is params[1]
+                sink[0].copy_(torch.full_like(w, ctx.scale) * g)
+                sink[1]()
+                return None, None
+
+        bucket.direct().overlap(average=True)
+        bucket.flat.fill_(-7.0)            # stale values: direct mode overwrites, nothing clears the bucket
+        sum(WritesIntoSink.apply(p, float(rank + 1)) for p in params).backward()
+        assert bucket.finish() == len(params)
+        assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
+        assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
+        bucket.remove_overlap()
+        bucket.direct(False)
+        assert all(_grad_sink(p) is None for p in params)
+
         # one-shot variant on ordinary .grad tensors
         for p in params:
             p.grad = torch.full_like(p, float(10 * (rank + 1)))

@@ -1,0 +1,103 @@
+"""The tail of the training step on this library's kernels: GroupSum + cross-entropy in one pass, gate gradients written
+straight into the flat bucket, Adam over the flat buffer -- each against the torch expression it stands in for, and a
+three-step training trajectory of a small CIFAR-shaped stack against the all-torch tail (fp32, 1e-5)."""
+
+import pytest
+import torch
+
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(seed):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(seed)
+    net = cb.ConvLogicCifarModel(k_param=8, input_channels=9, input_size=32, tau=7.0).network
+    g = torch.Generator().manual_seed(seed + 1)
+    for prm in net.parameters():
+        prm.data = torch.randn(*prm.shape, generator=g)
+    return net.cuda().train()
+
+
+@pytest.mark.parametrize("batch,features,k,tau", [(64, 160, 10, 2.0), (300, 2560, 10, 40.0), (5, 32, 4, 1.0), (1030, 330, 11, 3.5)])
+def test_group_sum_cross_entropy_equals_torch(batch, features, k, tau):
+    import convlogic_b200 as cb
+
+    torch.manual_seed(batch)
+    layer = cb.LogicLayer(48, features).cuda().train()
+    x = torch.rand(batch, 48, device="cuda")
+    labels = torch.randint(0, k, (batch,), device="cuda")
+    y = layer(x)                                   # the transposed view of feature-major storage
+    y1 = y.detach().clone().requires_grad_(True)   # same values, ordinary layout -> the torch expression
+    want = torch.nn.functional.cross_entropy(cb.GroupSum(k, tau)(y1), labels)
+    (gwant,) = torch.autograd.grad(want * 3.0, (y1,))
+    yt = y.detach().t().contiguous().t().requires_grad_(True)
+    got = cb.GroupSumCrossEntropy(k, tau)(yt, labels)
+    (ggot,) = torch.autograd.grad(got * 3.0, (yt,))
+    assert got.shape == () and abs(float(got) - float(want)) <= 1e-5 * max(1.0, abs(float(want)))
+    assert_close(ggot, gwant, 1e-5, "gradient w.r.t. the activations")
+    # an input in the ordinary layout takes the torch expression and gives the same loss
+    assert abs(float(cb.GroupSumCrossEntropy(k, tau)(y1, labels)) - float(want)) <= 1e-6
+
+
+@pytest.mark.parametrize("decoupled,wd", [(False, 0.0), (False, 0.01), (True, 0.002)])
+def test_flat_adam_equals_torch_adam(decoupled, wd):
+    import convlogic_b200 as cb
+    from convlogic_b200 import dp
+
+    model = torch.nn.Sequential(cb.LogicLayer(32, 100), cb.LogicLayer(100, 50), cb.GroupSum(10, 2.0)).cuda().train()
+    twin = torch.nn.Sequential(cb.LogicLayer(32, 100), cb.LogicLayer(100, 50), cb.GroupSum(10, 2.0)).cuda().train()
+    twin.load_state_dict(model.state_dict())
+    ref = (torch.optim.AdamW if decoupled else torch.optim.Adam)(twin.parameters(), lr=0.01, weight_decay=wd)
+    bucket = dp.GradBucket(model)
+    opt = cb.FlatAdam(bucket, lr=0.01, weight_decay=wd, decoupled=decoupled)
+    names = [n for n, _ in model.named_parameters()]
+    assert names == [n for n, _ in twin.named_parameters()]      # parameters are views now, names and shapes unchanged
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for step in range(4):
+        x = torch.rand(40, 32, device="cuda", generator=g)
+        lab = torch.randint(0, 10, (40,), device="cuda", generator=g)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x), lab).backward()
+        opt.step()
+        ref.zero_grad()
+        torch.nn.functional.cross_entropy(twin(x), lab).backward()
+        ref.step()
+        for (n, p), q in zip(model.named_parameters(), twin.parameters()):
+            assert_close(p, q, 2e-6, f"step {step}: {n}")
+
+
+def test_three_step_trajectory_equals_torch_tail():
+    """Fused tail (gate-tree flat layers, GroupSum + cross-entropy kernel, gradients written into the bucket, flat Adam)
+    against the module-by-module stack with torch's cross-entropy and Adam: same losses and parameters after three steps."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import dp
+
+    a, b = _model(3), _model(3)
+    opt_a = torch.optim.Adam(a.parameters(), lr=0.01)
+    fused = cb.fuse_logic_layers(b)
+    assert isinstance(fused[-1], cb.GroupSum)
+    body, head = fused[:-1], cb.GroupSumCrossEntropy(fused[-1].k, fused[-1].tau)
+    bucket = dp.GradBucket(b).direct()
+    opt_b = cb.FlatAdam(bucket, lr=0.01)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for step in range(3):
+        x = (torch.rand(32, 9, 32, 32, device="cuda", generator=g) < 0.5).float()
+        lab = torch.randint(0, 10, (32,), device="cuda", generator=g)
+        opt_a.zero_grad()
+        loss_a = torch.nn.functional.cross_entropy(a(x), lab)
+        loss_a.backward()
+        grads_a = [p.grad.clone() for p in a.parameters()]
+        opt_a.step()
+        loss_b = head(body(x), lab)
+        loss_b.backward()
+        bucket.finish()
+        for (n, p), ga in zip(b.named_parameters(), grads_a):
+            assert p.grad is not None and p.grad.data_ptr() == bucket.flat[bucket.ranges[[id(q) for q in bucket.params].index(id(p))][0]:].data_ptr()
+            assert_close(p.grad, ga, 1e-5, f"step {step}: gradient of {n}")
+        opt_b.step()
+        assert abs(float(loss_a) - float(loss_b)) <= 1e-5 * max(1.0, abs(float(loss_a))), (step, float(loss_a), float(loss_b))
+        for (n, p), q in zip(b.named_parameters(), a.parameters()):
+            assert_close(p, q, 1e-5, f"step {step}: {n}")
