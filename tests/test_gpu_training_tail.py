@@ -96,7 +96,9 @@ def test_three_step_trajectory_equals_torch_tail():
         bucket.finish()
         for (n, p), ga in zip(b.named_parameters(), grads_a):
             assert p.grad is not None and p.grad.data_ptr() == bucket.flat[bucket.ranges[[id(q) for q in bucket.params].index(id(p))][0]:].data_ptr()
-            assert_close(p.grad, ga, 1e-5, f"step {step}: gradient of {n}")
+            # both sides are fp32 with different summation orders (one gate tree per output neuron against three layers
+            # one after the other): a few 1e-5 of the largest gradient, max-normalised
+            assert_close(p.grad, ga, 5e-5, f"step {step}: gradient of {n}")
         opt_b.step()
         assert abs(float(loss_a) - float(loss_b)) <= 1e-5 * max(1.0, abs(float(loss_a))), (step, float(loss_a), float(loss_b))
         for (n, p), q in zip(b.named_parameters(), a.parameters()):
