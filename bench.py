@@ -329,7 +329,7 @@ def run_c3(ctx, args, with_cpu=True):
     imgs = C3_BATCH * world * args.steps
     peak, kind = measured_peaks()
     alg = c3_algorithmic_bytes(C3_BATCH)
-    kernels = kernel_table(trace, alg, peak)
+    kernels = kernel_table(trace, alg, peak, top=12)
     top = kernels[0] if kernels else {}
     traced_ms = sum(v[1] for v in trace.values())
     rec = {

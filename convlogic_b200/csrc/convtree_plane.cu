@@ -150,9 +150,9 @@ template <int S> struct FwdCfg {
     static constexpr int IMG = R * P;                            // floats of one staged plane
     static constexpr int SLOT = (NIMG * IMG + 31) / 32 * 32;     // floats of one slot (NIMG planes of one channel)
     static constexpr int STAGE_BYTES = 2 * SLOT * 4;
-    static constexpr int STAGES = 4;
-    static constexpr int SMEM = GROUPS * STAGES * STAGE_BYTES;
     static constexpr bool TMA = UseTma<S>::value;
+    static constexpr int STAGES = TMA ? 4 : 3;
+    static constexpr int SMEM = GROUPS * STAGES * STAGE_BYTES;
     static constexpr int GSIZE = WIDE ? kThreads : 32;
     static constexpr int CPQ = NIMG * 2 * S * (S / 4) / GSIZE;   // 16-byte copies per thread and iteration (cp.async staging)
     static_assert(WIDE ? (TPI == kThreads && NIMG == 2) : (32 % TPI == 0 && NIMG == 2 * (32 / TPI)), "thread mapping");
@@ -291,26 +291,25 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n0, &full[gid][st]);
     };
     // cp.async staging: which 16-byte pieces this thread moves is the same for every iteration
-    int coff[Cf::CPQ], cimg[Cf::CPQ];
+    const float *csrc[Cf::CPQ]; // the piece in the batch's first image slot; advances by NIMG images per iteration
+    int cimg[Cf::CPQ];
     uint32_t cdst[Cf::CPQ];
 #pragma unroll
     for (int q = 0; q < Cf::CPQ; ++q) {
         const int u = gt + q * Cf::GSIZE;
         constexpr int W4 = S / 4;
         const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
-        coff[q] = (slot ? ch_b : ch_a) * HW + row * S + col4 * 4;
-        cimg[q] = img;
+        csrc[q] = x + ((size_t)(n_lo + img) * s.Ci + (slot ? ch_b : ch_a)) * HW + row * S + col4 * 4;
+        cimg[q] = n_lo + img;
         cdst[q] = clb_tma::smem_addr(gbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
     }
+    const size_t cstep = (size_t)Cf::NIMG * s.Ci * HW;
     auto issue_cp = [&](int it) {   // every thread of the group; always commits, so that the group counts stay aligned
         if (it < iters) {
             const int st = it % Cf::STAGES;
-            const int n0 = n_lo + it * Cf::NIMG;
 #pragma unroll
-            for (int q = 0; q < Cf::CPQ; ++q) {
-                const int n = min(n0 + cimg[q], s.N - 1); // images past the end: any valid plane, the results are not stored
-                cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), x + (size_t)n * s.Ci * HW + coff[q]);
-            }
+            for (int q = 0; q < Cf::CPQ; ++q)   // an image past the end of the batch is not fetched: its slot keeps older (finite) data,
+                if (cimg[q] + it * Cf::NIMG < s.N) cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), csrc[q] + (size_t)it * cstep); // never stored
         }
         cp_async_commit();
     };
@@ -388,7 +387,9 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         CLB_FWD_STAGE(0)
         CLB_FWD_STAGE(1)
         CLB_FWD_STAGE(2)
-        CLB_FWD_STAGE(3)
+        if constexpr (Cf::STAGES > 3) {
+            CLB_FWD_STAGE(3)
+        }
 #undef CLB_FWD_STAGE
     }
     if (failed && leader) {
@@ -546,26 +547,25 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     };
     // cp.async staging (small images): the 16-byte pieces this lane moves, the same for every iteration
     constexpr int CPQ = Cf::UNITS / 32;
-    int coff[CPQ], cimg[CPQ];
+    const float *csrc[CPQ];
+    int cimg[CPQ];
     uint32_t cdst[CPQ];
 #pragma unroll
     for (int q = 0; q < CPQ; ++q) {
         const int u = lane + 32 * q;
         constexpr int W4 = S / 4;
         const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
-        coff[q] = (slot ? ch_b : ch_a) * HW + row * S + col4 * 4;
-        cimg[q] = img;
+        csrc[q] = x + ((size_t)(n_lo + img) * s.Ci + (slot ? ch_b : ch_a)) * HW + row * S + col4 * 4;
+        cimg[q] = n_lo + img;
         cdst[q] = clb_tma::smem_addr(wbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
     }
+    const size_t cstep = (size_t)Cf::NIMG * s.Ci * HW;
     auto issue_cp = [&](int it) {   // every lane; always commits, so that the group counts stay aligned
         if (it < iters) {
             const int st = it % XST;
-            const int n0 = n_lo + it * Cf::NIMG;
 #pragma unroll
-            for (int q = 0; q < CPQ; ++q) {
-                const int n = min(n0 + cimg[q], s.N - 1);
-                cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), x + (size_t)n * s.Ci * HW + coff[q]);
-            }
+            for (int q = 0; q < CPQ; ++q)   // an image past the end of the batch is not fetched (its upstream gradient reads as zero)
+                if (cimg[q] + it * Cf::NIMG < s.N) cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), csrc[q] + (size_t)it * cstep);
         }
         cp_async_commit();
     };

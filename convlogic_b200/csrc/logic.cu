@@ -457,19 +457,79 @@ struct TreeTables {
     const float *w[3];   // logits (or mixtures) of the three layers
 };
 
-__device__ __forceinline__ Gate<float> tree_gate(const TreeTables &tt, long long t, int g, int wmode)
+// ---- the seven gates of a tree on the warp's lanes: the quad of lanes 4g..4g+3 owns gate g (lanes 28..31 idle), lane
+// q = lane & 3 of a quad holds entries 4q..4q+3 of the gate's 16.  Gate id j = 4q + i has truth-table bits (q >> 1,
+// q & 1, i >> 1, i & 1), so the coefficients of the multilinear form follow from three sums of the lane's four entries.
+__device__ __forceinline__ float quad_sum(float v)
 {
-    const int layer = g < 4 ? 0 : (g < 6 ? 1 : 2);
-    return gate_load<float>(tt.w[layer] + (long long)__ldg(tt.node + t * 7 + g) * 16, wmode);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-// lanes 0..6 hold gate g = lane; everybody gets all seven
-__device__ __forceinline__ void tree_gates_broadcast(const Gate<float> &mine, Gate<float> (&g)[7])
+// the lane's four entries of the mixture over the 16 gates (zeros on an idle lane); every lane of the warp calls this
+__device__ __forceinline__ void quad_mixture(const float *__restrict__ w16, int wmode, int q, bool active, float (&p)[4])
 {
 #pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = active ? __ldg(w16 + 4 * q + i) : 0.f;
+    if (wmode == CLB_W_SOFTMAX) {
+        float m = fmaxf(fmaxf(p[0], p[1]), fmaxf(p[2], p[3]));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = expf(p[i] - m);
+        const float inv = 1.f / quad_sum((p[0] + p[1]) + (p[2] + p[3]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] *= inv;
+    } else if (wmode == CLB_W_ARGMAX) {   // the first largest entry, as a scan from entry 0 finds it
+        float m = p[0];
+        int best = 4 * q;
+#pragma unroll
+        for (int i = 1; i < 4; ++i)
+            if (p[i] > m) m = p[i], best = 4 * q + i;
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m, o);
+            const int bo = __shfl_xor_sync(0xffffffffu, best, o);
+            if (mo > m || (mo == m && bo < best)) m = mo, best = bo;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = (4 * q + i == best) ? 1.f : 0.f;
+    }
+}
+
+// coefficients of the quad's gate from the four lanes' mixture entries (every lane of the quad gets them)
+__device__ __forceinline__ Gate<float> quad_gate(const float (&p)[4], int q)
+{
+    const float q3 = (float)(q >> 1), q2 = (float)(q & 1);
+    const float all = (p[0] + p[1]) + (p[2] + p[3]), hi = p[2] + p[3], odd = p[1] + p[3];
+    Gate<float> g;
+    g.k1 = quad_sum(q3 * all);
+    g.ka = quad_sum(hi - q3 * all);
+    g.kb = quad_sum((q2 - q3) * all);
+    g.kab = quad_sum(odd - hi + (q3 - q2) * all);
+    return g;
+}
+
+// neuron behind the lane's gate (lane < 28) and that neuron's row of 16 values
+__device__ __forceinline__ long long tree_node(const TreeTables &tt, long long t, int lane) { return __ldg(tt.node + t * 7 + (lane >> 2)); }
+__device__ __forceinline__ const float *tree_row(const TreeTables &tt, int lane, long long n)
+{
+    const int g = lane >> 2;
+    return tt.w[g < 4 ? 0 : (g < 6 ? 1 : 2)] + n * 16;
+}
+
+// every lane gets all seven gates
+__device__ __forceinline__ void tree_gates(const TreeTables &tt, long long t, int lane, int wmode, Gate<float> (&g)[7])
+{
+    const bool active = lane < 28;
+    const long long n = active ? tree_node(tt, t, lane) : 0;
+    float p[4];
+    quad_mixture(tree_row(tt, active ? lane : 0, n), wmode, lane & 3, active, p);
+    const Gate<float> mine = quad_gate(p, lane & 3);
+#pragma unroll
     for (int i = 0; i < 7; ++i) {
-        g[i].k1 = __shfl_sync(0xffffffffu, mine.k1, i), g[i].ka = __shfl_sync(0xffffffffu, mine.ka, i);
-        g[i].kb = __shfl_sync(0xffffffffu, mine.kb, i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, i);
+        g[i].k1 = __shfl_sync(0xffffffffu, mine.k1, 4 * i), g[i].ka = __shfl_sync(0xffffffffu, mine.ka, 4 * i);
+        g[i].kb = __shfl_sync(0xffffffffu, mine.kb, 4 * i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, 4 * i);
     }
 }
 
@@ -480,9 +540,8 @@ __global__ void __launch_bounds__(256) logic_tree_fwd_kernel(const float *__rest
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     for (long long t = warp; t < T; t += nwarps) {
-        Gate<float> mine = {0.f, 0.f, 0.f, 0.f}, g[7];
-        if (lane < 7) mine = tree_gate(tt, t, lane, wmode);
-        tree_gates_broadcast(mine, g);
+        Gate<float> g[7];
+        tree_gates(tt, t, lane, wmode, g);
         const float *row[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
@@ -509,9 +568,8 @@ __global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__r
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     for (long long t = warp; t < T; t += nwarps) {
-        Gate<float> mine = {0.f, 0.f, 0.f, 0.f}, g[7];
-        if (lane < 7) mine = tree_gate(tt, t, lane, wmode);
-        tree_gates_broadcast(mine, g);
+        Gate<float> g[7];
+        tree_gates(tt, t, lane, wmode, g);
         const float *row[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
@@ -551,18 +609,40 @@ __global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__r
                 vstore<float, V>(tapgrad + (t * 8 + 2 * p + 1) * B + b0, tb);
             }
         }
-        // batch totals of the 28 sums (xor butterfly: every lane ends with all of them), then lane g finishes gate g
+        // batch totals: a transposed butterfly leaves total i on lane i, i.e. basis sum k = lane & 3 of gate lane >> 2 on
+        // the lane that owns entries 4k..4k+3 of that gate; the quad then finishes the gate's 16 gradients together
+        float v[32];
 #pragma unroll
-        for (int i = 0; i < 28; ++i) bs[i] = warp_sum<float>(bs[i]);
-        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = 0; i < 32; ++i) v[i] = i < 28 ? bs[i] : 0.f;
 #pragma unroll
-        for (int gi = 0; gi < 7; ++gi)
-            if (lane == gi) s4[0] = bs[4 * gi], s4[1] = bs[4 * gi + 1], s4[2] = bs[4 * gi + 2], s4[3] = bs[4 * gi + 3];
-        if (lane < 7) {
-            const int layer = lane < 4 ? 0 : (lane < 6 ? 1 : 2);
-            const long long n = __ldg(tt.node + t * 7 + lane);
-            float *out = (layer == 0 ? gw0 : layer == 1 ? gw1 : gw2) + n * 16;
-            gate_grad_store<float>(s4, tt.w[layer] + n * 16, wmode, out);
+        for (int half = 16; half >= 1; half >>= 1) {
+            const bool upper = (lane & half) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float keep = upper ? v[i + half] : v[i];
+                const float send = upper ? v[i] : v[i + half];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+            }
+        }
+        float s4[4], p[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s4[k] = __shfl_sync(0xffffffffu, v[0], (lane & ~3) + k);
+        const long long n = lane < 28 ? tree_node(tt, t, lane) : 0;
+        if (wmode == CLB_W_SOFTMAX) quad_mixture(tree_row(tt, lane < 28 ? lane : 0, n), wmode, lane & 3, lane < 28, p); // again: not kept across the loop
+        const int q = lane & 3;
+        const float q3 = (float)(q >> 1), q2 = (float)(q & 1);
+        const float base = (q3 - q2) * s4[0] - q3 * s4[1] + (q2 - q3) * s4[2] + q3 * s4[3];
+        float gr[4] = {base, base + s4[0], base + (s4[1] - s4[0]), base + s4[1]}; // entry i adds (i & 1) s0 + (i >> 1) (s1 - s0)
+        if (wmode == CLB_W_SOFTMAX) {
+            const float dot = quad_sum((p[0] * gr[0] + p[1] * gr[1]) + (p[2] * gr[2] + p[3] * gr[3]));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) gr[i] = p[i] * (gr[i] - dot);
+        }
+        if (lane < 28) {
+            const int gi = lane >> 2;
+            float *out = (gi < 4 ? gw0 : gi < 6 ? gw1 : gw2) + n * 16 + 4 * q;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = gr[i];
         }
     }
 }
