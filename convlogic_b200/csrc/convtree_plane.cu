@@ -122,10 +122,25 @@ template <int OFF> __device__ __forceinline__ void sts_f32(uint32_t addr, float 
     asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "f"(v) : "memory");
 }
 
+template <int OFF> __device__ __forceinline__ float4 lds_v4(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ void sts_v4_zero(uint32_t addr)
+{
+    asm volatile("st.shared.v4.f32 [%0+%1], {%2, %2, %2, %2};" ::"r"(addr), "n"(OFF), "f"(0.f) : "memory");
+}
+
 // 16-byte asynchronous copy global -> shared (L2 only), commit / wait of the calling thread's copy groups
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+template <int OFF> __device__ __forceinline__ void cp_async16_off(uint32_t dst, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
@@ -290,9 +305,10 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[gid][st]);
         clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n0, &full[gid][st]);
     };
-    // cp.async staging: which 16-byte pieces this thread moves is the same for every iteration
-    const float *csrc[Cf::CPQ]; // the piece in the batch's first image slot; advances by NIMG images per iteration
-    int cimg[Cf::CPQ];
+    // cp.async staging: which 16-byte pieces this thread moves is the same for every iteration; the source pointers run
+    // along with the iterations (NIMG images further each time), cp_iters = iterations in which the piece's image exists
+    const float *csrc[Cf::CPQ];
+    int cp_iters[Cf::CPQ];
     uint32_t cdst[Cf::CPQ];
 #pragma unroll
     for (int q = 0; q < Cf::CPQ; ++q) {
@@ -300,19 +316,21 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         constexpr int W4 = S / 4;
         const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
         csrc[q] = x + ((size_t)(n_lo + img) * s.Ci + (slot ? ch_b : ch_a)) * HW + row * S + col4 * 4;
-        cimg[q] = n_lo + img;
+        cp_iters[q] = (n_hi - n_lo - img + Cf::NIMG - 1) / Cf::NIMG;
         cdst[q] = clb_tma::smem_addr(gbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
     }
     const size_t cstep = (size_t)Cf::NIMG * s.Ci * HW;
-    auto issue_cp = [&](int it) {   // every thread of the group; always commits, so that the group counts stay aligned
-        if (it < iters) {
-            const int st = it % Cf::STAGES;
-#pragma unroll
-            for (int q = 0; q < Cf::CPQ; ++q)   // an image past the end of the batch is not fetched: its slot keeps older (finite) data,
-                if (cimg[q] + it * Cf::NIMG < s.N) cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), csrc[q] + (size_t)it * cstep); // never stored
-        }
-        cp_async_commit();
-    };
+    // Called once per iteration in rising order (the pointers advance); always commits, so that the group counts stay
+    // aligned.  An image past the end of the part is not fetched: its slot keeps older (finite) data that is never stored.
+#define CLB_FWD_ISSUE_CP(ST, IT)                                                                                          \
+    {                                                                                                                     \
+        _Pragma("unroll") for (int q = 0; q < Cf::CPQ; ++q)                                                               \
+        {                                                                                                                 \
+            if ((IT) < cp_iters[q]) cp_async16_off<(ST) * Cf::STAGE_BYTES>(cdst[q], csrc[q]);                             \
+            csrc[q] += cstep;                                                                                             \
+        }                                                                                                                 \
+        cp_async_commit();                                                                                                \
+    }
     if (Cf::TMA) {
         if (leader)
             for (int it = 0; it < Cf::STAGES && it < iters; ++it) issue(it);
@@ -321,49 +339,41 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         for (int i = gt * 4; i < Cf::STAGES * Cf::STAGE_BYTES / 4; i += Cf::GSIZE * 4)
             *reinterpret_cast<float4 *>(reinterpret_cast<float *>(gbase) + i) = make_float4(0.f, 0.f, 0.f, 0.f);
         group_sync();
-        for (int it = 0; it < Cf::STAGES; ++it) issue_cp(it);
+        CLB_FWD_ISSUE_CP(0, 0)
+        CLB_FWD_ISSUE_CP(1, 1)
+        CLB_FWD_ISSUE_CP(2, 2)
+        static_assert(Cf::TMA || Cf::STAGES == 3, "prologue of the cp.async ring");
     }
 
+    // 2x2 pool: lanes ox and ox^1 hold the two columns of a window, each for both images of the pair.  The even lane
+    // pools and stores the pair's first image, the odd lane the second; each hands the other the half it does not need.
     const bool odd = ox & 1;
+    const int my_img = 2 * pair_local + (odd ? 1 : 0);
+    const int my_iters = (n_hi - n_lo - my_img + Cf::NIMG - 1) / Cf::NIMG;   // iterations in which that image exists
+    const size_t o0 = ((size_t)(n_lo + my_img) * s.C + c) * I + py * Cf::WP + (ox >> 1);
+    const size_t ostep = (size_t)Cf::NIMG * s.C * I;
+    const bool want_amax = amax != nullptr;
+    float *yp = y + o0;                        // run along with the iterations
+    uint8_t *ap = want_amax ? amax + o0 : nullptr;
     bool failed = false;
     int it = 0;
-    auto finish = [&](const f32x2(&z)[2], bool ok_in) -> bool {
-        // The tile has been read by the whole group: the leader may refill this stage.  The same vote tells every
-        // thread whether anyone's wait ran out (never expected): then nothing of this iteration is stored.
-        const bool ok = Cf::WIDE ? (__syncthreads_and(ok_in ? 1 : 0) != 0) : (__all_sync(0xffffffffu, ok_in ? 1 : 0) != 0);
-        if (!ok) return false;
-        if (Cf::TMA) {
-            if (leader && it + Cf::STAGES < iters) issue(it + Cf::STAGES);
-        } else {
-            issue_cp(it + Cf::STAGES);
+    auto pool_store = [&](const f32x2(&z)[2]) {
+        const float m0 = odd ? hi_of(z[0]) : lo_of(z[0]), m1 = odd ? hi_of(z[1]) : lo_of(z[1]);   // my image, my column
+        const float t0 = odd ? lo_of(z[0]) : hi_of(z[0]), t1 = odd ? lo_of(z[1]) : hi_of(z[1]);   // the other lane's image
+        const float r0 = __shfl_xor_sync(0xffffffffu, t0, 1), r1 = __shfl_xor_sync(0xffffffffu, t1, 1); // my image, other column
+        // candidates in scan order (0,0),(0,1),(1,0),(1,1); the even lane holds the even column
+        const float c0 = odd ? r0 : m0, c1 = odd ? m0 : r0, c2 = odd ? r1 : m1, c3 = odd ? m1 : r1;
+        float best = c0;
+        int bd = 0;
+        if (c1 > best) best = c1, bd = 1; // strict '>' in scan order keeps the first maximum
+        if (c2 > best) best = c2, bd = 2;
+        if (c3 > best) best = c3, bd = 3;
+        if (it < my_iters) {
+            *yp = best;
+            if (want_amax) *ap = (uint8_t)bd;
         }
-        // 2x2 pool: lanes ox and ox^1 hold the two columns; candidates in scan order (0,0),(0,1),(1,0),(1,1)
-        const f32x2 q0 = __shfl_xor_sync(0xffffffffu, z[0], 1), q1 = __shfl_xor_sync(0xffffffffu, z[1], 1);
-        const f32x2 d0 = odd ? q0 : z[0], d1 = odd ? z[0] : q0, d2 = odd ? q1 : z[1], d3 = odd ? z[1] : q1;
-        float best[2] = {lo_of(d0), hi_of(d0)};
-        int bd[2] = {0, 0};
-        if (lo_of(d1) > best[0]) best[0] = lo_of(d1), bd[0] = 1; // strict '>' in scan order keeps the first maximum
-        if (hi_of(d1) > best[1]) best[1] = hi_of(d1), bd[1] = 1;
-        if (lo_of(d2) > best[0]) best[0] = lo_of(d2), bd[0] = 2;
-        if (hi_of(d2) > best[1]) best[1] = hi_of(d2), bd[1] = 2;
-        if (lo_of(d3) > best[0]) best[0] = lo_of(d3), bd[0] = 3;
-        if (hi_of(d3) > best[1]) best[1] = hi_of(d3), bd[1] = 3;
-        const int na = n_lo + it * Cf::NIMG + 2 * pair_local;
-        const size_t o = ((size_t)na * s.C + c) * I + py * Cf::WP + (ox >> 1);
-        // even lanes store the values, odd lanes the arg-max bytes, of both images of the pair
-        if (na < n_hi) {
-            if (!odd)
-                y[o] = best[0];
-            else if (amax != nullptr)
-                amax[o] = (uint8_t)bd[0];
-        }
-        if (na + 1 < n_hi) {
-            if (!odd)
-                y[o + (size_t)s.C * I] = best[1];
-            else if (amax != nullptr)
-                amax[o + (size_t)s.C * I] = (uint8_t)bd[1];
-        }
-        return true;
+        yp += ostep;
+        if (want_amax) ap += ostep;
     };
     // the ring is walked with the stage index as a compile-time constant: every load is [register + immediate]
     while (it < iters && !failed) {
@@ -371,7 +381,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
 #define CLB_FWD_STAGE(ST)                                                                                                 \
     if (it < iters && !failed) {                                                                                          \
         bool ok = true;                                                                                                   \
-        if (Cf::TMA) {                                                                                                    \
+        if constexpr (Cf::TMA) {                                                                                          \
             ok = clb_tma::mbar_wait(&full[gid][ST], parity);                                                              \
         } else {                                                                                                          \
             cp_async_wait<Cf::STAGES - 1>();                                                                              \
@@ -379,10 +389,22 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
         }                                                                                                                 \
         f32x2 z[2];                                                                                                       \
         fwd_stage<S, ST>(toff, g, z);                                                                                     \
-        if (finish(z, ok))                                                                                                \
+        /* The tile has been read by the whole group: refill this stage.  With TMA the same vote tells every thread    */ \
+        /* whether anyone's wait ran out (never expected): then nothing of this iteration is stored.                   */ \
+        if constexpr (Cf::TMA) {                                                                                          \
+            ok = Cf::WIDE ? (__syncthreads_and(ok ? 1 : 0) != 0) : (__all_sync(0xffffffffu, ok ? 1 : 0) != 0);            \
+            if (!ok)                                                                                                      \
+                failed = true;                                                                                            \
+            else if (leader && it + Cf::STAGES < iters)                                                                   \
+                issue(it + Cf::STAGES);                                                                                   \
+        } else {                                                                                                          \
+            group_sync();                                                                                                 \
+            CLB_FWD_ISSUE_CP(ST, it + Cf::STAGES)                                                                         \
+        }                                                                                                                 \
+        if (!failed) {                                                                                                    \
+            pool_store(z);                                                                                                \
             ++it;                                                                                                         \
-        else                                                                                                              \
-            failed = true;                                                                                                \
+        }                                                                                                                 \
     }
         CLB_FWD_STAGE(0)
         CLB_FWD_STAGE(1)
@@ -391,6 +413,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
             CLB_FWD_STAGE(3)
         }
 #undef CLB_FWD_STAGE
+#undef CLB_FWD_ISSUE_CP
     }
     if (failed && leader) {
         g_plane_error = 1;
@@ -545,10 +568,11 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         clb_tma::load_box_4d(dst, &xmap, -kLead, -1, ch_a, n0, &full[warp][st]);
         clb_tma::load_box_4d(dst + Cf::SLOT * 4, &xmap, -kLead, -1, ch_b, n0, &full[warp][st]);
     };
-    // cp.async staging (small images): the 16-byte pieces this lane moves, the same for every iteration
+    // cp.async staging (small images): the 16-byte pieces this lane moves, the same for every iteration; the source
+    // pointers run along with the iterations, cp_iters = iterations in which the piece's image exists
     constexpr int CPQ = Cf::UNITS / 32;
     const float *csrc[CPQ];
-    int cimg[CPQ];
+    int cp_iters[CPQ];
     uint32_t cdst[CPQ];
 #pragma unroll
     for (int q = 0; q < CPQ; ++q) {
@@ -556,19 +580,21 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         constexpr int W4 = S / 4;
         const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
         csrc[q] = x + ((size_t)(n_lo + img) * s.Ci + (slot ? ch_b : ch_a)) * HW + row * S + col4 * 4;
-        cimg[q] = n_lo + img;
+        cp_iters[q] = usable ? (n_hi - n_lo - img + Cf::NIMG - 1) / Cf::NIMG : 0;
         cdst[q] = clb_tma::smem_addr(wbase) + 4u * (uint32_t)(slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4);
     }
     const size_t cstep = (size_t)Cf::NIMG * s.Ci * HW;
-    auto issue_cp = [&](int it) {   // every lane; always commits, so that the group counts stay aligned
-        if (it < iters) {
-            const int st = it % XST;
-#pragma unroll
-            for (int q = 0; q < CPQ; ++q)   // an image past the end of the batch is not fetched (its upstream gradient reads as zero)
-                if (cimg[q] + it * Cf::NIMG < s.N) cp_async16(cdst[q] + (uint32_t)(st * Cf::STAGE_BYTES), csrc[q] + (size_t)it * cstep);
-        }
-        cp_async_commit();
-    };
+    // once per iteration in rising order; always commits, so that the group counts stay aligned; an image past the end of
+    // the part is not fetched (its upstream gradient reads as zero)
+#define CLB_BWD_ISSUE_CP(ST, IT)                                                                                          \
+    {                                                                                                                     \
+        _Pragma("unroll") for (int q = 0; q < CPQ; ++q)                                                                   \
+        {                                                                                                                 \
+            if ((IT) < cp_iters[q]) cp_async16_off<(ST) * Cf::STAGE_BYTES>(cdst[q], csrc[q]);                             \
+            csrc[q] += cstep;                                                                                             \
+        }                                                                                                                 \
+        cp_async_commit();                                                                                                \
+    }
     if (Cf::TMA) {
         if (lane == 0)
             for (int it = 0; it < XST && it < iters; ++it) issue(it);
@@ -576,7 +602,10 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         for (int i = lane * 4; i < XST * Cf::STAGE_FLOATS; i += 128)   // the halo is zeroed once; copies write the interior
             *reinterpret_cast<float4 *>(reinterpret_cast<float *>(wbase) + i) = make_float4(0.f, 0.f, 0.f, 0.f);
         __syncwarp();
-        for (int it = 0; it < XST; ++it) issue_cp(it);
+        CLB_BWD_ISSUE_CP(0, 0)
+        CLB_BWD_ISSUE_CP(1, 1)
+        CLB_BWD_ISSUE_CP(2, 2)
+        static_assert(XST == 3, "prologue of the cp.async ring");
     }
 
     // upstream gradient and arg-max: fetched one iteration ahead
@@ -597,19 +626,24 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     bool failed = false;
     int it = 0;
     __syncwarp();
+    // write-out: the lane's float4 units of the gradient tile are the cells its cp.async pieces have in a stage
+    float *pdst[CPQ];
+#pragma unroll
+    for (int q = 0; q < CPQ; ++q) {
+        const int u = lane + 32 * q;
+        constexpr int W4 = S / 4;
+        const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
+        pdst[q] = planes + (((size_t)(n_lo + img) * s.C + c) * 2 + slot) * HW + row * S + col4 * 4;
+    }
+    const size_t pstep = (size_t)Cf::NIMG * s.C * 2 * HW;
     auto finish = [&]() {
         // write the interior of the gradient planes out and clear it for the next iteration
-        const int nb0 = n_lo + it * Cf::NIMG;
 #pragma unroll
-        for (int q = 0; q < Cf::UNITS / 32; ++q) {
-            const int u = lane + 32 * q;
-            constexpr int W4 = S / 4;
-            const int col4 = u % W4, row = (u / W4) % S, slot = (u / (W4 * S)) & 1, img = u / (W4 * S * 2);
-            float *src = gt + slot * Cf::SLOT + img * Cf::IMG + (row + 1) * Cf::P + kLead + col4 * 4;
-            const float4 v = *reinterpret_cast<float4 *>(src);
-            *reinterpret_cast<float4 *>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (nb0 + img < n_hi)
-                *reinterpret_cast<float4 *>(planes + (((size_t)(nb0 + img) * s.C + c) * 2 + slot) * HW + row * S + col4 * 4) = v;
+        for (int q = 0; q < CPQ; ++q) {
+            const float4 v = lds_v4<Cf::GT_BYTES>(cdst[q]);
+            sts_v4_zero<Cf::GT_BYTES>(cdst[q]);
+            if (it < cp_iters[q]) *reinterpret_cast<float4 *>(pdst[q]) = v;
+            pdst[q] += pstep;
         }
         __syncwarp();
     };
@@ -638,7 +672,7 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
             if (Cf::TMA) {                                                                                                \
                 if (lane == 0 && it + XST < iters) issue(it + XST);                                                       \
             } else {                                                                                                      \
-                issue_cp(it + XST);                                                                                       \
+                CLB_BWD_ISSUE_CP(ST, it + XST)                                                                            \
             }                                                                                                             \
             finish();                                                                                                     \
             ++it;                                                                                                         \
@@ -648,6 +682,7 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
         CLB_BWD_STAGE(1)
         CLB_BWD_STAGE(2)
 #undef CLB_BWD_STAGE
+#undef CLB_BWD_ISSUE_CP
     }
     if (failed && lane == 0) {
         g_plane_error = 1;
