@@ -872,6 +872,8 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_w_plane32_kernel(const 
 __global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict__ planes, const int32_t *__restrict__ start,
                                                         const int32_t *__restrict__ entry, float *__restrict__ gx, int N, int Ci, int C, int HW4)
 {
+    // (Measured slower at batch 256: two units per thread a grid stride apart with eight streaming loads in flight,
+    // 0.32 -> 0.40 ms per step; walking the images last to first to catch what pass 1 left in L2, 0.32 -> 0.33 ms.)
     const long long total = (long long)N * Ci * HW4;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int e = (int)(i % HW4);
