@@ -89,6 +89,33 @@ int sm_count()
     }
     return n;
 }
+namespace {
+struct SmemEntry {
+    const void *kernel;
+    int dev, bytes;
+};
+std::mutex g_smem_mu;
+SmemEntry g_smem[256];
+int g_smem_n = 0;
+} // namespace
+cudaError_t ensure_dynamic_smem_ptr(const void *kernel, int bytes)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cudaGetLastError();
+    std::lock_guard<std::mutex> lock(g_smem_mu);
+    SmemEntry *slot = nullptr;
+    for (int i = 0; i < g_smem_n; ++i)
+        if (g_smem[i].kernel == kernel && g_smem[i].dev == dev) {
+            if (g_smem[i].bytes >= bytes) return cudaSuccess;
+            slot = &g_smem[i];
+            break;
+        }
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    if (!slot && g_smem_n < 256) slot = &g_smem[g_smem_n++]; // a full table only costs the repeated driver call
+    if (slot) *slot = SmemEntry{kernel, dev, bytes};
+    return cudaSuccess;
+}
 } // namespace clb_host
 
 extern "C" int clb_tune(int key, long long value)

@@ -156,6 +156,13 @@ inline int check_launch(int n = 1)
 }
 long long tune_get(int key); // clb_tune's current value
 int sm_count();              // multiprocessors of the current device, asked once per device
+// Raises a kernel's dynamic shared-memory limit to `bytes`; the driver is asked once per (kernel, device), later
+// calls with the same or a smaller size are a table look-up.
+cudaError_t ensure_dynamic_smem_ptr(const void *kernel, int bytes);
+template <typename K> inline cudaError_t ensure_dynamic_smem(K kernel, int bytes)
+{
+    return ensure_dynamic_smem_ptr(reinterpret_cast<const void *>(kernel), bytes);
+}
 // Launch tracing (clb_trace / clb_trace_report): while it is on, a traced launch is bracketed by two CUDA
 // events on its stream; off, the cost is one relaxed atomic load.
 bool trace_enabled();

@@ -1011,7 +1011,7 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
         const size_t smem2 = sizeof(GrpRec) * kGrpBatch + (size_t)nb * cg * 4 * PL * sizeof(float);
         if (smem2 <= 227 * 1024) {
             auto k = convtree_bwd_x_grp_kernel;
-            if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess) return check_launch(0);
+            if (clb_host::ensure_dynamic_smem(k, (int)smem2) != cudaSuccess) return check_launch(0);
             CLB_TRACED("convtree_bwd_x_grp_kernel", st, k<<<grid, 256, smem2, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx,
                                                                                      grp_start, grp_list, cg, nb, s, wmode));
             return check_launch();
@@ -1019,12 +1019,12 @@ static int launch_bwd_x(const void *gy, const void *x, const void *w, const int3
     }
     if (dtype == CLB_F32) {
         auto k = conv_bwd_x_kernel<float, FUSED>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
+        if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch();
         CLB_TRACED("conv_bwd_x_kernel", st, k<<<grid, 256, smem, st>>>((const float *)gy, (const float *)x, (const float *)w, sel, amax, (float *)gx, grp_start,
                                                                         grp_list, cg, nb, s, wmode));
     } else {
         auto k = conv_bwd_x_kernel<double, FUSED>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch();
+        if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch();
         CLB_TRACED("conv_bwd_x_kernel", st, k<<<grid, 256, smem, st>>>((const double *)gy, (const double *)x, (const double *)w, sel, amax, (double *)gx,
                                                                         grp_start, grp_list, cg, nb, s, wmode));
     }
@@ -1308,7 +1308,7 @@ extern "C" int clb_convtree_bwd(const void *gy, const void *x, const void *w, co
                                    gy_s, x_s, (const float *)w, sel, amax_s, partial + (size_t)sl * plan.parts * C * 28, tapgrad, ss, wmode));
                     ++launched;
                     auto go = [&](auto k) {
-                        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+                        if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return false;
                         CLB_TRACED("convtree_bwd_x_scatter_kernel", st,
                                    k<<<dim3((ss.N + nb - 1) / nb, G), sthreads, smem, st>>>(tapgrad, sel, amax_s, gx_s, grp_start, grp_list, cg, nb, ss));
                         return true;

@@ -1181,7 +1181,7 @@ static int launch_fwd_pair(const float *x, const float *w, const int32_t *sel, f
                            int blocks_per_sm, cudaStream_t st)
 {
     auto k = convtree_fwd_pair_kernel<PWH>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch(0);
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
     long long grid = (long long)sm_count() * blocks_per_sm;
     if (grid > units) grid = units;
@@ -1194,7 +1194,7 @@ static int launch_fwd(const float *x, const float *w, const int32_t *sel, float 
                       int blocks_per_sm, cudaStream_t st)
 {
     auto k = convtree_fwd_tile_kernel<WPT, PWH>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch(0);
     const long long units = (long long)((s.N + s.G - 1) / s.G) * s.C;
     long long grid = (long long)sm_count() * blocks_per_sm;
     if (grid > units) grid = units;
@@ -1230,12 +1230,12 @@ static int launch_fwd_chan(const float *x, const float *w, const int32_t *sel, f
     if (parts < 1) parts = 1;
     if (G % 2 == 0 && (G / 2) * I <= kFastThreads) { // image pairs: 64-bit tap loads, packed two-float FMAs
         auto k2 = convtree_fwd_chan_pair_kernel;
-        if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+        if (clb_host::ensure_dynamic_smem(k2, (int)smem) != cudaSuccess) return check_launch(0);
         CLB_TRACED("convtree_fwd_chan_pair_kernel", st, k2<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4));
         return check_launch();
     }
     auto k = convtree_fwd_chan_kernel<WPT>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch(0);
     CLB_TRACED("convtree_fwd_chan_kernel", st, k<<<dim3(parts, C), kFastThreads, smem, st>>>(x, w, sel, y, amax, s, q4));
     return check_launch();
 }
@@ -1367,7 +1367,7 @@ int clb_convtree_bwd_fast_f32(const float *gy, const float *x, const float *w, c
     const size_t tile_floats = gx ? (size_t)grid * 2 * s.G * Ci * H * W : 0;
     float *wpartial = tiles + ((tile_floats + 3) / 4) * 4;
     auto launch = [&](auto kern, int threads) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        if (clb_host::ensure_dynamic_smem(kern, (int)smem) != cudaSuccess) return false;
         CLB_TRACED("convtree_bwd_cls_kernel", st, kern<<<grid, threads, smem, st>>>(gy, x, w, sel, amax, gx, tiles, wpartial, s));
         return true;
     };

@@ -950,7 +950,7 @@ int launch_fwd(const float *x, const float *w, const int32_t *sel, float *y, uin
     CUtensorMap map;
     if (!clb_tma::make_plane_map(&map, x, N, Ci, S, S, Cf::P, Cf::R, Cf::NIMG)) return CLB_ERR_SHAPE;
     auto k = convtree_fwd_plane_kernel<S>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, Cf::SMEM) != cudaSuccess) return check_launch(0);
     const int parts = plane_parts(N, C, Cf::NIMG, Cf::WIDE ? 6 : 12);
     const Args a{N, Ci, C, wmode, parts};
     const long long tasks = (long long)C * parts;
@@ -969,7 +969,7 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     CUtensorMap map;
     if (!clb_tma::make_plane_map(&map, x, N, Ci, S, S, Cf::P, Cf::R, Cf::NIMG)) return CLB_ERR_SHAPE;
     auto k = convtree_bwd_plane_kernel<S>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, Cf::SMEM) != cudaSuccess) return check_launch(0);
     const int parts = bwd_parts<S>(N, C);
     const Args a{N, Ci, C, wmode, parts};
     const long long tasks = (long long)C * parts;
@@ -1064,7 +1064,7 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
         CUtensorMap map32;
         if (!clb_tma::make_plane_map(&map32, (const float *)x, N, Ci, 32, 32, BwdW32::P, BwdW32::R, 1)) return CLB_ERR_SHAPE;
         auto k32 = convtree_bwd_w_plane32_kernel;
-        if (cudaFuncSetAttribute(k32, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdW32::SMEM) != cudaSuccess) return check_launch(0);
+        if (clb_host::ensure_dynamic_smem(k32, BwdW32::SMEM) != cudaSuccess) return check_launch(0);
         cudaStream_t st32 = (cudaStream_t)stream;
         const Args a32{N, Ci, C, wmode, parts32};
         CLB_TRACED("convtree_bwd_w_plane32_kernel", st32,

@@ -359,7 +359,15 @@ __global__ void __launch_bounds__(256) group_sum_ce_finalize_kernel(const float 
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
             float t = 0.f;
-            for (int p = 0; p < parts; ++p) t += partial[((long long)p * k + c) * B + b];
+            int p = 0;
+            for (; p + 8 <= parts; p += 8) { // eight independent loads in flight, added in part order
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __ldg(partial + ((long long)(p + j) * k + c) * B + b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t += v[j];
+            }
+            for (; p < parts; ++p) t += __ldg(partial + ((long long)p * k + c) * B + b);
             sc[c] = t / tau;
             mx = fmaxf(mx, sc[c]);
         }
@@ -534,7 +542,7 @@ __device__ __forceinline__ void tree_gates(const TreeTables &tt, long long t, in
 }
 
 template <int V>
-__global__ void __launch_bounds__(256) logic_tree_fwd_kernel(const float *__restrict__ x, TreeTables tt, float *__restrict__ y, long long T,
+__global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__restrict__ x, TreeTables tt, float *__restrict__ y, long long T,
                                                              long long B, int wmode)
 {
     const int lane = threadIdx.x & 31;

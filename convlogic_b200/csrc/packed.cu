@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(256) thermometer_pack_kernel(const PIX *__rest
                                                                long long words32, int to_slab)
 {
     __shared__ unsigned sm[kThermoLevels * 32 * 9];
+    __shared__ unsigned lut[256]; // uint8 pixels: level mask of every pixel value
     const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
     const int p = blockIdx.x * 32 + lane;
     const long long n0 = (long long)blockIdx.y * 256;
@@ -120,15 +121,46 @@ __global__ void __launch_bounds__(256) thermometer_pack_kernel(const PIX *__rest
 #pragma unroll
         for (int i = 0; i < kThermoLevels; ++i) th[i] = i < nl ? __ldg(thr + l0 + i) : 0.f;
         unsigned word[kThermoLevels];
+        if constexpr (sizeof(PIX) == 1) {
+            // uint8 pixels take 256 values: thread t builds the level mask of value t once per block (the same float
+            // expression as below, so the bits are the same), a sample is then one byte load and one table look-up,
+            // and a 32x32 bit transpose in registers turns the 32 samples' level masks into the 32 levels' sample words.
+            __syncthreads(); // the previous pass no longer reads the table
+            {
+                const float v = __fdiv_rn((float)threadIdx.x, 255.0f);
+                unsigned m = 0u;
 #pragma unroll
-        for (int i = 0; i < kThermoLevels; ++i) word[i] = 0u;
+                for (int i = 0; i < kThermoLevels; ++i) m |= ((i < nl && v > th[i]) ? 1u : 0u) << i;
+                lut[threadIdx.x] = m;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const long long n = n0 + wv * 32 + j;
+                word[j] = (n < N && p < P) ? lut[__ldg(reinterpret_cast<const uint8_t *>(pix) + n * P + p)] : 0u;
+            }
+            unsigned m = 0x0000FFFFu;
+#pragma unroll
+            for (int j = 16; j != 0; j >>= 1) {
+#pragma unroll
+                for (int k = 0; k < 32; k = (k + j + 1) & ~j) {
+                    const unsigned t = ((word[k] >> j) ^ word[k + j]) & m;
+                    word[k + j] ^= t;
+                    word[k] ^= t << j;
+                }
+                m ^= m << (j >> 1);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kThermoLevels; ++i) word[i] = 0u;
 #pragma unroll 4
-        for (int j = 0; j < 32; ++j) {
-            const long long n = n0 + wv * 32 + j;
-            if (n < N && p < P) {
-                const float v = pixel_value<PIX>(pix + n * P + p);
+            for (int j = 0; j < 32; ++j) {
+                const long long n = n0 + wv * 32 + j;
+                if (n < N && p < P) {
+                    const float v = pixel_value<PIX>(pix + n * P + p);
 #pragma unroll
-                for (int i = 0; i < kThermoLevels; ++i) word[i] |= (v > th[i] ? 1u : 0u) << j;
+                    for (int i = 0; i < kThermoLevels; ++i) word[i] |= (v > th[i] ? 1u : 0u) << j;
+                }
             }
         }
         __syncthreads(); // the previous pass has been written out
@@ -1000,7 +1032,7 @@ extern "C" int clb_packed_convtree_slab(const void *x, const uint8_t *ops, const
     s.items = C * s.n_ug;
     const bool mux = tune_get(CLB_TUNE_SLAB_MUX) != 0;
     auto k = mux ? packed_convtree_slab_kernel<true> : packed_convtree_slab_kernel<false>;
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return check_launch(0);
+    if (clb_host::ensure_dynamic_smem(k, (int)smem) != cudaSuccess) return check_launch(0);
     int bps = (int)((227 * 1024) / (smem + 1024));
     const int by_regs = 512 / threads < 2 ? 2 : (512 / threads > 8 ? 8 : 512 / threads); // 112 registers per thread
     if (bps > by_regs) bps = by_regs;
