@@ -235,13 +235,14 @@ __global__ void __launch_bounds__(256) packed_logic_v4_kernel(const uint4 *__res
 template <typename V4, int M>
 __global__ void __launch_bounds__(256) packed_tree_kernel(const V4 *__restrict__ x, const int32_t *__restrict__ leaf,
                                                           const uint8_t *__restrict__ ops, V4 *__restrict__ y, long long out_dim,
-                                                          long long units)
+                                                          long long units, long long u_lo, long long u_n)
 {
+    // one launch covers units [u_lo, u_lo + u_n) of every row
     constexpr int L = 1 << M, G = L - 1;
     constexpr int W = sizeof(V4) / 4;
-    const long long total = out_dim * units;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long j = i / units, u = i % units;
+    const long long total = out_dim * u_n;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+        const long long j = t / u_n, u = u_lo + t % u_n, i = j * units + u;
         unsigned v[L][W];
 #pragma unroll
         for (int k = 0; k < L; ++k) {
@@ -896,18 +897,29 @@ extern "C" int clb_packed_tree(const void *x, const int32_t *leaf, const uint8_t
     cudaStream_t st = (cudaStream_t)stream;
     if (rowbytes % 16 == 0 && aligned_to(x, 16) && aligned_to(y, 16)) {
         const long long units = rowbytes / 16;
-        const int grid = flat_grid(out_dim * units, 256);
-        if (levels == 2)
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units));
-        else
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units));
+        // The leaves are gathered from all over the input: when it is larger than about three quarters of the 126 MB L2, the
+        // rows are walked in pieces (a range of units = a range of samples at a time), so that the piece of the input in
+        // use stays cached.  Measured on a 134 MB input: 0.64 ms in one piece, 0.50 in two or four, 0.56 in eight.
+        long long pieces = 1;
+        while (in_dim * rowbytes / pieces > (96LL << 20) && units % (pieces * 2) == 0 && units / (pieces * 2) >= 8) pieces *= 2;
+        const long long u_n = units / pieces;
+        const int grid = flat_grid(out_dim * u_n, 256);
+        for (long long pc = 0; pc < pieces; ++pc) {
+            if (levels == 2)
+                CLB_TRACED("packed_tree_kernel", st,
+                           packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
+            else
+                CLB_TRACED("packed_tree_kernel", st,
+                           packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
+        }
+        return check_launch((int)pieces);
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         const int grid = flat_grid(out_dim * units, 256);
         if (levels == 2)
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units));
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
         else
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units));
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
     } else {
         return CLB_ERR_SHAPE; // rows of 64-bit words only
     }
