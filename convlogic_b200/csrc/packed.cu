@@ -199,9 +199,13 @@ __global__ void __launch_bounds__(256) packed_logic_kernel(const U *__restrict__
                                                            const int64_t *__restrict__ ib, const uint8_t *__restrict__ ops,
                                                            U *__restrict__ y, long long out_dim, long long units)
 {
-    const long long total = out_dim * units;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long j = i / units, u = i % units;
+    // (neuron, unit) of the thread's items by carried additions: one 64-bit division per thread, none per item
+    const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    const long long dj = stride / units, du = stride - dj * units;
+    long long j = i0 / units, u = i0 - j * units;
+    for (long long i = i0; j < out_dim; i += stride, j += dj, u += du) {
+        if (u >= units) u -= units, ++j;
+        if (j >= out_dim) break;
         const OpMasks<U> m = op_masks<U>(ops[j]);
         y[i] = op_apply<U>(m, x[ia[j] * units + u], x[ib[j] * units + u]);
     }
@@ -212,9 +216,13 @@ __global__ void __launch_bounds__(256) packed_logic_v4_kernel(const uint4 *__res
                                                               const int64_t *__restrict__ ib, const uint8_t *__restrict__ ops,
                                                               uint4 *__restrict__ y, long long out_dim, long long units)
 {
-    const long long total = out_dim * units;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long j = i / units, u = i % units;
+    // (neuron, unit) of the thread's items by carried additions: one 64-bit division per thread, none per item
+    const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    const long long dj = stride / units, du = stride - dj * units;
+    long long j = i0 / units, u = i0 - j * units;
+    for (long long i = i0; j < out_dim; i += stride, j += dj, u += du) {
+        if (u >= units) u -= units, ++j;
+        if (j >= out_dim) break;
         const OpMasks<unsigned> m = op_masks<unsigned>(ops[j]);
         const uint4 a = __ldg(x + ia[j] * units + u), b = __ldg(x + ib[j] * units + u);
         uint4 r;
@@ -240,9 +248,14 @@ __global__ void __launch_bounds__(256) packed_tree_kernel(const V4 *__restrict__
     // one launch covers units [u_lo, u_lo + u_n) of every row
     constexpr int L = 1 << M, G = L - 1;
     constexpr int W = sizeof(V4) / 4;
-    const long long total = out_dim * u_n;
-    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-        const long long j = t / u_n, u = u_lo + t % u_n, i = j * units + u;
+    // (tree, unit) of the thread's items by carried additions: one 64-bit division per thread instead of two per item
+    const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    const long long dj = stride / u_n, du = stride - dj * u_n;
+    long long j = t0 / u_n, ur = t0 - j * u_n;
+    for (; j < out_dim; j += dj, ur += du) {
+        if (ur >= u_n) ur -= u_n, ++j;
+        if (j >= out_dim) break;
+        const long long u = u_lo + ur, i = j * units + u;
         unsigned v[L][W];
 #pragma unroll
         for (int k = 0; k < L; ++k) {
