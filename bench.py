@@ -229,6 +229,7 @@ def c3_algorithmic_bytes(batch):
         "logic_tree_fwd_kernel": fin + fout,
         "logic_tree_bwd_kernel": fout + fin,
         "row_segment_sum_kernel": fin,
+        "transpose_f32_kernel": 4 * fin,   # [batch, features] <-> [features, batch] in front of the flat part: two copies, read + write
     }
     out = {k: v * batch for k, v in per_image.items()}
     out["step"] = 15.80e6 * batch + 0.47e9   # activations + parameter / Adam traffic

@@ -72,6 +72,7 @@ _SIGNATURES = {
     "clb_group_sum_scratch_bytes": ([_i64, _i64, _i, _i], _sz),
     "clb_group_sum_fwd": ([_vp, _vp, _vp, _sz, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_group_sum_ce": ([_vp] * 6 + [_sz, _i64, _i64, _i, C.c_double, _vp], _i),
+    "clb_transpose_f32": ([_vp, _vp, _i64, _i64, _vp], _i),
     "clb_adam_step": ([_vp] * 4 + [_i64] + [C.c_double] * 5 + [_i64, _i, _vp], _i),
     "clb_group_sum_bwd_scaled": ([_vp, _vp, _vp, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_group_sum_bwd": ([_vp, _vp, _i64, _i64, _i, C.c_double, _i, _vp], _i),

@@ -392,6 +392,27 @@ __global__ void __launch_bounds__(256) group_sum_ce_finalize_kernel(const float 
     if (threadIdx.x == 0) *loss = red[0] / (float)B;
 }
 
+// out[c][r] = in[r][c]: 32 x 32 tiles through shared memory (33-float rows: no bank conflicts), both sides coalesced.
+// The flat layers work on feature-major activations [features][batch]; this is the copy between that and the
+// [batch][features] tensors of the layers around them.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float *__restrict__ in, float *__restrict__ out, long long R, long long Cc)
+{
+    __shared__ float tile[32][33];
+    const long long c0 = (long long)blockIdx.x * 32, r0 = (long long)blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long r = r0 + ty + 8 * i, c = c0 + tx;
+        if (r < R && c < Cc) tile[ty + 8 * i][tx] = __ldg(in + r * Cc + c);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long c = c0 + ty + 8 * i, r = r0 + tx;
+        if (r < R && c < Cc) out[c * R + r] = tile[tx][ty + 8 * i];
+    }
+}
+
 // Adam / AdamW over one flat parameter buffer (src/convlogic/model.py:179-180 uses torch.optim.AdamW): one thread per
 // four elements, 128-bit accesses.  step_size = lr / (1 - beta1^t), bc2_sqrt = sqrt(1 - beta2^t).
 __global__ void __launch_bounds__(256) adam_step_kernel(float *__restrict__ p, const float *__restrict__ g, float *__restrict__ m,
@@ -849,6 +870,17 @@ extern "C" int clb_group_sum_ce(const float *y, const int64_t *labels, float *sc
     CLB_TRACED("group_sum_ce_finalize_kernel", st,
                group_sum_ce_finalize_kernel<<<1, 256, 0, st>>>((const float *)scratch, labels, scores, dscore, loss, B, k, parts, (float)tau));
     return check_launch(2);
+}
+
+extern "C" int clb_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, void *stream)
+{
+    if (!in || !out || rows < 0 || cols < 0 || in == out) return CLB_ERR_ARG;
+    if (rows == 0 || cols == 0) return CLB_OK;
+    const long long gx = (cols + 31) / 32, gy = (rows + 31) / 32;
+    if (gy > 65535 || gx > 0x7fffffffLL) return CLB_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    CLB_TRACED("transpose_f32_kernel", st, transpose_f32_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, st>>>(in, out, rows, cols));
+    return check_launch();
 }
 
 extern "C" int clb_adam_step(float *p, const float *g, float *m, float *v, int64_t n, double lr, double beta1, double beta2, double eps,

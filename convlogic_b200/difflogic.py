@@ -11,7 +11,8 @@ import torch
 
 from . import ops
 from ._lib import W_ARGMAX, W_SOFTMAX
-from .functional import GradFactor, GroupSumCrossEntropyFunction, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction
+from .functional import (GradFactor, GroupSumCrossEntropyFunction, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction,
+                         to_feature_major)
 from .packbitstensor import PackBitsTensor
 
 
@@ -88,7 +89,7 @@ class LogicLayer(torch.nn.Module):
     def forward_cuda(self, x):
         assert x.is_cuda, f"x must be a CUDA tensor, got device: {x.device}"
         assert x.ndim == 2, x.ndim
-        x = x.transpose(0, 1).contiguous()  # feature-major; free when x came from another LogicLayer
+        x = to_feature_major(x)  # free when x came from another LogicLayer
         assert x.shape[0] == self.in_dim, (x.shape, self.in_dim)
         w = self.weights if self.weights.dtype == x.dtype else self.weights.to(x.dtype)
         args = (x, self.indices_0, self.indices_1, w, self.given_x_indices_of_y_start, self.given_x_indices_of_y)
@@ -230,7 +231,7 @@ class FusedLogicLayers(torch.nn.Module):
                 x = layer(x)
             return x
         assert x.shape[1] == first.in_dim, (x.shape, first.in_dim)
-        x_fm = x.transpose(0, 1).contiguous()
+        x_fm = to_feature_major(x)
         w = [l.weights for l in self.layers]
         if self.training:
             y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_SOFTMAX)

@@ -88,7 +88,10 @@ class GradBucket:
             self._rebind(p, lo, hi)
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self._group) == 1:
             return
-        self._works.append(dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=self._group, async_op=True))
+        # NCCL averages inside the collective; other backends (gloo on CPU ranks) sum, finish() then divides
+        self._in_op_average = self._average and dist.get_backend(self._group) == "nccl"
+        op = dist.ReduceOp.AVG if self._in_op_average else dist.ReduceOp.SUM
+        self._works.append(dist.all_reduce(self.flat[lo:hi], op=op, group=self._group, async_op=True))
 
     # ---- kernels write their gate gradients straight into the bucket
     def direct(self, on=True):
@@ -110,7 +113,7 @@ class GradBucket:
         works, self._works = self._works, []
         for w in works:
             w.wait()
-        if works and self._average:
+        if works and self._average and not getattr(self, "_in_op_average", False):
             self.flat.div_(dist.get_world_size(self._group))
         return len(works)
 

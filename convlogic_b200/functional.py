@@ -204,3 +204,24 @@ class GroupSumCrossEntropyFunction(torch.autograd.Function):
         (dscore,) = ctx.saved_tensors
         f, k, tau = ctx.meta
         return ops.group_sum_bwd(dscore, f, k, tau, scale=gloss.reshape(1).to(dscore.dtype).contiguous()), None, None, None
+
+
+class FeatureMajorFunction(torch.autograd.Function):
+    """[batch, features] -> contiguous [features, batch] (and the same copy back for the gradient) with the library's
+    tiled transpose instead of a strided torch copy: the layout change in front of the flat layers."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return ops.transpose2d(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ops.transpose2d(g.contiguous())
+
+
+def to_feature_major(x):
+    """Feature-major copy of a 2-D activation; free (a view) when x is the transposed view a flat layer returned."""
+    xt = x.transpose(0, 1)
+    if xt.is_contiguous() or not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.numel()):
+        return xt.contiguous()
+    return FeatureMajorFunction.apply(x)

@@ -562,6 +562,16 @@ def group_sum_ce(y_fm, labels, k, tau, want_scores=False):
     return loss, dscore, scores
 
 
+def transpose2d(x):
+    """Contiguous [cols, rows] copy of a contiguous float32 [rows, cols] tensor (one tiled kernel)."""
+    check_input(x)
+    if x.dim() != 2 or x.dtype != torch.float32 or not x.is_contiguous():
+        raise RuntimeError("convlogic_b200: transpose2d expects a contiguous 2-D float32 tensor")
+    out = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)
+    check(lib().clb_transpose_f32(ptr(x), ptr(out), x.shape[0], x.shape[1], stream()))
+    return out
+
+
 def adam_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, decoupled):
     """One Adam / AdamW step over flat fp32 buffers, in place."""
     check_input(p, g, m, v)

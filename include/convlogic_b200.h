@@ -337,6 +337,11 @@ int clb_group_sum_bwd_scaled(const void *gout, const void *scale, void *gy, int6
 int clb_group_sum_ce(const float *y, const int64_t *labels, float *scores, float *dscore, float *loss, void *scratch,
                      size_t scratch_bytes, int64_t F, int64_t B, int k, double tau, void *stream);
 
+/* out [cols][rows] = transpose of in [rows][cols], fp32, out != in.  The copy between the [batch][features] tensors of
+ * the conv blocks / the caller and the feature-major [features][batch] activations of the flat layers (the reference
+ * keeps [batch][features] and transposes inside its kernels' indexing, difflogic_kernel.cu:60-93).  rows <= 2 097 120. */
+int clb_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, void *stream);
+
 /* One Adam / AdamW step over a flat fp32 parameter buffer (all gate logits of a model in one array, their gradients in
  * another); stands in for torch.optim.AdamW as configured at src/convlogic/model.py:179-180.  step counts from 1;
  * decoupled != 0: AdamW (p *= 1 - lr * weight_decay), else the weight decay is added to the gradient.  All four arrays

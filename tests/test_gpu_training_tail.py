@@ -121,3 +121,19 @@ def test_three_step_trajectory_equals_torch_tail():
             assert float(diff.max()) <= 0.1 * 0.01, (step, n, float(diff.max()))
             off = float((diff > 1e-5 * float(q.abs().max())).float().mean())
             assert off <= 1e-3, (step, n, off)
+
+
+@pytest.mark.parametrize("rows,cols", [(256, 32768), (37, 1001), (1, 5), (1031, 64)])
+def test_tiled_transpose_equals_torch(rows, cols):
+    from convlogic_b200 import ops
+    from convlogic_b200.functional import to_feature_major
+
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = torch.randn(rows, cols, device="cuda", generator=g)
+    assert torch.equal(ops.transpose2d(x), x.t().contiguous())
+    xr = x.clone().requires_grad_(True)
+    y = to_feature_major(xr)
+    gy = torch.randn(cols, rows, device="cuda", generator=g)
+    y.backward(gy)
+    assert torch.equal(y, x.t()) and torch.equal(xr.grad, gy.t()) and xr.grad.is_contiguous()
+    assert to_feature_major(x.t()).data_ptr() == x.data_ptr()   # the transposed view of a flat layer's output: no copy
