@@ -156,8 +156,10 @@ class Ctx:
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        t0 = time.perf_counter()
         for i in range(steps):
             fn(i)
+        self.host_ms = (time.perf_counter() - t0) * 1e3   # host time to enqueue the timed steps (no device wait unless fn has one)
         e1.record()
         torch.cuda.synchronize()
         self.barrier()
@@ -182,12 +184,30 @@ def traced(fn, steps):
     return {k: (n / steps, ms / steps) for k, (n, ms) in rep.items()}
 
 
-def kernel_table(trace, alg_bytes, peak, top=5):
-    """The `top` slowest kernels of a traced step with their algorithmic bytes and HBM fraction."""
+# DRAM bytes (read + write) ncu counted for each kernel, summed over the kernel's launches in ONE step (c3, c2, c5) or
+# one 8192-image chunk (c4) of the default workload sizes: dram__bytes.sum over one capture of the same bench command
+# per workload (c5: the 64 000-neuron case of the same kernels, scaled by 4 to 256 000 neurons; its traffic grows with
+# the neuron count).  Other sizes report null.
+NCU_TRAFFIC = {
+    "c3": {"convtree_bwd_plane_kernel": 1929.2e6, "plane_sum_kernel": 1511.2e6, "logic_tree_bwd_kernel": 1110.9e6,
+           "row_segment_sum_kernel": 706.1e6, "convtree_fwd_plane_kernel": 377.8e6, "adam_step_kernel": 244.0e6,
+           "logic_tree_fwd_kernel": 194.8e6, "convtree_bwd_w_plane32_kernel": 98.0e6, "convtree_fwd_pair_kernel": 38.3e6,
+           "group_sum_partial_kernel": 87.6e6, "group_sum_bwd_kernel": 26.0e6},
+    "c4": {"packed_convtree_slab_kernel": 5536.8e6, "packed_tree_kernel": 1641.5e6, "group_popcount_kernel": 677.1e6,
+           "packed_rows_to_slab_kernel": 224.7e6, "thermometer_pack_kernel": 66.8e6},
+    "c2": {"convtree_fwd_pair_kernel": 37.3e6, "convtree_bwd_cls_kernel": 105.4e6, "convtree_bwd_post_kernel": 33.1e6},
+    "c5": {"logic_bwd_x_kernel": 7 * 4 * 1254.0e6, "logic_bwd_w_kernel": 7 * 4 * 741.0e6 + 4 * 288.5e6,
+           "logic_fwd_kernel": 7 * 4 * 707.5e6 + 4 * 227.0e6},
+}
+
+
+def kernel_table(trace, alg_bytes, peak, top=5, traffic=None):
+    """The `top` slowest kernels of a traced step with their algorithmic bytes, HBM fraction and measured DRAM traffic."""
     rows = []
     for name, (launches, ms) in sorted(trace.items(), key=lambda kv: -kv[1][1])[:top]:
         b = alg_bytes.get(name)
-        row = {"kernel": name, "launches_per_step": round(launches, 2), "ms_per_step": round(ms, 5), "algorithmic_bytes": b}
+        row = {"kernel": name, "launches_per_step": round(launches, 2), "ms_per_step": round(ms, 5), "algorithmic_bytes": b,
+               "traffic": (traffic or {}).get(name)}
         if b:
             row["achieved_gbs"] = b / (ms * 1e-3) / 1e9
             row["frac"] = row["achieved_gbs"] / peak
@@ -319,6 +339,7 @@ def run_c3(ctx, args, with_cpu=True):
     lib = _lib.lib()
     sampler = ClockSampler(ctx.local, rank == 0).start()
     ms = ctx.timed(step, args.steps, args.warmup)
+    host_ms = ctx.host_ms
     l0 = lib.clb_kernel_launches()
     step(0)
     launches = lib.clb_kernel_launches() - l0
@@ -330,7 +351,7 @@ def run_c3(ctx, args, with_cpu=True):
     imgs = C3_BATCH * world * args.steps
     peak, kind = measured_peaks()
     alg = c3_algorithmic_bytes(C3_BATCH)
-    kernels = kernel_table(trace, alg, peak, top=12)
+    kernels = kernel_table(trace, alg, peak, top=12, traffic=NCU_TRAFFIC["c3"])
     top = kernels[0] if kernels else {}
     traced_ms = sum(v[1] for v in trace.values())
     rec = {
@@ -343,9 +364,10 @@ def run_c3(ctx, args, with_cpu=True):
                         "device, the loss read back every step"},
         "gpu_launches": int(launches) * args.steps,
         "gpu_launches_per_step": int(launches),
+        "host_enqueue_ms_per_step": host_ms / args.steps,   # Python + ctypes + torch time to enqueue a step; below ms_per_step = the GPU binds
         "parameters": bucket.numel,
         "roofline": {"bound": "hbm", "kernel": top.get("kernel"), "achieved": top.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
-                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": None,
+                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": top.get("traffic"),
                      "step_frac": alg["step"] / (ms / args.steps * 1e-3) / 1e9 / peak, "step_algorithmic_bytes": alg["step"],
                      "kernels": kernels, "traced_library_ms_per_step": round(traced_ms, 5),
                      "note": "kernel times: CUDA events the library records around each launch on the launching stream, in a "
@@ -442,7 +464,7 @@ def run_c4(ctx, args):
     peak, kind = measured_peaks()
     per_image = {"packed_convtree_slab_kernel": 44672 + 65536 + 65536 + 49152, "packed_tree_kernel": 16384 + 81920,
                  "group_popcount_kernel": 81920 + 40, "thermometer_pack_kernel": 3072 + 11904}
-    kernels = kernel_table(trace, {k: v * chunk for k, v in per_image.items()}, peak)
+    kernels = kernel_table(trace, {k: v * chunk for k, v in per_image.items()}, peak, traffic=NCU_TRAFFIC["c4"] if chunk == 8192 else None)
     top = kernels[0] if kernels else {}
     alg = 1388200.0 * (hi - lo)   # layer-by-layer algorithmic bytes of this rank's shard
     rec = {
@@ -460,7 +482,7 @@ def run_c4(ctx, args):
         "gpu_launches": int(launches_chunk) * n_chunks * steps, "gpu_launches_per_chunk": int(launches_chunk), "blob_bytes": len(cnet.blob),
         "equals_float_eval": equals_float, "equals_module_path": equals_modules,
         "roofline": {"bound": "hbm", "kernel": top.get("kernel"), "achieved": top.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
-                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": None,
+                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": top.get("traffic"),
                      "step_frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "kernels": kernels,
                      "note": "kernels per chunk; step_frac: 1 388 200 layer-by-layer algorithmic bytes per image over the whole pipeline"},
         "clocks": clocks}
@@ -560,7 +582,7 @@ def run_c2(ctx, args):
     peak, kind = measured_peaks()
     alg = c2_algorithmic_bytes()
     names = {"convtree_fwd_pair_kernel": alg["fwd"], "convtree_fwd_tile_kernel": alg["fwd"], "convtree_bwd_cls_kernel": alg["bwd"]}
-    kernels = kernel_table(trace, names, peak)
+    kernels = kernel_table(trace, names, peak, traffic=NCU_TRAFFIC["c2"])
     top = kernels[0] if kernels else {}
     imgs = b * world * steps
     rec = {
@@ -575,7 +597,7 @@ def run_c2(ctx, args):
         "gpu_launches": int(launches) * steps,
         "kernel_ms": {k: round(v[1], 5) for k, v in trace.items()},
         "roofline": {"bound": "hbm", "kernel": top.get("kernel"), "achieved": top.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
-                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": None,
+                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": top.get("traffic"),
                      "step_frac": alg["step"] / (ms / steps * 1e-3) / 1e9 / peak, "kernels": kernels,
                      "note": "not HBM-bound: shared-memory gathers and instruction issue bind both kernels"},
         "clocks": clocks}
@@ -656,7 +678,7 @@ def run_c5(ctx, args):
         "logic_bwd_x_kernel": (depth - 1) * 3 * row,                # all but the first layer: gy + x + gx
         "group_sum_partial_kernel": row, "group_sum_bwd_kernel": row,
     }
-    kernels = kernel_table(trace, names, peak)
+    kernels = kernel_table(trace, names, peak, traffic=NCU_TRAFFIC["c5"] if (width, depth, batch) == (256000, 8, 1024) else None)
     top = kernels[0] if kernels else {}
     # forward: layer 1 in + out, the others 2 rows each, GroupSum read; backward: 3 rows per layer, the first gy + x
     # (the GroupSum gradient counted as fused into the last layer): 39.9 GB at 256000 x 8
@@ -669,7 +691,7 @@ def run_c5(ctx, args):
                    "l2": f"every activation is {row / 1e9:.2f} GB (> 126 MB L2)"},
         "gpu_launches": int(launches) * steps,
         "roofline": {"bound": "hbm", "kernel": top.get("kernel"), "achieved": top.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
-                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": None,
+                     "frac": top.get("frac"), "peak_kind": f"of {kind}", "algorithmic_bytes": top.get("algorithmic_bytes"), "traffic": top.get("traffic"),
                      "step_frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "kernels": kernels,
                      "note": f"whole step {alg / 1e9:.1f} GB algorithmic; per kernel: gathered rows counted once per use (12 B in + 4 B out per "
                              "neuron and sample in the forward)"},

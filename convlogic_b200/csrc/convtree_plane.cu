@@ -35,14 +35,20 @@ constexpr int kLead = 4; // columns in front of the image in a staged row: 16 by
 
 // Geometry of a square S x S layer (3x3 window, padding 1): staged pitch P, rows R, images per box.
 template <int S> struct Geo;
+// The forward kernel's tile may have its own pitch and plane size (FWD_P, FWD_IMG >= R * FWD_P): a warp's lanes are
+// (image pair, pooled row, column), and the pitch and the distance between pairs are chosen so that the 32 lanes of a tap
+// load fall into 32 different banks.  16x16: 2 rows x 16 columns, rows 48 floats apart (bank 16).  8x8: 4 rows x 8 columns,
+// rows 40 apart (banks 0, 8, 16, 24).  4x4: 4 pairs x 2 rows x 4 columns; rows 16 apart (pitch 8: the right halo of a row is
+// the always-zero lead cell of the next one), pairs 68 apart (banks 0, 4, 8, 12), a pair being images p and p + 4 of the
+// warp's eight.
 template <> struct Geo<16> {
-    static constexpr int P = 24, R = 18, FWD_NIMG = 2, BWD_NIMG = 1, BWD_WPT = 2;
+    static constexpr int P = 24, R = 18, FWD_NIMG = 2, BWD_NIMG = 1, BWD_WPT = 2, FWD_P = 24, FWD_IMG = 18 * 24;
 };
 template <> struct Geo<8> {
-    static constexpr int P = 20, R = 10, FWD_NIMG = 2, BWD_NIMG = 2, BWD_WPT = 1;
+    static constexpr int P = 20, R = 10, FWD_NIMG = 2, BWD_NIMG = 2, BWD_WPT = 1, FWD_P = 20, FWD_IMG = 10 * 20;
 };
 template <> struct Geo<4> {
-    static constexpr int P = 12, R = 6, FWD_NIMG = 8, BWD_NIMG = 8, BWD_WPT = 1;
+    static constexpr int P = 12, R = 6, FWD_NIMG = 8, BWD_NIMG = 8, BWD_WPT = 1, FWD_P = 8, FWD_IMG = 68;
 };
 
 struct Args {
@@ -157,15 +163,19 @@ template <int S> struct UseTma {
 // =========================================================================================== forward
 template <int S> struct FwdCfg {
     using G = Geo<S>;
-    static constexpr int P = G::P, R = G::R, NIMG = G::FWD_NIMG;
+    static constexpr int P = G::FWD_P, R = G::R, NIMG = G::FWD_NIMG;
     static constexpr int WO = S, HP = S / 2, WP = S / 2, I = HP * WP;
     static constexpr int TPI = HP * WO;                          // threads per image pair
     static constexpr bool WIDE = TPI >= kThreads;                // one group of 128 threads, else four warps on their own
     static constexpr int GROUPS = WIDE ? 1 : kThreads / 32;
-    static constexpr int IMG = R * P;                            // floats of one staged plane
+    static constexpr int IMG = G::FWD_IMG;                       // floats of one staged plane (R * P + padding)
     static constexpr int SLOT = (NIMG * IMG + 31) / 32 * 32;     // floats of one slot (NIMG planes of one channel)
     static constexpr int STAGE_BYTES = 2 * SLOT * 4;
     static constexpr bool TMA = UseTma<S>::value;
+    // pair p of a group = images (2p, 2p + 1) of its batch, or (p, p + NIMG / 2) when several pairs share a warp
+    static constexpr bool SPLIT_PAIRS = NIMG > 2;
+    static constexpr int PAIR_STRIDE = SPLIT_PAIRS ? IMG : 2 * IMG, SECOND = SPLIT_PAIRS ? (NIMG / 2) * IMG : IMG;
+    static_assert(IMG >= R * P && IMG % 4 == 0 && P % 4 == 0 && (!TMA || IMG == R * P), "tile geometry");
     static constexpr int STAGES = TMA ? 4 : 3;
     static constexpr int SMEM = GROUPS * STAGES * STAGE_BYTES;
     static constexpr int GSIZE = WIDE ? kThreads : 32;
@@ -178,7 +188,7 @@ template <int S> struct FwdCfg {
 template <int S, int ST> __device__ __forceinline__ void fwd_stage(const uint32_t (&toff)[8], const Gate2 (&g)[7], f32x2 (&z)[2])
 {
     using Cf = FwdCfg<S>;
-    constexpr int B = ST * Cf::STAGE_BYTES, ROWB = Cf::P * 4, IMGB = Cf::IMG * 4;
+    constexpr int B = ST * Cf::STAGE_BYTES, ROWB = Cf::P * 4, IMGB = Cf::SECOND * 4;
     {
         f32x2 v[8];
 #pragma unroll
@@ -286,7 +296,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     const int t = gt - pair_local * Cf::TPI;
     const int py = t / Cf::WO, ox = t - py * Cf::WO;
     unsigned char *gbase = smem_raw + (size_t)gid * Cf::STAGES * Cf::STAGE_BYTES;
-    const uint32_t thr = clb_tma::smem_addr(gbase) + 4u * (uint32_t)(2 * pair_local * Cf::IMG + 2 * py * Cf::P + ox);
+    const uint32_t thr = clb_tma::smem_addr(gbase) + 4u * (uint32_t)(pair_local * Cf::PAIR_STRIDE + 2 * py * Cf::P + ox);
     uint32_t toff[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -348,7 +358,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     // 2x2 pool: lanes ox and ox^1 hold the two columns of a window, each for both images of the pair.  The even lane
     // pools and stores the pair's first image, the odd lane the second; each hands the other the half it does not need.
     const bool odd = ox & 1;
-    const int my_img = 2 * pair_local + (odd ? 1 : 0);
+    const int my_img = Cf::SPLIT_PAIRS ? pair_local + (odd ? Cf::NIMG / 2 : 0) : 2 * pair_local + (odd ? 1 : 0);
     const int my_iters = (n_hi - n_lo - my_img + Cf::NIMG - 1) / Cf::NIMG;   // iterations in which that image exists
     const size_t o0 = ((size_t)(n_lo + my_img) * s.C + c) * I + py * Cf::WP + (ox >> 1);
     const size_t ostep = (size_t)Cf::NIMG * s.C * I;

@@ -717,34 +717,36 @@ __global__ void __launch_bounds__(256, 2) packed_convtree_slab_kernel(const uint
     const int toff = ub * s.SS + 2 * py * 2 * s.pwh + px;
     const int RS = 2 * s.pwh;
 
-    // items are (output channel c, slab group ug), ug fastest; a block takes every gridDim.x-th one and keeps the
-    // (c, ug) of its current and next two items by carrying additions instead of dividing
+    // items are (slab group ug, output channel c), c fastest: the blocks that run at the same time work on the same
+    // few slabs of ALL input channels (a few MB, L2-resident) instead of all slabs of a few channels, so the planes are
+    // fetched from DRAM once although every input channel is read by several output channels.  A block takes every
+    // gridDim.x-th item and keeps the (c, ug) of its current and next two items by carrying additions instead of dividing.
     const int first = blockIdx.x, stride = gridDim.x;
-    const int dc = stride / s.n_ug, dug = stride - dc * s.n_ug;
+    const int dug = stride / s.C, dc = stride - dug * s.C;
     auto advance = [&](int &c, int &ug) {
         c += dc, ug += dug;
-        if (ug >= s.n_ug) ug -= s.n_ug, ++c;
+        if (c >= s.C) c -= s.C, ++ug;
     };
-    int c0 = first / s.n_ug, ug0 = first - c0 * s.n_ug, c1 = c0, ug1 = ug0;
+    int ug0 = first / s.C, c0 = first - ug0 * s.C, c1 = c0, ug1 = ug0;
     advance(c1, ug1);
     int c2 = c1, ug2 = ug1;
     advance(c2, ug2);
-    if (c0 < s.C) fetch_rec(c0, rec[0]);
-    if (c1 < s.C) fetch_rec(c1, rec[1]);
+    if (ug0 < s.n_ug) fetch_rec(c0, rec[0]);
+    if (ug1 < s.n_ug) fetch_rec(c1, rec[1]);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads(); // records, copy offsets and halo zeros in place
-    if (c0 < s.C) stage(ug0, rec[0], tile);
+    if (ug0 < s.n_ug) stage(ug0, rec[0], tile);
     cp_async_commit();
     int cur = 0, r0 = 0; // tile buffer and record slot of the current item
-    for (; c0 < s.C; cur ^= 1, r0 = r0 == 2 ? 0 : r0 + 1) {
+    for (; ug0 < s.n_ug; cur ^= 1, r0 = r0 == 2 ? 0 : r0 + 1) {
         const int r1 = r0 == 2 ? 0 : r0 + 1, r2 = r1 == 2 ? 0 : r1 + 1;
         // one barrier per item: this item's planes and the next item's record have landed, and every thread is
         // done with the previous item, whose tile buffer and whose predecessor's record slot are refilled now
         cp_async_wait<0>();
         __syncthreads();
-        if (c2 < s.C) fetch_rec(c2, rec[r2]);
-        if (c1 < s.C) stage(ug1, rec[r1], tile + (cur ^ 1) * buf_elems);
+        if (ug2 < s.n_ug) fetch_rec(c2, rec[r2]);
+        if (ug1 < s.n_ug) stage(ug1, rec[r1], tile + (cur ^ 1) * buf_elems);
         cp_async_commit();
         const int c = c0, u0 = ug0 * s.UB;
         c0 = c1, ug0 = ug1, c1 = c2, ug1 = ug2;
