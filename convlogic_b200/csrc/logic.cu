@@ -561,6 +561,19 @@ __device__ __forceinline__ void tree_gates(const TreeTables &tt, long long t, in
         g[i].kb = __shfl_sync(0xffffffffu, mine.kb, 4 * i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, 4 * i);
     }
 }
+// the same with the lane's neuron already known (lanes >= 28: any value)
+__device__ __forceinline__ void tree_gates_of(const TreeTables &tt, long long n, int lane, int wmode, Gate<float> (&g)[7])
+{
+    const bool active = lane < 28;
+    float p[4];
+    quad_mixture(tree_row(tt, active ? lane : 0, n), wmode, lane & 3, active, p);
+    const Gate<float> mine = quad_gate(p, lane & 3);
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+        g[i].k1 = __shfl_sync(0xffffffffu, mine.k1, 4 * i), g[i].ka = __shfl_sync(0xffffffffu, mine.ka, 4 * i);
+        g[i].kb = __shfl_sync(0xffffffffu, mine.kb, 4 * i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, 4 * i);
+    }
+}
 
 template <int V>
 __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__restrict__ x, TreeTables tt, float *__restrict__ y, long long T,
@@ -568,12 +581,20 @@ __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__r
 {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    // The tables of a tree (leaf rows on lanes 0..7, the gates' neurons on lanes 0..27) are fetched one tree ahead, so that
+    // a tree's own chain of dependent loads is one hop (the rows, the logits) instead of two (index, then data).
+    int my_leaf = (warp < T && lane < 8) ? __ldg(tt.leaf + warp * 8 + lane) : 0;
+    int my_node = (warp < T && lane < 28) ? __ldg(tt.node + warp * 7 + (lane >> 2)) : 0;
     for (long long t = warp; t < T; t += nwarps) {
+        const long long tn = t + nwarps;
+        const int nx_leaf = (tn < T && lane < 8) ? __ldg(tt.leaf + tn * 8 + lane) : 0;
+        const int nx_node = (tn < T && lane < 28) ? __ldg(tt.node + tn * 7 + (lane >> 2)) : 0;
         Gate<float> g[7];
-        tree_gates(tt, t, lane, wmode, g);
+        tree_gates_of(tt, my_node, lane, wmode, g);
         const float *row[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
+        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__shfl_sync(0xffffffffu, my_leaf, k) * B;
+        my_leaf = nx_leaf, my_node = nx_node;
         for (long long b0 = (long long)lane * V; b0 < B; b0 += 32 * V) {
             float a[8][V], r[V];
 #pragma unroll
@@ -596,6 +617,8 @@ __global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__r
 {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    // (Fetching the index tables one tree ahead, as the forward kernel does, costs this kernel three more live registers at
+    // its limit of 128: measured 0.30 -> 0.33 ms at c3; with the row addresses re-made by shuffles every trip, 0.36 ms.)
     for (long long t = warp; t < T; t += nwarps) {
         Gate<float> g[7];
         tree_gates(tt, t, lane, wmode, g);
