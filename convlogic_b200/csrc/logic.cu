@@ -561,11 +561,10 @@ __device__ __forceinline__ void tree_gates(const TreeTables &tt, long long t, in
         g[i].kb = __shfl_sync(0xffffffffu, mine.kb, 4 * i), g[i].kab = __shfl_sync(0xffffffffu, mine.kab, 4 * i);
     }
 }
-// the same with the lane's neuron already known (lanes >= 28: any value)
-__device__ __forceinline__ void tree_gates_of(const TreeTables &tt, long long n, int lane, int wmode, Gate<float> (&g)[7])
+// the same with the lane's neuron already known (lanes >= 28: any value); p = the lane's four mixture entries
+__device__ __forceinline__ void tree_gates_of(const TreeTables &tt, long long n, int lane, int wmode, Gate<float> (&g)[7], float (&p)[4])
 {
     const bool active = lane < 28;
-    float p[4];
     quad_mixture(tree_row(tt, active ? lane : 0, n), wmode, lane & 3, active, p);
     const Gate<float> mine = quad_gate(p, lane & 3);
 #pragma unroll
@@ -590,7 +589,8 @@ __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__r
         const int nx_leaf = (tn < T && lane < 8) ? __ldg(tt.leaf + tn * 8 + lane) : 0;
         const int nx_node = (tn < T && lane < 28) ? __ldg(tt.node + tn * 7 + (lane >> 2)) : 0;
         Gate<float> g[7];
-        tree_gates_of(tt, my_node, lane, wmode, g);
+        float pq[4];
+        tree_gates_of(tt, my_node, lane, wmode, g, pq);
         const float *row[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) row[k] = x + (long long)__shfl_sync(0xffffffffu, my_leaf, k) * B;
@@ -611,20 +611,26 @@ __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__r
 }
 
 template <int V>
-__global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
+__global__ void __launch_bounds__(128, 3) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
                                                              float *__restrict__ tapgrad, float *__restrict__ gw0, float *__restrict__ gw1,
                                                              float *__restrict__ gw2, long long T, long long B, int wmode)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-    // (Fetching the index tables one tree ahead, as the forward kernel does, costs this kernel three more live registers at
-    // its limit of 128: measured 0.30 -> 0.33 ms at c3; with the row addresses re-made by shuffles every trip, 0.36 ms.)
+    // 128-thread blocks, three per SM: 168 registers, nothing spilled (at 256 threads x 2 blocks the limit of 128 registers
+    // spilled 144 bytes).  The index tables are fetched one tree ahead, as in the forward kernel.
+    int my_leaf = (warp < T && lane < 8) ? __ldg(tt.leaf + warp * 8 + lane) : 0;
+    int my_node = (warp < T && lane < 28) ? __ldg(tt.node + warp * 7 + (lane >> 2)) : 0;
     for (long long t = warp; t < T; t += nwarps) {
+        const long long tn = t + nwarps;
+        const int nx_leaf = (tn < T && lane < 8) ? __ldg(tt.leaf + tn * 8 + lane) : 0;
+        const int nx_node = (tn < T && lane < 28) ? __ldg(tt.node + tn * 7 + (lane >> 2)) : 0;
         Gate<float> g[7];
-        tree_gates(tt, t, lane, wmode, g);
+        float pq[4]; // the lane's four mixture entries, kept for the soft-max Jacobian at the end
+        tree_gates_of(tt, my_node, lane, wmode, g, pq);
         const float *row[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__ldg(tt.leaf + t * 8 + k) * B;
+        for (int k = 0; k < 8; ++k) row[k] = x + (long long)__shfl_sync(0xffffffffu, my_leaf, k) * B;
         float bs[28];
 #pragma unroll
         for (int i = 0; i < 28; ++i) bs[i] = 0.f;
@@ -676,11 +682,12 @@ __global__ void __launch_bounds__(256, 2) logic_tree_bwd_kernel(const float *__r
                 v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
             }
         }
-        float s4[4], p[4];
+        float s4[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) s4[k] = __shfl_sync(0xffffffffu, v[0], (lane & ~3) + k);
-        const long long n = lane < 28 ? tree_node(tt, t, lane) : 0;
-        if (wmode == CLB_W_SOFTMAX) quad_mixture(tree_row(tt, lane < 28 ? lane : 0, n), wmode, lane & 3, lane < 28, p); // again: not kept across the loop
+        const float(&p)[4] = pq;
+        const long long n = my_node;
+        my_leaf = nx_leaf, my_node = nx_node;
         const int q = lane & 3;
         const float q3 = (float)(q >> 1), q2 = (float)(q & 1);
         const float base = (q3 - q2) * s4[0] - q3 * s4[1] + (q2 - q3) * s4[2] + q3 * s4[3];
@@ -989,9 +996,9 @@ extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int
     int launched = 0;
     if (T > 0) {
         if (vec)
-            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4><<<2 * logic_grid(T), 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
         else
-            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1><<<logic_grid(T), 256, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1><<<2 * logic_grid(T), 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
         ++launched;
     }
     if (gx) {
