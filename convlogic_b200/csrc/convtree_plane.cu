@@ -879,13 +879,38 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_w_plane32_kernel(const 
 
 // Pass 2: gx[n][ch] = sum of the gradient planes (c, slot) that belong to input channel ch, in list order.
 // `start` [Ci + 1], `entry` [..] = 2*c + slot.  One float4 per thread; grid-stride over N * Ci * HW / 4.
-__global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict__ planes, const int32_t *__restrict__ start,
-                                                        const int32_t *__restrict__ entry, float *__restrict__ gx, int N, int Ci, int C, int HW4)
+// The first fin.blocks blocks of the same launch finish the gate gradient instead (one thread per gate: the per-part basis
+// sums added in part order, then the 16 gradients): one launch less per layer and step.
+struct GateFinish {
+    const float *partial, *w;
+    float *gw;
+    int parts, wmode, blocks;
+    long long ngates;
+};
+__device__ __forceinline__ void gate_finish_thread(const GateFinish &fin, long long gi)
 {
+    if (gi >= fin.ngates) return;
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < fin.parts; ++p) {
+        const float4 q = *reinterpret_cast<const float4 *>(fin.partial + ((size_t)p * fin.ngates + gi) * 4);
+        sums[0] += q.x, sums[1] += q.y, sums[2] += q.z, sums[3] += q.w;
+    }
+    gate_grad_store<float>(sums, fin.w + gi * 16, fin.wmode, fin.gw + gi * 16);
+}
+
+__global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict__ planes, const int32_t *__restrict__ start,
+                                                        const int32_t *__restrict__ entry, float *__restrict__ gx, int N, int Ci, int C, int HW4,
+                                                        GateFinish fin)
+{
+    if ((int)blockIdx.x < fin.blocks) {
+        gate_finish_thread(fin, (long long)blockIdx.x * blockDim.x + threadIdx.x);
+        return;
+    }
+    const long long block = (long long)blockIdx.x - fin.blocks, nblocks = (long long)gridDim.x - fin.blocks;
     // (Measured slower at batch 256: two units per thread a grid stride apart with eight streaming loads in flight,
     // 0.32 -> 0.40 ms per step; walking the images last to first to catch what pass 1 left in L2, 0.32 -> 0.33 ms.)
     const long long total = (long long)N * Ci * HW4;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    for (long long i = block * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
         const int e = (int)(i % HW4);
         const long long r = i / HW4;
         const int ch = (int)(r % Ci);
@@ -1103,14 +1128,11 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
     long long blocks = (total + 255) / 256;
     const long long cap = (long long)sm_count() * 32;
     if (blocks > cap) blocks = cap;
-    CLB_TRACED("plane_sum_kernel", st, plane_sum_kernel<<<(unsigned)blocks, 256, 0, st>>>(planes, ch_start, ch_entry, (float *)gx, N, Ci, C, HW4));
+    GateFinish fin{partial, wf, (float *)gw, parts, wmode, 0, (long long)C * 7};
+    if (gw) fin.blocks = (int)((fin.ngates + 255) / 256);
+    CLB_TRACED("plane_sum_kernel", st,
+               plane_sum_kernel<<<(unsigned)(blocks + fin.blocks), 256, 0, st>>>(planes, ch_start, ch_entry, (float *)gx, N, Ci, C, HW4, fin));
     ++launched;
-    if (gw) {
-        const long long ngates = (long long)C * 7;
-        CLB_TRACED("plane_gate_finalize_kernel", st,
-                   plane_gate_finalize_kernel<<<(int)((ngates + 127) / 128), 128, 0, st>>>(partial, wf, (float *)gw, parts, ngates, wmode));
-        ++launched;
-    }
     return check_launch(launched);
 }
 
