@@ -901,6 +901,7 @@ __device__ __forceinline__ void gate_finish_thread(const GateFinish &fin, long l
     gate_grad_store<float>(sums, fin.w + gi * 16, fin.wmode, fin.gw + gi * 16);
 }
 
+template <typename IDX>
 __global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict__ planes, const int32_t *__restrict__ start,
                                                         const int32_t *__restrict__ entry, float *__restrict__ gx, int N, int Ci, int C, int HW4,
                                                         GateFinish fin)
@@ -909,15 +910,16 @@ __global__ void __launch_bounds__(256) plane_sum_kernel(const float *__restrict_
         gate_finish_thread(fin, (long long)blockIdx.x * blockDim.x + threadIdx.x);
         return;
     }
-    const long long block = (long long)blockIdx.x - fin.blocks, nblocks = (long long)gridDim.x - fin.blocks;
+    // IDX: 32-bit when the output has fewer than 2^31 float4 units (the three index divisions per unit are then cheap)
+    const IDX block = (IDX)blockIdx.x - (IDX)fin.blocks, nblocks = (IDX)gridDim.x - (IDX)fin.blocks;
     // (Measured slower at batch 256: two units per thread a grid stride apart with eight streaming loads in flight,
     // 0.32 -> 0.40 ms per step; walking the images last to first to catch what pass 1 left in L2, 0.32 -> 0.33 ms.)
-    const long long total = (long long)N * Ci * HW4;
-    for (long long i = block * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
-        const int e = (int)(i % HW4);
-        const long long r = i / HW4;
-        const int ch = (int)(r % Ci);
-        const long long n = r / Ci;
+    const IDX total = (IDX)N * (IDX)Ci * (IDX)HW4;
+    for (IDX i = block * (IDX)blockDim.x + (IDX)threadIdx.x; i < total; i += nblocks * (IDX)blockDim.x) {
+        const int e = (int)(i % (IDX)HW4);
+        const IDX r = i / (IDX)HW4;
+        const int ch = (int)(r % (IDX)Ci);
+        const IDX n = r / (IDX)Ci;
         const int lo = start[ch], hi = start[ch + 1];
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 *base = reinterpret_cast<const float4 *>(planes) + (size_t)n * C * 2 * HW4 + e;
@@ -1133,8 +1135,12 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
     if (blocks > cap) blocks = cap;
     GateFinish fin{partial, wf, (float *)gw, parts, wmode, 0, (long long)C * 7};
     if (gw) fin.blocks = (int)((fin.ngates + 255) / 256);
-    CLB_TRACED("plane_sum_kernel", st,
-               plane_sum_kernel<<<(unsigned)(blocks + fin.blocks), 256, 0, st>>>(planes, ch_start, ch_entry, (float *)gx, N, Ci, C, HW4, fin));
+    if (total + (blocks + fin.blocks) * 256 < 0x7fffffffLL)
+        CLB_TRACED("plane_sum_kernel", st,
+                   plane_sum_kernel<unsigned><<<(unsigned)(blocks + fin.blocks), 256, 0, st>>>(planes, ch_start, ch_entry, (float *)gx, N, Ci, C, HW4, fin));
+    else
+        CLB_TRACED("plane_sum_kernel", st,
+                   plane_sum_kernel<long long><<<(unsigned)(blocks + fin.blocks), 256, 0, st>>>(planes, ch_start, ch_entry, (float *)gx, N, Ci, C, HW4, fin));
     ++launched;
     return check_launch(launched);
 }
