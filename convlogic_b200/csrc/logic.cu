@@ -343,46 +343,54 @@ __global__ void group_sum_finalize_kernel(const T *__restrict__ partial, T *__re
     out[b * k + c] = t / tau;
 }
 
-// GroupSum + cross-entropy in one finish (src/convlogic/model.py:137-152: CrossEntropyLoss on the GroupSum scores):
+// GroupSum + cross-entropy finish (src/convlogic/model.py:137-152: CrossEntropyLoss on the GroupSum scores):
 // scores[b][c] = (sum of the parts) / tau, loss = mean_b (logsumexp(scores[b]) - scores[b][label_b]), and
 // dscore[b][c] = (softmax(scores[b])[c] - [c == label_b]) / B, the gradient of the mean loss w.r.t. the scores.
-// ONE block: a thread owns samples b = tid, tid + 256, ...; the per-sample losses are added in a fixed tree.  k <= 32.
-__global__ void __launch_bounds__(256) group_sum_ce_finalize_kernel(const float *__restrict__ partial, const int64_t *__restrict__ labels,
-                                                                    float *__restrict__ scores, float *__restrict__ dscore,
-                                                                    float *__restrict__ loss, long long B, int k, int parts, float tau)
+// A warp per sample, lane c = class c (k <= 32): the parts are added in part order with all loads in flight, the
+// soft-max is two warp reductions.  The sample's loss overwrites partial[b] (part 0, class 0 of that sample: read by this
+// warp alone, before the write); group_sum_loss_mean_kernel adds the B losses in a fixed tree.
+__global__ void __launch_bounds__(256) group_sum_ce_sample_kernel(float *__restrict__ partial, const int64_t *__restrict__ labels,
+                                                                  float *__restrict__ scores, float *__restrict__ dscore, long long B, int k,
+                                                                  int parts, float tau)
+{
+    const int lane = threadIdx.x & 31;
+    const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (b >= B) return; // the whole warp
+    float sc = -3.0e38f;
+    if (lane < k) {
+        float t = 0.f;
+        int p = 0;
+        for (; p + 8 <= parts; p += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = partial[((long long)(p + j) * k + lane) * B + b];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t += v[j];
+        }
+        for (; p < parts; ++p) t += partial[((long long)p * k + lane) * B + b];
+        sc = t / tau;
+    }
+    float mx = sc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float e = lane < k ? expf(sc - mx) : 0.f;
+    const float sum = warp_sum<float>(e);
+    const int lab = (int)labels[b];
+    const bool lab_ok = lab >= 0 && lab < k;
+    const float sc_lab = __shfl_sync(0xffffffffu, sc, lab_ok ? lab : 0);
+    if (lane < k) {
+        if (scores != nullptr) scores[b * k + lane] = sc;
+        dscore[b * k + lane] = (e / sum - (lane == lab ? 1.f : 0.f)) / (float)B;
+    }
+    __syncwarp();
+    if (lane == 0) partial[b] = mx + logf(sum) - (lab_ok ? sc_lab : 0.f);
+}
+
+__global__ void __launch_bounds__(256) group_sum_loss_mean_kernel(const float *__restrict__ sample_loss, float *__restrict__ loss, long long B)
 {
     __shared__ float red[256];
     float mine = 0.f;
-    for (long long b = threadIdx.x; b < B; b += 256) {
-        float sc[32];
-        float mx = -3.0e38f;
-#pragma unroll 1
-        for (int c = 0; c < k; ++c) {
-            float t = 0.f;
-            int p = 0;
-            for (; p + 8 <= parts; p += 8) { // eight independent loads in flight, added in part order
-                float v[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = __ldg(partial + ((long long)(p + j) * k + c) * B + b);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t += v[j];
-            }
-            for (; p < parts; ++p) t += __ldg(partial + ((long long)p * k + c) * B + b);
-            sc[c] = t / tau;
-            mx = fmaxf(mx, sc[c]);
-        }
-        float sum = 0.f;
-        for (int c = 0; c < k; ++c) sum += expf(sc[c] - mx);
-        const float lse = mx + logf(sum);
-        const int lab = (int)labels[b];
-        const float inv = 1.f / sum, invB = 1.f / (float)B;
-        for (int c = 0; c < k; ++c) {
-            const float pr = expf(sc[c] - mx) * inv;
-            if (scores != nullptr) scores[b * k + c] = sc[c];
-            dscore[b * k + c] = (pr - (c == lab ? 1.f : 0.f)) * invB;
-        }
-        mine += lse - ((lab >= 0 && lab < k) ? sc[lab] : 0.f);
-    }
+    for (long long b = threadIdx.x; b < B; b += 256) mine += sample_loss[b];
     red[threadIdx.x] = mine;
     __syncthreads();
     for (int half = 128; half >= 1; half >>= 1) {
@@ -897,9 +905,10 @@ extern "C" int clb_group_sum_ce(const float *y, const int64_t *labels, float *sc
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid((unsigned)((B + 31) / 32), (unsigned)k, (unsigned)parts);
     CLB_TRACED("group_sum_partial_kernel", st, group_sum_partial_kernel<float><<<grid, 256, 0, st>>>(y, (float *)scratch, S, B, k));
-    CLB_TRACED("group_sum_ce_finalize_kernel", st,
-               group_sum_ce_finalize_kernel<<<1, 256, 0, st>>>((const float *)scratch, labels, scores, dscore, loss, B, k, parts, (float)tau));
-    return check_launch(2);
+    CLB_TRACED("group_sum_ce_sample_kernel", st,
+               group_sum_ce_sample_kernel<<<(unsigned)((B + 7) / 8), 256, 0, st>>>((float *)scratch, labels, scores, dscore, B, k, parts, (float)tau));
+    CLB_TRACED("group_sum_loss_mean_kernel", st, group_sum_loss_mean_kernel<<<1, 256, 0, st>>>((const float *)scratch, loss, B));
+    return check_launch(3);
 }
 
 extern "C" int clb_transpose_f32(const float *in, float *out, int64_t rows, int64_t cols, void *stream)

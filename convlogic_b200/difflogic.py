@@ -213,6 +213,9 @@ class FusedLogicLayers(torch.nn.Module):
         n0 = torch.stack([idx[1][0][n1], idx[1][1][n1]], -1).reshape(self.out_dim, 4)   # their four first-layer neurons
         leaf = torch.stack([idx[0][0][n0], idx[0][1][n0]], -1).reshape(self.out_dim, 8)
         node = torch.cat([n0, n1, n2], 1)
+        # every neuron of the first two layers sits in some tree (true of the models' halving stacks): the backward kernel
+        # then writes every gate gradient, and the buffers it is given need no clearing
+        self.covers_all = bool(n0.unique().numel() == layers[0].out_dim and n1.unique().numel() == layers[1].out_dim)
         order = torch.sort(leaf.reshape(-1), stable=True)                          # leaf slots grouped by feature
         start = torch.zeros(self.in_dim + 1, dtype=torch.int64)
         start[1:] = torch.cumsum(torch.bincount(leaf.reshape(-1), minlength=self.in_dim), 0)
@@ -234,10 +237,10 @@ class FusedLogicLayers(torch.nn.Module):
         x_fm = to_feature_major(x)
         w = [l.weights for l in self.layers]
         if self.training:
-            y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_SOFTMAX)
+            y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_SOFTMAX, self.covers_all)
         else:
             with torch.no_grad():
-                y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_ARGMAX)
+                y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_ARGMAX, self.covers_all)
         return y.transpose(0, 1)
 
     def extra_repr(self):

@@ -93,6 +93,19 @@ class GradBucket:
         op = dist.ReduceOp.AVG if self._in_op_average else dist.ReduceOp.SUM
         self._works.append(dist.all_reduce(self.flat[lo:hi], op=op, group=self._group, async_op=True))
 
+    def _ranges_ready(self, ranges):
+        """Several slices written by one backward kernel: neighbours in the bucket are exchanged as one piece."""
+        if not self._hooks:
+            return
+        merged = []
+        for lo, hi in sorted(ranges):
+            if merged and merged[-1][1] == lo:
+                merged[-1][1] = hi
+            else:
+                merged.append([lo, hi])
+        for lo, hi in merged:
+            self._slice_ready(lo, hi)
+
     # ---- kernels write their gate gradients straight into the bucket
     def direct(self, on=True):
         """From now on the backward kernels of this library write each layer's gate gradient straight into its slice
@@ -102,7 +115,8 @@ class GradBucket:
         active the slice is all-reduced the moment its kernel has been enqueued, as the hooks would do."""
         for p, (lo, hi) in zip(self.params, self.ranges):
             if on:
-                p._clb_grad_sink = (self.flat[lo:hi].view_as(p), lambda lo=lo, hi=hi: self._slice_ready(lo, hi) if self._hooks else None)
+                p._clb_grad_sink = (self.flat[lo:hi].view_as(p), lambda lo=lo, hi=hi: self._slice_ready(lo, hi) if self._hooks else None,
+                                    self._ranges_ready, (lo, hi))
             elif hasattr(p, "_clb_grad_sink"):
                 del p._clb_grad_sink
         self._direct = bool(on)

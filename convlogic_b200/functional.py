@@ -167,10 +167,10 @@ class LogicTreeFunction(torch.autograd.Function):
     """Three flat layers fused into one gate tree per neuron of the last one (feature-major in and out)."""
 
     @staticmethod
-    def forward(ctx, x_fm, w0, w1, w2, leaf, node, start, slots, wmode):
+    def forward(ctx, x_fm, w0, w1, w2, leaf, node, start, slots, wmode, covers_all=False):
         x_fm, w0, w1, w2 = x_fm.contiguous(), w0.contiguous(), w1.contiguous(), w2.contiguous()
         ctx.save_for_backward(x_fm, w0, w1, w2, leaf, node, start, slots)
-        ctx.wmode = wmode
+        ctx.wmode, ctx.covers_all = wmode, covers_all
         return ops.logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode)
 
     @staticmethod
@@ -179,13 +179,17 @@ class LogicTreeFunction(torch.autograd.Function):
         sinks = [_grad_sink(w) for w in (w0, w1, w2)]
         direct = ctx.wmode != W_ARGMAX and all(s is not None for s in sinks)
         gx, g0, g1, g2 = ops.logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy.contiguous(), start, slots, ctx.wmode,
-                                            need_gx=ctx.needs_input_grad[0], gw_out=[s[0] for s in sinks] if direct else None)
+                                            need_gx=ctx.needs_input_grad[0], gw_out=[s[0] for s in sinks] if direct else None,
+                                            clear_gw=not ctx.covers_all)
         if direct:
-            for s in sinks:
-                s[1]()
+            if all(len(s) > 2 and s[2] == sinks[0][2] for s in sinks):
+                sinks[0][2]([s[3] for s in sinks])   # one bucket: neighbouring slices go out as one exchange
+            else:
+                for s in sinks:
+                    s[1]()
         if ctx.wmode == W_ARGMAX or direct:
             g0 = g1 = g2 = None
-        return gx, g0, g1, g2, None, None, None, None, None
+        return gx, g0, g1, g2, None, None, None, None, None, None
 
 
 class GroupSumCrossEntropyFunction(torch.autograd.Function):

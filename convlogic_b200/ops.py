@@ -532,13 +532,17 @@ def logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode):
     return y
 
 
-def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True, gw_out=None):
+def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True, gw_out=None, clear_gw=True):
     """Gradients of ``logic_tree_fwd``: (gx [in, B] or None, gw0, gw1, gw2).  ``gw_out``: three contiguous tensors to
-    receive the gate gradients (cleared first: a neuron no tree reads keeps a zero gradient)."""
+    receive the gate gradients (cleared first: a neuron no tree reads keeps a zero gradient; ``clear_gw=False`` when the
+    caller knows that every neuron sits in a tree)."""
     check_input(x_fm, leaf, node, w0, w1, w2, gy, start, slots)
     t, b, in_dim = leaf.shape[0], x_fm.shape[1], x_fm.shape[0]
     tapgrad = torch.empty((max(t * 8, 1), b), dtype=torch.float32, device=x_fm.device)
-    gws = [torch.zeros_like(w) for w in (w0, w1, w2)] if gw_out is None else [g.zero_() for g in gw_out]
+    if gw_out is None:
+        gws = [torch.zeros_like(w) if clear_gw else torch.empty_like(w) for w in (w0, w1, w2)]
+    else:
+        gws = [g.zero_() if clear_gw else g for g in gw_out]
     gx = torch.empty_like(x_fm) if need_gx else None
     check(lib().clb_logic_tree_bwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(gy), ptr(tapgrad), ptr(gws[0]),
                                    ptr(gws[1]), ptr(gws[2]), ptr(gx), ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))

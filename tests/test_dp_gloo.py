@@ -106,6 +106,12 @@ def _worker(rank, world, port, fail_rank):
         assert bucket.finish() == len(params)
         assert torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
         assert all(p.grad.data_ptr() == bucket.flat[lo:hi].data_ptr() for p, (lo, hi) in zip(params, bucket.ranges))
+        # a kernel that writes several neighbouring slices (the fused flat layers) reports them together: one exchange
+        bucket.flat.fill_(float(rank + 1))
+        sinks = [_grad_sink(p) for p in params]
+        assert all(len(s) == 4 and s[2] == sinks[0][2] for s in sinks)
+        sinks[0][2]([s[3] for s in sinks])
+        assert bucket.finish() == 1 and torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
         bucket.remove_overlap()
         bucket.direct(False)
         assert all(_grad_sink(p) is None for p in params)
