@@ -302,8 +302,11 @@ def run_c3(ctx, args, with_cpu=True):
         else:
             loss = head(body(x), lab)
         loss.backward()
-        bucket.finish()
-        opt.step()
+        if args.torch_tail:
+            bucket.finish()
+            opt.step()
+        else:
+            opt.finish_and_step()   # the update of all but the last-exchanged slice runs under that exchange
         return loss
 
     def step(i):

@@ -38,7 +38,7 @@ class GradBucket:
             p.grad = self.flat[off:off + p.numel()].view_as(p)
             self.ranges.append((off, off + p.numel()))
             off += p.numel()
-        self._works, self._hooks, self._group, self._average = [], [], None, True
+        self._works, self._work_ranges, self._hooks, self._group, self._average = [], [], [], None, True
         self.rebinds = 0
         self._direct = False
 
@@ -79,7 +79,7 @@ class GradBucket:
     def remove_overlap(self):
         for h in self._hooks:
             h.remove()
-        self._hooks, self._works = [], []
+        self._hooks, self._works, self._work_ranges = [], [], []
 
     def _slice_ready(self, lo, hi, p=None):
         if p is not None:
@@ -92,6 +92,7 @@ class GradBucket:
         self._in_op_average = self._average and dist.get_backend(self._group) == "nccl"
         op = dist.ReduceOp.AVG if self._in_op_average else dist.ReduceOp.SUM
         self._works.append(dist.all_reduce(self.flat[lo:hi], op=op, group=self._group, async_op=True))
+        self._work_ranges.append((lo, hi))
 
     def _ranges_ready(self, ranges):
         """Several slices written by one backward kernel: neighbours in the bucket are exchanged as one piece."""
@@ -124,12 +125,24 @@ class GradBucket:
 
     def finish(self):
         """Waits for the slices in flight (the waits are stream-side for NCCL) and applies the averaging."""
-        works, self._works = self._works, []
+        works, self._works, self._work_ranges = self._works, [], []
         for w in works:
             w.wait()
         if works and self._average and not getattr(self, "_in_op_average", False):
             self.flat.div_(dist.get_world_size(self._group))
         return len(works)
+
+    def finish_but_last(self):
+        """Waits for every exchange in flight except the one issued last (the first layer's small gradient, which the
+        backward pass produces at its very end) and returns that one's element range [lo, hi), or None when nothing stays
+        in flight.  Only with averaging inside the collective (NCCL): otherwise the same as ``finish()``."""
+        if len(self._works) < 2 or (self._average and not getattr(self, "_in_op_average", False)):
+            self.finish()
+            return None
+        for w in self._works[:-1]:
+            w.wait()
+        self._works, self._work_ranges = self._works[-1:], self._work_ranges[-1:]
+        return self._work_ranges[0]
 
     def allreduce(self, group=None, average=True, async_op=False):
         """Sum (or mean) over ranks.  A no-op without an initialised process group."""
@@ -203,11 +216,30 @@ class FlatAdam:
         del set_to_none
         self.bucket.zero()
 
-    def step(self):
+    def _update(self, lo, hi):
         from . import ops
 
+        if hi > lo:
+            ops.adam_step(self.params[lo:hi], self.bucket.flat[lo:hi], self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi], self.lr, self.betas[0],
+                          self.betas[1], self.eps, self.weight_decay, self.steps, self.decoupled)
+
+    def step(self):
         if not self.bucket._direct:
             self.bucket._rebind_all()  # gradients that autograd re-allocated are copied into the bucket first
         self.steps += 1
-        ops.adam_step(self.params, self.bucket.flat, self.exp_avg, self.exp_avg_sq, self.lr, self.betas[0], self.betas[1], self.eps,
-                      self.weight_decay, self.steps, self.decoupled)
+        self._update(0, self.bucket.numel)
+
+    def finish_and_step(self):
+        """``bucket.finish()`` + ``step()`` for data-parallel runs with the overlapped exchange: the update of everything
+        but the slice whose exchange was issued last runs while that exchange is still in flight, the update of that
+        slice after it.  Same result as the two calls."""
+        left = self.bucket.finish_but_last()
+        if left is None:
+            return self.step()
+        if not self.bucket._direct:
+            self.bucket._rebind_all()
+        self.steps += 1
+        self._update(0, left[0])
+        self._update(left[1], self.bucket.numel)
+        self.bucket.finish()
+        self._update(left[0], left[1])

@@ -112,6 +112,10 @@ def _worker(rank, world, port, fail_rank):
         assert all(len(s) == 4 and s[2] == sinks[0][2] for s in sinks)
         sinks[0][2]([s[3] for s in sinks])
         assert bucket.finish() == 1 and torch.allclose(bucket.flat, torch.full_like(bucket.flat, 1.5))
+        # all exchanges but the last-issued one: gloo sums and finish() divides, so the call degrades to finish()
+        for s in sinks:
+            s[1]()
+        assert bucket.finish_but_last() is None and not bucket._works
         bucket.remove_overlap()
         bucket.direct(False)
         assert all(_grad_sink(p) is None for p in params)

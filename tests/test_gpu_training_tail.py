@@ -137,3 +137,28 @@ def test_tiled_transpose_equals_torch(rows, cols):
     y.backward(gy)
     assert torch.equal(y, x.t()) and torch.equal(xr.grad, gy.t()) and xr.grad.is_contiguous()
     assert to_feature_major(x.t()).data_ptr() == x.data_ptr()   # the transposed view of a flat layer's output: no copy
+
+
+def test_adam_update_in_two_pieces_equals_one_step():
+    """FlatAdam.finish_and_step updates the slice whose exchange is still in flight after the rest: with a stand-in for the
+    exchange (one GPU), parameters and moments must equal those of a plain step, bit for bit."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import dp
+
+    def make():
+        torch.manual_seed(11)
+        m = torch.nn.Sequential(cb.LogicLayer(32, 96), cb.LogicLayer(96, 48), cb.GroupSum(8, 2.0)).cuda()
+        bucket = dp.GradBucket(m)
+        return m, bucket, cb.FlatAdam(bucket, lr=0.01)
+
+    (ma, ba, oa), (mb, bb, ob) = make(), make()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    for step in range(2):
+        grad = torch.randn(ba.numel, device="cuda", generator=g)
+        ba.flat.copy_(grad), bb.flat.copy_(grad)
+        oa.step()
+        lo, hi = bb.ranges[0]                      # pretend the first layer's exchange is the one still in flight
+        bb.finish_but_last = lambda lo=lo, hi=hi: (lo, hi)
+        ob.finish_and_step()
+        assert oa.steps == ob.steps == step + 1
+        assert torch.equal(oa.params, ob.params) and torch.equal(oa.exp_avg, ob.exp_avg) and torch.equal(oa.exp_avg_sq, ob.exp_avg_sq)
