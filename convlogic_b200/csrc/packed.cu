@@ -530,39 +530,11 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// a[w] = gate(a[w], b[w]) for N words; `op` is uniform over the block, so the switch does not diverge.  Every case is
-// ONE lop3 per word written IN PLACE (the "+r" constraint): with plain C expressions the sixteen cases of a switch end
-// in different registers and the compiler reconciles them with moves at the join -- more moves than logic operations.
-// Truth-table immediates for (A, B) = (0xF0, 0xCC); the third operand is unused (every table is symmetric in it).
-template <int N>
-__device__ __forceinline__ void gate_words(int op, unsigned (&a)[N], const unsigned (&b)[N])
-{
-#define CLB_GATE_CASE(i, lut)                                                                                                    \
-    case i:                                                                                                                      \
-        _Pragma("unroll") for (int w = 0; w < N; ++w) asm("lop3.b32 %0, %0, %1, %1, " #lut ";" : "+r"(a[w]) : "r"(b[w]));        \
-        break;
-    switch (op & 15) {
-        CLB_GATE_CASE(0, 0x00)  // 0
-        CLB_GATE_CASE(1, 0xC0)  // A & B
-        CLB_GATE_CASE(2, 0x30)  // A & ~B
-        CLB_GATE_CASE(3, 0xF0)  // A
-        CLB_GATE_CASE(4, 0x0C)  // ~A & B
-        CLB_GATE_CASE(5, 0xCC)  // B
-        CLB_GATE_CASE(6, 0x3C)  // A ^ B
-        CLB_GATE_CASE(7, 0xFC)  // A | B
-        CLB_GATE_CASE(8, 0x03)  // ~(A | B)
-        CLB_GATE_CASE(9, 0xC3)  // ~(A ^ B)
-        CLB_GATE_CASE(10, 0x33) // ~B
-        CLB_GATE_CASE(11, 0xF3) // A | ~B
-        CLB_GATE_CASE(12, 0x0F) // ~A
-        CLB_GATE_CASE(13, 0xCF) // ~A | B
-        CLB_GATE_CASE(14, 0x3F) // ~(A & B)
-        CLB_GATE_CASE(15, 0xFF) // 1
-    }
-#undef CLB_GATE_CASE
-}
-
-// The same sixteen cases behind ONE indexed branch (brx.idx over a table of the sixteen case labels) instead of the
+// a[w] = gate(a[w], b[w]) for eight words; `op` is uniform over the block.  Every case is ONE lop3 per word written IN PLACE
+// (the "+r" constraint): with plain C expressions the sixteen cases end in different registers and the compiler reconciles
+// them with moves at the join -- more moves than logic operations.  Truth-table immediates for (A, B) = (0xF0, 0xCC); the
+// third operand is unused (every table is symmetric in it).
+// The sixteen cases sit behind ONE indexed branch (brx.idx over a table of the sixteen case labels) instead of the
 // compare-and-branch tree a C switch compiles to (13 control instructions per gate, more than its 8 lop3).  `op` is uniform
 // over the block, so the branch is declared uniform.  Eight words, in place.
 __device__ __forceinline__ void gate_words_brx(int op, unsigned (&a)[8], const unsigned (&b)[8])
