@@ -134,10 +134,12 @@ __global__ void __launch_bounds__(256) thermometer_pack_kernel(const PIX *__rest
                 lut[threadIdx.x] = m;
             }
             __syncthreads();
+            {
+                const long long nb = n0 + wv * 32;                  // first of the warp's 32 samples
+                const int live = p < P ? (int)min((long long)32, N - nb) : 0; // how many of them exist (<= 0: none)
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(pix) + nb * P + p;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const long long n = n0 + wv * 32 + j;
-                word[j] = (n < N && p < P) ? lut[__ldg(reinterpret_cast<const uint8_t *>(pix) + n * P + p)] : 0u;
+                for (int j = 0; j < 32; ++j) word[j] = j < live ? lut[__ldg(src + (long long)j * P)] : 0u;
             }
             unsigned m = 0x0000FFFFu;
 #pragma unroll
@@ -168,25 +170,30 @@ __global__ void __launch_bounds__(256) thermometer_pack_kernel(const PIX *__rest
         for (int i = 0; i < kThermoLevels; ++i) sm[(i * 32 + lane) * 9 + wv] = word[i];
         __syncthreads();
         const long long w0 = n0 / 32; // first 32-bit word of this block in a row
+        // Write-out: element e = thread + 256 * level, so a thread's (position, word) never changes and only the level
+        // walks: one shared load, one store and two additions per level.
         if (!to_slab) {
-            // element e -> (level, position, word): 8 consecutive lanes write the 32 bytes of one row
-            for (int e = threadIdx.x; e < nl * 256; e += 256) {
-                const int w = e & 7, pos = (e >> 3) & 31, i = e >> 8;
-                const int pp = blockIdx.x * 32 + pos;
-                if (pp < P && w0 + w < words32) out[((long long)(l0 + i) * P + pp) * words32 + w0 + w] = sm[(i * 32 + pos) * 9 + w];
+            // (level, position, word): 8 consecutive lanes write the 32 bytes of one row
+            const int w = threadIdx.x & 7, pos = (threadIdx.x >> 3) & 31;
+            const int pp = blockIdx.x * 32 + pos;
+            if (pp < P && w0 + w < words32) {
+                unsigned *dst = out + ((long long)l0 * P + pp) * words32 + w0 + w;
+                const unsigned *srcw = sm + pos * 9 + w;
+                const long long dstep = (long long)P * words32;
+                for (int i = 0; i < nl; ++i) dst[i * dstep] = srcw[i * 32 * 9];
             }
         } else {
             // slab layout [feature channel][U][HW] of 16-byte units: 4 consecutive lanes write one unit
             const long long U = words32 / 4;
-            for (int e = threadIdx.x; e < nl * 256; e += 256) {
-                const int q = e & 3, pos = (e >> 2) & 31, u2 = (e >> 7) & 1, i = e >> 8;
-                const int pp = blockIdx.x * 32 + pos;
-                const long long u = w0 / 4 + u2;
-                if (pp < P && u < U) {
-                    const int c = pp / HW, yx = pp - c * HW;
-                    const long long ch = (long long)(l0 + i) * (P / HW) + c;
-                    out[((ch * U + u) * HW + yx) * 4 + q] = sm[(i * 32 + pos) * 9 + u2 * 4 + q];
-                }
+            const int q = threadIdx.x & 3, pos = (threadIdx.x >> 2) & 31, u2 = (threadIdx.x >> 7) & 1;
+            const int pp = blockIdx.x * 32 + pos;
+            const long long u = w0 / 4 + u2;
+            if (pp < P && u < U) {
+                const int c = pp / HW, yx = pp - c * HW;
+                unsigned *dst = out + ((((long long)l0 * (P / HW) + c) * U + u) * HW + yx) * 4 + q;
+                const unsigned *srcw = sm + pos * 9 + u2 * 4 + q;
+                const long long dstep = (long long)(P / HW) * U * HW * 4;
+                for (int i = 0; i < nl; ++i) dst[i * dstep] = srcw[i * 32 * 9];
             }
         }
     }
