@@ -285,7 +285,12 @@ def run_c3(ctx, args, with_cpu=True):
         bucket = dp.GradBucket(net).overlap(average=True)
         opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
     else:                 # the library's own tail: GroupSum + cross-entropy kernel, gradients written into the bucket, flat Adam
-        body, head = net[:-1], cb.GroupSumCrossEntropy(net[-1].k, net[-1].tau)
+        if isinstance(net[-2], cb.FusedLogicLayers) and not args.separate_head:
+            # the fused flat layers and the loss head as one autograd node (the gradient tensor between them is never written)
+            body, trees, gs = net[:-2], net[-2], net[-1]
+            head = lambda feats, lab: trees.cross_entropy(feats, lab, gs.k, gs.tau)  # noqa: E731
+        else:
+            body, head = net[:-1], cb.GroupSumCrossEntropy(net[-1].k, net[-1].tau)
         bucket = dp.GradBucket(net).direct().overlap(average=True)
         opt = cb.FlatAdam(bucket, lr=0.01)
     sets = 4
@@ -910,6 +915,7 @@ def main():
                     help="override the library's slice size of the two-pass conv backward (0 = whole batch in one slice)")
     ap.add_argument("--plane-kernels", type=int, default=None, choices=[0, 1],
                     help="override the library's choice of the TMA-staged many-channel conv kernels (0 = the older staged kernels)")
+    ap.add_argument("--separate-head", action="store_true", help="c3: GroupSumCrossEntropy as its own autograd node behind the fused flat layers")
     ap.add_argument("--torch-tail", action="store_true",
                     help="c3: torch's cross-entropy, .grad accumulation and fused Adam instead of the library's fused tail")
     ap.add_argument("--slab-mux", type=int, default=None, choices=[0, 1], help="override how the packed slab kernel applies gates")

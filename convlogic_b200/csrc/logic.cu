@@ -618,10 +618,20 @@ __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__r
     }
 }
 
-template <int V>
+// HEAD: the upstream gradient is not a tensor [T][B] but the GroupSum + cross-entropy head's d loss / d score [B][k]:
+// tree t belongs to class t / S and gy[t][b] = dscore[b][class] / (tau / scale), exactly what group_sum_bwd_kernel would
+// have written -- the [T][B] gradient is then neither written nor read.
+struct TreeHead {
+    const float *dscore, *scale; // scale: the scalar gradient that reaches the loss, on the device
+    int k;
+    unsigned S;                  // trees per class
+    float tau;
+};
+
+template <int V, bool HEAD>
 __global__ void __launch_bounds__(128, 3) logic_tree_bwd_kernel(const float *__restrict__ x, TreeTables tt, const float *__restrict__ gy,
                                                              float *__restrict__ tapgrad, float *__restrict__ gw0, float *__restrict__ gw1,
-                                                             float *__restrict__ gw2, long long T, long long B, int wmode)
+                                                             float *__restrict__ gw2, long long T, long long B, int wmode, TreeHead head)
 {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -646,7 +656,14 @@ __global__ void __launch_bounds__(128, 3) logic_tree_bwd_kernel(const float *__r
             float a[8][V], dz[V], dg[4][V];
 #pragma unroll
             for (int k = 0; k < 8; ++k) vload<float, V>(row[k] + b0, a[k]);
-            vload<float, V>(gy + t * B + b0, dz);
+            if (HEAD) {
+                const float taus = head.tau / __ldg(head.scale);
+                const float *ds = head.dscore + b0 * head.k + (unsigned)t / head.S;
+#pragma unroll
+                for (int e = 0; e < V; ++e) dz[e] = __ldg(ds + e * head.k) / taus;
+            } else {
+                vload<float, V>(gy + t * B + b0, dz);
+            }
 #pragma unroll
             for (int e = 0; e < V; ++e) {
                 const float g0 = gate_eval<float>(g[0], a[0][e], a[1][e]), g1 = gate_eval<float>(g[1], a[2][e], a[3][e]);
@@ -991,23 +1008,29 @@ extern "C" int clb_logic_tree_fwd(const float *x, const int32_t *leaf, const int
 
 // tapgrad: scratch of T*8*B floats.  gw0/gw1/gw2 must be zeroed by the caller: neurons no tree uses keep zero.
 // start int64 [in_dim + 1], list int32 [T*8]: the leaf slots (t*8 + k) grouped by the input feature they read.
-extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
-                                  const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2, float *gx, const int64_t *start,
-                                  const int32_t *list, int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)
+static int logic_tree_bwd_impl(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
+                               const float *gy, const TreeHead *head, float *tapgrad, float *gw0, float *gw1, float *gw2, float *gx,
+                               const int64_t *start, const int32_t *list, int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)
 {
-    if (!tree_args_ok(x, leaf, node, w0, w1, w2, T, B, wmode) || !gy || !tapgrad || !gw0 || !gw1 || !gw2 || in_dim <= 0) return CLB_ERR_ARG;
+    if (!tree_args_ok(x, leaf, node, w0, w1, w2, T, B, wmode) || (!gy && !head) || !tapgrad || !gw0 || !gw1 || !gw2 || in_dim <= 0) return CLB_ERR_ARG;
     if (gx && (!start || !list)) return CLB_ERR_ARG;
     if (T * 8 > 0x7fffffffLL) return CLB_ERR_SHAPE;
     if (B == 0) return CLB_OK;
     TreeTables tt{leaf, node, {w0, w1, w2}};
     cudaStream_t st = (cudaStream_t)stream;
-    const bool vec = B % 4 == 0 && aligned16(x) && aligned16(gy) && aligned16(tapgrad) && (!gx || aligned16(gx));
+    const bool vec = B % 4 == 0 && aligned16(x) && (head || aligned16(gy)) && aligned16(tapgrad) && (!gx || aligned16(gx));
+    const TreeHead none{nullptr, nullptr, 1, 1u, 1.f};
     int launched = 0;
     if (T > 0) {
-        if (vec)
-            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4><<<2 * logic_grid(T), 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
+        const int grid = 2 * logic_grid(T);
+        if (head && vec)
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4, true><<<grid, 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode, *head));
+        else if (head)
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1, true><<<grid, 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode, *head));
+        else if (vec)
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<4, false><<<grid, 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode, none));
         else
-            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1><<<2 * logic_grid(T), 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode));
+            CLB_TRACED("logic_tree_bwd_kernel", st, logic_tree_bwd_kernel<1, false><<<grid, 128, 0, st>>>(x, tt, gy, tapgrad, gw0, gw1, gw2, T, B, wmode, none));
         ++launched;
     }
     if (gx) {
@@ -1018,4 +1041,23 @@ extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int
         ++launched;
     }
     return check_launch(launched);
+}
+
+extern "C" int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
+                                  const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2, float *gx, const int64_t *start,
+                                  const int32_t *list, int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)
+{
+    if (!gy) return CLB_ERR_ARG;
+    return logic_tree_bwd_impl(x, leaf, node, w0, w1, w2, gy, nullptr, tapgrad, gw0, gw1, gw2, gx, start, list, in_dim, T, B, wmode, stream);
+}
+
+extern "C" int clb_logic_tree_bwd_scores(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                                         const float *w2, const float *dscore, const float *scale, int k, double tau, float *tapgrad,
+                                         float *gw0, float *gw1, float *gw2, float *gx, const int64_t *start, const int32_t *list,
+                                         int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)
+{
+    if (!dscore || !scale || k <= 0 || tau == 0.0) return CLB_ERR_ARG;
+    if (T % k) return CLB_ERR_SHAPE;
+    const TreeHead head{dscore, scale, k, (unsigned)(T / k > 0 ? T / k : 1), (float)tau};
+    return logic_tree_bwd_impl(x, leaf, node, w0, w1, w2, nullptr, &head, tapgrad, gw0, gw1, gw2, gx, start, list, in_dim, T, B, wmode, stream);
 }

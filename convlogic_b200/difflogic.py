@@ -11,8 +11,8 @@ import torch
 
 from . import ops
 from ._lib import W_ARGMAX, W_SOFTMAX
-from .functional import (GradFactor, GroupSumCrossEntropyFunction, GroupSumFunction, LogicLayerCudaFunction, LogicTreeFunction,
-                         to_feature_major)
+from .functional import (GradFactor, GroupSumCrossEntropyFunction, GroupSumFunction, LogicLayerCudaFunction,
+                         LogicTreeCrossEntropyFunction, LogicTreeFunction, to_feature_major)
 from .packbitstensor import PackBitsTensor
 
 
@@ -242,6 +242,21 @@ class FusedLogicLayers(torch.nn.Module):
             with torch.no_grad():
                 y = LogicTreeFunction.apply(x_fm, w[0], w[1], w[2], self.leaf, self.node, self.leaf_start, self.leaf_slots, W_ARGMAX, self.covers_all)
         return y.transpose(0, 1)
+
+    def cross_entropy(self, x, labels, k, tau=1.0):
+        """``cross_entropy(GroupSum(k, tau)(self(x)), labels)`` of a training step as one autograd node: same loss and
+        gradients as the three calls (src/convlogic/model.py:137-152), but the gradient tensor between the flat layers
+        and the class sums is never materialised.  Falls back to the separate modules for inputs the fused path does not
+        take (see ``forward``), for eval mode and for more than 32 classes."""
+        fused = (self.training and not isinstance(x, PackBitsTensor) and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
+                 and all(l.grad_factor == 1.0 for l in self.layers) and x.shape[0] > 0 and k <= 32 and self.out_dim % k == 0
+                 and labels.dtype == torch.int64)
+        if not fused:
+            return GroupSumCrossEntropy(k, tau)(self(x), labels)
+        assert x.shape[1] == self.layers[0].in_dim, (x.shape, self.layers[0].in_dim)
+        w = [l.weights for l in self.layers]
+        return LogicTreeCrossEntropyFunction.apply(to_feature_major(x), w[0], w[1], w[2], self.leaf, self.node, self.leaf_start,
+                                                   self.leaf_slots, labels, k, float(tau), self.covers_all)
 
     def extra_repr(self):
         return f"{self.in_dim} -> {' -> '.join(str(l.out_dim) for l in self.layers)}"

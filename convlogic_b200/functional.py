@@ -210,6 +210,39 @@ class GroupSumCrossEntropyFunction(torch.autograd.Function):
         return ops.group_sum_bwd(dscore, f, k, tau, scale=gloss.reshape(1).to(dscore.dtype).contiguous()), None, None, None
 
 
+class LogicTreeCrossEntropyFunction(torch.autograd.Function):
+    """The fused flat layers followed by GroupSum(k, tau) and the mean cross-entropy as ONE autograd node: the backward
+    pass derives the trees' upstream gradient from the head's score gradient inside the tree kernel, so the [T, B]
+    gradient tensor between the two is neither written (the GroupSum backward kernel is not launched) nor read."""
+
+    @staticmethod
+    def forward(ctx, x_fm, w0, w1, w2, leaf, node, start, slots, labels, k, tau, covers_all=False):
+        x_fm, w0, w1, w2 = x_fm.contiguous(), w0.contiguous(), w1.contiguous(), w2.contiguous()
+        y = ops.logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, W_SOFTMAX)
+        loss, dscore, _ = ops.group_sum_ce(y, labels.contiguous(), k, tau)
+        ctx.save_for_backward(x_fm, w0, w1, w2, leaf, node, start, slots, dscore)
+        ctx.meta = (k, tau, covers_all)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, gloss):
+        x_fm, w0, w1, w2, leaf, node, start, slots, dscore = ctx.saved_tensors
+        k, tau, covers_all = ctx.meta
+        sinks = [_grad_sink(w) for w in (w0, w1, w2)]
+        direct = all(s is not None for s in sinks)
+        head = (dscore, gloss.reshape(1).to(torch.float32).contiguous(), k, tau)
+        gx, g0, g1, g2 = ops.logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, None, start, slots, W_SOFTMAX, need_gx=ctx.needs_input_grad[0],
+                                            gw_out=[s[0] for s in sinks] if direct else None, clear_gw=not covers_all, head=head)
+        if direct:
+            if all(len(s) > 2 and s[2] == sinks[0][2] for s in sinks):
+                sinks[0][2]([s[3] for s in sinks])
+            else:
+                for s in sinks:
+                    s[1]()
+            g0 = g1 = g2 = None
+        return (gx, g0, g1, g2) + (None,) * 8
+
+
 class FeatureMajorFunction(torch.autograd.Function):
     """[batch, features] -> contiguous [features, batch] (and the same copy back for the gradient) with the library's
     tiled transpose instead of a strided torch copy: the layout change in front of the flat layers."""

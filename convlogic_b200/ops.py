@@ -532,11 +532,19 @@ def logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, wmode):
     return y
 
 
-def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True, gw_out=None, clear_gw=True):
+def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_gx=True, gw_out=None, clear_gw=True, head=None):
     """Gradients of ``logic_tree_fwd``: (gx [in, B] or None, gw0, gw1, gw2).  ``gw_out``: three contiguous tensors to
     receive the gate gradients (cleared first: a neuron no tree reads keeps a zero gradient; ``clear_gw=False`` when the
-    caller knows that every neuron sits in a tree)."""
-    check_input(x_fm, leaf, node, w0, w1, w2, gy, start, slots)
+    caller knows that every neuron sits in a tree).  ``head = (dscore [B, k], scale [1], k, tau)`` instead of ``gy``: the
+    trees feed GroupSum + cross-entropy, and the upstream gradient is derived from that head's score gradient inside
+    the kernel."""
+    if head is None:
+        check_input(x_fm, leaf, node, w0, w1, w2, gy, start, slots)
+    else:
+        check_input(x_fm, leaf, node, w0, w1, w2, head[0], head[1], start, slots)
+        if head[0].dtype != torch.float32 or head[1].dtype != torch.float32 or tuple(head[0].shape) != (x_fm.shape[1], head[2]) \
+                or head[1].numel() != 1 or leaf.shape[0] % head[2]:
+            raise RuntimeError("convlogic_b200: the head of logic_tree_bwd is (dscore float32 [B, k], scale float32 [1], k, tau)")
     t, b, in_dim = leaf.shape[0], x_fm.shape[1], x_fm.shape[0]
     tapgrad = torch.empty((max(t * 8, 1), b), dtype=torch.float32, device=x_fm.device)
     if gw_out is None:
@@ -544,8 +552,13 @@ def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_g
     else:
         gws = [g.zero_() if clear_gw else g for g in gw_out]
     gx = torch.empty_like(x_fm) if need_gx else None
-    check(lib().clb_logic_tree_bwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(gy), ptr(tapgrad), ptr(gws[0]),
-                                   ptr(gws[1]), ptr(gws[2]), ptr(gx), ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))
+    if head is None:
+        check(lib().clb_logic_tree_bwd(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(gy), ptr(tapgrad), ptr(gws[0]),
+                                       ptr(gws[1]), ptr(gws[2]), ptr(gx), ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))
+    else:
+        check(lib().clb_logic_tree_bwd_scores(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(head[0]), ptr(head[1]),
+                                              int(head[2]), float(head[3]), ptr(tapgrad), ptr(gws[0]), ptr(gws[1]), ptr(gws[2]), ptr(gx),
+                                              ptr(start), ptr(slots), in_dim, t, b, wmode, stream()))
     return gx, gws[0], gws[1], gws[2]
 
 

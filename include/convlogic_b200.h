@@ -315,6 +315,14 @@ int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node,
                        const float *w2, const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2,
                        float *gx, const int64_t *start, const int32_t *list, int64_t in_dim, int64_t T, int64_t B,
                        int wmode, void *stream);
+/* The same backward when the trees feed GroupSum + cross-entropy (clb_group_sum_ce): instead of the gradient tensor
+ * gy [T][B] it takes that head's dscore [B][k], the scalar gradient that reaches the loss (`scale`, one float on the
+ * device) and tau; tree t belongs to class t / (T / k) and gy[t][b] = dscore[b][class] / (tau / scale), the values
+ * clb_group_sum_bwd_scaled would write -- bit for bit -- without the tensor being written or read. */
+int clb_logic_tree_bwd_scores(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                              const float *w2, const float *dscore, const float *scale, int k, double tau, float *tapgrad,
+                              float *gw0, float *gw1, float *gw2, float *gx, const int64_t *start, const int32_t *list,
+                              int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream);
 
 /* GroupSum on float activations (src/difflogic/difflogic.py:203-208: `x.reshape(..., k, F/k).sum(-1) / tau`), taken
  * directly from the feature-major [F, B] output of clb_logic_fwd: out [B, k] = sum over the class's F/k rows / tau.

@@ -162,3 +162,32 @@ def test_adam_update_in_two_pieces_equals_one_step():
         ob.finish_and_step()
         assert oa.steps == ob.steps == step + 1
         assert torch.equal(oa.params, ob.params) and torch.equal(oa.exp_avg, ob.exp_avg) and torch.equal(oa.exp_avg_sq, ob.exp_avg_sq)
+
+
+@pytest.mark.parametrize("batch", [64, 37])
+def test_fused_layers_with_the_loss_head_equal_the_separate_modules(batch):
+    """FusedLogicLayers.cross_entropy (trees + GroupSum + cross-entropy as one autograd node, the gradient between them
+    derived inside the tree kernel) against FusedLogicLayers -> GroupSumCrossEntropy: loss, input gradient and all gate
+    gradients bit for bit (the kernel computes the values the GroupSum backward kernel would have written)."""
+    import convlogic_b200 as cb
+
+    torch.manual_seed(4)
+    dims, k, tau = (40, 320, 160, 80), 10, 3.0
+    seq = torch.nn.Sequential(*[cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])], cb.GroupSum(k, tau)).cuda()
+    fused = cb.fuse_logic_layers(seq)[0].train()
+    g = torch.Generator(device="cuda").manual_seed(batch)
+    x = torch.rand(batch, dims[0], device="cuda", generator=g)
+    lab = torch.randint(0, k, (batch,), device="cuda", generator=g)
+
+    def grads(loss_fn):
+        for p in fused.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        loss = loss_fn(xi) * 1.7          # a scale other than one reaches the head's backward
+        loss.backward()
+        return [loss.detach(), xi.grad] + [p.grad.clone() for p in fused.parameters()]
+
+    a = grads(lambda xi: cb.GroupSumCrossEntropy(k, tau)(fused(xi), lab))
+    b = grads(lambda xi: fused.cross_entropy(xi, lab, k, tau))
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
