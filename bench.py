@@ -254,6 +254,7 @@ def c3_algorithmic_bytes(batch):
         "convtree_bwd_x_scatter_kernel": y1 + y2 + y3,                              # the input gradients
         "adam_step_kernel": 7 * 4 * 10694656 // batch,   # p, g, m, v read; p, m, v written (per step, not per image)
         "logic_tree_fwd_kernel": fin + fout,
+        "logic_tree_fwd_sum_kernel": fin,          # class sums instead of the activation: only the input is moved
         "logic_tree_bwd_kernel": fout + fin,
         "row_segment_sum_kernel": fin,
         "transpose_f32_kernel": 4 * fin,   # [batch, features] <-> [features, batch] in front of the flat part: two copies, read + write

@@ -69,6 +69,8 @@ _SIGNATURES = {
     "clb_thermometer_pack": ([_vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i64, _i, _vp], _i),
     "clb_logic_tree_fwd": ([_vp] * 7 + [_i64, _i64, _i, _vp], _i),
     "clb_logic_tree_bwd": ([_vp] * 14 + [_i64, _i64, _i64, _i, _vp], _i),
+    "clb_logic_tree_fwd_ce_scratch_bytes": ([_i64, _i64, _i], _sz),
+    "clb_logic_tree_fwd_ce": ([_vp] * 10 + [_sz, _i64, _i64, _i, C.c_double, _i, _vp], _i),
     "clb_logic_tree_bwd_scores": ([_vp] * 8 + [_i, C.c_double] + [_vp] * 7 + [_i64, _i64, _i64, _i, _vp], _i),
     "clb_group_sum_scratch_bytes": ([_i64, _i64, _i, _i], _sz),
     "clb_group_sum_fwd": ([_vp, _vp, _vp, _sz, _i64, _i64, _i, C.c_double, _i, _vp], _i),

@@ -618,6 +618,69 @@ __global__ void __launch_bounds__(256, 3) logic_tree_fwd_kernel(const float *__r
     }
 }
 
+// Forward of the trees when they feed GroupSum: the class sums directly, without the activation [T][B] (nothing but the
+// class sums reads it in a training step).  Block (part, class): its 8 warps share the trees of one part of one class
+// (tree i of the part goes to warp i % 8), a lane adds up the outputs of its samples over the warp's trees in tree order, the
+// 8 warps' sums are added in warp order: partial[(part * k + class) * B + b], the layout group_sum_ce_sample_kernel reads.
+template <int TR>
+__global__ void __launch_bounds__(256, TR <= 2 ? 3 : 2) logic_tree_fwd_sum_kernel(const float *__restrict__ x, TreeTables tt, float *__restrict__ partial,
+                                                                 long long T, long long B, int k, int wmode)
+{
+    __shared__ float red[8][TR * 128];
+    const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+    const int cls = blockIdx.y, part = blockIdx.x, parts = gridDim.x;
+    const long long S = T / k;
+    const long long t_lo = cls * S + S * part / parts, t_hi = cls * S + S * (part + 1) / parts;
+    float acc[TR][4];
+#pragma unroll
+    for (int tr = 0; tr < TR; ++tr)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[tr][e] = 0.f;
+    const long long t0 = t_lo + wv;
+    int my_leaf = (t0 < t_hi && lane < 8) ? __ldg(tt.leaf + t0 * 8 + lane) : 0;   // index tables one tree ahead
+    int my_node = (t0 < t_hi && lane < 28) ? __ldg(tt.node + t0 * 7 + (lane >> 2)) : 0;
+    for (long long t = t0; t < t_hi; t += 8) {
+        const long long tn = t + 8;
+        const int nx_leaf = (tn < t_hi && lane < 8) ? __ldg(tt.leaf + tn * 8 + lane) : 0;
+        const int nx_node = (tn < t_hi && lane < 28) ? __ldg(tt.node + tn * 7 + (lane >> 2)) : 0;
+        Gate<float> g[7];
+        float pq[4];
+        tree_gates_of(tt, my_node, lane, wmode, g, pq);
+        const float *row[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) row[q] = x + (long long)__shfl_sync(0xffffffffu, my_leaf, q) * B;
+        my_leaf = nx_leaf, my_node = nx_node;
+#pragma unroll
+        for (int tr = 0; tr < TR; ++tr) {
+            const long long b0 = ((long long)tr * 32 + lane) * 4;
+            if (b0 < B) {
+                float a[8][4];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) vload<float, 4>(row[q] + b0, a[q]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float g0 = gate_eval<float>(g[0], a[0][e], a[1][e]), g1 = gate_eval<float>(g[1], a[2][e], a[3][e]);
+                    const float g2 = gate_eval<float>(g[2], a[4][e], a[5][e]), g3 = gate_eval<float>(g[3], a[6][e], a[7][e]);
+                    acc[tr][e] += gate_eval<float>(g[6], gate_eval<float>(g[4], g0, g1), gate_eval<float>(g[5], g2, g3));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int tr = 0; tr < TR; ++tr)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[wv][(tr * 32 + lane) * 4 + e] = acc[tr][e];
+    __syncthreads();
+    for (int i = threadIdx.x; i < TR * 128; i += 256) {
+        if (i < B) {
+            float t = red[0][i];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) t += red[w][i];
+            partial[((long long)part * k + cls) * B + i] = t;
+        }
+    }
+}
+
 // HEAD: the upstream gradient is not a tensor [T][B] but the GroupSum + cross-entropy head's d loss / d score [B][k]:
 // tree t belongs to class t / S and gy[t][b] = dscore[b][class] / (tau / scale), exactly what group_sum_bwd_kernel would
 // have written -- the [T][B] gradient is then neither written nor read.
@@ -1008,6 +1071,45 @@ extern "C" int clb_logic_tree_fwd(const float *x, const int32_t *leaf, const int
 
 // tapgrad: scratch of T*8*B floats.  gw0/gw1/gw2 must be zeroed by the caller: neurons no tree uses keep zero.
 // start int64 [in_dim + 1], list int32 [T*8]: the leaf slots (t*8 + k) grouped by the input feature they read.
+// parts of a class for the fused forward + class sums: enough blocks to fill the GPU a few times over
+static int tree_sum_parts(int64_t T, int k)
+{
+    long long parts = ((long long)sm_count() * 4 + k - 1) / k;
+    const long long most = T / k / 8; // at least eight trees (one per warp) per part
+    if (parts > most) parts = most;
+    return (int)(parts < 1 ? 1 : parts);
+}
+
+extern "C" size_t clb_logic_tree_fwd_ce_scratch_bytes(int64_t T, int64_t B, int k)
+{
+    if (T <= 0 || B <= 0 || k <= 0 || T % k) return 0;
+    return (size_t)tree_sum_parts(T, k) * (size_t)k * (size_t)B * sizeof(float);
+}
+
+extern "C" int clb_logic_tree_fwd_ce(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                                     const float *w2, const int64_t *labels, float *dscore, float *loss, void *scratch,
+                                     size_t scratch_bytes, int64_t T, int64_t B, int k, double tau, int wmode, void *stream)
+{
+    if (!tree_args_ok(x, leaf, node, w0, w1, w2, T, B, wmode) || !labels || !dscore || !loss || k <= 0 || tau == 0.0) return CLB_ERR_ARG;
+    if (T <= 0 || B <= 0 || T % k || k > 32 || B % 4 || B > 512 || !aligned16(x) || T / k > 0x7fffffffLL) return CLB_ERR_SHAPE;
+    if (!scratch || scratch_bytes < clb_logic_tree_fwd_ce_scratch_bytes(T, B, k)) return CLB_ERR_SCRATCH;
+    TreeTables tt{leaf, node, {w0, w1, w2}};
+    cudaStream_t st = (cudaStream_t)stream;
+    const int parts = tree_sum_parts(T, k);
+    const dim3 grid((unsigned)parts, (unsigned)k);
+    float *partial = (float *)scratch;
+    if (B <= 128)
+        CLB_TRACED("logic_tree_fwd_sum_kernel", st, logic_tree_fwd_sum_kernel<1><<<grid, 256, 0, st>>>(x, tt, partial, T, B, k, wmode));
+    else if (B <= 256)
+        CLB_TRACED("logic_tree_fwd_sum_kernel", st, logic_tree_fwd_sum_kernel<2><<<grid, 256, 0, st>>>(x, tt, partial, T, B, k, wmode));
+    else
+        CLB_TRACED("logic_tree_fwd_sum_kernel", st, logic_tree_fwd_sum_kernel<4><<<grid, 256, 0, st>>>(x, tt, partial, T, B, k, wmode));
+    CLB_TRACED("group_sum_ce_sample_kernel", st,
+               group_sum_ce_sample_kernel<<<(unsigned)((B + 7) / 8), 256, 0, st>>>(partial, labels, nullptr, dscore, B, k, parts, (float)tau));
+    CLB_TRACED("group_sum_loss_mean_kernel", st, group_sum_loss_mean_kernel<<<1, 256, 0, st>>>(partial, loss, B));
+    return check_launch(3);
+}
+
 static int logic_tree_bwd_impl(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1, const float *w2,
                                const float *gy, const TreeHead *head, float *tapgrad, float *gw0, float *gw1, float *gw2, float *gx,
                                const int64_t *start, const int32_t *list, int64_t in_dim, int64_t T, int64_t B, int wmode, void *stream)

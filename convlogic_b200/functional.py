@@ -218,8 +218,11 @@ class LogicTreeCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_fm, w0, w1, w2, leaf, node, start, slots, labels, k, tau, covers_all=False):
         x_fm, w0, w1, w2 = x_fm.contiguous(), w0.contiguous(), w1.contiguous(), w2.contiguous()
-        y = ops.logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, W_SOFTMAX)
-        loss, dscore, _ = ops.group_sum_ce(y, labels.contiguous(), k, tau)
+        labels = labels.contiguous()
+        out = ops.logic_tree_fwd_ce(x_fm, leaf, node, w0, w1, w2, labels, k, tau, W_SOFTMAX)   # class sums without the activation
+        if out is None:
+            out = ops.group_sum_ce(ops.logic_tree_fwd(x_fm, leaf, node, w0, w1, w2, W_SOFTMAX), labels, k, tau)[:2]
+        loss, dscore = out
         ctx.save_for_backward(x_fm, w0, w1, w2, leaf, node, start, slots, dscore)
         ctx.meta = (k, tau, covers_all)
         return loss.reshape(())

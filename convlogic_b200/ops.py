@@ -562,6 +562,27 @@ def logic_tree_bwd(x_fm, leaf, node, w0, w1, w2, gy, start, slots, wmode, need_g
     return gx, gws[0], gws[1], gws[2]
 
 
+def logic_tree_fwd_ce(x_fm, leaf, node, w0, w1, w2, labels, k, tau, wmode):
+    """Fused flat layers + GroupSum + mean cross-entropy without the activation in between: (loss [1], dscore [B, k]),
+    or None for a shape that path does not take (the caller then runs ``logic_tree_fwd`` and ``group_sum_ce``)."""
+    check_input(x_fm, leaf, node, w0, w1, w2, labels)
+    t, b = leaf.shape[0], x_fm.shape[1]
+    if x_fm.dtype != torch.float32 or labels.dtype != torch.int64 or labels.shape != (b,):
+        raise RuntimeError("convlogic_b200: logic_tree_fwd_ce expects float32 [in, B] activations and int64 [B] labels")
+    nbytes = lib().clb_logic_tree_fwd_ce_scratch_bytes(t, b, k)
+    if nbytes == 0 or b % 4 or b > 512 or k > 32:
+        return None
+    loss = torch.empty(1, dtype=torch.float32, device=x_fm.device)
+    dscore = torch.empty((b, k), dtype=torch.float32, device=x_fm.device)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x_fm.device)
+    rc = lib().clb_logic_tree_fwd_ce(ptr(x_fm), ptr(leaf), ptr(node), ptr(w0), ptr(w1), ptr(w2), ptr(labels), ptr(dscore), ptr(loss),
+                                     ptr(scratch), nbytes, t, b, k, float(tau), wmode, stream())
+    if rc == _lib.ERR_SHAPE:
+        return None
+    check(rc)
+    return loss, dscore
+
+
 def group_sum_ce(y_fm, labels, k, tau, want_scores=False):
     """GroupSum + mean cross-entropy on feature-major activations [F, B]: (loss [1], dscore [B, k], scores or None)."""
     check_input(y_fm, labels)

@@ -315,6 +315,15 @@ int clb_logic_tree_bwd(const float *x, const int32_t *leaf, const int32_t *node,
                        const float *w2, const float *gy, float *tapgrad, float *gw0, float *gw1, float *gw2,
                        float *gx, const int64_t *start, const int32_t *list, int64_t in_dim, int64_t T, int64_t B,
                        int wmode, void *stream);
+/* The forward of a training step whose trees feed GroupSum(k, tau) + mean cross-entropy (src/convlogic/model.py:137-152 on
+ * top of src/difflogic/difflogic.py:203-208): the trees' outputs are added into their class sums as they are produced -- the
+ * activation y [T][B] is not written -- and the head finishes as in clb_group_sum_ce: loss (one float), dscore [B][k].
+ * labels int64 [B].  CLB_ERR_SHAPE for shapes it does not take (B > 512 or not a multiple of 4, k > 32, T % k != 0): run
+ * clb_logic_tree_fwd + clb_group_sum_ce there.  scratch: clb_logic_tree_fwd_ce_scratch_bytes(T, B, k). */
+size_t clb_logic_tree_fwd_ce_scratch_bytes(int64_t T, int64_t B, int k);
+int clb_logic_tree_fwd_ce(const float *x, const int32_t *leaf, const int32_t *node, const float *w0, const float *w1,
+                          const float *w2, const int64_t *labels, float *dscore, float *loss, void *scratch, size_t scratch_bytes,
+                          int64_t T, int64_t B, int k, double tau, int wmode, void *stream);
 /* The same backward when the trees feed GroupSum + cross-entropy (clb_group_sum_ce): instead of the gradient tensor
  * gy [T][B] it takes that head's dscore [B][k], the scalar gradient that reaches the loss (`scale`, one float on the
  * device) and tau; tree t belongs to class t / (T / k) and gy[t][b] = dscore[b][class] / (tau / scale), the values

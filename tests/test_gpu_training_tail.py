@@ -164,15 +164,18 @@ def test_adam_update_in_two_pieces_equals_one_step():
         assert torch.equal(oa.params, ob.params) and torch.equal(oa.exp_avg, ob.exp_avg) and torch.equal(oa.exp_avg_sq, ob.exp_avg_sq)
 
 
-@pytest.mark.parametrize("batch", [64, 37])
-def test_fused_layers_with_the_loss_head_equal_the_separate_modules(batch):
-    """FusedLogicLayers.cross_entropy (trees + GroupSum + cross-entropy as one autograd node, the gradient between them
-    derived inside the tree kernel) against FusedLogicLayers -> GroupSumCrossEntropy: loss, input gradient and all gate
-    gradients bit for bit (the kernel computes the values the GroupSum backward kernel would have written)."""
+@pytest.mark.parametrize("dims,batch", [((40, 320, 160, 80), 64), ((40, 320, 160, 80), 37), ((96, 2560, 1280, 640), 256),
+                                        ((96, 2560, 1280, 640), 132), ((64, 1280, 640, 320), 512)])
+def test_fused_layers_with_the_loss_head_equal_the_separate_modules(dims, batch):
+    """FusedLogicLayers.cross_entropy (trees + GroupSum + cross-entropy as one autograd node) against FusedLogicLayers ->
+    GroupSumCrossEntropy: loss, input gradient and all gate gradients.  With a batch the summing forward does not take (37)
+    only the backward differs -- it derives the values the GroupSum backward kernel would have written -- and everything is
+    equal bit for bit; with batch 64 the class sums are added in another order (fp32): 1e-6 on the loss, 1e-5 of the largest
+    entry on the gradients."""
     import convlogic_b200 as cb
 
     torch.manual_seed(4)
-    dims, k, tau = (40, 320, 160, 80), 10, 3.0
+    k, tau = 10, 3.0
     seq = torch.nn.Sequential(*[cb.LogicLayer(i, o) for i, o in zip(dims[:-1], dims[1:])], cb.GroupSum(k, tau)).cuda()
     fused = cb.fuse_logic_layers(seq)[0].train()
     g = torch.Generator(device="cuda").manual_seed(batch)
@@ -189,5 +192,10 @@ def test_fused_layers_with_the_loss_head_equal_the_separate_modules(batch):
 
     a = grads(lambda xi: cb.GroupSumCrossEntropy(k, tau)(fused(xi), lab))
     b = grads(lambda xi: fused.cross_entropy(xi, lab, k, tau))
-    for u, v in zip(a, b):
-        assert torch.equal(u, v)
+    if batch % 4:
+        for u, v in zip(a, b):
+            assert torch.equal(u, v)
+    else:
+        assert abs(float(a[0]) - float(b[0])) <= 1e-6 * abs(float(a[0]))
+        for i, (u, v) in enumerate(zip(a[1:], b[1:])):
+            assert_close(v, u, 1e-5, f"gradient {i}")
