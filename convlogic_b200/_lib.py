@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libconvlogic_b200.so")
 F32, F64 = 0, 1
 W_PROB, W_SOFTMAX, W_ARGMAX = 0, 1, 2
 SEL_UNBOUNDED = 0x100
+Y_FEATURE_MAJOR = 0x200   # wmode flag: the block's output / upstream gradient is [C][windows][N]
 TUNE_TAPGRAD_SLICE_BYTES = 1
 TUNE_PLANE_KERNELS = 2
 TUNE_SLAB_MUX = 3

@@ -64,7 +64,8 @@ class ConvLogicLayer(nn.Module):
         sel = self.selection.contiguous()
         geom = (*self.stride, *self.padding, *self.kernel)
         if self.complete:
-            return FullConvLogicFunction.apply(x, w, sel, *geom, self.return_intermediate, self.return_indices, wmode)
+            return FullConvLogicFunction.apply(x, w, sel, *geom, self.return_intermediate, self.return_indices, wmode,
+                                               getattr(self, "output_feature_major", False) and self.training)
         return ConvLogicFunction.apply(x, w, sel, *geom, wmode)
 
     def forward_cuda_eval(self, x: PackBitsTensor):

@@ -853,6 +853,9 @@ static int grid_x_for(long long total_items, int C)
     return (int)want;
 }
 
+// implemented in convtree_plane.cu; returns CLB_ERR_SHAPE when the shape is outside the plane kernels
+int clb_convtree_fwd_plane_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H, int W,
+                               int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st);
 // implemented in convtree_fast.cu; returns CLB_ERR_SHAPE when the shape is outside its fast path
 int clb_convtree_fwd_fast_f32(const float *x, const float *w, const int32_t *sel, float *y, uint8_t *amax, int N, int Ci, int H,
                               int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, cudaStream_t st);
@@ -862,7 +865,8 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
                                 int wmode, int dtype, void *stream)
 {
     const bool sel_unbounded = (wmode & CLB_SEL_UNBOUNDED) != 0;
-    wmode &= ~CLB_SEL_UNBOUNDED;
+    const bool y_fm = (wmode & CLB_Y_FEATURE_MAJOR) != 0;
+    wmode &= ~(CLB_SEL_UNBOUNDED | CLB_Y_FEATURE_MAJOR);
     ConvShape s;
     int rc = make_shape(s, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw, true);
     if (rc) return rc;
@@ -870,6 +874,11 @@ extern "C" int clb_convtree_fwd(const void *x, const void *w, const int32_t *sel
     if (N == 0 || C == 0) return CLB_OK;
     if (C > 65535) return CLB_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
+    if (y_fm) { // feature-major output: the plane kernels or nothing
+        if (dtype != CLB_F32 || x2 || idx || sel_unbounded) return CLB_ERR_SHAPE;
+        return clb_convtree_fwd_plane_f32((const float *)x, (const float *)w, sel, (float *)y, amax, N, Ci, H, W, C, sh, sw, ph, pw, kh, kw,
+                                          wmode | CLB_Y_FEATURE_MAJOR, st);
+    }
     if (dtype == CLB_F32 && !x2 && !idx && !sel_unbounded) {
         rc = clb_convtree_fwd_fast_f32((const float *)x, (const float *)w, sel, (float *)y, amax, N, Ci, H, W, C, sh, sw, ph, pw,
                                        kh, kw, wmode, st);

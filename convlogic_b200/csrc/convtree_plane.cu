@@ -54,6 +54,8 @@ template <> struct Geo<4> {
 struct Args {
     int N, Ci, C, wmode;
     int parts; // the batch is split into this many contiguous parts; a (channel, part) pair is one task
+    int y_fm;  // the block's output (forward) / upstream gradient (backward) is feature-major: [C][windows][N] instead of
+               // [N][C][windows] -- the layout the flat layers behind the last block work in; the arg-max bytes keep [N][C][windows]
 };
 
 __device__ int g_plane_error; // set when a bounded wait gave up (never expected); read by clb_plane_error()
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
                 }
             }
             const size_t o = ((size_t)(n_lo + img) * s.C + c) * I + win;
-            y[o] = best;
+            y[s.y_fm ? ((size_t)c * I + win) * s.N + (n_lo + img) : o] = best;
             if (amax != nullptr) amax[o] = (uint8_t)bd;
         }
         return;
@@ -363,7 +365,8 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
     const size_t o0 = ((size_t)(n_lo + my_img) * s.C + c) * I + py * Cf::WP + (ox >> 1);
     const size_t ostep = (size_t)Cf::NIMG * s.C * I;
     const bool want_amax = amax != nullptr;
-    float *yp = y + o0;                        // run along with the iterations
+    float *yp = y + (s.y_fm ? ((size_t)c * I + py * Cf::WP + (ox >> 1)) * s.N + (n_lo + my_img) : o0); // run along with the iterations
+    const size_t ystep = s.y_fm ? (size_t)Cf::NIMG : ostep;
     uint8_t *ap = want_amax ? amax + o0 : nullptr;
     bool failed = false;
     int it = 0;
@@ -382,7 +385,7 @@ __global__ void __launch_bounds__(kThreads) convtree_fwd_plane_kernel(const __gr
             *yp = best;
             if (want_amax) *ap = (uint8_t)bd;
         }
-        yp += ostep;
+        yp += ystep;
         if (want_amax) ap += ostep;
     };
     // the ring is walked with the stage index as a compile-time constant: every load is [register + immediate]
@@ -624,14 +627,26 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     // upstream gradient and arg-max: fetched one iteration ahead
     float dz_next[WPT];
     int bd_next[WPT];
+    // the window's element of the first iteration in gy (either layout) and in the arg-max tensor; later iterations are a
+    // constant step further
+    const float *gy0[WPT];
+    const uint8_t *am0[WPT];
+    int live_iters[WPT]; // iterations in which the window's image exists
+#pragma unroll
+    for (int j = 0; j < WPT; ++j) {
+        const int n = n_lo + img_local[j];
+        const size_t o = ((size_t)n * s.C + c) * I + win[j];
+        gy0[j] = gy + (s.y_fm ? ((size_t)c * I + win[j]) * s.N + n : o);
+        am0[j] = amax + o;
+        live_iters[j] = min(iters, (n_hi - n + Cf::NIMG - 1) / Cf::NIMG);
+    }
+    const size_t astep = (size_t)Cf::NIMG * s.C * I, gstep = s.y_fm ? (size_t)Cf::NIMG : astep;
     auto fetch = [&](int it) {
 #pragma unroll
         for (int j = 0; j < WPT; ++j) {
-            const int n = n_lo + it * Cf::NIMG + img_local[j];
-            const bool live = it < iters && n < n_hi;
-            const size_t o = ((size_t)n * s.C + c) * I + win[j];
-            dz_next[j] = live ? __ldg(gy + o) : 0.f;
-            bd_next[j] = live ? (int)__ldg(amax + o) : 0;
+            const bool live = it < live_iters[j];
+            dz_next[j] = live ? __ldg(gy0[j] + (size_t)it * gstep) : 0.f;
+            bd_next[j] = live ? (int)__ldg(am0[j] + (size_t)it * astep) : 0;
         }
     };
     fetch(0);
@@ -992,7 +1007,7 @@ int launch_fwd(const float *x, const float *w, const int32_t *sel, float *y, uin
     auto k = convtree_fwd_plane_kernel<S>;
     if (clb_host::ensure_dynamic_smem(k, Cf::SMEM) != cudaSuccess) return check_launch(0);
     const int parts = plane_parts(N, C, Cf::NIMG, Cf::WIDE ? 6 : 12);
-    const Args a{N, Ci, C, wmode, parts};
+    const Args a{N, Ci, C, wmode & 0xff, parts, (wmode & CLB_Y_FEATURE_MAJOR) ? 1 : 0};
     const long long tasks = (long long)C * parts;
     CLB_TRACED("convtree_fwd_plane_kernel", st,
                k<<<(unsigned)((tasks + Cf::GROUPS - 1) / Cf::GROUPS), kThreads, Cf::SMEM, st>>>(map, x, w, sel, y, amax, a));
@@ -1011,7 +1026,7 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     auto k = convtree_bwd_plane_kernel<S>;
     if (clb_host::ensure_dynamic_smem(k, Cf::SMEM) != cudaSuccess) return check_launch(0);
     const int parts = bwd_parts<S>(N, C);
-    const Args a{N, Ci, C, wmode, parts};
+    const Args a{N, Ci, C, wmode & 0xff, parts, (wmode & CLB_Y_FEATURE_MAJOR) ? 1 : 0};
     const long long tasks = (long long)C * parts;
     CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<(unsigned)((tasks + 3) / 4), kThreads, Cf::SMEM, st>>>(map, gy, x, w, sel, amax, partial, planes, a));
     return CLB_OK;
@@ -1093,11 +1108,14 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
                                       const int32_t *ch_start, const int32_t *ch_entry, void *scratch, size_t scratch_bytes, int N, int Ci, int H,
                                       int W, int C, int sh, int sw, int ph, int pw, int kh, int kw, int wmode, int dtype, void *stream)
 {
+    const int wmode_in = wmode; // may carry CLB_Y_FEATURE_MAJOR: gy is [C][windows][N]
+    wmode &= ~CLB_Y_FEATURE_MAJOR;
     if (!gy || !x || !w || !sel || !amax || (!gx && !gw) || !scratch || wmode < 0 || wmode > 2) return CLB_ERR_ARG;
     if (gx && (!ch_start || !ch_entry)) return CLB_ERR_ARG;
     if (dtype != CLB_F32 || !conv_args_ok(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw)) return CLB_ERR_SHAPE;
     const int side = plane_side(N, Ci, H, W, C, sh, sw, ph, pw, kh, kw);
     if (!side || (side == 32) != (gx == nullptr)) return CLB_ERR_SHAPE; // 32x32: gate gradient alone; smaller: both gradients
+    if (side == 32 && wmode_in != wmode) return CLB_ERR_SHAPE;          // the 32x32 kernel reads gy as [N][C][windows] only
     if (side == 32) {
         const int parts32 = bwd_parts_for(32, N, C);
         if (scratch_bytes < (size_t)parts32 * C * 28 * sizeof(float) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return CLB_ERR_SCRATCH;
@@ -1106,7 +1124,7 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
         auto k32 = convtree_bwd_w_plane32_kernel;
         if (clb_host::ensure_dynamic_smem(k32, BwdW32::SMEM) != cudaSuccess) return check_launch(0);
         cudaStream_t st32 = (cudaStream_t)stream;
-        const Args a32{N, Ci, C, wmode, parts32};
+        const Args a32{N, Ci, C, wmode, parts32, 0};
         CLB_TRACED("convtree_bwd_w_plane32_kernel", st32,
                    k32<<<(unsigned)((long long)C * parts32), kThreads, BwdW32::SMEM, st32>>>(map32, (const float *)gy, (const float *)w, sel, amax,
                                                                                            (float *)scratch, a32));
@@ -1123,9 +1141,9 @@ extern "C" int clb_convtree_bwd_plane(const void *gy, const void *x, const void 
     float *partial = (float *)scratch;
     float *planes = (float *)((unsigned char *)scratch + ((size_t)parts * C * 28 * sizeof(float) + 255) / 256 * 256);
     const float *gyf = (const float *)gy, *xf = (const float *)x, *wf = (const float *)w;
-    const int rc = side == 16  ? launch_bwd<16>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode, st)
-                   : side == 8 ? launch_bwd<8>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode, st)
-                               : launch_bwd<4>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode, st);
+    const int rc = side == 16  ? launch_bwd<16>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode_in, st)
+                   : side == 8 ? launch_bwd<8>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode_in, st)
+                               : launch_bwd<4>(gyf, xf, wf, sel, amax, partial, planes, N, Ci, C, wmode_in, st);
     if (rc != CLB_OK) return rc;
     int launched = 1;
     const int HW4 = H * W / 4;

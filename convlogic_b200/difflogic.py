@@ -262,9 +262,14 @@ class FusedLogicLayers(torch.nn.Module):
         return f"{self.in_dim} -> {' -> '.join(str(l.out_dim) for l in self.layers)}"
 
 
-def fuse_logic_layers(model):
+def fuse_logic_layers(model, feature_major_blocks=True):
     """A copy of an ``nn.Sequential`` in which every run of three LogicLayers that can be fused is replaced by a
-    ``FusedLogicLayers`` over the SAME layer objects (parameters are shared with ``model``)."""
+    ``FusedLogicLayers`` over the SAME layer objects (parameters are shared with ``model``).
+
+    ``feature_major_blocks``: a fused ConvLogic block that sits right in front of ``Flatten`` + flat layers is asked to
+    write its training output in the flat layers' layout (``output_feature_major`` on that -- shared -- layer object): what
+    it returns is then a non-contiguous [N, C, h, w] view whose ``flatten(1)`` the flat layers take without a copy, and the
+    gradient comes back the same way."""
     out, run = [], []
 
     def flush():
@@ -284,4 +289,9 @@ def fuse_logic_layers(model):
             flush()
             out.append(m)
     flush()
+    if feature_major_blocks:
+        for i in range(2, len(out)):
+            if (isinstance(out[i], (FusedLogicLayers, LogicLayer)) and isinstance(out[i - 1], torch.nn.Flatten)
+                    and type(out[i - 2]).__name__ == "ConvLogicLayer" and getattr(out[i - 2], "complete", False)):
+                out[i - 2].output_feature_major = True
     return torch.nn.Sequential(*out)

@@ -41,13 +41,14 @@ class GradFactor(Function):
 class FullConvLogicFunction(Function):
     @staticmethod
     def forward(ctx, x, w_prob, selection, stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w,
-                return_intermediate=False, return_indices=False, wmode=W_PROB):
+                return_intermediate=False, return_indices=False, wmode=W_PROB, y_feature_major=False):
         x = x.contiguous()
         w_prob = w_prob.contiguous()
         geom = (stride_h, stride_w, pad_h, pad_w, kernel_h, kernel_w)
         need_bwd = any(ctx.needs_input_grad[:2])
         y, amax, x2, x3, idx = ops.convtree_fwd(x, w_prob, selection, geom, wmode, want_amax=need_bwd,
-                                                want_intermediate=return_intermediate, want_indices=return_indices)
+                                                want_intermediate=return_intermediate, want_indices=return_indices,
+                                                y_feature_major=y_feature_major)
         ctx.save_for_backward(x, w_prob, selection, amax)
         ctx.geom, ctx.wmode = geom, wmode
         extra = []
@@ -63,7 +64,8 @@ class FullConvLogicFunction(Function):
     @staticmethod
     def backward(ctx, grad_y, *unused):
         x, w, sel, amax = ctx.saved_tensors
-        grad_y = grad_y.contiguous()
+        if not ops._is_feature_major(grad_y):   # a feature-major gradient (from flat layers behind this block) is read as it is
+            grad_y = grad_y.contiguous()
         need_gx = ctx.needs_input_grad[0]
         need_gw = ctx.needs_input_grad[1] and ctx.wmode != W_ARGMAX
         gx = gw = None
@@ -74,7 +76,7 @@ class FullConvLogicFunction(Function):
             if sink is not None:
                 sink[1]()
                 gw = None
-        return (gx, gw) + (None,) * 10
+        return (gx, gw) + (None,) * 11
 
 
 class ConvLogicFunction(Function):

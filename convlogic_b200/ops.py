@@ -45,7 +45,16 @@ def _sel_flag(sel, geom, ci):
 
 
 # ------------------------------------------------------------------------------ fused block
-def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False, want_indices=False):
+def _is_feature_major(t):
+    """A 4-D [N, C, h, w] tensor whose storage is the contiguous [C, h, w, N] one (what ``convtree_fwd`` returns with
+    ``y_feature_major`` and what autograd hands back through the flat layers' transposed views)."""
+    return t.dim() == 4 and not t.is_contiguous() and t.permute(1, 2, 3, 0).is_contiguous()
+
+
+def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False, want_indices=False, y_feature_major=False):
+    """``y_feature_major``: ask for the output in the flat layers' layout -- storage [C, h, w, N], returned as the
+    [N, C, h, w] view of it, so that ``flatten(1)`` and the flat layers' transposition are views.  Only the plane
+    kernels write it; for other shapes the ordinary layout comes back."""
     check_input(x, w, sel)
     n, ci, h, wd = x.shape
     c = w.shape[0]
@@ -69,6 +78,13 @@ def convtree_fwd(x, w, sel, geom, wmode, want_amax=True, want_intermediate=False
         idx = torch.empty((n, c, (ho // 2) * (wo // 2)), dtype=torch.int32, device=x.device)
     if n == 0 or c == 0:  # empty batch: nothing to launch
         return y, amax, x2, x3, idx
+    if y_feature_major and x.dtype == torch.float32 and not want_intermediate and not want_indices and not _sel_flag(sel, geom, ci):
+        y_fm = torch.empty((c, ho // 2, wo // 2, n), dtype=x.dtype, device=x.device)
+        rc = lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y_fm), ptr(amax), None, None, None, n, ci, h, wd, c, *geom,
+                                    wmode | _lib.Y_FEATURE_MAJOR, dtype_code(x), stream())
+        if rc != _lib.ERR_SHAPE:
+            check(rc)
+            return y_fm.permute(3, 0, 1, 2), amax, x2, x3, idx
     check(lib().clb_convtree_fwd(ptr(x), ptr(w), ptr(sel), ptr(y), ptr(amax), ptr(x2), ptr(x3), ptr(idx),
                                  n, ci, h, wd, c, *geom, wmode | _sel_flag(sel, geom, ci), dtype_code(x), stream()))
     return y, amax, x2, x3, idx
@@ -166,8 +182,10 @@ def convtree_bwd_x(gy, x, w, sel, amax, geom, wmode, use_scratch=True):
 
 def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True, gw_out=None):
     """Both gradients of the fused block in one C-ABI call; returns (gx or None, gw or None).  ``gw_out``: a contiguous
-    tensor of the gate tensor's shape to receive the gate gradient (e.g. a slice of a flat gradient bucket)."""
-    check_input(gy, x, w, sel)
+    tensor of the gate tensor's shape to receive the gate gradient (e.g. a slice of a flat gradient bucket).  ``gy`` may
+    be feature-major (see ``convtree_fwd``): the plane kernels read it as it is, other shapes get a contiguous copy."""
+    gy_fm = gy.is_cuda and _is_feature_major(gy)
+    check_input(x, w, sel) if gy_fm else check_input(gy, x, w, sel)
     _bwd_args_ok(gy, x, w, sel, amax, geom)
     n, ci, h, wd = x.shape
     c = w.shape[0]
@@ -188,10 +206,13 @@ def convtree_bwd(gy, x, w, sel, amax, geom, wmode, need_gx=True, need_gw=True, g
         if lists is not None:
             scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
             rc = lib().clb_convtree_bwd_plane(ptr(gy), ptr(x), ptr(w), ptr(sel), ptr(amax), ptr(gx), ptr(gw), ptr(lists[0]), ptr(lists[1]),
-                                              ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode, dtype_code(x), stream())
+                                              ptr(scratch), nbytes, n, ci, h, wd, c, *geom, wmode | (_lib.Y_FEATURE_MAJOR if gy_fm else 0),
+                                              dtype_code(x), stream())
             if rc != _lib.ERR_SHAPE:
                 check(rc)
                 return gx, gw
+    if gy_fm:
+        gy = gy.contiguous()
     nbytes = lib().clb_convtree_bwd_scratch_bytes(n, ci, h, wd, c, *geom, int(need_gx), int(need_gw), dtype_code(x))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
     if need_gx:

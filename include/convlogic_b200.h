@@ -53,6 +53,11 @@ extern "C" {
  * selections are served by the general kernels only; without this flag the caller guarantees
  * row < kh and col < kw for every tap. */
 #define CLB_SEL_UNBOUNDED 0x100
+/* OR this into `wmode` of clb_convtree_fwd / clb_convtree_bwd_plane: the block's output y (forward) or the upstream gradient
+ * gy (backward) is feature-major, [C][Ho/2 * Wo/2][N] instead of [N][C][Ho/2][Wo/2] -- the layout the flat layers behind a
+ * stack's last block work in (no transposed copy in between).  Only the many-channel plane kernels take it (3x3, stride 1,
+ * padding 1, images of 16x16 / 8x8 / 4x4, fp32): CLB_ERR_SHAPE otherwise.  The arg-max bytes keep [N][C][windows]. */
+#define CLB_Y_FEATURE_MAJOR 0x200
 
 int clb_version(void);
 const char *clb_status_string(int status);

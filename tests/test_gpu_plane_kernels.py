@@ -164,3 +164,59 @@ def test_gate_gradient_alone_of_a_32x32_block(n, ci, c):
     yf = oracle.full_convlogic(x, oracle.gate_probabilities(wo, True), sel, forced_idx=idx.cpu())[0]
     (gwo,) = torch.autograd.grad((yf * gy).sum(), (wo,))
     assert_close(gw, gwo, 1e-5, "gw vs oracle")
+
+
+@pytest.mark.parametrize("shape", [(37, 64, 24, 16), (33, 128, 20, 8), (130, 600, 10, 4), (5, 500, 9, 4)],
+                         ids=lambda s: "x".join(str(v) for v in s))
+def test_feature_major_output_and_gradient_layout(shape):
+    """The plane kernels writing y / reading gy in the flat layers' layout (storage [C, h, w, N]): same values, bit for
+    bit, as with the ordinary [N, C, h, w] tensors."""
+    from convlogic_b200 import ops
+    from convlogic_b200._lib import W_SOFTMAX
+
+    x, logits, sel, gy = _case(shape, 9)
+    xd, wd, sd, gd = x.cuda(), logits.cuda(), sel.cuda(), gy.cuda()
+    y, amax, _, _, _ = ops.convtree_fwd(xd, wd, sd, GEOM, W_SOFTMAX)
+    y_fm, amax_fm, _, _, _ = ops.convtree_fwd(xd, wd, sd, GEOM, W_SOFTMAX, y_feature_major=True)
+    assert ops._is_feature_major(y_fm) or shape[0] == 1
+    assert torch.equal(y_fm, y) and torch.equal(amax_fm, amax)
+    flat = y_fm.flatten(1)
+    assert flat.data_ptr() == y_fm.data_ptr() and flat.t().is_contiguous()      # views all the way to [features, batch]
+    gx, gw = ops.convtree_bwd(gd, xd, wd, sd, amax, GEOM, W_SOFTMAX)
+    gd_fm = gd.permute(1, 2, 3, 0).contiguous().permute(3, 0, 1, 2)            # the same values in feature-major storage
+    assert ops._is_feature_major(gd_fm)
+    gx2, gw2 = ops.convtree_bwd(gd_fm, xd, wd, sd, amax, GEOM, W_SOFTMAX)
+    assert torch.equal(gx, gx2) and torch.equal(gw, gw2)
+    assert _plane_error() == 0
+
+
+def test_block_in_front_of_flat_layers_hands_over_feature_major():
+    """fuse_logic_layers marks the block in front of Flatten + flat layers: loss and every gradient equal those of the
+    same stack with the ordinary layout, bit for bit, and no transposed copy is launched."""
+    import convlogic_b200 as cb
+    from convlogic_b200 import _lib
+
+    def build():
+        torch.manual_seed(21)
+        return torch.nn.Sequential(cb.ConvLogicLayer(64, 40, padding=1, complete=True), torch.nn.Flatten(), cb.LogicLayer(160, 1600),
+                                   cb.LogicLayer(1600, 800), cb.LogicLayer(800, 400), cb.GroupSum(10, 2.0)).cuda().train()
+
+    a = cb.fuse_logic_layers(build(), feature_major_blocks=False)
+    b = cb.fuse_logic_layers(build())
+    assert getattr(b[0], "output_feature_major", False) and not getattr(a[0], "output_feature_major", False)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.rand(48, 64, 4, 4, device="cuda", generator=g)
+    lab = torch.randint(0, 10, (48,), device="cuda", generator=g)
+    outs = []
+    for net in (a, b):
+        xi = x.clone().requires_grad_(True)
+        _lib.trace(True)
+        loss = torch.nn.functional.cross_entropy(net(xi), lab)
+        loss.backward()
+        torch.cuda.synchronize()
+        rep = _lib.trace_report()
+        _lib.trace(False)
+        outs.append(([loss.detach(), xi.grad] + [p.grad.clone() for p in net.parameters()], rep))
+    assert "transpose_f32_kernel" in outs[0][1] and "transpose_f32_kernel" not in outs[1][1], (outs[0][1], outs[1][1])
+    for u, v in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(u, v)
