@@ -281,7 +281,7 @@ def run_c3(ctx, args, with_cpu=True):
     from convlogic_b200 import _lib, dp
 
     dev, world, rank = ctx.dev, ctx.world, ctx.rank
-    net = cb.fuse_logic_layers(build_c3(dev)).train()   # the three flat layers run as one gate tree per output neuron
+    net = cb.fuse_logic_layers(build_c3(dev), feature_major_blocks=not args.no_feature_major).train()   # the three flat layers run as one gate tree per output neuron
     if args.torch_tail:   # torch's cross-entropy, gradient accumulation and fused Adam behind the library's layers
         bucket = dp.GradBucket(net).overlap(average=True)
         opt = torch.optim.Adam(net.parameters(), lr=0.01, fused=True)
@@ -916,6 +916,7 @@ def main():
                     help="override the library's slice size of the two-pass conv backward (0 = whole batch in one slice)")
     ap.add_argument("--plane-kernels", type=int, default=None, choices=[0, 1],
                     help="override the library's choice of the TMA-staged many-channel conv kernels (0 = the older staged kernels)")
+    ap.add_argument("--no-feature-major", action="store_true", help="c3: the last block hands [N, C, h, w] to the flat layers (two transposed copies per step)")
     ap.add_argument("--separate-head", action="store_true", help="c3: GroupSumCrossEntropy as its own autograd node behind the fused flat layers")
     ap.add_argument("--torch-tail", action="store_true",
                     help="c3: torch's cross-entropy, .grad accumulation and fused Adam instead of the library's fused tail")
