@@ -513,7 +513,7 @@ __device__ __forceinline__ void bwd_windows(const uint32_t (&base)[WPT], const u
     }
 }
 
-template <int S>
+template <int S, bool FM>
 __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __grid_constant__ CUtensorMap xmap, const float *__restrict__ gy,
                                                                       const float *__restrict__ x, const float *__restrict__ w,
                                                                       const int32_t *__restrict__ sel, const uint8_t *__restrict__ amax,
@@ -627,26 +627,17 @@ __global__ void __launch_bounds__(kThreads) convtree_bwd_plane_kernel(const __gr
     // upstream gradient and arg-max: fetched one iteration ahead
     float dz_next[WPT];
     int bd_next[WPT];
-    // the window's element of the first iteration in gy (either layout) and in the arg-max tensor; later iterations are a
-    // constant step further
-    const float *gy0[WPT];
-    const uint8_t *am0[WPT];
-    int live_iters[WPT]; // iterations in which the window's image exists
-#pragma unroll
-    for (int j = 0; j < WPT; ++j) {
-        const int n = n_lo + img_local[j];
-        const size_t o = ((size_t)n * s.C + c) * I + win[j];
-        gy0[j] = gy + (s.y_fm ? ((size_t)c * I + win[j]) * s.N + n : o);
-        am0[j] = amax + o;
-        live_iters[j] = min(iters, (n_hi - n + Cf::NIMG - 1) / Cf::NIMG);
-    }
-    const size_t astep = (size_t)Cf::NIMG * s.C * I, gstep = s.y_fm ? (size_t)Cf::NIMG : astep;
     auto fetch = [&](int it) {
 #pragma unroll
         for (int j = 0; j < WPT; ++j) {
-            const bool live = it < live_iters[j];
-            dz_next[j] = live ? __ldg(gy0[j] + (size_t)it * gstep) : 0.f;
-            bd_next[j] = live ? (int)__ldg(am0[j] + (size_t)it * astep) : 0;
+            const int n = n_lo + it * Cf::NIMG + img_local[j];
+            const bool live = it < iters && n < n_hi;
+            const size_t o = ((size_t)n * s.C + c) * I + win[j];
+            if constexpr (FM) // gy is [C][windows][N] (compile-time: the flag in the index arithmetic cost the 8x8 kernel 7 %)
+                dz_next[j] = live ? __ldg(gy + ((size_t)c * I + win[j]) * s.N + n) : 0.f;
+            else
+                dz_next[j] = live ? __ldg(gy + o) : 0.f;
+            bd_next[j] = live ? (int)__ldg(amax + o) : 0;
         }
     };
     fetch(0);
@@ -1023,10 +1014,11 @@ int launch_bwd(const float *gy, const float *x, const float *w, const int32_t *s
     using Cf = BwdCfg<S>;
     CUtensorMap map;
     if (!clb_tma::make_plane_map(&map, x, N, Ci, S, S, Cf::P, Cf::R, Cf::NIMG)) return CLB_ERR_SHAPE;
-    auto k = convtree_bwd_plane_kernel<S>;
+    const bool fm = (wmode & CLB_Y_FEATURE_MAJOR) != 0;
+    auto k = fm ? convtree_bwd_plane_kernel<S, true> : convtree_bwd_plane_kernel<S, false>;
     if (clb_host::ensure_dynamic_smem(k, Cf::SMEM) != cudaSuccess) return check_launch(0);
     const int parts = bwd_parts<S>(N, C);
-    const Args a{N, Ci, C, wmode & 0xff, parts, (wmode & CLB_Y_FEATURE_MAJOR) ? 1 : 0};
+    const Args a{N, Ci, C, wmode & 0xff, parts, fm ? 1 : 0};
     const long long tasks = (long long)C * parts;
     CLB_TRACED("convtree_bwd_plane_kernel", st, k<<<(unsigned)((tasks + 3) / 4), kThreads, Cf::SMEM, st>>>(map, gy, x, w, sel, amax, partial, planes, a));
     return CLB_OK;
