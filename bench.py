@@ -131,9 +131,9 @@ class Ctx:
             # The gradient exchange (42.8 MB per step at c3) runs under the backward kernels: on 2 and 4 GPUs NCCL's default
             # number of blocks takes SMs from them for longer than the transfer needs.  Measured c3 ms/step, default / 16 / 8 / 4
             # blocks: 2.46 / 2.42 / 2.42 / 2.52 on 2 GPUs, 2.47 / 2.46 / 2.43 / - on 4.  On 8 GPUs the ring is longer and 8
-            # blocks were too few (2.68 ms against 2.36 on one GPU): NCCL's own choice stays.  A value the caller set wins.
-            if self.world <= 4:
-                os.environ.setdefault("NCCL_MAX_CTAS", "8")
+            # blocks are too few: default / 32 / 16 / 12 / 8 blocks 2.366 / 2.365 / 2.365 / 2.356 / 2.439 ms (2.27 on one GPU).
+            # A value the caller set wins.
+            os.environ.setdefault("NCCL_MAX_CTAS", "8" if self.world <= 4 else "12")
             torch.cuda.set_device(self.local)
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
         else:
