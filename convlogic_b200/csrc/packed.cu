@@ -321,10 +321,16 @@ __global__ void __launch_bounds__(128) group_popcount_kernel(const unsigned *__r
         unsigned up[PLANES];
 #pragma unroll
         for (int p = 0; p < PLANES; ++p) up[p] = 0;
+        const unsigned *pr = base + r_lo * units; // walks down the rows: one addition per load, no multiplication
         for (long long r = r_lo; r < r_hi; r += 16) {
             unsigned v[16];
+            if (r + 16 <= r_hi) {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] = (r + q < r_hi) ? __ldg(base + (r + q) * units) : 0u;
+                for (int q = 0; q < 16; ++q) v[q] = __ldg(pr), pr += units;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 16; ++q) v[q] = (r + q < r_hi) ? __ldg(pr + q * units) : 0u;
+            }
             unsigned t2a, t2b, t4a, t4b, t8a, t8b, t16;
             csa(t2a, ones, ones, v[0], v[1]);
             csa(t2b, ones, ones, v[2], v[3]);
