@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256) packed_logic_v4_kernel(const uint4 *__res
 // intermediate activations (the largest tensors of the stack) are never written or read.  leaf [out][2^M] are the
 // input rows in tree order (gate p of the first level reads leaves 2p and 2p+1), ops [out][2^M - 1] the gate ids
 // level by level (first level, ..., root).  Rows move in 8- or 16-byte units like the single layer.
-template <typename V4, int M>
+template <typename V4, int M, typename IDX>
 __global__ void __launch_bounds__(256) packed_tree_kernel(const V4 *__restrict__ x, const int32_t *__restrict__ leaf,
                                                           const uint8_t *__restrict__ ops, V4 *__restrict__ y, long long out_dim,
                                                           long long units, long long u_lo, long long u_n)
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(256) packed_tree_kernel(const V4 *__restrict__
         unsigned v[L][W];
 #pragma unroll
         for (int k = 0; k < L; ++k) {
-            const V4 q = __ldg(x + (long long)__ldg(leaf + j * L + k) * units + u);
+            const V4 q = __ldg(x + ((IDX)__ldg(leaf + j * L + k) * (IDX)units + (IDX)u)); // IDX: 32 bits when the input has < 2^32 units
             const unsigned *qw = reinterpret_cast<const unsigned *>(&q);
 #pragma unroll
             for (int w = 0; w < W; ++w) v[k][w] = qw[w];
@@ -908,19 +908,23 @@ extern "C" int clb_packed_tree(const void *x, const int32_t *leaf, const uint8_t
         for (long long pc = 0; pc < pieces; ++pc) {
             if (levels == 2)
                 CLB_TRACED("packed_tree_kernel", st,
-                           packed_tree_kernel<uint4, 2><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
+                           packed_tree_kernel<uint4, 2, long long><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
             else
-                CLB_TRACED("packed_tree_kernel", st,
-                           packed_tree_kernel<uint4, 3><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
+                if (in_dim * units < 0xffffffffLL)
+                    CLB_TRACED("packed_tree_kernel", st,
+                               packed_tree_kernel<uint4, 3, unsigned><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
+                else
+                    CLB_TRACED("packed_tree_kernel", st,
+                               packed_tree_kernel<uint4, 3, long long><<<grid, 256, 0, st>>>((const uint4 *)x, leaf, ops, (uint4 *)y, out_dim, units, pc * u_n, u_n));
         }
         return check_launch((int)pieces);
     } else if (rowbytes % 8 == 0 && aligned_to(x, 8) && aligned_to(y, 8)) {
         const long long units = rowbytes / 8;
         const int grid = flat_grid(out_dim * units, 256);
         if (levels == 2)
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 2><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 2, long long><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
         else
-            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 3><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
+            CLB_TRACED("packed_tree_kernel", st, packed_tree_kernel<uint2, 3, long long><<<grid, 256, 0, st>>>((const uint2 *)x, leaf, ops, (uint2 *)y, out_dim, units, 0, units));
     } else {
         return CLB_ERR_SHAPE; // rows of 64-bit words only
     }
