@@ -198,8 +198,8 @@ NCU_TRAFFIC = {
     "c3": {"convtree_bwd_plane_kernel": 1930.7e6, "plane_sum_kernel": 1526.9e6, "logic_tree_bwd_kernel": 954.8e6,
            "row_segment_sum_kernel": 706.5e6, "convtree_fwd_plane_kernel": 383.1e6, "adam_step_kernel": 245.7e6,
            "logic_tree_fwd_sum_kernel": 92.1e6, "convtree_bwd_w_plane32_kernel": 97.8e6, "convtree_fwd_pair_kernel": 37.7e6},
-    "c4": {"packed_convtree_slab_kernel": 2321.0e6, "packed_tree_kernel": 1639.8e6, "group_popcount_kernel": 677.9e6,
-           "packed_rows_to_slab_kernel": 224.6e6, "thermometer_pack_kernel": 66.3e6},
+    "c4": {"packed_convtree_slab_kernel": 2317.2e6, "packed_tree_kernel": 1639.4e6, "group_popcount_kernel": 676.1e6,
+           "packed_rows_to_slab_kernel": 223.9e6, "thermometer_pack_kernel": 65.1e6},
     "c2": {"convtree_fwd_pair_kernel": 37.3e6, "convtree_bwd_cls_kernel": 105.4e6, "convtree_bwd_post_kernel": 33.1e6},
     "c5": {"logic_bwd_x_kernel": 7 * 4 * 1254.0e6, "logic_bwd_w_kernel": 7 * 4 * 741.0e6 + 4 * 288.5e6,
            "logic_fwd_kernel": 7 * 4 * 707.5e6 + 4 * 227.0e6},
